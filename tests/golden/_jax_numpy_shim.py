@@ -1,0 +1,92 @@
+"""A NumPy-backed stand-in for the small slice of the `jax` API that the
+reference's dense math modules use, so that the reference's OWN source files
+can be executed in an environment without JAX.
+
+Only `make_golden.py` uses this.  It is generation-time tooling: no test, no
+product path and no benchmark imports it.  It substitutes the array backend
+(NumPy, IEEE fp32/fp64 on the host) and nothing else: every formula that ends
+up in the golden files is evaluated by the reference's unmodified code.
+
+Covered API: `jax.numpy` array functions used by `src/algebraic/algebraic.py`,
+`src/algebraic/kernels/flash.py` (host-side helpers only) and
+`src/algebraic/kernels/fused_head.py` (host-side helpers only); `jax.lax.rsqrt`,
+`jax.lax.stop_gradient`; `jax.custom_vjp` as a primal pass-through.
+"""
+
+import sys
+import types
+
+import numpy as np
+
+
+def _einsum(subscripts, *operands, preferred_element_type=None, **kw):
+    if preferred_element_type is not None:
+        operands = [np.asarray(o).astype(preferred_element_type) for o in operands]
+    return np.einsum(subscripts, *operands, **kw)
+
+
+def _matmul(a, b, preferred_element_type=None):
+    if preferred_element_type is not None:
+        a = np.asarray(a).astype(preferred_element_type)
+        b = np.asarray(b).astype(preferred_element_type)
+    return np.matmul(a, b)
+
+
+class _CustomVjp:
+    """`jax.custom_vjp` reduced to its primal function."""
+
+    def __init__(self, fn, nondiff_argnums=()):
+        self.fn = fn
+        self.__doc__ = getattr(fn, "__doc__", None)
+        self.__name__ = getattr(fn, "__name__", "custom_vjp")
+
+    def defvjp(self, fwd, bwd):
+        return None
+
+    def __call__(self, *a, **k):
+        return self.fn(*a, **k)
+
+
+def _rsqrt(x):
+    x = np.asarray(x)
+    one = np.ones((), dtype=x.dtype)
+    return (one / np.sqrt(x)).astype(x.dtype)
+
+
+def install():
+    """Insert shim modules into ``sys.modules`` under the jax names."""
+    jax = types.ModuleType("jax")
+    jnp = types.ModuleType("jax.numpy")
+    lax = types.ModuleType("jax.lax")
+    experimental = types.ModuleType("jax.experimental")
+    pallas = types.ModuleType("jax.experimental.pallas")
+    pltpu = types.ModuleType("jax.experimental.pallas.tpu")
+
+    for name in ("float32", "float64", "int32", "bool_", "abs", "where", "mean", "max",
+                 "sum", "tril", "ones", "zeros", "arange", "take_along_axis", "minimum",
+                 "maximum", "concatenate", "full_like", "full", "sqrt", "promote_types",
+                 "expand_dims", "broadcast_to", "reshape", "transpose", "dtype", "pad",
+                 "logical_and", "logical_not", "tile", "linspace", "isfinite"):
+        setattr(jnp, name, getattr(np, name))
+    jnp.asarray = lambda x, dtype=None: np.asarray(x, dtype=dtype)
+    jnp.array = lambda x, dtype=None: np.array(x, dtype=dtype)
+    jnp.einsum = _einsum
+    jnp.matmul = _matmul
+    jnp.ndarray = np.ndarray
+
+    lax.rsqrt = _rsqrt
+    lax.stop_gradient = lambda x: x
+
+    jax.Array = np.ndarray
+    jax.custom_vjp = _CustomVjp
+    jax.numpy = jnp
+    jax.lax = lax
+    jax.experimental = experimental
+    experimental.pallas = pallas
+    pallas.tpu = pltpu
+
+    sys.modules.update({
+        "jax": jax, "jax.numpy": jnp, "jax.lax": lax, "jax.experimental": experimental,
+        "jax.experimental.pallas": pallas, "jax.experimental.pallas.tpu": pltpu,
+    })
+    return jax
