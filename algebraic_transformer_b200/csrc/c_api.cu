@@ -1,0 +1,325 @@
+// The C ABI declared in include/alg_b200.h: argument validation, workspace carving and
+// kernel selection.  Nothing here allocates or synchronises.
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "launchers.h"
+
+namespace alg {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  set_error("CUDA error %d (%s) at %s", int(e), cudaGetErrorString(e), what);
+  return ALG_ERR_CUDA;
+}
+
+namespace {
+
+const int64_t kDense[3] = {0, 0, 0};
+inline float __int_as_float_host(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+inline size_t elem_size(int dtype) { return dtype == ALG_BF16 ? 2 : 4; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// value^(1/n), n a power of two, by repeated square roots (src/algebraic/kernels/flash.py:106-112)
+double root_pow2(double value, int n) {
+  while (n > 1) { value = sqrt(value); n /= 2; }
+  return value;
+}
+
+bool strides_ok(const Strides3& s, int dtype) {
+  const int64_t vec = 16 / int64_t(elem_size(dtype));
+  return s.b % vec == 0 && s.h % vec == 0 && s.t % vec == 0 && s.t > 0;
+}
+
+int check_common(int D, int n, float c, int dtype) {
+  if (dtype != ALG_BF16 && dtype != ALG_F32) { set_error("dtype must be ALG_BF16 or ALG_F32"); return ALG_ERR_INVALID; }
+  if (D != 64 && D != 128) { set_error("head_dim must be 64 or 128, got %d", D); return ALG_ERR_UNSUPPORTED; }
+  if (n < 2 || n > 32 || ilog2_exact(n) < 0) {
+    set_error("asinh kernel needs n to be a power of two in [2, 32], got %d", n);
+    return ALG_ERR_INVALID;
+  }
+  if (!(c > 0.0f) || !isfinite(c)) { set_error("asinh scale c must be positive and finite"); return ALG_ERR_INVALID; }
+  return ALG_OK;
+}
+
+bool attn_has_prologue(const alg_attn_args* a) {
+  return a->q_gain != nullptr || a->k_gain != nullptr || a->cos != nullptr || a->sin != nullptr;
+}
+
+}  // namespace
+}  // namespace alg
+
+using namespace alg;
+
+extern "C" {
+
+int alg_version(void) { return ALG_B200_VERSION; }
+const char* alg_last_error(void) { return g_err; }
+
+int alg_qk_rms_fwd(const alg_qk_rms_args* a, void* stream) {
+  if (a == nullptr || a->x == nullptr || a->y == nullptr) { set_error("qk_rms: null argument"); return ALG_ERR_INVALID; }
+  if (a->dtype != ALG_BF16 && a->dtype != ALG_F32) { set_error("QK RMS kernel needs float32/BF16 input"); return ALG_ERR_INVALID; }
+  if (a->D != 64 && a->D != 128) { set_error("QK RMS kernel needs D=64 or D=128, got %d", a->D); return ALG_ERR_UNSUPPORTED; }
+  if (!(a->eps > 0.0f)) { set_error("QK RMS epsilon must be positive"); return ALG_ERR_INVALID; }
+  if (a->B < 0 || a->H < 0 || a->T < 0) { set_error("qk_rms: negative extent"); return ALG_ERR_INVALID; }
+  if ((a->cos == nullptr) != (a->sin == nullptr)) { set_error("qk_rms: cos and sin tables come as a pair"); return ALG_ERR_INVALID; }
+  PrepParams p{};
+  p.x = a->x; p.y = a->y; p.gain = a->gain; p.cos = a->cos; p.sin = a->sin; p.eps = a->eps;
+  p.normalise = 1; p.B = a->B; p.H = a->H; p.T = a->T; p.D = a->D;
+  p.xs = strides_or_dense(a->x_stride, a->H, a->T, a->D);
+  p.ys = strides_or_dense(a->y_stride, a->H, a->T, a->D);
+  if (!strides_ok(p.xs, a->dtype) || !strides_ok(p.ys, a->dtype) || !aligned16(a->x) || !aligned16(a->y)) {
+    set_error("qk_rms: rows must start on 16-byte boundaries");
+    return ALG_ERR_INVALID;
+  }
+  p.stat_mode = 0; p.stat_scale = 1.0f; p.stat_out = nullptr;
+  return launch_prep(p, a->dtype, static_cast<cudaStream_t>(stream));
+}
+
+size_t alg_attn_workspace_bytes(const alg_attn_args* a) {
+  if (a == nullptr) return 0;
+  size_t bytes = 256;                                   // guard words
+  if (attn_has_prologue(a)) {
+    const size_t es = elem_size(a->dtype);
+    bytes += align256(size_t(a->B) * a->H * a->Tq * a->D * es);
+    bytes += align256(size_t(a->B) * a->H * a->Tk * a->D * es);
+  }
+  return bytes;
+}
+
+int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a == nullptr || a->q == nullptr || a->k == nullptr || a->v == nullptr || a->o == nullptr) {
+    set_error("attention: null tensor argument");
+    return ALG_ERR_INVALID;
+  }
+  if (int rc = check_common(a->D, a->n, a->c, a->dtype)) return rc;
+  if (a->B < 0 || a->H < 0 || a->Tq < 0 || a->Tk < 1) { set_error("attention: bad extents"); return ALG_ERR_INVALID; }
+  if (a->causal && a->Tk < a->Tq) { set_error("causal attention needs Tk >= Tq"); return ALG_ERR_INVALID; }
+  if (a->variant < ALG_VARIANT_GUARD || a->variant > ALG_VARIANT_SHIFT) { set_error("unknown variant %d", a->variant); return ALG_ERR_INVALID; }
+  if (a->impl < ALG_IMPL_AUTO || a->impl > ALG_IMPL_TCGEN05) { set_error("unknown impl %d", a->impl); return ALG_ERR_INVALID; }
+  const bool prologue = attn_has_prologue(a);
+  if (prologue && ((a->cos == nullptr) != (a->sin == nullptr))) { set_error("attention: cos and sin tables come as a pair"); return ALG_ERR_INVALID; }
+  if (prologue && a->Tq != a->Tk) { set_error("attention: the fused QK prologue needs Tq == Tk"); return ALG_ERR_INVALID; }
+  const size_t need = alg_attn_workspace_bytes(a);
+  const bool need_ws = prologue || a->variant == ALG_VARIANT_GUARD;
+  if (need_ws && (a->workspace == nullptr || a->workspace_bytes < need || !aligned16(a->workspace))) {
+    set_error("attention: workspace of %zu bytes (16-byte aligned) required, got %zu", need, a->workspace_bytes);
+    return ALG_ERR_WORKSPACE;
+  }
+  if (a->B == 0 || a->H == 0 || a->Tq == 0) return ALG_OK;
+
+  AttnParams p{};
+  p.q = a->q; p.k = a->k; p.v = a->v; p.o = a->o; p.stat = a->stat; p.stat_kind = a->stat_kind; p.sink = a->sink;
+  p.B = a->B; p.H = a->H; p.Tq = a->Tq; p.Tk = a->Tk; p.D = a->D;
+  p.log2n = ilog2_exact(a->n);
+  p.scale = float(1.0 / (sqrt(double(a->D)) * double(a->c)));
+  p.inv_c = 1.0f / a->c;
+  p.causal = a->causal ? 1 : 0;
+  p.variant = a->variant;
+  p.qs = strides_or_dense(a->q_stride, a->H, a->Tq, a->D);
+  p.ks = strides_or_dense(a->k_stride, a->H, a->Tk, a->D);
+  p.vs = strides_or_dense(a->v_stride, a->H, a->Tk, a->D);
+  p.os = strides_or_dense(a->o_stride, a->H, a->Tq, a->D);
+  if (!strides_ok(p.qs, a->dtype) || !strides_ok(p.ks, a->dtype) || !strides_ok(p.vs, a->dtype) ||
+      !strides_ok(p.os, a->dtype) || !aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->o)) {
+    set_error("attention: rows must start on 16-byte boundaries");
+    return ALG_ERR_INVALID;
+  }
+  p.status = a->status;
+  p.score_clamp = a->score_clamp > 0.0f ? a->score_clamp : __int_as_float_host(0x7f800000);
+
+  unsigned char* ws = static_cast<unsigned char*>(a->workspace);
+  GuardWords* guard = reinterpret_cast<GuardWords*>(ws);
+  const bool guarded = a->variant == ALG_VARIANT_GUARD;
+  if (guarded) {
+    // src/algebraic/kernels/flash.py:744-748, 840-849
+    const double t = root_pow2(1e37 / (double(a->Tk) + 1.0), a->n);
+    const double clamp = 0.5 * (t - 1.0 / t);
+    const double bound = fmin(16.0, clamp / 2);
+    p.guard = guard;
+    p.guard_bound_sq = float((bound / 1.01) * (bound / 1.01));
+    p.guard_sink_bound = float(bound / 1.01);
+    p.guard_vmax = float(fmin(1e8, 1e37 / ((double(a->Tk) + (a->sink ? 1 : 0)) * pow(2 * bound + 1, a->n))));
+    ALG_CUDA_TRY(cudaMemsetAsync(guard, 0, sizeof(GuardWords), stream));
+  }
+  if (prologue || guarded) {
+    const size_t es = elem_size(a->dtype);
+    void* qn = ws + 256;
+    void* kn = ws + 256 + align256(size_t(a->B) * a->H * a->Tq * a->D * es);
+    PrepParams pp{};
+    pp.eps = a->eps; pp.B = a->B; pp.H = a->H; pp.D = a->D;
+    pp.cos = prologue ? a->cos : nullptr; pp.sin = prologue ? a->sin : nullptr;
+    pp.normalise = prologue ? 1 : 0;
+    // q
+    pp.x = a->q; pp.xs = p.qs; pp.T = a->Tq; pp.gain = a->q_gain;
+    pp.y = prologue ? qn : nullptr; pp.ys = strides_or_dense(kDense, a->H, a->Tq, a->D);
+    pp.stat_mode = guarded ? 1 : 0; pp.stat_scale = p.scale; pp.stat_out = &guard->q2;
+    if (int rc = launch_prep(pp, a->dtype, stream)) return rc;
+    // k
+    pp.x = a->k; pp.xs = p.ks; pp.T = a->Tk; pp.gain = a->k_gain;
+    pp.y = prologue ? kn : nullptr; pp.ys = strides_or_dense(kDense, a->H, a->Tk, a->D);
+    pp.stat_scale = 1.0f; pp.stat_out = &guard->k2;
+    if (int rc = launch_prep(pp, a->dtype, stream)) return rc;
+    if (guarded) {                                      // v: max |v| only
+      pp.x = a->v; pp.xs = p.vs; pp.y = nullptr; pp.gain = nullptr; pp.cos = nullptr; pp.sin = nullptr;
+      pp.normalise = 0; pp.stat_mode = 2; pp.stat_out = &guard->vmax;
+      if (int rc = launch_prep(pp, a->dtype, stream)) return rc;
+    }
+    if (prologue) {
+      p.q = qn; p.k = kn;
+      p.qs = strides_or_dense(kDense, a->H, a->Tq, a->D);
+      p.ks = strides_or_dense(kDense, a->H, a->Tk, a->D);
+    }
+  }
+
+  const bool fast_ok = a->variant != ALG_VARIANT_SHIFT && !(a->score_clamp > 0.0f) && attn_tcgen05_supports(p, a->dtype);
+  if (a->impl == ALG_IMPL_TCGEN05 && !fast_ok) {
+    set_error("attention: the tcgen05 kernel covers bf16, causal Tq == Tk multiple of 128, unshifted or guarded");
+    return ALG_ERR_UNSUPPORTED;
+  }
+  if (fast_ok && a->impl != ALG_IMPL_MMA) {
+    p.run_if = guarded ? 1 : 0;
+    if (int rc = launch_attn_tcgen05(p, stream)) return rc;
+    if (!guarded) return ALG_OK;
+    p.run_if = 2;                                       // the stable path runs only if the guard failed
+    return launch_attn_mma(p, a->dtype, stream);
+  }
+  p.run_if = 0;
+  return launch_attn_mma(p, a->dtype, stream);
+}
+
+size_t alg_decode_workspace_bytes(const alg_decode_args* a) {
+  if (a == nullptr) return 0;
+  return size_t(a->B) * a->H * decode_splits(a->B, a->H, a->Tk) * (a->D + 2) * sizeof(float);
+}
+
+int alg_attn_decode(const alg_decode_args* a, void* stream) {
+  if (a == nullptr || a->q == nullptr || a->k == nullptr || a->v == nullptr || a->o == nullptr) {
+    set_error("decode: null tensor argument");
+    return ALG_ERR_INVALID;
+  }
+  if (int rc = check_common(a->D, a->n, a->c, ALG_BF16)) return rc;
+  if (a->B < 0 || a->H < 0 || a->Tk < 1) { set_error("decode: bad extents"); return ALG_ERR_INVALID; }
+  const size_t need = alg_decode_workspace_bytes(a);
+  if (a->workspace == nullptr || a->workspace_bytes < need) {
+    set_error("decode: workspace of %zu bytes required, got %zu", need, a->workspace_bytes);
+    return ALG_ERR_WORKSPACE;
+  }
+  DecodeParams p{};
+  p.q = a->q; p.k = a->k; p.v = a->v; p.o = a->o; p.sink = a->sink;
+  p.B = a->B; p.H = a->H; p.Tk = a->Tk; p.D = a->D;
+  p.log2n = ilog2_exact(a->n);
+  p.scale = float(1.0 / (sqrt(double(a->D)) * double(a->c)));
+  p.inv_c = 1.0f / a->c;
+  p.ks = strides_or_dense(a->k_stride, a->H, a->Tk, a->D);
+  p.vs = strides_or_dense(a->v_stride, a->H, a->Tk, a->D);
+  if (!strides_ok(p.ks, ALG_BF16) || !strides_ok(p.vs, ALG_BF16) || !aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v)) {
+    set_error("decode: rows must start on 16-byte boundaries");
+    return ALG_ERR_INVALID;
+  }
+  p.splits = decode_splits(a->B, a->H, a->Tk);
+  p.part = static_cast<float*>(a->workspace);
+  return launch_decode(p, static_cast<cudaStream_t>(stream));
+}
+
+static int head_fill(const alg_head_args* a, HeadParams* p, bool* use_fast) {
+  if (a == nullptr || a->h == nullptr || a->e == nullptr || a->targets == nullptr || a->l_out == nullptr || a->zt_out == nullptr) {
+    set_error("head: null argument");
+    return ALG_ERR_INVALID;
+  }
+  if (a->n < 2 || a->n > 32 || ilog2_exact(a->n) < 0) { set_error("n must be a power of two"); return ALG_ERR_INVALID; }
+  if (!(a->c > 0.0f) || !isfinite(a->c)) { set_error("head scale c must be positive and finite"); return ALG_ERR_INVALID; }
+  if (a->N < 0 || a->d < 8 || a->d % 8 != 0 || a->V_local < 1 || a->V_total < a->V_local || a->vocab_offset < 0 ||
+      a->vocab_offset + a->V_local > a->V_total) {
+    set_error("head: bad extents (N=%d d=%d V_local=%d offset=%d V_total=%d)", a->N, a->d, a->V_local, a->vocab_offset, a->V_total);
+    return ALG_ERR_INVALID;
+  }
+  if (!aligned16(a->h) || !aligned16(a->e)) { set_error("head: h and e must be 16-byte aligned"); return ALG_ERR_INVALID; }
+  if (a->impl < ALG_IMPL_AUTO || a->impl > ALG_IMPL_TCGEN05) { set_error("unknown impl %d", a->impl); return ALG_ERR_INVALID; }
+  p->h = a->h; p->e = a->e; p->targets = a->targets; p->l_out = a->l_out; p->zt_out = a->zt_out;
+  p->N = a->N; p->d = a->d; p->V_local = a->V_local; p->vocab_offset = a->vocab_offset;
+  p->log2n = ilog2_exact(a->n);
+  p->inv_c = 1.0f / a->c;
+  p->clamp = float(0.25 * root_pow2(1e38 / double(a->V_total), a->n));   // fused_head.py:273
+  p->status = a->status;
+  const bool fast = head_tcgen05_supports(*p);
+  if (a->impl == ALG_IMPL_TCGEN05 && !fast) {
+    set_error("head: the tcgen05 kernel needs d to be a multiple of 64");
+    return ALG_ERR_UNSUPPORTED;
+  }
+  *use_fast = fast && a->impl != ALG_IMPL_MMA;
+  p->splits = *use_fast ? head_tcgen05_splits(a->N, a->V_local) : head_mma_splits(a->N, a->V_local);
+  return ALG_OK;
+}
+
+size_t alg_head_workspace_bytes(const alg_head_args* a) {
+  if (a == nullptr) return 0;
+  // large enough for either kernel family, so that `impl` can change between calls
+  int s = head_mma_splits(a->N, a->V_local);
+  const int s2 = head_tcgen05_splits(a->N, a->V_local);
+  if (s2 > s) s = s2;
+  return align256(size_t(2) * s * size_t(a->N > 0 ? a->N : 0) * sizeof(float));
+}
+
+int alg_head_fwd(const alg_head_args* a, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  HeadParams p{};
+  bool fast = false;
+  if (int rc = head_fill(a, &p, &fast)) return rc;
+  if (a->N == 0) return ALG_OK;
+  const size_t need = size_t(2) * p.splits * size_t(a->N) * sizeof(float);
+  if (a->workspace == nullptr || a->workspace_bytes < need || !aligned16(a->workspace)) {
+    set_error("head: workspace of %zu bytes required, got %zu", alg_head_workspace_bytes(a), a->workspace_bytes);
+    return ALG_ERR_WORKSPACE;
+  }
+  p.l_part = static_cast<float*>(a->workspace);
+  p.zt_part = p.l_part + size_t(p.splits) * a->N;
+  if (int rc = fast ? launch_head_tcgen05(p, stream) : launch_head_mma(p, stream)) return rc;
+  return launch_head_reduce(p, stream);
+}
+
+size_t alg_head_finalize_workspace_bytes(int N) {
+  return align256(size_t(head_finalize_blocks(N > 0 ? N : 0)) * sizeof(float) + 16);
+}
+
+int alg_head_finalize(const float* l, const float* zt, int N, int n, float c, int V_total,
+                      float* pt, float* nll, float* obj, void* workspace, size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (l == nullptr || zt == nullptr || N < 0 || V_total < 1) { set_error("head_finalize: bad argument"); return ALG_ERR_INVALID; }
+  if (n < 2 || n > 32 || ilog2_exact(n) < 0) { set_error("n must be a power of two"); return ALG_ERR_INVALID; }
+  if (N == 0) return ALG_OK;
+  float* sums = nullptr;
+  unsigned* ticket = nullptr;
+  if (obj != nullptr) {
+    if (workspace == nullptr || workspace_bytes < alg_head_finalize_workspace_bytes(N)) {
+      set_error("head_finalize: workspace of %zu bytes required", alg_head_finalize_workspace_bytes(N));
+      return ALG_ERR_WORKSPACE;
+    }
+    ticket = static_cast<unsigned*>(workspace);
+    sums = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + 16);
+    ALG_CUDA_TRY(cudaMemsetAsync(ticket, 0, sizeof(unsigned), stream));
+  }
+  const float clamp = float(0.25 * root_pow2(1e38 / double(V_total), n));
+  return launch_head_finalize(l, zt, N, ilog2_exact(n), 1.0f / c, clamp, pt, nll, obj, sums, ticket, stream);
+}
+
+int alg_cast_f32_to_bf16(const float* src, void* dst, size_t count, void* stream) {
+  if (count != 0 && (src == nullptr || dst == nullptr)) { set_error("cast: null argument"); return ALG_ERR_INVALID; }
+  if (!aligned16(src) || !aligned16(dst)) { set_error("cast: pointers must be 16-byte aligned"); return ALG_ERR_INVALID; }
+  return launch_cast(src, dst, count, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,110 @@
+// Host-side launch interfaces between the C-ABI layer (c_api.cu) and the kernel files.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace alg {
+
+// ---- qk_prep.cu ---------------------------------------------------------------------
+struct PrepParams {
+  const void* x;
+  void* y;                 // nullptr: statistics only
+  const float* gain;       // nullptr: unit gain
+  const float* cos;        // nullptr: no rotation
+  const float* sin;
+  float eps;
+  int normalise;           // 0: pass-through (used for guard statistics on ready-made q/k/v)
+  int B, H, T, D;
+  Strides3 xs, ys;
+  int stat_mode;           // 0 none, 1 max squared row norm of round(x*stat_scale), 2 max |x|
+  float stat_scale;
+  unsigned* stat_out;
+};
+int launch_prep(const PrepParams& p, int dtype, cudaStream_t stream);
+int launch_cast(const float* src, void* dst, size_t count, cudaStream_t stream);
+
+// ---- attention ----------------------------------------------------------------------
+struct AttnParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* stat;
+  int* stat_kind;
+  const float* sink;       // (H) logit units or nullptr
+  int B, H, Tq, Tk, D;
+  int log2n;
+  float scale;             // 1 / (sqrt(D) c): score -> kernel units
+  float inv_c;
+  int causal;
+  int variant;             // ALG_VARIANT_*
+  Strides3 qs, ks, vs, os;
+  const GuardWords* guard; // required when variant == GUARD
+  float guard_bound_sq;    // (bound/1.01)^2
+  float guard_sink_bound;  // bound/1.01
+  float guard_vmax;
+  float score_clamp;       // unshifted path: x <- min(x, score_clamp); +inf when off
+  int run_if;              // 0 always, 1 only when the guard holds, 2 only when it fails
+  int* status;
+};
+int launch_attn_mma(const AttnParams& p, int dtype, cudaStream_t stream);
+bool attn_tcgen05_supports(const AttnParams& p, int dtype);
+int launch_attn_tcgen05(const AttnParams& p, cudaStream_t stream);
+
+// Shared by both attention kernels: does this launch use the max-shifted form?
+__device__ __forceinline__ bool attn_use_shift(const AttnParams& p) {
+  if (p.variant == ALG_VARIANT_NOSHIFT) return false;
+  if (p.variant == ALG_VARIANT_SHIFT) return true;
+  bool ok = guard_in_range(p.guard, p.guard_bound_sq, p.guard_vmax);
+  if (p.sink != nullptr)
+    for (int h = 0; h < p.H; ++h) ok = ok && (fabsf(p.sink[h] * p.inv_c) <= p.guard_sink_bound);
+  return !ok;
+}
+
+// ---- decode -------------------------------------------------------------------------
+struct DecodeParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  const float* sink;
+  int B, H, Tk, D;
+  int log2n;
+  float scale, inv_c;
+  Strides3 ks, vs;
+  int splits;
+  float* part;             // (B*H, splits, D + 2) fp32 partials: acc[D], m, l
+};
+int decode_splits(int B, int H, int Tk);
+int launch_decode(const DecodeParams& p, cudaStream_t stream);
+
+// ---- Alg-CE head --------------------------------------------------------------------
+struct HeadParams {
+  const void* h;
+  const void* e;
+  const int32_t* targets;
+  float* l_out;
+  float* zt_out;
+  int N, d, V_local, vocab_offset;
+  int log2n;
+  float inv_c, clamp;
+  int splits;              // vocab splits per row block (partials reduced by head_reduce)
+  float* l_part;           // (splits, N)
+  float* zt_part;          // (splits, N)
+  int* status;
+};
+int head_mma_splits(int N, int V_local);
+int launch_head_mma(const HeadParams& p, cudaStream_t stream);
+bool head_tcgen05_supports(const HeadParams& p);
+int head_tcgen05_splits(int N, int V_local);
+int launch_head_tcgen05(const HeadParams& p, cudaStream_t stream);
+int launch_head_reduce(const HeadParams& p, cudaStream_t stream);
+int launch_head_finalize(const float* l, const float* zt, int N, int log2n, float inv_c, float clamp,
+                         float* pt, float* nll, float* obj, float* block_sums, unsigned* ticket,
+                         cudaStream_t stream);
+int head_finalize_blocks(int N);
+
+}  // namespace alg

@@ -1,0 +1,343 @@
+"""Python entry points with the reference's call surface, driving the C ABI.
+
+    flash_attention(q, k, v, sink_logit, kind="asinh", n, c, range_guard=...)   src/algebraic/kernels/flash.py:763-772
+    fused_head(h, embed, targets, kind="alg_ce", n, c, block_n, block_v)        src/algebraic/kernels/fused_head.py:260
+    qk_rms_norm(x, gain, eps, block=...)                                        src/algebraic/kernels/qk_norm.py:62
+    position tables cayley_table_geometric(head_dim, seq_len, ...)              src/algebraic/algebraic.py:152-169
+
+Tensors are CUDA `torch.Tensor`s; PyTorch is only the owner of device memory and
+streams here.  Every op runs a hand-written sm_100a kernel from
+`lib/libalg_b200.so`; there is no eager or CPU fallback, and argument errors are
+raised as `ValueError` where the reference raises them.
+"""
+
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib as L
+
+_DTYPES = {torch.bfloat16: L.ALG_BF16, torch.float32: L.ALG_F32}
+_workspaces = {}
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _workspace(device, nbytes: int, tag: str) -> torch.Tensor:
+    """A cached, grow-only scratch buffer per (device, tag): ops enqueue on one stream."""
+    key = (device.index, tag)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("algebraic_transformer_b200 ops need CUDA tensors (there is no CPU path)")
+
+
+def _strides3(t: torch.Tensor):
+    if t.stride(-1) != 1:
+        raise ValueError("the last (head_dim) axis must be contiguous")
+    return L.I64x3(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _root(value: float, n: int) -> float:
+    out = float(value)
+    while n > 1:
+        out = math.sqrt(out)
+        n //= 2
+    return out
+
+
+# --------------------------------------------------------------------------- tables
+
+def cayley_powers(w: torch.Tensor, seq_len: int):
+    """(cos, sin) rows ((1+iw)^2/(1+w^2))^m for m < seq_len, fp32, built on the host by
+    binary exponentiation with renormalised squarings (src/algebraic/algebraic.py:124-149).
+    Computed once per (head_dim, seq_len); not a hot kernel."""
+    w = w.to(torch.float32).cpu()
+    w2 = w * w
+    c = (1.0 - w2) / (1.0 + w2)
+    s = (2.0 * w) / (1.0 + w2)
+    pos = torch.arange(seq_len, dtype=torch.int32)
+    out_c = torch.ones((seq_len, w.shape[0]), dtype=torch.float32)
+    out_s = torch.zeros((seq_len, w.shape[0]), dtype=torch.float32)
+    bit = 0
+    while (1 << bit) < seq_len:
+        take = ((pos >> bit) & 1).bool()[:, None]
+        out_c, out_s = (torch.where(take, out_c * c - out_s * s, out_c),
+                        torch.where(take, out_c * s + out_s * c, out_s))
+        c, s = c * c - s * s, 2.0 * c * s
+        inv = torch.rsqrt(c * c + s * s)
+        c, s = c * inv, s * inv
+        bit += 1
+    inv = torch.rsqrt(out_c * out_c + out_s * out_s)
+    return out_c * inv, out_s * inv
+
+
+def cayley_table_geometric(head_dim: int, seq_len: int, base: float = 10000.0, w0: float = 0.5,
+                           fraction: float = 1.0, device=None):
+    """Geometric frequency grid w_k = w0 base^(-k/half); tables of shape (T, D/2)."""
+    half = head_dim // 2
+    levels = int(round(math.log2(half)))
+    if 1 << levels != half:
+        raise ValueError("geometric Cayley grid needs head_dim/2 to be a power of two")
+    root = float(base)
+    for _ in range(levels):
+        root = math.sqrt(root)
+    ratio = 1.0 / root
+    active = int(round(fraction * half))
+    w = torch.tensor([w0 * ratio ** i if i < active else 0.0 for i in range(half)], dtype=torch.float64)
+    c, s = cayley_powers(w.to(torch.float32), seq_len)
+    if device is not None:
+        c, s = c.to(device), s.to(device)
+    return c, s
+
+
+# --------------------------------------------------------------------------- qk_rms
+
+def qk_rms_norm(x: torch.Tensor, gain: Optional[torch.Tensor], eps: float = 1e-5, *, block: int = 1024,
+                cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RMS-normalise the rows of (B,H,T,D) with a learned gain; with `cos`/`sin` also apply
+    the Cayley rotation in the same pass.  `block` is accepted for call compatibility (the
+    CUDA kernel picks its own tiling) but validated as the reference does."""
+    _require_cuda(x, gain, cos, sin)
+    if x.ndim < 2 or x.shape[-1] not in (64, 128) or (gain is not None and gain.shape != (x.shape[-1],)):
+        raise ValueError("QK RMS kernel needs D=64 or D=128 and a one-dimensional gain")
+    if x.dtype not in _DTYPES or (gain is not None and gain.dtype != torch.float32):
+        raise ValueError("QK RMS kernel needs float32/BF16 input and float32 gain")
+    if block < 8 or block % 8:
+        raise ValueError("QK RMS row count must be divisible by a block aligned to eight rows")
+    if eps <= 0:
+        raise ValueError("QK RMS epsilon must be positive")
+    D = x.shape[-1]
+    x4 = x.reshape(1, 1, -1, D) if x.ndim != 4 else x
+    if (cos is None) != (sin is None):
+        raise ValueError("cos and sin tables come as a pair")
+    if cos is not None:
+        if x.ndim != 4 or cos.shape[0] < x.shape[-2] or cos.shape[1] != D // 2:
+            raise ValueError("rotation tables must have shape (>=T, D/2) and x must be (B,H,T,D)")
+        cos, sin = cos.contiguous().float(), sin.contiguous().float()
+    y = torch.empty(x4.shape, dtype=x.dtype, device=x.device) if out is None else out.view(x4.shape)
+    a = L.QkRmsArgs(x=x4.data_ptr(), y=y.data_ptr(), gain=_ptr(gain), cos=_ptr(cos), sin=_ptr(sin),
+                    eps=float(eps), B=x4.shape[0], H=x4.shape[1], T=x4.shape[2], D=D, dtype=_DTYPES[x.dtype],
+                    x_stride=_strides3(x4), y_stride=_strides3(y))
+    L.check(L.load().alg_qk_rms_fwd(a, _stream()))
+    return y.view(x.shape)
+
+
+# ------------------------------------------------------------------------ attention
+
+def flash_clamp(seq_len: int, n: int) -> float:
+    """Upper score clamp of the unguarded unshifted link (src/algebraic/kernels/flash.py:744-748)."""
+    t = _root(1e37 / (seq_len + 1), n)
+    return 0.5 * (t - 1.0 / t)
+
+
+def flash_attention(q, k, v, sink_logit=None, *, kind: str = "softmax", n: int = 16, c: float = 16.0,
+                    block: int = 512, block_q: Optional[int] = None, block_k: Optional[int] = None,
+                    shift: Optional[bool] = None, fast_rho: Optional[bool] = None,
+                    inv_stat: Optional[bool] = None, compact_stat: bool = True, poly_rho: bool = False,
+                    range_guard: bool = False, resident_bwd: Optional[bool] = None,
+                    diagonal_bwd: Optional[bool] = None, diagonal_fwd: Optional[bool] = None,
+                    head_resident: Optional[bool] = None,
+                    q_gain=None, k_gain=None, cos=None, sin=None, eps: float = 1e-5,
+                    causal: bool = True, return_stat: bool = False, impl: str = "auto", out=None):
+    """Causal asinh-power attention on (B,H,T,D); `sink_logit` broadcastable to (H,).
+
+    Same keywords as the reference entry point.  TPU tiling/residency knobs (`block*`,
+    `resident_bwd`, `diagonal_*`, `head_resident`, `compact_stat`, `fast_rho`) are validated
+    where the reference validates them and otherwise have no effect on a GPU.  Extras:
+    `q_gain/k_gain/cos/sin/eps` run the QK-norm + Cayley rotation of the layer in front of
+    the attention inside the same call; `return_stat=True` also returns the per-row
+    statistic and which kind it is; `impl` forces a kernel family ("auto", "mma",
+    "tcgen05").  `kind="softmax"` (the reference's control arm) is not built."""
+    _require_cuda(q, k, v)
+    if kind == "softmax":
+        raise NotImplementedError("only the algebraic (kind='asinh') arm is built for B200")
+    if kind != "asinh":
+        raise ValueError(f"unknown attention kernel: {kind}")
+    if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
+        raise ValueError("q, k, v must be (B, H, T, D)")
+    B, H, T, D = q.shape
+    Tk = k.shape[2]
+    bq = min(block_q or block, T)
+    bk = min(block_k or block, T)
+    if T % bq or T % bk:
+        raise ValueError(f"sequence length {T} must be divisible by blocks ({bq}, {bk})")
+    if n < 2 or n & (n - 1):
+        raise ValueError("asinh kernel needs n to be a power of two")
+    if not math.isfinite(c) or c <= 0:
+        raise ValueError("asinh scale c must be positive and finite")
+    clamp = flash_clamp(T, n)
+    if shift is None:
+        shift = clamp < 20.0
+    if inv_stat is None:
+        inv_stat = not shift
+    if inv_stat and shift:
+        raise ValueError("inverse-denominator statistic requires shift=False")
+    if poly_rho:
+        raise ValueError("bounded radical approximation is not built; use the exact radical")
+    if head_resident is True and not (T == 2048 and D == 64 and q.dtype == torch.bfloat16):
+        raise ValueError("whole-head residency needs resident bfloat16 T=2048,D=64, "
+                         "512-square public tiles, and compact statistics")
+    if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError("q, k, v must share dtype float32 or bfloat16")
+    if k.shape != (B, H, Tk, D) or v.shape != (B, H, Tk, D):
+        raise ValueError("k and v must be (B, H, Tk, D) matching q")
+    if range_guard and n <= 32:
+        variant, score_clamp = L.ALG_VARIANT_GUARD, 0.0
+    elif shift:
+        variant, score_clamp = L.ALG_VARIANT_SHIFT, 0.0
+    else:
+        variant, score_clamp = L.ALG_VARIANT_NOSHIFT, clamp
+
+    sink = None
+    if sink_logit is not None:
+        s = torch.as_tensor(sink_logit, dtype=torch.float32, device=q.device).reshape(-1)
+        sink = s.expand(H).contiguous() if s.numel() == 1 else s.contiguous()
+        if sink.numel() != H:
+            raise ValueError("sink_logit must broadcast to (H,)")
+    for t in (q_gain, k_gain):
+        if t is not None and (t.dtype != torch.float32 or t.shape != (D,)):
+            raise ValueError("q_gain / k_gain must be float32 of shape (D,)")
+    if cos is not None:
+        cos, sin = cos.contiguous().float(), sin.contiguous().float()
+    o = torch.empty((B, H, T, D), dtype=q.dtype, device=q.device) if out is None else out
+    stat = torch.empty((B, H, T), dtype=torch.float32, device=q.device) if return_stat else None
+    stat_kind = torch.zeros(1, dtype=torch.int32, device=q.device) if return_stat else None
+    a = L.AttnArgs(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), o=o.data_ptr(), stat=_ptr(stat),
+                   stat_kind=_ptr(stat_kind), sink=_ptr(sink), q_gain=_ptr(q_gain), k_gain=_ptr(k_gain),
+                   cos=_ptr(cos), sin=_ptr(sin), eps=float(eps), B=B, H=H, Tq=T, Tk=Tk, D=D, n=int(n),
+                   c=float(c), causal=int(bool(causal)), variant=variant, dtype=_DTYPES[q.dtype],
+                   impl=L.IMPL[impl], score_clamp=float(score_clamp), q_stride=_strides3(q),
+                   k_stride=_strides3(k), v_stride=_strides3(v), o_stride=_strides3(o))
+    lib = L.load()
+    ws = _workspace(q.device, lib.alg_attn_workspace_bytes(a), "attn")
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    L.check(lib.alg_attn_fwd(a, _stream()))
+    if return_stat:
+        return o, stat, stat_kind
+    return o
+
+
+def decode_attention(q, k, v, sink_logit=None, *, n: int = 16, c: float = 8.0, out=None):
+    """One query per (batch, head) against a (B,H,Tk,D) bf16 KV cache, every key visible.
+    The reference has no decode kernel; semantics follow its dense weights with an all-true
+    mask (src/algebraic/algebraic.py:186-204)."""
+    _require_cuda(q, k, v)
+    B, H, Tq, D = q.shape
+    if Tq != 1:
+        raise ValueError("decode_attention takes exactly one query row per head")
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise ValueError("decode_attention needs bfloat16 q, k, v")
+    if n < 2 or n & (n - 1):
+        raise ValueError("asinh kernel needs n to be a power of two")
+    Tk = k.shape[2]
+    sink = None
+    if sink_logit is not None:
+        s = torch.as_tensor(sink_logit, dtype=torch.float32, device=q.device).reshape(-1)
+        sink = s.expand(H).contiguous() if s.numel() == 1 else s.contiguous()
+    q = q.contiguous()
+    o = torch.empty((B, H, 1, D), dtype=q.dtype, device=q.device) if out is None else out
+    a = L.DecodeArgs(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), o=o.data_ptr(), sink=_ptr(sink),
+                     B=B, H=H, Tk=Tk, D=D, n=int(n), c=float(c), k_stride=_strides3(k), v_stride=_strides3(v))
+    lib = L.load()
+    ws = _workspace(q.device, lib.alg_decode_workspace_bytes(a), "decode")
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    L.check(lib.alg_attn_decode(a, _stream()))
+    return o
+
+
+# ----------------------------------------------------------------------------- head
+
+def cast_embedding(embed: torch.Tensor) -> torch.Tensor:
+    """fp32 (V,d) -> bf16 with the library's cast kernel (the reference casts per call)."""
+    _require_cuda(embed)
+    if embed.dtype == torch.bfloat16:
+        return embed.contiguous()
+    e32 = embed.contiguous().float()
+    out = torch.empty(e32.shape, dtype=torch.bfloat16, device=embed.device)
+    L.check(L.load().alg_cast_f32_to_bf16(e32.data_ptr(), out.data_ptr(), e32.numel(), _stream()))
+    return out
+
+
+def head_statistic(h, e_bf16, targets, *, n: int, c: float, vocab_offset: int = 0,
+                   vocab_total: Optional[int] = None, impl: str = "auto", out=None):
+    """Per-row (l, zt) of one vocabulary shard as a (2, N) fp32 tensor: row 0 the partial
+    normaliser, row 1 the target logit (0 where the target is not in the shard)."""
+    N, d = h.shape
+    V_local = e_bf16.shape[0]
+    stats = torch.empty((2, N), dtype=torch.float32, device=h.device) if out is None else out
+    if V_local == 0:                                   # a rank that owns no vocabulary tile
+        return stats.zero_()
+    a = L.HeadArgs(h=h.data_ptr(), e=e_bf16.data_ptr(), targets=targets.data_ptr(), l_out=stats[0].data_ptr(),
+                   zt_out=stats[1].data_ptr(), N=N, d=d, V_local=V_local, vocab_offset=int(vocab_offset),
+                   V_total=int(vocab_total or V_local), n=int(n), c=float(c), impl=L.IMPL[impl])
+    lib = L.load()
+    ws = _workspace(h.device, lib.alg_head_workspace_bytes(a), "head")
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    L.check(lib.alg_head_fwd(a, _stream()))
+    return stats
+
+
+def head_finalize(stats, *, n: int, c: float, vocab_total: int, want_nll: bool = False):
+    """(objective, p_target[, nll]) from the (all-reduced) (2, N) statistic."""
+    N = stats.shape[1]
+    dev = stats.device
+    pt = torch.empty(N, dtype=torch.float32, device=dev)
+    nll = torch.empty(N, dtype=torch.float32, device=dev) if want_nll else None
+    obj = torch.empty((), dtype=torch.float32, device=dev)
+    lib = L.load()
+    ws = _workspace(dev, lib.alg_head_finalize_workspace_bytes(N), "head_fin")
+    L.check(lib.alg_head_finalize(stats[0].data_ptr(), stats[1].data_ptr(), N, int(n), float(c), int(vocab_total),
+                                  pt.data_ptr(), _ptr(nll), obj.data_ptr(), ws.data_ptr(), ws.numel(), _stream()))
+    return (obj, pt, nll) if want_nll else (obj, pt)
+
+
+def fused_head(h, embed, targets, *, kind: str = "ce", n: int = 16, c: float = 16.0, block_n: int = 128,
+               block_v: int = 512, vocab_offset: int = 0, vocab_total: Optional[int] = None,
+               group=None, want_nll: bool = False, impl: str = "auto"):
+    """Fused tied-embedding projection and Alg-CE likelihood: returns `(objective,
+    p_target)` like the reference (`want_nll=True` appends the per-token NLL).
+
+    `embed` is this rank's vocabulary shard: rows [vocab_offset, vocab_offset + V_local) of a
+    `vocab_total`-row embedding (defaults: the whole thing).  With a `torch.distributed`
+    `group`, the per-row partials (normaliser, target logit) of all shards are summed with one
+    all-reduce before the telemetry is formed.  `kind="ce"` (softmax control arm) is not built."""
+    _require_cuda(h, embed, targets)
+    if kind not in ("ce", "alg_ce"):
+        raise ValueError(kind)
+    if kind == "ce":
+        raise NotImplementedError("only the algebraic (kind='alg_ce') head is built for B200")
+    if n & (n - 1):
+        raise ValueError("n must be a power of two")
+    if h.ndim != 2 or embed.ndim != 2 or h.shape[1] != embed.shape[1]:
+        raise ValueError("h must be (N, d) and embed (V, d)")
+    N = h.shape[0]
+    bn = min(block_n, N)
+    if N % bn:
+        raise ValueError(f"token count {N} must be divisible by block {bn}")
+    if h.dtype != torch.bfloat16:
+        raise ValueError("fused_head needs bfloat16 hidden states")
+    h = h.contiguous()
+    e = cast_embedding(embed)
+    t = targets.reshape(N).to(torch.int32).contiguous()
+    V_total = int(vocab_total or embed.shape[0])
+    stats = head_statistic(h, e, t, n=n, c=c, vocab_offset=vocab_offset, vocab_total=V_total, impl=impl)
+    if group is not None:
+        import torch.distributed as dist
+        dist.all_reduce(stats, op=dist.ReduceOp.SUM, group=group)
+    return head_finalize(stats, n=n, c=c, vocab_total=V_total, want_nll=want_nll)

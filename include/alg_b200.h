@@ -1,0 +1,205 @@
+/*
+ * alg_b200 — C ABI of the B200 (sm_100a) kernels for the Algebraic Transformer's
+ * forward hot path: QK RMS-norm + Cayley rotation, asinh-power attention, the
+ * fused Alg-CE head, and single-query decode.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless the comment says "host";
+ *   - the library allocates nothing: outputs, workspaces and the status word are
+ *     the caller's; `alg_*_workspace_bytes` says how much scratch a call needs;
+ *   - calls only enqueue work on `stream` (a cudaStream_t passed as void*), they
+ *     never synchronise;
+ *   - return value 0 = enqueued, < 0 = ALG_ERR_* raised BEFORE any launch, with a
+ *     human-readable reason in alg_last_error() (thread-local);
+ *   - device-side problems (a bounded wait that ran out) are reported through the
+ *     caller's `status` word: it is left untouched on success and set to a non-zero
+ *     ALG_DEV_* code otherwise; the kernel returns instead of trapping.
+ *
+ * Each entry point names the reference interface it stands in for, by the file's
+ * path inside the reference project (tasmaikeni13/algebraic-transformer).
+ */
+#ifndef ALG_B200_H_
+#define ALG_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ALG_B200_VERSION 100
+
+#if defined(__GNUC__)
+#define ALG_API __attribute__((visibility("default")))
+#else
+#define ALG_API
+#endif
+
+enum {
+  ALG_OK = 0,
+  ALG_ERR_INVALID = -1,      /* bad shape / dtype / null pointer / alignment      */
+  ALG_ERR_UNSUPPORTED = -2,  /* valid request this build has no kernel for        */
+  ALG_ERR_CUDA = -3,         /* a CUDA runtime / driver call failed               */
+  ALG_ERR_WORKSPACE = -4     /* workspace missing or smaller than required        */
+};
+
+enum { ALG_DEV_OK = 0, ALG_DEV_TIMEOUT = 1, ALG_DEV_BAD_STATE = 2 };
+
+enum { ALG_BF16 = 0, ALG_F32 = 1 };
+
+/* Accumulation strategy of the attention weights (src/algebraic/kernels/flash.py:732-760,
+ * 834-856): GUARD evaluates the reference's run-time range guard on the device and takes
+ * the unshifted fast path when it holds, the max-shifted stable path otherwise. */
+enum { ALG_VARIANT_GUARD = 0, ALG_VARIANT_NOSHIFT = 1, ALG_VARIANT_SHIFT = 2 };
+
+/* Which kernel family runs.  AUTO picks the tcgen05/TMEM kernel whenever the shape
+ * qualifies and the legacy-MMA kernel otherwise; the other two force one family and
+ * fail with ALG_ERR_UNSUPPORTED if it cannot run the request. */
+enum { ALG_IMPL_AUTO = 0, ALG_IMPL_MMA = 1, ALG_IMPL_TCGEN05 = 2 };
+
+ALG_API int alg_version(void);
+ALG_API const char* alg_last_error(void);
+
+/* ------------------------------------------------------------------------------------
+ * QK RMS normalisation (+ optional Cayley rotation).
+ * Replaces: qk_rms_norm(x, gain, eps)          src/algebraic/kernels/qk_norm.py:62-76
+ *           rms_norm                            src/algebraic/algebraic.py:76-83
+ *           apply_rotary (when cos/sin given)   src/algebraic/algebraic.py:172-179
+ * x, y: (B, H, T, D) with D contiguous; `x_stride`/`y_stride` are the element strides of
+ * (batch, head, row), so transposed views such as a (B, T, H*D) projection output can be
+ * read in place; all 0 means densely packed.  gain: (D) fp32 or NULL (no gain).
+ * cos, sin: (T, D/2) fp32 or both NULL.  y may alias x.  D in {64, 128}.
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  const void* x;
+  void* y;
+  const float* gain;
+  const float* cos;
+  const float* sin;
+  float eps;
+  int B, H, T, D;
+  int dtype;               /* ALG_BF16 | ALG_F32 (input and output) */
+  int64_t x_stride[3];     /* elements: batch, head, row; all 0 = contiguous (B,H,T,D) */
+  int64_t y_stride[3];
+} alg_qk_rms_args;
+
+ALG_API int alg_qk_rms_fwd(const alg_qk_rms_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Asinh-power attention forward.
+ * Replaces: flash_attention(q,k,v,sink_logit,kind="asinh",n,c,range_guard=...)
+ *                                               src/algebraic/kernels/flash.py:763-857
+ *           (call site model._attention,       src/algebraic/model.py:145-155)
+ *           and, with q_gain/k_gain/cos/sin given, the QK-norm + rotation that precede
+ *           it in model._block                  src/algebraic/model.py:170-174
+ * q: (B,H,Tq,D), k,v: (B,H,Tk,D), o: (B,H,Tq,D) in `dtype`; D contiguous, other strides
+ * free (all 0 = contiguous).  sink: (H) fp32 logit units, or NULL.  stat: (B,H,Tq) fp32
+ * or NULL — the per-row statistic a backward pass consumes (flash.py:271-284): 1/l on
+ * the unshifted path, rho(-m) l^(-1/n) on the shifted one.  stat_kind (1 int, device,
+ * may be NULL) receives which of the two was written (ALG_VARIANT_NOSHIFT/SHIFT).
+ * causal: key j visible to query i iff j <= i + (Tk - Tq).  n: power of two in [2, 32].
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* stat;
+  int* stat_kind;
+  const float* sink;
+  const float* q_gain;     /* fused prologue: all four of q_gain,k_gain,cos,sin or none */
+  const float* k_gain;
+  const float* cos;
+  const float* sin;
+  float eps;
+  int B, H, Tq, Tk, D;
+  int n;
+  float c;
+  int causal;
+  int variant;             /* ALG_VARIANT_* */
+  int dtype;               /* ALG_BF16 | ALG_F32 */
+  int impl;                /* ALG_IMPL_* */
+  float score_clamp;       /* > 0: unshifted weights use min(x, score_clamp), the reference's
+                              explicit unguarded shift=False link (flash.py:744-748); <= 0: off */
+  int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3];
+  void* workspace;
+  size_t workspace_bytes;
+  int* status;             /* device int, may be NULL */
+} alg_attn_args;
+
+ALG_API size_t alg_attn_workspace_bytes(const alg_attn_args* args);
+ALG_API int alg_attn_fwd(const alg_attn_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Single-query decode against a KV cache (Tq = 1, every key visible), split over keys.
+ * No reference kernel exists (the reference re-runs the full forward per token,
+ * src/algebraic/benchmarking.py:250-263); semantics are asinh_power_weights with an
+ * all-true mask, src/algebraic/algebraic.py:186-204.  Uses the max-shifted form.
+ * q: (B,H,1,D), k,v: (B,H,Tk,D) bf16, o: (B,H,1,D) bf16.
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  const float* sink;
+  int B, H, Tk, D;
+  int n;
+  float c;
+  int64_t k_stride[3], v_stride[3];
+  void* workspace;
+  size_t workspace_bytes;
+} alg_decode_args;
+
+ALG_API size_t alg_decode_workspace_bytes(const alg_decode_args* args);
+ALG_API int alg_attn_decode(const alg_decode_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Fused Alg-CE head, forward, over one vocabulary shard.
+ * Replaces: fused_head(h, embed, targets, kind="alg_ce", n, c)
+ *                                               src/algebraic/kernels/fused_head.py:260-275
+ *           (_fwd_kernel :72-117; call site model.head_loss, src/algebraic/model.py:211-231)
+ * h: (N,d) bf16.  e: (V_local,d) bf16 — rows [vocab_offset, vocab_offset+V_local) of the
+ * tied embedding, already cast.  targets: (N) int32 GLOBAL ids.  Outputs, fp32 (N):
+ *   l_out  = sum over the shard's columns of rho_fast(min(z/c, clamp))^n
+ *   zt_out = the target's logit if the target lies in this shard, else 0
+ * with clamp = 0.25 (1e38 / V_total)^(1/n).  No (N x V) logits are written anywhere.
+ * Summing l_out and zt_out over shards (one all-reduce) gives the full statistic.
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  const void* h;
+  const void* e;
+  const int32_t* targets;
+  float* l_out;
+  float* zt_out;
+  int N, d, V_local, vocab_offset, V_total;
+  int n;
+  float c;
+  int impl;                /* ALG_IMPL_* */
+  void* workspace;
+  size_t workspace_bytes;
+  int* status;
+} alg_head_args;
+
+ALG_API size_t alg_head_workspace_bytes(const alg_head_args* args);
+ALG_API int alg_head_fwd(const alg_head_args* args, void* stream);
+
+/* Telemetry from the (all-reduced) statistic.
+ * Replaces: _telemetry + the _inv_root finalize  src/algebraic/kernels/fused_head.py:116,219-229
+ *           NLL = -log(max(pt,1e-30))            src/algebraic/train.py:239
+ * pt, nll: (N) fp32 (either may be NULL); obj: 1 fp32 = mean(1 - pt) (may be NULL).
+ * workspace: alg_head_finalize_workspace_bytes(N) bytes. */
+ALG_API size_t alg_head_finalize_workspace_bytes(int N);
+ALG_API int alg_head_finalize(const float* l, const float* zt, int N, int n, float c, int V_total,
+                      float* pt, float* nll, float* obj,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* fp32 -> bf16 cast of the embedding shard (the reference casts E per call,
+ * src/algebraic/kernels/fused_head.py:165; model.py:225). */
+ALG_API int alg_cast_f32_to_bf16(const float* src, void* dst, size_t count, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ALG_B200_H_ */

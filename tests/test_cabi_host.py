@@ -1,0 +1,132 @@
+"""CPU checks of the drop-in boundary: the library loads, exports every symbol the
+header declares, rejects bad arguments before any launch, and the host-side logic
+(partitioning, argument validation of the Python surface, position tables) is right."""
+
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import algebraic_transformer_b200 as A
+from algebraic_transformer_b200 import _lib as L
+from oracle import algebraic_ref as R
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "alg_b200.h")).read()
+    declared = set(re.findall(r"ALG_API\s+[\w\s\*]+?\b(alg_\w+)\s*\(", header))
+    assert declared, "no declarations parsed"
+    assert declared == set(L.SYMBOLS), (declared ^ set(L.SYMBOLS))
+    lib = L.load()
+    raw = C.CDLL(L.LIB_PATH)
+    for name in declared:
+        assert getattr(raw, name) is not None
+    assert lib.alg_version() == 100
+
+
+def test_invalid_arguments_fail_before_launch():
+    lib = L.load()
+    a = L.AttnArgs()                                   # all null
+    assert lib.alg_attn_fwd(a, None) == L.ALG_ERR_INVALID
+    assert b"null" in lib.alg_last_error()
+    a = L.AttnArgs(q=16, k=16, v=16, o=16, B=1, H=1, Tq=8, Tk=8, D=48, n=16, c=8.0)
+    assert lib.alg_attn_fwd(a, None) == L.ALG_ERR_UNSUPPORTED
+    a.D, a.n = 64, 12
+    assert lib.alg_attn_fwd(a, None) == L.ALG_ERR_INVALID
+    assert b"power of two" in lib.alg_last_error()
+    a.n, a.variant = 16, L.ALG_VARIANT_GUARD             # guard needs a workspace
+    assert lib.alg_attn_fwd(a, None) == L.ALG_ERR_WORKSPACE
+    h = L.HeadArgs(h=16, e=16, targets=16, l_out=16, zt_out=16, N=128, d=64, V_local=10, vocab_offset=5,
+                   V_total=12, n=8, c=2.0)
+    assert lib.alg_head_fwd(h, None) == L.ALG_ERR_INVALID   # shard exceeds the vocabulary
+    q = L.QkRmsArgs(x=16, y=16, eps=0.0, B=1, H=1, T=1, D=64)
+    assert lib.alg_qk_rms_fwd(q, None) == L.ALG_ERR_INVALID
+    with pytest.raises(ValueError):
+        L.check(L.ALG_ERR_INVALID)
+
+
+def test_workspace_sizes():
+    lib = L.load()
+    a = L.AttnArgs(B=2, H=3, Tq=512, Tk=512, D=64, dtype=L.ALG_BF16)
+    assert lib.alg_attn_workspace_bytes(a) == 256
+    a.cos = 16
+    assert lib.alg_attn_workspace_bytes(a) == 256 + 2 * (2 * 3 * 512 * 64 * 2)
+    h = L.HeadArgs(N=8192, d=768, V_local=50304)
+    assert lib.alg_head_workspace_bytes(h) >= 2 * 8192 * 4
+    assert lib.alg_head_finalize_workspace_bytes(8192) >= 32 * 4 + 16
+
+
+def test_python_surface_validation_matches_reference_errors():
+    x = torch.zeros(1, 1, 512, 64)
+    with pytest.raises(ValueError, match="CUDA"):
+        A.flash_attention(x, x, x, kind="asinh")
+    # the remaining checks run before any device work, on meta-like CUDA-less tensors
+    class FakeCuda(torch.Tensor):
+        @property
+        def is_cuda(self):
+            return True
+    xf = x.as_subclass(FakeCuda)
+    with pytest.raises(ValueError, match="divisible by blocks"):
+        A.flash_attention(xf[:, :, :500], xf[:, :, :500], xf[:, :, :500], kind="asinh", block=128)
+    with pytest.raises(ValueError, match="power of two"):
+        A.flash_attention(xf, xf, xf, kind="asinh", n=12)
+    with pytest.raises(ValueError, match="positive and finite"):
+        A.flash_attention(xf, xf, xf, kind="asinh", c=0.0)
+    with pytest.raises(ValueError, match="unknown attention kernel"):
+        A.flash_attention(xf, xf, xf, kind="linear")
+    with pytest.raises(ValueError, match="inverse-denominator"):
+        A.flash_attention(xf, xf, xf, kind="asinh", shift=True, inv_stat=True)
+    with pytest.raises(ValueError, match="whole-head residency"):
+        A.flash_attention(xf, xf, xf, kind="asinh", c=8.0, head_resident=True)
+    with pytest.raises(NotImplementedError):
+        A.flash_attention(xf, xf, xf)                  # softmax control arm: not built
+    h = torch.zeros(100, 64, dtype=torch.bfloat16).as_subclass(FakeCuda)
+    e = torch.zeros(300, 64).as_subclass(FakeCuda)
+    t = torch.zeros(100, dtype=torch.int64).as_subclass(FakeCuda)
+    with pytest.raises(ValueError, match="power of two"):
+        A.fused_head(h, e, t, kind="alg_ce", n=12)
+    with pytest.raises(ValueError, match="must be divisible by block"):
+        A.fused_head(torch.zeros(200, 64, dtype=torch.bfloat16).as_subclass(FakeCuda), e, t, kind="alg_ce",
+                     n=8, block_n=128)
+    with pytest.raises(ValueError):
+        A.fused_head(h, e, t, kind="mse")
+    g = torch.ones(64).as_subclass(FakeCuda)
+    with pytest.raises(ValueError, match="epsilon"):
+        A.qk_rms_norm(xf, g, 0.0)
+    with pytest.raises(ValueError, match="D=64"):
+        A.qk_rms_norm(torch.zeros(4, 48).as_subclass(FakeCuda), torch.ones(48).as_subclass(FakeCuda))
+    with pytest.raises(ValueError, match="eight rows"):
+        A.qk_rms_norm(xf, g, block=4)
+
+
+def test_host_tables_match_oracle(golden):
+    for D, T in ((64, 300), (128, 257)):
+        c, s = A.cayley_table_geometric(D, T)
+        np.testing.assert_allclose(c, golden[f"cayley_cos_D{D}_T{T}"], atol=2e-6)
+        np.testing.assert_allclose(s, golden[f"cayley_sin_D{D}_T{T}"], atol=2e-6)
+    c, s = A.cayley_table_geometric(64, 1024)
+    c2, s2 = R.cayley_table_geometric(64, 1024)
+    assert torch.equal(c, c2) and torch.equal(s, s2)
+    with pytest.raises(ValueError):
+        A.cayley_table_geometric(96, 8)
+    assert A.flash_clamp(1024, 16) == R.flash_clamp(1024, 16)
+
+
+def test_partitioning_rules():
+    for V, world in ((50304, 8), (50304, 4), (32000, 8), (50257, 8), (1000, 3), (100, 8)):
+        spans = [A.vocab_shard(V, r, world) for r in range(world)]
+        assert spans[0][0] == 0 and sum(n for _, n in spans) == V
+        for (lo, n), (lo2, _) in zip(spans, spans[1:]):
+            assert lo + n == lo2 and (lo % 128 == 0 or n == 0)
+        tiles = [-(-n // 128) for _, n in spans]
+        assert max(tiles) - min(tiles) <= 1
+    assert [A.vocab_shard(50304, r, 8)[1] // 128 for r in range(8)].count(50) == 1   # 393 = 7*49 + 50
+    for units, world in ((16, 8), (48, 8), (16, 3), (5, 8)):
+        spans = [A.unit_shard(units, r, world) for r in range(world)]
+        assert sum(n for _, n in spans) == units
+        assert all(a[0] + a[1] == b[0] for a, b in zip(spans, spans[1:]))
