@@ -56,6 +56,7 @@ class HeadArgs(C.Structure):
 SYMBOLS = {
     "alg_version": (C.c_int, []),
     "alg_last_error": (C.c_char_p, []),
+    "alg_kernel_launches": (C.c_ulonglong, []),
     "alg_qk_rms_fwd": (C.c_int, [C.POINTER(QkRmsArgs), C.c_void_p]),
     "alg_attn_workspace_bytes": (C.c_size_t, [C.POINTER(AttnArgs)]),
     "alg_attn_fwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),

@@ -305,6 +305,7 @@ int launch_one(const AttnParams& p, cudaStream_t stream) {
   dim3 grid((p.Tq + BM - 1) / BM, p.H, p.B);
   kern<<<grid, NTHREADS, smem, stream>>>(p);
   ALG_CUDA_TRY(cudaGetLastError());
+  count_launch();
   return ALG_OK;
 }
 

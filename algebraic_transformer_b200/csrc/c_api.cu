@@ -1,6 +1,7 @@
 // The C ABI declared in include/alg_b200.h: argument validation, workspace carving and
 // kernel selection.  Nothing here allocates or synchronises.
 #include <math.h>
+#include <atomic>
 #include <stdarg.h>
 #include <stdio.h>
 #include <string.h>
@@ -23,6 +24,9 @@ int cuda_fail(cudaError_t e, const char* what) {
   set_error("CUDA error %d (%s) at %s", int(e), cudaGetErrorString(e), what);
   return ALG_ERR_CUDA;
 }
+
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 
 namespace {
 
@@ -67,6 +71,7 @@ extern "C" {
 
 int alg_version(void) { return ALG_B200_VERSION; }
 const char* alg_last_error(void) { return g_err; }
+unsigned long long alg_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int alg_qk_rms_fwd(const alg_qk_rms_args* a, void* stream) {
   if (a == nullptr || a->x == nullptr || a->y == nullptr) { set_error("qk_rms: null argument"); return ALG_ERR_INVALID; }

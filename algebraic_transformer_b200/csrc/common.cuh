@@ -14,6 +14,7 @@ namespace alg {
 // ---- host-side error plumbing -------------------------------------------------------
 void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
+void count_launch(int n = 1);   // bumps the process-wide kernel-launch counter (alg_kernel_launches)
 
 #define ALG_CUDA_TRY(expr)                                     \
   do {                                                         \

@@ -160,6 +160,7 @@ int launch_decode(const DecodeParams& p, cudaStream_t stream) {
     return ALG_ERR_UNSUPPORTED;
   }
   ALG_CUDA_TRY(cudaGetLastError());
+  count_launch(2);
   return ALG_OK;
 }
 

@@ -226,12 +226,14 @@ int launch_head_mma(const HeadParams& p, cudaStream_t stream) {
   dim3 grid((p.N + BM - 1) / BM, p.splits);
   head_mma_kernel<<<grid, NTHREADS, 2 * STAGE_BYTES, stream>>>(p);
   ALG_CUDA_TRY(cudaGetLastError());
+  count_launch();
   return ALG_OK;
 }
 
 int launch_head_reduce(const HeadParams& p, cudaStream_t stream) {
   head_reduce_kernel<<<(p.N + 255) / 256, 256, 0, stream>>>(p.l_part, p.zt_part, p.N, p.splits, p.l_out, p.zt_out);
   ALG_CUDA_TRY(cudaGetLastError());
+  count_launch();
   return ALG_OK;
 }
 
@@ -243,6 +245,7 @@ int launch_head_finalize(const float* l, const float* zt, int N, int log2n, floa
   head_finalize_kernel<<<head_finalize_blocks(N), FIN_THREADS, 0, stream>>>(
       l, zt, N, log2n, inv_c, clamp, pt, nll, obj, block_sums, ticket);
   ALG_CUDA_TRY(cudaGetLastError());
+  count_launch();
   return ALG_OK;
 }
 

@@ -147,6 +147,7 @@ static int launch_t(const PrepParams& p, cudaStream_t stream) {
   if (blocks > cap) blocks = cap;
   qk_prep_kernel<T, D><<<dim3(unsigned(blocks)), 256, 0, stream>>>(p);
   ALG_CUDA_TRY(cudaGetLastError());
+  count_launch();
   return ALG_OK;
 }
 
@@ -187,6 +188,7 @@ int launch_cast(const float* src, void* dst, size_t count, cudaStream_t stream) 
   if (blocks == 0) blocks = 1;
   cast_f32_bf16_kernel<<<unsigned(blocks), 256, 0, stream>>>(src, reinterpret_cast<__nv_bfloat16*>(dst), count);
   ALG_CUDA_TRY(cudaGetLastError());
+  count_launch();
   return ALG_OK;
 }
 

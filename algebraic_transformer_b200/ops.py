@@ -154,7 +154,8 @@ def flash_attention(q, k, v, sink_logit=None, *, kind: str = "softmax", n: int =
                     diagonal_bwd: Optional[bool] = None, diagonal_fwd: Optional[bool] = None,
                     head_resident: Optional[bool] = None,
                     q_gain=None, k_gain=None, cos=None, sin=None, eps: float = 1e-5,
-                    causal: bool = True, return_stat: bool = False, impl: str = "auto", out=None):
+                    causal: bool = True, return_stat: bool = False, impl: str = "auto", out=None,
+                    bounded_scores: bool = False):
     """Causal asinh-power attention on (B,H,T,D); `sink_logit` broadcastable to (H,).
 
     Same keywords as the reference entry point.  TPU tiling/residency knobs (`block*`,
@@ -202,7 +203,9 @@ def flash_attention(q, k, v, sink_logit=None, *, kind: str = "softmax", n: int =
     elif shift:
         variant, score_clamp = L.ALG_VARIANT_SHIFT, 0.0
     else:
-        variant, score_clamp = L.ALG_VARIANT_NOSHIFT, clamp
+        # `bounded_scores` is the reference's internal flag of the guard's in-range branch
+        # (flash.py:850): the caller vouches for the score range, so no upper clamp is applied.
+        variant, score_clamp = L.ALG_VARIANT_NOSHIFT, (0.0 if bounded_scores else clamp)
 
     sink = None
     if sink_logit is not None:
@@ -218,6 +221,8 @@ def flash_attention(q, k, v, sink_logit=None, *, kind: str = "softmax", n: int =
     o = torch.empty((B, H, T, D), dtype=q.dtype, device=q.device) if out is None else out
     stat = torch.empty((B, H, T), dtype=torch.float32, device=q.device) if return_stat else None
     stat_kind = torch.zeros(1, dtype=torch.int32, device=q.device) if return_stat else None
+    if q.numel() == 0:
+        return (o, stat, stat_kind) if return_stat else o
     a = L.AttnArgs(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), o=o.data_ptr(), stat=_ptr(stat),
                    stat_kind=_ptr(stat_kind), sink=_ptr(sink), q_gain=_ptr(q_gain), k_gain=_ptr(k_gain),
                    cos=_ptr(cos), sin=_ptr(sin), eps=float(eps), B=B, H=H, Tq=T, Tk=Tk, D=D, n=int(n),
@@ -231,6 +236,13 @@ def flash_attention(q, k, v, sink_logit=None, *, kind: str = "softmax", n: int =
     if return_stat:
         return o, stat, stat_kind
     return o
+
+
+def _attention_unshifted_unclamped(q, k, v, sink_logit=None, *, n=16, c=8.0, impl="auto", out=None):
+    """The attention kernel the range guard selects when it holds, launched directly with no
+    guard pre-pass (benchmarks use it to time that kernel alone)."""
+    return flash_attention(q, k, v, sink_logit, kind="asinh", n=n, c=c, shift=False, bounded_scores=True,
+                           impl=impl, out=out)
 
 
 def decode_attention(q, k, v, sink_logit=None, *, n: int = 16, c: float = 8.0, out=None):

@@ -1,0 +1,407 @@
+"""Benchmark of the algebraic forward hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline workload (BASELINE config 5 at the length its target is quoted on): asinh-power
+attention forward, bf16, causal, batch 1 x 16 heads x head_dim 128 x seq 8192 PER GPU,
+range-guarded, sink present, n=16, c=8.  Units are (batch, head) pairs; at N GPUs every
+rank runs its own 16 units (weak scaling, no collective on the attention path).
+metric = causal forward TFLOP/s with the reference's FLOP convention 4*B*H*T^2*D/2.
+
+One JSON line on stdout (rank 0).  Besides the contract keys it carries
+  roofline     : the attention kernel alone, timed with CUDA events, against the measured
+                 dense bf16 peak of MEASURED_PEAKS.json
+  cpu_baseline : the CPU oracle timed on this host on a bounded sample
+  e2e          : the same metric through the public Python call with pinned HOST buffers,
+                 host->device copies of q,k,v and the device->host copy of o inside the
+                 timed region
+  extra        : the other hot-path kernels (fused Alg-CE head incl. its all-reduce at N>1,
+                 qk_rms, decode) with their own roofline fractions.
+`--impl reference` times the reference's CPU path (its restatement in oracle/, since JAX
+cannot be installed here) on a bounded sample per step, rank 0 only.
+"""
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+ATTN = dict(B=1, H=16, T=8192, D=128, n=16, c=8.0)
+HEAD = dict(N=8192, d=768, V=50304, n=8, c=2.0, target_hi=50257)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel, from the ncu
+# capture summarised under profiles/ (None until a capture of the current kernel exists).
+ATTN_DRAM_TRAFFIC_BYTES = None
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        p["_source"] = "measured"
+        return p
+    p = dict(FALLBACK_PEAKS)
+    p["_source"] = "fallback"
+    return p
+
+
+def attn_flops(B, H, T, D):
+    return 4.0 * B * H * T * T * D / 2.0
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.lines = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); smax.append(float(parts[2])); power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # the busiest half of the samples is the load the kernels ran under
+        hot = sorted(zip(power, sm))[len(sm) // 2:] if sm else []
+        med = sorted(x[1] for x in hot)[len(hot) // 2] if hot else None
+        return {"sm_mhz": med, "sm_max_mhz": max(smax) if smax else None, "reasons": sorted(reasons),
+                "samples": len(sm), "power_w_max": max(power) if power else None}
+
+
+def make_attn_inputs(device, seed, B=None):
+    g = torch.Generator().manual_seed(seed)
+    B = B or ATTN["B"]
+    shape = (B, ATTN["H"], ATTN["T"], ATTN["D"])
+    q, k, v = (torch.randn(shape, generator=g).bfloat16() for _ in range(3))
+    return q, k, v
+
+
+def run_reference_arm(args, rank):
+    """The reference's CPU implementation of the path (restated in oracle/; JAX is not
+    installable here).  Each step is a bounded sample: one (batch, head) unit at full T."""
+    if rank != 0:
+        return
+    from oracle import algebraic_ref as R
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(0)
+    T, D = ATTN["T"], ATTN["D"]
+    q, k, v = (torch.randn((1, 1, T, D), generator=g).bfloat16() for _ in range(3))
+    sink = torch.zeros(1)
+
+    def step():
+        return R.asinh_attention(q, k, v, n=ATTN["n"], c=ATTN["c"], sink_logit=sink, row_block=1024)
+
+    for _ in range(max(1, min(args.warmup, 2))):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    val = attn_flops(1, 1, T, D) / dt / 1e12
+    sample = f"1 of {ATTN['B'] * ATTN['H']} (batch, head) units per step at full T={T}, D={D}, bf16 inputs, fp32 math"
+    out = {"impl": "reference", "metric": "asinh_attn_fwd_tflops", "value": val, "unit": "TFLOP/s",
+           "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+           "data": "synthetic", "config": workload_config(args.gpus),
+           "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+           "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+           "note": "CPU restatement of src/algebraic/algebraic.py asinh_attention (JAX unavailable offline)"}
+    print(json.dumps(out), flush=True)
+
+
+def workload_config(n_gpus):
+    return {"workload": "asinh attention forward, BASELINE config 5 @ seq 8192 (bf16, causal, range-guarded, sink)",
+            "batch_per_gpu": ATTN["B"], "heads": ATTN["H"], "seq_len": ATTN["T"], "head_dim": ATTN["D"],
+            "n": ATTN["n"], "c": ATTN["c"], "units_per_gpu": ATTN["B"] * ATTN["H"],
+            "parallelism": f"(batch,head) units x{n_gpus}, no collective",
+            "l2_policy": "two input sets alternate (2 x 134 MB of q,k,v,o > 126 MB L2)",
+            "flop_convention": "4*B*H*T^2*D/2 (reference scripts/bench_attention.py:50)"}
+
+
+def cuda_time(fn, iters, sync):
+    """Average milliseconds per call of fn over `iters` back-to-back calls, CUDA events on the
+    current stream, synchronised on both sides."""
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    start.record()
+    for i in range(iters):
+        fn(i)
+    end.record()
+    sync()
+    return start.elapsed_time(end) / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--kernel", default="auto", choices=["auto", "mma", "tcgen05"],
+                    help="attention/head kernel family (auto = tcgen05 where it applies)")
+    ap.add_argument("--skip-extra", action="store_true", help="headline workload only")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    import torch.distributed as dist
+    import algebraic_transformer_b200 as A
+    from algebraic_transformer_b200 import _lib
+    from algebraic_transformer_b200.dist import init_from_env, vocab_shard
+
+    rank, world, local = init_from_env("nccl")
+    if world != args.gpus:
+        if rank == 0:
+            print(f"warning: --gpus {args.gpus} but WORLD_SIZE {world}; using {world}", file=sys.stderr)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    lib = _lib.load()
+    pk = peaks()
+
+    def sync():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---------------- headline: guarded attention, inputs resident in HBM ----------------
+    B, H, T, D = ATTN["B"], ATTN["H"], ATTN["T"], ATTN["D"]
+    host_sets = [make_attn_inputs(dev, 1000 * rank + s) for s in range(2)]
+    dev_sets = [tuple(t.to(dev) for t in hs) for hs in host_sets]
+    outs = [torch.empty((B, H, T, D), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    sink = torch.zeros(H, dtype=torch.float32, device=dev)
+
+    def attn_step(i, variant_guard=True):
+        q, k, v = dev_sets[i & 1]
+        A.flash_attention(q, k, v, sink, kind="asinh", n=ATTN["n"], c=ATTN["c"], range_guard=variant_guard,
+                          shift=False, impl=args.kernel, out=outs[i & 1])
+
+    for i in range(args.warmup):
+        attn_step(i)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.alg_kernel_launches()
+    ms = max_over_ranks(cuda_time(attn_step, args.steps, sync))
+    launches = lib.alg_kernel_launches() - launches0
+    flops_rank = attn_flops(B, H, T, D)
+    value = flops_rank * world / (ms * 1e-3) / 1e12
+
+    # the attention kernel alone (no guard pre-pass), for the roofline line.  An explicit
+    # unshifted launch with the score clamp runs the legacy kernel; the guarded call above is
+    # the one that selects the tcgen05 kernel, so time it through a guard-free internal path.
+    def attn_only(i):
+        q, k, v = dev_sets[i & 1]
+        A.ops._attention_unshifted_unclamped(q, k, v, sink, n=ATTN["n"], c=ATTN["c"], impl=args.kernel,
+                                             out=outs[i & 1])
+
+    for i in range(3):
+        attn_only(i)
+    ms_kernel = max_over_ranks(cuda_time(attn_only, args.steps, sync))
+    clocks = sampler.stop() if rank == 0 else None
+    peak_tf = float(pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    achieved = flops_rank / (ms_kernel * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
+                "frac": achieved / peak_tf, "traffic": ATTN_DRAM_TRAFFIC_BYTES,
+                "kernel_ms": ms_kernel, "peak_source": pk["_source"] + " (burst bf16 GEMM)",
+                "algorithmic_flops_per_launch": flops_rank}
+
+    # ---------------- e2e: host buffers, copies inside the timed region --------------------
+    pinned = [tuple(t.pin_memory() for t in hs) for hs in host_sets]
+    o_host = torch.empty((B, H, T, D), dtype=torch.bfloat16).pin_memory()
+    stage = [torch.empty((B, H, T, D), dtype=torch.bfloat16, device=dev) for _ in range(3)]
+
+    def e2e_step(i):
+        for dst, src in zip(stage, pinned[i & 1]):
+            dst.copy_(src, non_blocking=True)
+        o = A.flash_attention(stage[0], stage[1], stage[2], sink, kind="asinh", n=ATTN["n"], c=ATTN["c"],
+                              range_guard=True, impl=args.kernel, out=outs[0])
+        o_host.copy_(o, non_blocking=True)
+
+    for i in range(2):
+        e2e_step(i)
+    e2e_steps = max(3, min(args.steps, 10))
+    ms_e2e = max_over_ranks(cuda_time(e2e_step, e2e_steps, sync))
+    tensor_bytes = B * H * T * D * 2
+    e2e = {"value": flops_rank * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+           "h2d_bytes_per_step": 3 * tensor_bytes, "d2h_bytes_per_step": tensor_bytes, "ms_per_step": ms_e2e}
+
+    extra = {}
+    if not args.skip_extra:
+        extra = run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, args)
+
+    cpu_baseline = None
+    if rank == 0 and world == 1:
+        cpu_baseline = time_cpu_baseline()
+
+    if rank == 0:
+        out = {"metric": "asinh_attn_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+               "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+               "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+               "config": workload_config(world), "roofline": roofline, "cpu_baseline": cpu_baseline,
+               "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+               "frac_of_bf16_peak_whole_step": value / world / peak_tf, "extra": extra,
+               "library": os.path.relpath(_lib.LIB_PATH, ROOT), "kernel_family": args.kernel}
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def time_cpu_baseline():
+    """The CPU oracle on a bounded sample of the headline workload: a few (batch, head) units
+    at full sequence length, all host threads."""
+    from oracle import algebraic_ref as R
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    T, D = ATTN["T"], ATTN["D"]
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn((1, 1, T, D), generator=g).bfloat16() for _ in range(3))
+    sink = torch.zeros(1)
+    R.asinh_attention(q[:, :, :1024], k[:, :, :1024], v[:, :, :1024], n=16, c=8.0, sink_logit=sink)  # warm threads
+    units, t0 = 0, time.perf_counter()
+    while units < 4 and (time.perf_counter() - t0 < 20.0 or units == 0):
+        R.asinh_attention(q, k, v, n=ATTN["n"], c=ATTN["c"], sink_logit=sink, row_block=1024)
+        units += 1
+    dt = time.perf_counter() - t0
+    return {"value": attn_flops(1, units, T, D) / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "sample": f"{units} of {ATTN['B'] * ATTN['H']} (batch, head) units at full T={T}, D={D} "
+                      f"({dt:.1f} s of CPU work); oracle/algebraic_ref.py asinh_attention, fp32 math, torch CPU threads"}
+
+
+def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, args):
+    """Head (vocab-sharded, with its all-reduce at N>1), qk_rms and decode."""
+    extra = {}
+    peak_tf = float(pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    peak_bw = float(pk.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+    iters = max(5, min(args.steps, 20))
+    # ---- fused Alg-CE head: BASELINE config 2, vocabulary sharded over ranks ----
+    N, d, V = HEAD["N"], HEAD["d"], HEAD["V"]
+    g = torch.Generator().manual_seed(0)
+    h = torch.randn((N, d), generator=g).bfloat16().to(dev)
+    lo, cnt = vocab_shard(V, rank, world)
+    ge = torch.Generator().manual_seed(1 + rank)
+    e = (torch.randn((cnt, d), generator=ge) * 0.02).bfloat16().to(dev)
+    t = torch.randint(0, HEAD["target_hi"], (N,), generator=g).to(torch.int32).to(dev)
+    stats = torch.empty((2, N), dtype=torch.float32, device=dev)
+
+    def head_step(i):
+        A.head_statistic(h, e, t, n=HEAD["n"], c=HEAD["c"], vocab_offset=lo, vocab_total=V, impl=args.kernel,
+                         out=stats)
+        if world > 1:
+            dist.all_reduce(stats, op=dist.ReduceOp.SUM)
+        A.head_finalize(stats, n=HEAD["n"], c=HEAD["c"], vocab_total=V)
+
+    def head_kernel_only(i):
+        A.head_statistic(h, e, t, n=HEAD["n"], c=HEAD["c"], vocab_offset=lo, vocab_total=V, impl=args.kernel,
+                         out=stats)
+
+    for i in range(3):
+        head_step(i)
+    ms_head = max_over_ranks(cuda_time(head_step, iters, sync))
+    ms_head_k = max_over_ranks(cuda_time(head_kernel_only, iters, sync))
+    fl = 2.0 * N * d * V
+    extra["alg_ce_head"] = {
+        "workload": f"BASELINE config 2: N={N}, d={d}, V={V} bf16, vocab sharded x{world}",
+        "tflops": fl / (ms_head * 1e-3) / 1e12, "ms_per_step": ms_head,
+        "kernel_ms": ms_head_k, "kernel_tflops_per_gpu": 2.0 * N * d * cnt / (ms_head_k * 1e-3) / 1e12,
+        "frac_of_bf16_peak": 2.0 * N * d * cnt / (ms_head_k * 1e-3) / 1e12 / peak_tf,
+        "collective": "none" if world == 1 else "one NCCL all-reduce of (2,N) fp32 per step",
+        "logits_bytes_written": 0}
+    if world > 1:
+        return extra
+    # ---- standalone qk_rms (+ rotation): HBM bound ----
+    B, H, T, D = 1, 16, 32768, 128
+    x = torch.randn((B, H, T, D), generator=g).bfloat16().to(dev)
+    y = torch.empty_like(x)
+    gain = torch.ones(D, device=dev)
+    cos, sin = A.cayley_table_geometric(D, T, device=dev)
+    for rot in (False, True):
+        kw = dict(cos=cos, sin=sin) if rot else {}
+        fn = lambda i: A.qk_rms_norm(x, gain, out=y, **kw)  # noqa: E731
+        for i in range(3):
+            fn(i)
+        ms_r = cuda_time(fn, iters, sync)
+        nbytes = 2.0 * x.numel() * 2
+        extra["qk_rms_rot" if rot else "qk_rms"] = {
+            "workload": f"(1,16,{T},{D}) bf16 (134 MB in + 134 MB out, > L2)", "ms": ms_r,
+            "gbs": nbytes / (ms_r * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms_r * 1e-3) / 1e9 / peak_bw}
+    # ---- single-query decode against a 32768-token KV cache: HBM bound ----
+    k = x
+    v = torch.randn((B, H, T, D), generator=g).bfloat16().to(dev)
+    qd = torch.randn((B, H, 1, D), generator=g).bfloat16().to(dev)
+    od = torch.empty((B, H, 1, D), dtype=torch.bfloat16, device=dev)
+    sink = torch.zeros(H, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    fn = lambda i: A.decode_attention(qd, k, v, sink, n=16, c=8.0, out=od)  # noqa: E731
+    for i in range(3):
+        fn(i)
+    # 268 MB of K,V > L2, so back-to-back launches already stream from HBM
+    ms_d = cuda_time(fn, iters, sync)
+    nbytes = 2.0 * k.numel() * 2
+    extra["decode"] = {"workload": f"Tq=1 vs KV cache (1,16,{T},{D}) bf16 = 268 MB", "ms": ms_d,
+                       "gbs": nbytes / (ms_d * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms_d * 1e-3) / 1e9 / peak_bw}
+    del flush
+    return extra
+
+
+if __name__ == "__main__":
+    main()

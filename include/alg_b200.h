@@ -60,6 +60,9 @@ enum { ALG_IMPL_AUTO = 0, ALG_IMPL_MMA = 1, ALG_IMPL_TCGEN05 = 2 };
 
 ALG_API int alg_version(void);
 ALG_API const char* alg_last_error(void);
+/* Number of kernels this library has launched in this process so far (diagnostics: lets a
+ * caller verify that work ran on the GPU kernels here and count launches per step). */
+ALG_API unsigned long long alg_kernel_launches(void);
 
 /* ------------------------------------------------------------------------------------
  * QK RMS normalisation (+ optional Cayley rotation).

@@ -224,11 +224,13 @@ def asinh_attention(q, k, v, *, n: int, c: float, sink_logit=None, causal: bool 
     step = row_block if row_block > 0 else Tq
     for r0 in range(0, Tq, step):
         r1 = min(Tq, r0 + step)
-        kmax = r1 if causal else Tk
+        kmax = min(Tk, r1 + (Tk - Tq)) if causal else Tk
         s = torch.matmul(q[:, :, r0:r1].to(acc), kf[:, :, :kmax].transpose(-1, -2))
         s = s * (1.0 / math.sqrt(D))
         if causal:
-            rows = torch.arange(r0, r1)[:, None]
+            # query i sits at absolute position i + (Tk - Tq): square problems are the
+            # reference's tril mask, Tq < Tk is "the last Tq rows of the square problem"
+            rows = torch.arange(r0, r1)[:, None] + (Tk - Tq)
             cols = torch.arange(kmax)[None, :]
             mask = (cols <= rows)[None, None]
         else:
