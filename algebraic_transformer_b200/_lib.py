@@ -64,6 +64,7 @@ SYMBOLS = {
     "alg_attn_decode": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "alg_head_workspace_bytes": (C.c_size_t, [C.POINTER(HeadArgs)]),
     "alg_head_fwd": (C.c_int, [C.POINTER(HeadArgs), C.c_void_p]),
+    "alg_head_fwd_static": (C.c_int, [C.POINTER(HeadArgs), C.c_void_p]),
     "alg_head_finalize_workspace_bytes": (C.c_size_t, [C.c_int]),
     "alg_head_finalize": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_int,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),

@@ -240,7 +240,8 @@ int alg_attn_decode(const alg_decode_args* a, void* stream) {
   return launch_decode(p, static_cast<cudaStream_t>(stream));
 }
 
-static int head_fill(const alg_head_args* a, HeadParams* p, bool* use_fast) {
+// Validation and parameter derivation shared by every head entry point (not exported).
+int head_fill(const alg_head_args* a, HeadParams* p, bool* use_fast) {
   if (a == nullptr || a->h == nullptr || a->e == nullptr || a->targets == nullptr || a->l_out == nullptr || a->zt_out == nullptr) {
     set_error("head: null argument");
     return ALG_ERR_INVALID;

@@ -106,5 +106,7 @@ int launch_head_finalize(const float* l, const float* zt, int N, int log2n, floa
                          float* pt, float* nll, float* obj, float* block_sums, unsigned* ticket,
                          cudaStream_t stream);
 int head_finalize_blocks(int N);
+// c_api.cu: argument checks + HeadParams derivation common to the head entry points
+extern "C" int head_fill(const alg_head_args* a, HeadParams* p, bool* use_fast);
 
 }  // namespace alg

@@ -305,6 +305,21 @@ def head_statistic(h, e_bf16, targets, *, n: int, c: float, vocab_offset: int = 
     return stats
 
 
+def head_statistic_no_alloc(h, e_bf16, targets, out, *, n: int, c: float, vocab_offset: int = 0,
+                            vocab_total: Optional[int] = None, impl: str = "auto"):
+    """`head_statistic` through `alg_head_fwd_static`: the same (2, N) statistic, written
+    into the caller's `out`, with the kernel's scratch taken from the array built into the
+    library instead of a workspace allocated here.  Meant for callers that may not allocate
+    device memory at call time; problems whose partials exceed the built-in array raise
+    ValueError.  Calls on one device share that array, so do not let two of them overlap."""
+    N, d = h.shape
+    a = L.HeadArgs(h=h.data_ptr(), e=e_bf16.data_ptr(), targets=targets.data_ptr(), l_out=out[0].data_ptr(),
+                   zt_out=out[1].data_ptr(), N=N, d=d, V_local=e_bf16.shape[0], vocab_offset=int(vocab_offset),
+                   V_total=int(vocab_total or e_bf16.shape[0]), n=int(n), c=float(c), impl=L.IMPL[impl])
+    L.check(L.load().alg_head_fwd_static(a, _stream()))
+    return out
+
+
 def head_finalize(stats, *, n: int, c: float, vocab_total: int, want_nll: bool = False):
     """(objective, p_target[, nll]) from the (all-reduced) (2, N) statistic."""
     N = stats.shape[1]

@@ -188,6 +188,28 @@ typedef struct {
 ALG_API size_t alg_head_workspace_bytes(const alg_head_args* args);
 ALG_API int alg_head_fwd(const alg_head_args* args, void* stream);
 
+/* The same computation as alg_head_fwd for callers that cannot allocate device memory and
+ * therefore cannot supply `workspace` — for example a custom-call handler under a runtime
+ * that owns every device buffer and hands the handler only its operands and results, or a
+ * long-running server whose memory plan is frozen after start-up.
+ * This entry point has no counterpart in the reference.
+ *   - `workspace`, `workspace_bytes` are ignored.  The split partials go to a fixed array
+ *     of ALG_HEAD_STATIC_SCRATCH_BYTES compiled into the library; every GPU that loads the
+ *     library keeps that much memory reserved until the process ends.
+ *   - Limit: 8 * N * (partial slots) bytes must fit in the array — N = 8192 tokens with the
+ *     full 50304-row vocabulary does; larger problems are refused with ALG_ERR_WORKSPACE
+ *     and a message, and should use alg_head_fwd.
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine.  The first call
+ *     on each device looks up the array's device address (with that device current); make
+ *     that first call outside any stream capture.
+ *   - All calls on a device share the one array, and a call overwrites what the previous
+ *     one left there (nothing in it has to be cleared).  Two calls whose kernels may
+ *     overlap on the GPU — different streams, no ordering between them — race on it;
+ *     serialise them, or give one of them alg_head_fwd with its own workspace.
+ * Inputs, outputs and results are exactly those of alg_head_fwd. */
+#define ALG_HEAD_STATIC_SCRATCH_BYTES (4u << 20)
+ALG_API int alg_head_fwd_static(const alg_head_args* args, void* stream);
+
 /* Telemetry from the (all-reduced) statistic.
  * Replaces: _telemetry + the _inv_root finalize  src/algebraic/kernels/fused_head.py:116,219-229
  *           NLL = -log(max(pt,1e-30))            src/algebraic/train.py:239
