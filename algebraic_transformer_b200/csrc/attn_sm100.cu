@@ -52,6 +52,68 @@ struct __align__(16) Control {
   int shift_mode;
 };
 
+// 32 scores -> 32 weights rho_fast(s * scale)^n, two at a time on the packed fp32 pipe
+// (fma.f32x2 / mul.f32x2); row-sum partials in `la`, `lb`; bf16 pairs in `packed`.
+template <int LOG2N, bool DIAG>
+__device__ __forceinline__ void weigh32(const uint32_t* s, float scale, int col0, int r, float2& la, float2& lb,
+                                        uint32_t* packed) {
+  const float2 sc = make_float2(scale, scale), one = make_float2(1.f, 1.f);
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    float2 x0 = __fmul2_rn(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc);
+    float2 x1 = __fmul2_rn(make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), sc);
+    const float2 rad0 = __ffma2_rn(x0, x0, one), rad1 = __ffma2_rn(x1, x1, one);
+    const float2 rs0 = make_float2(rsqrt_approx(rad0.x), rsqrt_approx(rad0.y));
+    const float2 rs1 = make_float2(rsqrt_approx(rad1.x), rsqrt_approx(rad1.y));
+    float2 t0 = __ffma2_rn(rad0, rs0, x0), t1 = __ffma2_rn(rad1, rs1, x1);
+#pragma unroll
+    for (int k = 0; k < LOG2N; ++k) { t0 = __fmul2_rn(t0, t0); t1 = __fmul2_rn(t1, t1); }
+    if (DIAG) {                                     // causal mask inside the diagonal tile
+      t0.x = (col0 + i <= r) ? t0.x : 0.f;     t0.y = (col0 + i + 1 <= r) ? t0.y : 0.f;
+      t1.x = (col0 + i + 2 <= r) ? t1.x : 0.f; t1.y = (col0 + i + 3 <= r) ? t1.y : 0.f;
+    }
+    la = __fadd2_rn(la, t0);
+    lb = __fadd2_rn(lb, t1);
+    packed[i >> 1] = pack_bf16(t0.x, t0.y);
+    packed[(i >> 1) + 1] = pack_bf16(t1.x, t1.y);
+  }
+}
+
+// 32 keys = 4 chunks of 16 bytes in this row's 128-byte line of panel (chunk / 2)
+__device__ __forceinline__ void store_p32(unsigned char* p_row, int rsw, int chunk, const uint32_t* packed) {
+  unsigned char* line = p_row + (chunk >> 1) * PANEL_BYTES;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int c16 = (chunk & 1) * 4 + c;
+    *reinterpret_cast<uint4*>(line + ((c16 ^ rsw) << 4)) =
+        make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+  }
+}
+
+// One 128-key score tile of this thread's row: TMEM -> weights -> swizzled shared P.  The
+// load of the next 32 columns is in flight while the current 32 are evaluated.
+template <int LOG2N, bool DIAG>
+__device__ __forceinline__ void weigh_tile(uint32_t s_taddr, unsigned char* p_row, int rsw, int r, float scale,
+                                           float2& la, float2& lb) {
+  uint32_t a[32], b[32], packed[16];
+  tmem_ld_32x32(s_taddr, a);
+  tmem_ld_wait_for(a);
+  tmem_ld_32x32(s_taddr + 32, b);
+  weigh32<LOG2N, DIAG>(a, scale, 0, r, la, lb, packed);
+  store_p32(p_row, rsw, 0, packed);
+  tmem_ld_wait_for(b);
+  tmem_ld_32x32(s_taddr + 64, a);
+  weigh32<LOG2N, DIAG>(b, scale, 32, r, la, lb, packed);
+  store_p32(p_row, rsw, 1, packed);
+  tmem_ld_wait_for(a);
+  tmem_ld_32x32(s_taddr + 96, b);
+  weigh32<LOG2N, DIAG>(a, scale, 64, r, la, lb, packed);
+  store_p32(p_row, rsw, 2, packed);
+  tmem_ld_wait_for(b);
+  weigh32<LOG2N, DIAG>(b, scale, 96, r, la, lb, packed);
+  store_p32(p_row, rsw, 3, packed);
+}
+
 template <int D> constexpr size_t smem_bytes() { return size_t(Cfg<D>::CTL_OFF) + sizeof(Control) + 1024; }
 
 template <int D, int LOG2N>
@@ -154,35 +216,35 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int vidx = 2 * j + 1, kidx = 2 * j + 2;
         bool k_ready = false;
         if (!kv_wait(vidx)) { ok = false; break; }
+        // P_w(j) ready means S_w(j) has been consumed: the next S_w goes first (its weight
+        // group is waiting for it), the P.V product of this tile second.
         if (j < n0) {
           if (!bw.wait(&ctl->p_full[0], j & 1u)) { ok = false; break; }
-          tc_fence_after();
-          issue_pv(0, vidx, j == 0);
-          umma_commit(&ctl->p_free[0]);
           if (j + 1 < n0) {
             if (!kv_wait(kidx)) { ok = false; break; }
             k_ready = true;
             tc_fence_after();
             issue_s(0, kidx);
             umma_commit(&ctl->s_full[0]);
-          } else {
-            umma_commit(&ctl->o_full[0]);
           }
+          tc_fence_after();
+          issue_pv(0, vidx, j == 0);
+          umma_commit(&ctl->p_free[0]);
+          if (j + 1 == n0) umma_commit(&ctl->o_full[0]);
         }
         if (!bw.wait(&ctl->p_full[1], j & 1u)) { ok = false; break; }
-        tc_fence_after();
-        issue_pv(1, vidx, j == 0);
-        umma_commit(&ctl->p_free[1]);
-        umma_commit(&ctl->kv_empty[vidx % C::NKV]);
         if (j + 1 < n1) {
           if (!k_ready && !kv_wait(kidx)) { ok = false; break; }
           tc_fence_after();
           issue_s(1, kidx);
           umma_commit(&ctl->s_full[1]);
           umma_commit(&ctl->kv_empty[kidx % C::NKV]);
-        } else {
-          umma_commit(&ctl->o_full[1]);
         }
+        tc_fence_after();
+        issue_pv(1, vidx, j == 0);
+        umma_commit(&ctl->p_free[1]);
+        umma_commit(&ctl->kv_empty[vidx % C::NKV]);
+        if (j + 1 == n1) umma_commit(&ctl->o_full[1]);
       }
     }
   } else {
@@ -195,44 +257,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int rsw = r & 7;
     float l = 0.f;
     if (p.sink != nullptr) l = pow2n<LOG2N>(rho_stable(p.sink[h] * p.inv_c));
+    const uint32_t s_taddr = tmem_base + lane_sel + C::S_COL + w * 128;
+    float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
     bool ok = true;
     for (int j = 0; j < nk && ok; ++j) {
       if (!bw.wait(&ctl->s_full[w], j & 1u)) { ok = false; break; }
       tc_fence_after();
       if (j > 0 && !bw.wait(&ctl->p_free[w], (j - 1) & 1u)) { ok = false; break; }
-      const bool diag = (j == nk - 1);
-      float l0 = 0.f, l1 = 0.f;
-#pragma unroll 1
-      for (int chunk = 0; chunk < 4; ++chunk) {
-        uint32_t s[32];
-        tmem_ld_32x32(tmem_base + lane_sel + C::S_COL + w * 128 + chunk * 32, s);
-        tmem_ld_wait();
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float w0 = pow2n<LOG2N>(rho_fast(__uint_as_float(s[i]) * p.scale));
-          float w1 = pow2n<LOG2N>(rho_fast(__uint_as_float(s[i + 1]) * p.scale));
-          if (diag) {                               // causal mask inside the diagonal tile
-            w0 = (chunk * 32 + i <= r) ? w0 : 0.f;
-            w1 = (chunk * 32 + i + 1 <= r) ? w1 : 0.f;
-          }
-          l0 += w0; l1 += w1;
-          packed[i >> 1] = pack_bf16(w0, w1);
-        }
-        // 32 keys = 4 chunks of 16 bytes in this row's 128-byte line of panel (chunk / 2)
-        unsigned char* line = p_row + (chunk >> 1) * PANEL_BYTES;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int c16 = (chunk & 1) * 4 + c;
-          *reinterpret_cast<uint4*>(line + ((c16 ^ rsw) << 4)) =
-              make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-        }
-      }
-      l += l0 + l1;
+      if (j == nk - 1) weigh_tile<LOG2N, true>(s_taddr, p_row, rsw, r, p.scale, la, lb);   // diagonal tile: masked
+      else weigh_tile<LOG2N, false>(s_taddr, p_row, rsw, r, p.scale, la, lb);
       tc_fence_before();
       fence_async_shared();                         // P stores -> visible to the tensor core's reads
       mbar_arrive(&ctl->p_full[w]);
     }
+    l += (la.x + la.y) + (lb.x + lb.y);
     if (ok && bw.wait(&ctl->o_full[w], 0)) {
       tc_fence_after();
       const float inv = 1.0f / l;
