@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "lib", "libalg_b200.so")
+# ALG_B200_LIB selects another build of the same ABI (e.g. an instrumented one).
+LIB_PATH = os.environ.get("ALG_B200_LIB") or os.path.join(PKG, "lib", "libalg_b200.so")
 
 ALG_OK = 0
 ALG_ERR_INVALID, ALG_ERR_UNSUPPORTED, ALG_ERR_CUDA, ALG_ERR_WORKSPACE = -1, -2, -3, -4

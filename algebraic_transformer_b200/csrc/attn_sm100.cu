@@ -8,12 +8,19 @@
 //
 // One CTA owns 256 consecutive query rows of one (batch, head): two 128-row tiles.
 //   warp 0 (one lane)  TMA: both Q tiles once, then K_j / V_j tiles through a ring
-//   warp 1 (one lane)  tcgen05.mma: S_w = Q_w K_j^T into TMEM, O_w += P_w V_j from shared P_w
+//   warp 1 (one lane)  tcgen05.mma: S_w = Q_w K_j^T (both operands in shared memory) and
+//                      O_w += P_w V_j with P_w read from TENSOR MEMORY (the A operand) and
+//                      V_j from shared memory as an MN-major B operand
 //   warps 2..5         weights for query tile 0: tcgen05.ld S_0 (one thread = one row),
-//                      x -> rho_fast(x)^n in fp32, row sum, bf16 P_0 into swizzled shared memory
+//                      x -> rho_fast(x)^n in packed fp32, row sum, bf16 P_0 written back
+//                      with tcgen05.st over the columns S_0 occupied
 //   warps 6..9         the same for query tile 1
-// The two weight groups run out of phase, so the tensor pipe works for one while the other
-// evaluates rho.  TMEM: S_0, S_1 (128 columns each) + O_0, O_1 (head_dim columns each).
+// The two tiles run out of phase, so the tensor pipe works for one while the other
+// evaluates rho.  TMEM (512 columns): S_0, S_1 (128 each; P_w aliases the first 64 columns
+// of S_w as packed bf16) + O_0, O_1 (head_dim each).  P never touches shared memory, which
+// leaves the tensor core's shared-memory operand path to Q, K and V alone.  The tensor pipe
+// executes one thread's MMAs in issue order, so issuing S_w(j+1) after P_w(j).V_j is what
+// protects P_w(j) from being overwritten, and S_w(j+1) complete implies P_w(j).V_j complete.
 // Key tiles above the diagonal are never loaded; only the diagonal tile evaluates a mask.
 // Every mbarrier wait is bounded (sm100_ptx.cuh); on a timeout the kernel reports
 // ALG_DEV_TIMEOUT through the status word and returns.
@@ -28,25 +35,24 @@ using namespace sm100;
 
 constexpr int BQ = 128, BKEY = 128, NTHREADS = 320;
 constexpr int PANEL_BYTES = 128 * 128;          // 128 rows x 64 bf16, one swizzle-128B panel
-constexpr int P_BYTES = 2 * PANEL_BYTES;        // 128 rows x 128 keys bf16
 constexpr uint32_t TMEM_COLS = 512;
+constexpr int MAX_NKV = 10;
 
 template <int D> struct Cfg {
   static constexpr int PANELS = D / 64;
   static constexpr int TILE_BYTES = PANELS * PANEL_BYTES;   // one Q / K / V tile
-  static constexpr int NKV = (D == 128) ? 3 : 6;            // K/V ring depth (tiles)
+  static constexpr int NKV = (D == 128) ? 5 : 10;           // K/V ring depth (tiles)
   static constexpr int Q_OFF = 0;
-  static constexpr int P_OFF = 2 * TILE_BYTES;
-  static constexpr int KV_OFF = P_OFF + 2 * P_BYTES;
+  static constexpr int KV_OFF = 2 * TILE_BYTES;
   static constexpr int CTL_OFF = KV_OFF + NKV * TILE_BYTES;
-  static constexpr uint32_t S_COL = 0;                      // S_w at S_COL + 128 w
+  static constexpr uint32_t S_COL = 0;                      // S_w at S_COL + 128 w; P_w = its first 64 columns
   static constexpr uint32_t O_COL = 256;                    // O_w at O_COL + D w
   static constexpr uint32_t IDESC_S = make_idesc_bf16(BQ, BKEY, 0, 0);
   static constexpr uint32_t IDESC_PV = make_idesc_bf16(BQ, D, 0, 1);   // V is [key][d]: MN-major B
 };
 
 struct __align__(16) Control {
-  uint64_t q_full, kv_full[6], kv_empty[6], s_full[2], p_full[2], p_free[2], o_full[2];
+  uint64_t q_full, kv_full[MAX_NKV], kv_empty[MAX_NKV], s_full[2], p_full[2], o_full[2];
   uint32_t tmem_base;
   int abort_flag;
   int shift_mode;
@@ -79,42 +85,39 @@ __device__ __forceinline__ void weigh32(const uint32_t* s, float scale, int col0
   }
 }
 
-// 32 keys = 4 chunks of 16 bytes in this row's 128-byte line of panel (chunk / 2)
-__device__ __forceinline__ void store_p32(unsigned char* p_row, int rsw, int chunk, const uint32_t* packed) {
-  unsigned char* line = p_row + (chunk >> 1) * PANEL_BYTES;
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    const int c16 = (chunk & 1) * 4 + c;
-    *reinterpret_cast<uint4*>(line + ((c16 ^ rsw) << 4)) =
-        make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-  }
-}
-
-// One 128-key score tile of this thread's row: TMEM -> weights -> swizzled shared P.  The
-// load of the next 32 columns is in flight while the current 32 are evaluated.
+// One 128-key score tile of this thread's row: S from TMEM -> weights -> packed bf16 P back
+// into TMEM over the same columns.  Columns 32c..32c+31 of S become columns 16c..16c+15 of
+// P, always at or below what has already been read, and the load of the next 32 columns is
+// in flight while the current 32 are evaluated.
 template <int LOG2N, bool DIAG>
-__device__ __forceinline__ void weigh_tile(uint32_t s_taddr, unsigned char* p_row, int rsw, int r, float scale,
-                                           float2& la, float2& lb) {
+__device__ __forceinline__ void weigh_tile(uint32_t s_taddr, int r, float scale, float2& la, float2& lb) {
   uint32_t a[32], b[32], packed[16];
   tmem_ld_32x32(s_taddr, a);
   tmem_ld_wait_for(a);
   tmem_ld_32x32(s_taddr + 32, b);
   weigh32<LOG2N, DIAG>(a, scale, 0, r, la, lb, packed);
-  store_p32(p_row, rsw, 0, packed);
+  tmem_st_32x16(s_taddr, packed);
   tmem_ld_wait_for(b);
   tmem_ld_32x32(s_taddr + 64, a);
   weigh32<LOG2N, DIAG>(b, scale, 32, r, la, lb, packed);
-  store_p32(p_row, rsw, 1, packed);
+  tmem_st_32x16(s_taddr + 16, packed);
   tmem_ld_wait_for(a);
   tmem_ld_32x32(s_taddr + 96, b);
   weigh32<LOG2N, DIAG>(a, scale, 64, r, la, lb, packed);
-  store_p32(p_row, rsw, 2, packed);
+  tmem_st_32x16(s_taddr + 32, packed);
   tmem_ld_wait_for(b);
   weigh32<LOG2N, DIAG>(b, scale, 96, r, la, lb, packed);
-  store_p32(p_row, rsw, 3, packed);
+  tmem_st_32x16(s_taddr + 48, packed);
+  tmem_st_wait();
 }
 
 template <int D> constexpr size_t smem_bytes() { return size_t(Cfg<D>::CTL_OFF) + sizeof(Control) + 1024; }
+
+#ifdef ALG_ATTN_TIMING   // optional instrumentation build: cycle counters written into `stat`
+#define ALG_T(acc, expr) [&] { const long long t_ = clock64(); const bool r_ = (expr); acc += clock64() - t_; return r_; }()
+#else
+#define ALG_T(acc, expr) (expr)
+#endif
 
 template <int D, int LOG2N>
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -136,7 +139,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     for (int w = 0; w < 2; ++w) {
       mbar_init(&ctl->s_full[w], 1);
       mbar_init(&ctl->p_full[w], 128);
-      mbar_init(&ctl->p_free[w], 1);
       mbar_init(&ctl->o_full[w], 1);
     }
     ctl->abort_flag = 0;
@@ -161,6 +163,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const int b = bh / p.H, h = bh % p.H;
   const int row0 = blk * 2 * BQ;
   const int n0 = 2 * blk + 1, n1 = 2 * blk + 2;   // key tiles needed by query tile 0 / 1
+  long long tm0 = 0, tm1 = 0, tm2 = 0;            // timing accumulators (instrumentation build only)
+  (void)tm0; (void)tm1; (void)tm2;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -184,8 +188,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t q_addr = smem_u32(smem + C::Q_OFF), p_addr = smem_u32(smem + C::P_OFF);
-      const uint32_t kv_addr = smem_u32(smem + C::KV_OFF);
+      const uint32_t q_addr = smem_u32(smem + C::Q_OFF), kv_addr = smem_u32(smem + C::KV_OFF);
       auto kv_wait = [&](int idx) { return bw.wait(&ctl->kv_full[idx % C::NKV], (idx / C::NKV) & 1u); };
       auto issue_s = [&](int w, int idx) {            // S_w = Q_w K^T
         const uint32_t qa = q_addr + w * C::TILE_BYTES, ka = kv_addr + (idx % C::NKV) * C::TILE_BYTES;
@@ -196,15 +199,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                       make_sw128_desc(ka + off, 16, 1024), C::IDESC_S, ks != 0 ? 1u : 0u);
         }
       };
-      auto issue_pv = [&](int w, int idx, bool first) {   // O_w += P_w V
-        const uint32_t pa = p_addr + w * P_BYTES, va = kv_addr + (idx % C::NKV) * C::TILE_BYTES;
+      auto issue_pv = [&](int w, int idx, bool first) {   // O_w += P_w V, P_w from tensor memory
+        const uint32_t va = kv_addr + (idx % C::NKV) * C::TILE_BYTES;
 #pragma unroll
-        for (int ks = 0; ks < BKEY / 16; ++ks) {
-          const uint32_t aoff = (ks >> 2) * PANEL_BYTES + (ks & 3) * 32;
-          umma_f16_ss(tmem_base + C::O_COL + w * D, make_sw128_desc(pa + aoff, 16, 1024),
+        for (int ks = 0; ks < BKEY / 16; ++ks)        // 16 keys = 8 packed-bf16 columns of P per step
+          umma_f16_ts(tmem_base + C::O_COL + w * D, tmem_base + C::S_COL + w * 128 + ks * 8,
                       make_sw128_desc(va + ks * 2048, PANEL_BYTES, 1024), C::IDESC_PV, (first && ks == 0) ? 0u : 1u);
-        }
       };
+#ifdef ALG_ATTN_TIMING
+      const long long t_begin = clock64();
+#endif
       bool ok = bw.wait(&ctl->q_full, 0) && kv_wait(0);
       if (ok) {
         tc_fence_after();
@@ -215,37 +219,41 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       for (int j = 0; j < n1 && ok; ++j) {
         const int vidx = 2 * j + 1, kidx = 2 * j + 2;
         bool k_ready = false;
-        if (!kv_wait(vidx)) { ok = false; break; }
-        // P_w(j) ready means S_w(j) has been consumed: the next S_w goes first (its weight
-        // group is waiting for it), the P.V product of this tile second.
+        if (!ALG_T(tm0, kv_wait(vidx))) { ok = false; break; }
         if (j < n0) {
-          if (!bw.wait(&ctl->p_full[0], j & 1u)) { ok = false; break; }
-          if (j + 1 < n0) {
-            if (!kv_wait(kidx)) { ok = false; break; }
-            k_ready = true;
-            tc_fence_after();
-            issue_s(0, kidx);
-            umma_commit(&ctl->s_full[0]);
-          }
+          if (!ALG_T(tm1, bw.wait(&ctl->p_full[0], j & 1u))) { ok = false; break; }
           tc_fence_after();
           issue_pv(0, vidx, j == 0);
-          umma_commit(&ctl->p_free[0]);
-          if (j + 1 == n0) umma_commit(&ctl->o_full[0]);
+          if (j + 1 < n0) {
+            if (!ALG_T(tm0, kv_wait(kidx))) { ok = false; break; }
+            k_ready = true;
+            tc_fence_after();
+            issue_s(0, kidx);                       // after P_0.V: may overwrite P_0
+            umma_commit(&ctl->s_full[0]);
+          } else {
+            umma_commit(&ctl->o_full[0]);
+          }
         }
-        if (!bw.wait(&ctl->p_full[1], j & 1u)) { ok = false; break; }
+        if (!ALG_T(tm2, bw.wait(&ctl->p_full[1], j & 1u))) { ok = false; break; }
+        tc_fence_after();
+        issue_pv(1, vidx, j == 0);
+        umma_commit(&ctl->kv_empty[vidx % C::NKV]);
         if (j + 1 < n1) {
-          if (!k_ready && !kv_wait(kidx)) { ok = false; break; }
+          if (!k_ready && !ALG_T(tm0, kv_wait(kidx))) { ok = false; break; }
           tc_fence_after();
           issue_s(1, kidx);
           umma_commit(&ctl->s_full[1]);
           umma_commit(&ctl->kv_empty[kidx % C::NKV]);
+        } else {
+          umma_commit(&ctl->o_full[1]);
         }
-        tc_fence_after();
-        issue_pv(1, vidx, j == 0);
-        umma_commit(&ctl->p_free[1]);
-        umma_commit(&ctl->kv_empty[vidx % C::NKV]);
-        if (j + 1 == n1) umma_commit(&ctl->o_full[1]);
       }
+#ifdef ALG_ATTN_TIMING
+      if (blockIdx.x == 0 && p.stat != nullptr) {
+        float* dbg = p.stat + 16;
+        dbg[0] = float(tm0); dbg[1] = float(tm1); dbg[2] = float(tm2); dbg[3] = float(clock64() - t_begin);
+      }
+#endif
     }
   } else {
     const int w = (warp - 2) >> 2;                  // query tile of this weight group
@@ -253,23 +261,34 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int r = quarter * 32 + lane;              // row inside the query tile
     const int nk = (w == 0) ? n0 : n1;
     const uint32_t lane_sel = uint32_t(quarter * 32) << 16;
-    unsigned char* p_row = smem + C::P_OFF + w * P_BYTES + r * 128;
-    const int rsw = r & 7;
     float l = 0.f;
     if (p.sink != nullptr) l = pow2n<LOG2N>(rho_stable(p.sink[h] * p.inv_c));
     const uint32_t s_taddr = tmem_base + lane_sel + C::S_COL + w * 128;
     float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
     bool ok = true;
+#ifdef ALG_ATTN_TIMING
+    const long long t_begin = clock64();
+#endif
     for (int j = 0; j < nk && ok; ++j) {
-      if (!bw.wait(&ctl->s_full[w], j & 1u)) { ok = false; break; }
+      if (!ALG_T(tm0, bw.wait(&ctl->s_full[w], j & 1u))) { ok = false; break; }
       tc_fence_after();
-      if (j > 0 && !bw.wait(&ctl->p_free[w], (j - 1) & 1u)) { ok = false; break; }
-      if (j == nk - 1) weigh_tile<LOG2N, true>(s_taddr, p_row, rsw, r, p.scale, la, lb);   // diagonal tile: masked
-      else weigh_tile<LOG2N, false>(s_taddr, p_row, rsw, r, p.scale, la, lb);
+#ifdef ALG_ATTN_TIMING
+      const long long tc0 = clock64();
+#endif
+      if (j == nk - 1) weigh_tile<LOG2N, true>(s_taddr, r, p.scale, la, lb);   // diagonal tile: masked
+      else weigh_tile<LOG2N, false>(s_taddr, r, p.scale, la, lb);
       tc_fence_before();
-      fence_async_shared();                         // P stores -> visible to the tensor core's reads
       mbar_arrive(&ctl->p_full[w]);
+#ifdef ALG_ATTN_TIMING
+      tm1 += clock64() - tc0;
+#endif
     }
+#ifdef ALG_ATTN_TIMING
+    if (blockIdx.x == 0 && r == 0 && p.stat != nullptr) {
+      float* dbg = p.stat + 8 * w;
+      dbg[0] = float(tm0); dbg[1] = 0.f; dbg[2] = float(tm1); dbg[3] = float(clock64() - t_begin); dbg[4] = float(nk);
+    }
+#endif
     l += (la.x + la.y) + (lb.x + lb.y);
     if (ok && bw.wait(&ctl->o_full[w], 0)) {
       tc_fence_after();
@@ -280,7 +299,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       for (int chunk = 0; chunk < D / 32; ++chunk) {
         uint32_t o[32];
         tmem_ld_32x32(tmem_base + lane_sel + C::O_COL + w * D + chunk * 32, o);
-        tmem_ld_wait();
+        tmem_ld_wait_for(o);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint4 val;
@@ -291,7 +310,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           *reinterpret_cast<uint4*>(orow + chunk * 32 + c * 8) = val;
         }
       }
+#ifndef ALG_ATTN_TIMING
       if (p.stat != nullptr) p.stat[(int64_t(b) * p.H + h) * p.Tq + row] = inv;
+#endif
     }
   }
 
