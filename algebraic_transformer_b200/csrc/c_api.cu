@@ -164,6 +164,7 @@ int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
     const size_t es = elem_size(a->dtype);
     void* qn = ws + 256;
     void* kn = ws + 256 + align256(size_t(a->B) * a->H * a->Tq * a->D * es);
+    PrepBatch batch{};
     PrepParams pp{};
     pp.eps = a->eps; pp.B = a->B; pp.H = a->H; pp.D = a->D;
     pp.cos = prologue ? a->cos : nullptr; pp.sin = prologue ? a->sin : nullptr;
@@ -172,17 +173,18 @@ int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
     pp.x = a->q; pp.xs = p.qs; pp.T = a->Tq; pp.gain = a->q_gain;
     pp.y = prologue ? qn : nullptr; pp.ys = strides_or_dense(kDense, a->H, a->Tq, a->D);
     pp.stat_mode = guarded ? 1 : 0; pp.stat_scale = p.scale; pp.stat_out = &guard->q2;
-    if (int rc = launch_prep(pp, a->dtype, stream)) return rc;
+    batch.t[batch.count++] = pp;
     // k
     pp.x = a->k; pp.xs = p.ks; pp.T = a->Tk; pp.gain = a->k_gain;
     pp.y = prologue ? kn : nullptr; pp.ys = strides_or_dense(kDense, a->H, a->Tk, a->D);
     pp.stat_scale = 1.0f; pp.stat_out = &guard->k2;
-    if (int rc = launch_prep(pp, a->dtype, stream)) return rc;
+    batch.t[batch.count++] = pp;
     if (guarded) {                                      // v: max |v| only
       pp.x = a->v; pp.xs = p.vs; pp.y = nullptr; pp.gain = nullptr; pp.cos = nullptr; pp.sin = nullptr;
       pp.normalise = 0; pp.stat_mode = 2; pp.stat_out = &guard->vmax;
-      if (int rc = launch_prep(pp, a->dtype, stream)) return rc;
+      batch.t[batch.count++] = pp;
     }
+    if (int rc = launch_prep_batch(batch, a->dtype, stream)) return rc;   // one launch for all of them
     if (prologue) {
       p.q = qn; p.k = kn;
       p.qs = strides_or_dense(kDense, a->H, a->Tq, a->D);

@@ -23,7 +23,12 @@ struct PrepParams {
   float stat_scale;
   unsigned* stat_out;
 };
+struct PrepBatch {         // up to three tensors (q, k, v) of one dtype / head_dim in one launch
+  PrepParams t[3];
+  int count;
+};
 int launch_prep(const PrepParams& p, int dtype, cudaStream_t stream);
+int launch_prep_batch(const PrepBatch& batch, int dtype, cudaStream_t stream);
 int launch_cast(const float* src, void* dst, size_t count, cudaStream_t stream);
 
 // ---- attention ----------------------------------------------------------------------

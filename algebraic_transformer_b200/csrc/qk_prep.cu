@@ -1,8 +1,12 @@
 // QK RMS-normalisation, Cayley rotation and the range-guard maxima in one HBM-bound pass.
 //
 // One 16-byte vector per lane, D*sizeof(T)/16 lanes per row, so a warp streams whole
-// rows with fully coalesced 128-bit loads and stores.  The rotate-half partner of an
-// element lives in lane ^ (lanes_per_row/2) and is fetched with one shuffle.
+// rows with fully coalesced 128-bit loads and stores.  A warp owns a few positions (b, t)
+// and walks over the heads, four heads per step with all four loads issued before any is
+// used (memory-level parallelism), so the rotation table row of a position is loaded once
+// and reused for every head.  The rotate-half partner of an element lives in lane ^
+// (lanes_per_row/2) and is fetched with one shuffle.  Up to three tensors (q, k, v) are
+// processed by one launch (blockIdx.y selects the tensor).
 //
 // Semantics (reference paths): rms_norm src/algebraic/algebraic.py:76-83 (fp32 math, one
 // rounding to the I/O dtype), apply_rotary src/algebraic/algebraic.py:172-179 (tables cast
@@ -16,10 +20,9 @@ namespace alg {
 template <typename T> struct Vec16;
 template <> struct Vec16<float> {
   static constexpr int N = 4;
-  static __device__ __forceinline__ void load(const float* p, float* v) {
-    float4 r = *reinterpret_cast<const float4*>(p);
-    v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
-  }
+  using Raw = float4;
+  static __device__ __forceinline__ Raw load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void unpack(const Raw& r, float* v) { v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w; }
   static __device__ __forceinline__ void store(float* p, const float* v) {
     *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
   }
@@ -27,8 +30,9 @@ template <> struct Vec16<float> {
 };
 template <> struct Vec16<__nv_bfloat16> {
   static constexpr int N = 8;
-  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
-    uint4 r = *reinterpret_cast<const uint4*>(p);
+  using Raw = uint4;
+  static __device__ __forceinline__ Raw load(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
+  static __device__ __forceinline__ void unpack(const Raw& r, float* v) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -43,88 +47,106 @@ template <> struct Vec16<__nv_bfloat16> {
     for (int i = 0; i < 4; ++i) w[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
     *reinterpret_cast<uint4*>(p) = r;
   }
-  static __device__ __forceinline__ float round(float x) {
-    return __bfloat162float(__float2bfloat16_rn(x));
-  }
+  static __device__ __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 };
 
+constexpr int HEADS_PER_STEP = 4;
+
 template <typename T, int D>
-__global__ void __launch_bounds__(256) qk_prep_kernel(PrepParams p) {
+__global__ void __launch_bounds__(256) qk_prep_kernel(const PrepBatch batch) {
   using V = Vec16<T>;
   constexpr int VEC = V::N;
   constexpr int LPR = D / VEC;         // lanes per row
-  constexpr int RPW = 32 / LPR;        // rows per warp
+  constexpr int RPW = 32 / LPR;        // positions per warp step
   constexpr int HALF = D / 2;
+  const PrepParams& p = batch.t[blockIdx.y];
   const int lane = threadIdx.x & 31;
   const int lir = lane % LPR;          // lane in row
   const int sub = lane / LPR;
-  const int64_t rows = int64_t(p.B) * p.H * p.T;
+  const int64_t positions = int64_t(p.B) * p.T;
   const int64_t warp_global = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t warps_total = (int64_t(gridDim.x) * blockDim.x) >> 5;
+  const bool first = lir < LPR / 2;
+  const int j0 = (lir % (LPR / 2)) * VEC;
 
   float gain[VEC];
 #pragma unroll
   for (int i = 0; i < VEC; ++i) gain[i] = (p.gain != nullptr) ? p.gain[lir * VEC + i] : 1.0f;
 
   float stat = 0.0f;
-  for (int64_t r0 = warp_global * RPW; r0 < rows; r0 += warps_total * RPW) {
-    const int64_t row = r0 + sub;
-    const bool live = row < rows;
-    const int64_t rr = live ? row : rows - 1;
-    const int t = int(rr % p.T);
-    const int64_t bh = rr / p.T;
-    const int h = int(bh % p.H);
-    const int64_t b = bh / p.H;
-    const T* src = reinterpret_cast<const T*>(p.x) + b * p.xs.b + h * p.xs.h + t * p.xs.t + lir * VEC;
-    float v[VEC];
-    V::load(src, v);
+  for (int64_t g0 = warp_global * RPW; g0 < positions; g0 += warps_total * RPW) {
+    const int64_t pos = g0 + sub;
+    const bool live = pos < positions;
+    const int64_t pp = live ? pos : positions - 1;
+    const int t = int(pp % p.T);
+    const int64_t b = pp / p.T;
+    const T* src0 = reinterpret_cast<const T*>(p.x) + b * p.xs.b + int64_t(t) * p.xs.t + lir * VEC;
+    T* dst0 = (p.y != nullptr) ? reinterpret_cast<T*>(p.y) + b * p.ys.b + int64_t(t) * p.ys.t + lir * VEC : nullptr;
 
-    if (p.normalise) {
-      float ss = 0.0f;
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) ss = fmaf(v[i], v[i], ss);
-#pragma unroll
-      for (int o = LPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      const float tau = rsqrtf(ss * (1.0f / D) + p.eps);
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) v[i] = V::round((v[i] * tau) * gain[i]);
-    }
+    float c[VEC], s[VEC];              // this position's table row, cast to T, signed for the half
     if (p.cos != nullptr) {
-      const bool first = lir < LPR / 2;
-      const int j0 = (lir % (LPR / 2)) * VEC;
-      const float* ct = p.cos + int64_t(t) * HALF + j0;
-      const float* st = p.sin + int64_t(t) * HALF + j0;
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        const float other = __shfl_xor_sync(0xffffffffu, v[i], LPR / 2);
-        const float c = V::round(ct[i]), s = V::round(st[i]);
-        const float x1 = first ? v[i] : other;
-        const float x2 = first ? other : v[i];
-        // first half: x1 c - x2 s ; second half: x1 s + x2 c, each product rounded to T
-        const float a = V::round(x1 * (first ? c : s));
-        const float bb = V::round(x2 * (first ? s : c));
-        v[i] = V::round(first ? a - bb : a + bb);
+      for (int i = 0; i < VEC; i += 4) {
+        const float4 cv = *reinterpret_cast<const float4*>(p.cos + int64_t(t) * HALF + j0 + i);
+        const float4 sv = *reinterpret_cast<const float4*>(p.sin + int64_t(t) * HALF + j0 + i);
+        c[i] = V::round(cv.x); c[i + 1] = V::round(cv.y); c[i + 2] = V::round(cv.z); c[i + 3] = V::round(cv.w);
+        s[i] = V::round(sv.x); s[i + 1] = V::round(sv.y); s[i + 2] = V::round(sv.z); s[i + 3] = V::round(sv.w);
       }
     }
-    if (p.y != nullptr && live) {
-      T* dst = reinterpret_cast<T*>(p.y) + b * p.ys.b + h * p.ys.h + t * p.ys.t + lir * VEC;
-      V::store(dst, v);
-    }
-    if (p.stat_mode == 1) {            // squared row norm of the re-rounded scaled row
-      float ss = 0.0f;
+
+    for (int h0 = 0; h0 < p.H; h0 += HEADS_PER_STEP) {
+      typename V::Raw raw[HEADS_PER_STEP];
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        const float s = V::round(v[i] * p.stat_scale);
-        ss = fmaf(s, s, ss);
+      for (int u = 0; u < HEADS_PER_STEP; ++u) {
+        const int h = min(h0 + u, p.H - 1);
+        raw[u] = V::load(src0 + int64_t(h) * p.xs.h);
       }
 #pragma unroll
-      for (int o = LPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      if (live) stat = fmaxf(stat, ss);
-    } else if (p.stat_mode == 2) {     // max |x|
-      float m = 0.0f;
+      for (int u = 0; u < HEADS_PER_STEP; ++u) {
+        const int h = h0 + u;
+        const bool on = live && h < p.H;         // uniform per lane group; shuffles below stay warp-wide
+        float v[VEC];
+        V::unpack(raw[u], v);
+        if (p.normalise) {
+          float ss = 0.0f;
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) m = fmaxf(m, fabsf(v[i]));
-      if (live) stat = fmaxf(stat, m);
+          for (int i = 0; i < VEC; ++i) ss = fmaf(v[i], v[i], ss);
+#pragma unroll
+          for (int o = LPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+          const float tau = rsqrtf(ss * (1.0f / D) + p.eps);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) v[i] = V::round((v[i] * tau) * gain[i]);
+        }
+        if (p.cos != nullptr) {
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], LPR / 2);
+            // first half: x1 c - x2 s ; second half: x1 s + x2 c, each product rounded to T
+            const float x1 = first ? v[i] : other;
+            const float x2 = first ? other : v[i];
+            const float a = V::round(x1 * (first ? c[i] : s[i]));
+            const float bb = V::round(x2 * (first ? s[i] : c[i]));
+            v[i] = V::round(first ? a - bb : a + bb);
+          }
+        }
+        if (dst0 != nullptr && on) V::store(dst0 + int64_t(h) * p.ys.h, v);
+        if (p.stat_mode == 1) {          // squared row norm of the re-rounded scaled row
+          float ss = 0.0f;
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) {
+            const float sc = V::round(v[i] * p.stat_scale);
+            ss = fmaf(sc, sc, ss);
+          }
+#pragma unroll
+          for (int o = LPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+          if (on) stat = fmaxf(stat, ss);
+        } else if (p.stat_mode == 2) {   // max |x|
+          float m = 0.0f;
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) m = fmaxf(m, fabsf(v[i]));
+          if (on) stat = fmaxf(stat, m);
+        }
+      }
     }
   }
   if (p.stat_mode != 0) {
@@ -136,32 +158,48 @@ __global__ void __launch_bounds__(256) qk_prep_kernel(PrepParams p) {
 }
 
 template <typename T, int D>
-static int launch_t(const PrepParams& p, cudaStream_t stream) {
+static int launch_t(const PrepBatch& batch, cudaStream_t stream) {
   constexpr int LPR = D * int(sizeof(T)) / 16;
   constexpr int RPW = 32 / LPR;
-  const int64_t rows = int64_t(p.B) * p.H * p.T;
-  if (rows == 0) return ALG_OK;
-  const int64_t warps = (rows + RPW - 1) / RPW;
+  int64_t positions = 0;
+  for (int i = 0; i < batch.count; ++i) {
+    const int64_t n = int64_t(batch.t[i].B) * batch.t[i].T;
+    if (n > positions) positions = n;
+    if (batch.t[i].H == 0) return ALG_OK;
+  }
+  if (positions == 0) return ALG_OK;
+  const int64_t warps = (positions + RPW - 1) / RPW;
   int64_t blocks = (warps + 7) / 8;
   const int64_t cap = 148 * 16;        // a few waves of resident CTAs; grid-stride covers the rest
   if (blocks > cap) blocks = cap;
-  qk_prep_kernel<T, D><<<dim3(unsigned(blocks)), 256, 0, stream>>>(p);
+  qk_prep_kernel<T, D><<<dim3(unsigned(blocks), unsigned(batch.count)), 256, 0, stream>>>(batch);
   ALG_CUDA_TRY(cudaGetLastError());
   count_launch();
   return ALG_OK;
 }
 
-int launch_prep(const PrepParams& p, int dtype, cudaStream_t stream) {
-  if (p.D != 64 && p.D != 128) {
-    set_error("QK prologue needs head_dim 64 or 128, got %d", p.D);
+int launch_prep_batch(const PrepBatch& batch, int dtype, cudaStream_t stream) {
+  if (batch.count < 1 || batch.count > 3) {
+    set_error("internal: prep batch of %d tensors", batch.count);
+    return ALG_ERR_INVALID;
+  }
+  const int D = batch.t[0].D;
+  if (D != 64 && D != 128) {
+    set_error("QK prologue needs head_dim 64 or 128, got %d", D);
     return ALG_ERR_UNSUPPORTED;
   }
   if (dtype == ALG_BF16)
-    return p.D == 64 ? launch_t<__nv_bfloat16, 64>(p, stream) : launch_t<__nv_bfloat16, 128>(p, stream);
-  if (dtype == ALG_F32)
-    return p.D == 64 ? launch_t<float, 64>(p, stream) : launch_t<float, 128>(p, stream);
+    return D == 64 ? launch_t<__nv_bfloat16, 64>(batch, stream) : launch_t<__nv_bfloat16, 128>(batch, stream);
+  if (dtype == ALG_F32) return D == 64 ? launch_t<float, 64>(batch, stream) : launch_t<float, 128>(batch, stream);
   set_error("unknown dtype %d", dtype);
   return ALG_ERR_INVALID;
+}
+
+int launch_prep(const PrepParams& p, int dtype, cudaStream_t stream) {
+  PrepBatch batch{};
+  batch.t[0] = p;
+  batch.count = 1;
+  return launch_prep_batch(batch, dtype, stream);
 }
 
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
