@@ -180,11 +180,15 @@ int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
     pp.stat_scale = 1.0f; pp.stat_out = &guard->k2;
     batch.t[batch.count++] = pp;
     if (guarded) {                                      // v: max |v| only
+      if (prologue) {                                   // q,k are normalised in their own launch
+        if (int rc = launch_prep_batch(batch, a->dtype, stream)) return rc;
+        batch.count = 0;
+      }
       pp.x = a->v; pp.xs = p.vs; pp.y = nullptr; pp.gain = nullptr; pp.cos = nullptr; pp.sin = nullptr;
       pp.normalise = 0; pp.stat_mode = 2; pp.stat_out = &guard->vmax;
       batch.t[batch.count++] = pp;
     }
-    if (int rc = launch_prep_batch(batch, a->dtype, stream)) return rc;   // one launch for all of them
+    if (int rc = launch_prep_batch(batch, a->dtype, stream)) return rc;   // statistics-only tensors share a launch
     if (prologue) {
       p.q = qn; p.k = kn;
       p.qs = strides_or_dense(kDense, a->H, a->Tq, a->D);

@@ -52,8 +52,10 @@ template <> struct Vec16<__nv_bfloat16> {
 
 constexpr int HEADS_PER_STEP = 4;
 
-template <typename T, int D>
-__global__ void __launch_bounds__(256) qk_prep_kernel(const PrepBatch batch) {
+// MODE 0: statistics only (guard maxima of ready-made q / k / v); 1: normalise (+ gain);
+// 2: normalise + rotate.  Modes 1 and 2 can also accumulate a statistic in the same pass.
+template <typename T, int D, int MODE>
+__global__ void __launch_bounds__(256, MODE == 0 ? 4 : 2) qk_prep_kernel(const PrepBatch batch) {
   using V = Vec16<T>;
   constexpr int VEC = V::N;
   constexpr int LPR = D / VEC;         // lanes per row
@@ -70,8 +72,10 @@ __global__ void __launch_bounds__(256) qk_prep_kernel(const PrepBatch batch) {
   const int j0 = (lir % (LPR / 2)) * VEC;
 
   float gain[VEC];
+  if constexpr (MODE >= 1) {
 #pragma unroll
-  for (int i = 0; i < VEC; ++i) gain[i] = (p.gain != nullptr) ? p.gain[lir * VEC + i] : 1.0f;
+    for (int i = 0; i < VEC; ++i) gain[i] = (p.gain != nullptr) ? p.gain[lir * VEC + i] : 1.0f;
+  }
 
   float stat = 0.0f;
   for (int64_t g0 = warp_global * RPW; g0 < positions; g0 += warps_total * RPW) {
@@ -81,10 +85,10 @@ __global__ void __launch_bounds__(256) qk_prep_kernel(const PrepBatch batch) {
     const int t = int(pp % p.T);
     const int64_t b = pp / p.T;
     const T* src0 = reinterpret_cast<const T*>(p.x) + b * p.xs.b + int64_t(t) * p.xs.t + lir * VEC;
-    T* dst0 = (p.y != nullptr) ? reinterpret_cast<T*>(p.y) + b * p.ys.b + int64_t(t) * p.ys.t + lir * VEC : nullptr;
+    T* dst0 = (MODE >= 1 && p.y != nullptr) ? reinterpret_cast<T*>(p.y) + b * p.ys.b + int64_t(t) * p.ys.t + lir * VEC : nullptr;
 
     float c[VEC], s[VEC];              // this position's table row, cast to T, signed for the half
-    if (p.cos != nullptr) {
+    if constexpr (MODE == 2) {
 #pragma unroll
       for (int i = 0; i < VEC; i += 4) {
         const float4 cv = *reinterpret_cast<const float4*>(p.cos + int64_t(t) * HALF + j0 + i);
@@ -107,7 +111,7 @@ __global__ void __launch_bounds__(256) qk_prep_kernel(const PrepBatch batch) {
         const bool on = live && h < p.H;         // uniform per lane group; shuffles below stay warp-wide
         float v[VEC];
         V::unpack(raw[u], v);
-        if (p.normalise) {
+        if constexpr (MODE >= 1) {
           float ss = 0.0f;
 #pragma unroll
           for (int i = 0; i < VEC; ++i) ss = fmaf(v[i], v[i], ss);
@@ -117,7 +121,7 @@ __global__ void __launch_bounds__(256) qk_prep_kernel(const PrepBatch batch) {
 #pragma unroll
           for (int i = 0; i < VEC; ++i) v[i] = V::round((v[i] * tau) * gain[i]);
         }
-        if (p.cos != nullptr) {
+        if constexpr (MODE == 2) {
 #pragma unroll
           for (int i = 0; i < VEC; ++i) {
             const float other = __shfl_xor_sync(0xffffffffu, v[i], LPR / 2);
@@ -129,7 +133,7 @@ __global__ void __launch_bounds__(256) qk_prep_kernel(const PrepBatch batch) {
             v[i] = V::round(first ? a - bb : a + bb);
           }
         }
-        if (dst0 != nullptr && on) V::store(dst0 + int64_t(h) * p.ys.h, v);
+        if (MODE >= 1 && dst0 != nullptr && on) V::store(dst0 + int64_t(h) * p.ys.h, v);
         if (p.stat_mode == 1) {          // squared row norm of the re-rounded scaled row
           float ss = 0.0f;
 #pragma unroll
@@ -159,6 +163,12 @@ __global__ void __launch_bounds__(256) qk_prep_kernel(const PrepBatch batch) {
 
 template <typename T, int D>
 static int launch_t(const PrepBatch& batch, cudaStream_t stream) {
+  // every tensor of a batch runs the same mode (the callers group them that way)
+  const int mode = !batch.t[0].normalise ? 0 : (batch.t[0].cos != nullptr ? 2 : 1);
+  for (int i = 1; i < batch.count; ++i) {
+    const int m = !batch.t[i].normalise ? 0 : (batch.t[i].cos != nullptr ? 2 : 1);
+    if (m != mode) { set_error("internal: mixed modes in one prep batch"); return ALG_ERR_INVALID; }
+  }
   constexpr int LPR = D * int(sizeof(T)) / 16;
   constexpr int RPW = 32 / LPR;
   int64_t positions = 0;
@@ -172,7 +182,10 @@ static int launch_t(const PrepBatch& batch, cudaStream_t stream) {
   int64_t blocks = (warps + 7) / 8;
   const int64_t cap = 148 * 16;        // a few waves of resident CTAs; grid-stride covers the rest
   if (blocks > cap) blocks = cap;
-  qk_prep_kernel<T, D><<<dim3(unsigned(blocks), unsigned(batch.count)), 256, 0, stream>>>(batch);
+  const dim3 grid(unsigned(blocks), unsigned(batch.count));
+  if (mode == 0) qk_prep_kernel<T, D, 0><<<grid, 256, 0, stream>>>(batch);
+  else if (mode == 1) qk_prep_kernel<T, D, 1><<<grid, 256, 0, stream>>>(batch);
+  else qk_prep_kernel<T, D, 2><<<grid, 256, 0, stream>>>(batch);
   ALG_CUDA_TRY(cudaGetLastError());
   count_launch();
   return ALG_OK;
