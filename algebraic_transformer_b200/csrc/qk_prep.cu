@@ -55,7 +55,7 @@ constexpr int HEADS_PER_STEP = 4;
 // MODE 0: statistics only (guard maxima of ready-made q / k / v); 1: normalise (+ gain);
 // 2: normalise + rotate.  Modes 1 and 2 can also accumulate a statistic in the same pass.
 template <typename T, int D, int MODE>
-__global__ void __launch_bounds__(256, MODE == 0 ? 4 : 2) qk_prep_kernel(const PrepBatch batch) {
+__global__ void __launch_bounds__(256, MODE == 0 ? 4 : 3) qk_prep_kernel(const PrepBatch batch) {
   using V = Vec16<T>;
   constexpr int VEC = V::N;
   constexpr int LPR = D / VEC;         // lanes per row

@@ -234,13 +234,23 @@ def main():
         A.flash_attention(q, k, v, sink, kind="asinh", n=ATTN["n"], c=ATTN["c"], range_guard=variant_guard,
                           shift=False, impl=args.kernel, out=outs[i & 1])
 
-    for i in range(args.warmup):
-        attn_step(i)
-    sampler = ClockSampler(local)
+    from algebraic_transformer_b200.clocks import NvmlSampler
+    sampler = NvmlSampler(local)
     if rank == 0:
         sampler.start()
+    for i in range(args.warmup):
+        attn_step(i)
+    # keep the GPU under the same load for a moment before timing, so that the clocks the
+    # timed steps see are the steady ones (untimed, on top of the W warm-up steps)
+    t_hold = time.perf_counter()
+    while time.perf_counter() - t_hold < 0.25:
+        for i in range(8):
+            attn_step(i)
+        torch.cuda.synchronize()
     launches0 = lib.alg_kernel_launches()
+    t_region0 = time.perf_counter()
     ms = max_over_ranks(cuda_time(attn_step, args.steps, sync))
+    t_region1 = time.perf_counter()
     launches = lib.alg_kernel_launches() - launches0
     flops_rank = attn_flops(B, H, T, D)
     value = flops_rank * world / (ms * 1e-3) / 1e12
@@ -256,7 +266,10 @@ def main():
     for i in range(3):
         attn_only(i)
     ms_kernel = max_over_ranks(cuda_time(attn_only, args.steps, sync))
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = None
+    if rank == 0:
+        sampler.stop()
+        clocks = sampler.summary(t_region0, t_region1)
     peak_tf = float(pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
     achieved = flops_rank / (ms_kernel * 1e-3) / 1e12
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",

@@ -1,0 +1,64 @@
+"""Two-GPU checks (skipped on a single-GPU box): the vocabulary-sharded Alg-CE head with its
+NCCL all-reduce, and attention over disjoint (batch, head) unit blocks, each rank one GPU."""
+
+import os
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    import torch.distributed as dist
+    import algebraic_transformer_b200 as A
+    from algebraic_transformer_b200.dist import init_from_env, unit_shard, vocab_shard
+    from oracle import algebraic_ref as R
+    init_from_env("nccl")
+    dev = torch.device("cuda", rank)
+    g = torch.Generator().manual_seed(21)
+    # ---- head: every rank holds all of h, its own vocabulary rows of E
+    N, d, V = 512, 256, 12500
+    h = torch.randn((N, d), generator=g).bfloat16()
+    E = torch.randn((V, d), generator=g) * 0.1
+    t = torch.randint(0, V, (N,), generator=g)
+    lo, cnt = vocab_shard(V, rank, world)
+    obj, pt, nll = A.fused_head(h.to(dev), E[lo:lo + cnt].to(dev), t.to(dev), kind="alg_ce", n=8, c=2.0,
+                                vocab_offset=lo, vocab_total=V, group=dist.group.WORLD, want_nll=True)
+    obj_w, pt_w = R.fused_head(h, E, t, n=8, c=2.0)
+    e_head = float((nll.cpu().double() - R.nll_from_pt(pt_w).double()).norm() / R.nll_from_pt(pt_w).double().norm())
+    ok_head = e_head < 1e-2 and abs(float(obj) - float(obj_w)) < 2e-3 * abs(float(obj_w))
+    # ---- attention: (batch, head) units dealt out in contiguous blocks, no communication
+    B, H, T, D = 1, 6, 512, 64
+    q, k, v = (torch.randn((B, H, T, D), generator=g).bfloat16() for _ in range(3))
+    u0, un = unit_shard(B * H, rank, world)
+    sl = slice(u0, u0 + un)
+    o = A.flash_attention(q[:, sl].to(dev), k[:, sl].to(dev), v[:, sl].to(dev), torch.zeros(un, device=dev),
+                          kind="asinh", n=16, c=8.0, range_guard=True)
+    want = R.asinh_attention(q[:, sl], k[:, sl], v[:, sl], n=16, c=8.0, sink_logit=torch.zeros(un))
+    e_attn = float((o.cpu().double() - want.double()).norm() / want.double().norm())
+    ret[rank] = (bool(ok_head), e_head, e_attn)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_two_gpu_sharded_head_and_unit_parallel_attention():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    world = 2
+    port = 29800 + os.getpid() % 150
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
+    for r in range(world):
+        ok_head, e_head, e_attn = ret[r]
+        assert ok_head, (r, e_head)
+        assert e_attn < 1e-2, (r, e_attn)
