@@ -90,14 +90,21 @@ __global__ void __launch_bounds__(NTHREADS) attn_mma_kernel(const AttnParams p) 
   const bool shift_mode = s_shift != 0;
   if ((p.run_if == 1 && shift_mode) || (p.run_if == 2 && !shift_mode)) return;
 
-  const int qt = int(gridDim.x) - 1 - int(blockIdx.x);   // long (late) query tiles first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // Persistent over work items (query tile, head, batch), long (late) query tiles first.  A
+  // small grid keeps the launch cheap when the kernel only has to find out that the other
+  // kernel family is doing the work (run_if).
+  const int nqt = (p.Tq + BM - 1) / BM;
+  const int total_items = nqt * p.H * p.B;
+  for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+  const int qt = nqt - 1 - item / (p.H * p.B);
+  const int h = item % p.H, b = (item / p.H) % p.B;
   const int q0 = qt * BM;
+  __syncthreads();                                        // the previous item's reads of sQ are done
   const int off = p.Tk - p.Tq;                            // causal: key j visible iff j <= i + off
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
 
-  if (blockIdx.x == 0 && h == 0 && b == 0 && threadIdx.x == 0 && p.stat_kind != nullptr)
+  if (item == 0 && threadIdx.x == 0 && p.stat_kind != nullptr)
     *p.stat_kind = shift_mode ? ALG_VARIANT_SHIFT : ALG_VARIANT_NOSHIFT;
 
   const T* qb = reinterpret_cast<const T*>(p.q) + b * p.qs.b + h * p.qs.h;
@@ -290,6 +297,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_mma_kernel(const AttnParams p) 
       p.stat[(int64_t(b) * p.H + h) * p.Tq + row] = st;
     }
   }
+  }  // work items
 }
 
 template <typename T, int D, bool SPLIT>
@@ -302,7 +310,9 @@ int launch_one(const AttnParams& p, cudaStream_t stream) {
     ALG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     configured = true;
   }
-  dim3 grid((p.Tq + BM - 1) / BM, p.H, p.B);
+  const long long items = (long long)((p.Tq + BM - 1) / BM) * p.H * p.B;
+  const int cap = 148 * 8;                             // a few resident CTAs per SM; the loop covers the rest
+  const unsigned grid = unsigned(items < cap ? items : cap);
   kern<<<grid, NTHREADS, smem, stream>>>(p);
   ALG_CUDA_TRY(cudaGetLastError());
   count_launch();

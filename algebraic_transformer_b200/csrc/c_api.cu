@@ -242,6 +242,8 @@ int alg_attn_decode(const alg_decode_args* a, void* stream) {
     return ALG_ERR_INVALID;
   }
   p.splits = decode_splits(a->B, a->H, a->Tk);
+  p.keys_per_split = decode_keys_per_split(a->B, a->H, a->Tk);
+  p.status = nullptr;
   p.part = static_cast<float*>(a->workspace);
   return launch_decode(p, static_cast<cudaStream_t>(stream));
 }

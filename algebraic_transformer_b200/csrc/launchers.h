@@ -81,9 +81,12 @@ struct DecodeParams {
   float scale, inv_c;
   Strides3 ks, vs;
   int splits;
+  int keys_per_split;      // multiple of the 64-key tile
   float* part;             // (B*H, splits, D + 2) fp32 partials: acc[D], m, l
+  int* status;
 };
 int decode_splits(int B, int H, int Tk);
+int decode_keys_per_split(int B, int H, int Tk);
 int launch_decode(const DecodeParams& p, cudaStream_t stream);
 
 // ---- Alg-CE head --------------------------------------------------------------------

@@ -40,7 +40,7 @@ HEAD = dict(N=8192, d=768, V=50304, n=8, c=2.0, target_hi=50257)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel, from the ncu
 # capture summarised under profiles/ (None until a capture of the current kernel exists).
-ATTN_DRAM_TRAFFIC_BYTES = None
+ATTN_DRAM_TRAFFIC_BYTES = 159.0e6
 
 
 def peaks():
