@@ -138,6 +138,32 @@ def qk_rms_norm(x: torch.Tensor, gain: Optional[torch.Tensor], eps: float = 1e-5
     return y.view(x.shape)
 
 
+def rms_norm(x: torch.Tensor, gain: Optional[torch.Tensor], eps: float = 1e-5, out=None) -> torch.Tensor:
+    """RMS normalisation over the last axis of a contiguous bf16 tensor (the model's `_norm`,
+    src/algebraic/model.py:141-143): fp32 math, one rounding to bf16."""
+    _require_cuda(x, gain)
+    if x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise ValueError("rms_norm needs a contiguous bfloat16 tensor")
+    d = x.shape[-1]
+    y = torch.empty_like(x) if out is None else out
+    g = None if gain is None else gain.contiguous().float()
+    L.check(L.load().alg_rms_norm_fwd(x.data_ptr(), _ptr(g), y.data_ptr(), x.numel() // d, d, float(eps), _stream()))
+    return y
+
+
+def alu_glu(gate: torch.Tensor, up: torch.Tensor, beta: float = 0.5, out=None) -> torch.Tensor:
+    """gate * alu(up, beta), the ALU-GLU gating of the feed-forward block
+    (src/algebraic/model.py:184-193, src/algebraic/algebraic.py:86-105)."""
+    _require_cuda(gate, up)
+    if gate.dtype != torch.bfloat16 or up.dtype != torch.bfloat16 or gate.shape != up.shape:
+        raise ValueError("alu_glu needs two bfloat16 tensors of one shape")
+    if not (gate.is_contiguous() and up.is_contiguous()):
+        raise ValueError("alu_glu needs contiguous tensors")
+    y = torch.empty_like(gate) if out is None else out
+    L.check(L.load().alg_alu_glu_fwd(gate.data_ptr(), up.data_ptr(), y.data_ptr(), gate.numel(), float(beta), _stream()))
+    return y
+
+
 # ------------------------------------------------------------------------ attention
 
 def flash_clamp(seq_len: int, n: int) -> float:

@@ -1,0 +1,144 @@
+"""Prefill (forward-only) of the algebraic Transformer, hosted in PyTorch around the kernels.
+
+Mirrors the reference's model forward for the `algebraic` preset
+(src/algebraic/model.py:162-231, src/algebraic/config.py:8-42): embedding gather ->
+RMS(embed_gain) -> L x [RMS -> QKV GEMMs -> QK-norm + Cayley rotation + asinh attention
+(one library call) -> out-projection + residual -> RMS -> gate/up GEMMs -> gate * ALU(up)
+-> down GEMM + residual] -> final RMS -> fused Alg-CE head over all positions.
+GEMMs are plain library GEMMs (cuBLAS through torch); every other stage is a kernel of
+this package.  Projections are consumed in place as strided (B,H,T,D) views and the
+attention output is written straight into (B,T,H*D) layout, so no transposes are copied.
+
+Multi-GPU (one process per GPU): the batch is split over ranks (weights replicated, no
+communication in the body), the final hidden states are all-gathered, and the head runs
+vocabulary-sharded with one all-reduce of the per-row statistic.
+"""
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import ops
+from .dist import vocab_shard
+
+SIZES = {   # src/algebraic/config.py:8-14
+    "proxy": dict(d_model=384, n_layers=8, n_heads=6, d_ff=1024),
+    "125m": dict(d_model=768, n_layers=12, n_heads=12, d_ff=2048),
+    "350m": dict(d_model=1024, n_layers=24, n_heads=16, d_ff=2688),
+    "1b": dict(d_model=1536, n_layers=32, n_heads=24, d_ff=4224),
+}
+
+
+@dataclass(frozen=True)
+class PrefillConfig:
+    """The `algebraic` preset's constants (src/algebraic/config.py:32-35, model.py:24-63)."""
+    vocab_size: int = 32768
+    d_model: int = 384
+    n_layers: int = 8
+    n_heads: int = 6
+    d_ff: int = 1024
+    eps: float = 1e-5
+    alu_beta: float = 0.5
+    rope_base: float = 10000.0
+    attn_n: int = 16
+    attn_c: float = 8.0
+    head_n: int = 8
+    head_c: float = 2.0
+    init_std: float = 0.02
+
+    @property
+    def head_dim(self) -> int:
+        return self.d_model // self.n_heads
+
+    @staticmethod
+    def preset(size: str, **overrides) -> "PrefillConfig":
+        return PrefillConfig(**{**SIZES[size], **overrides})
+
+    def flops_per_token(self, seq_len: int) -> float:
+        """Forward FLOPs per token: GEMMs + causal attention + head (2 N d V)."""
+        d, f, L, V = self.d_model, self.d_ff, self.n_layers, self.vocab_size
+        return 2.0 * (L * (4 * d * d + 3 * d * f) + V * d) + L * 4.0 * seq_len * d / 2.0
+
+
+def init_params(cfg: PrefillConfig, seed: int = 0, device="cpu"):
+    """Random-init parameters with the reference's shapes and scales
+    (src/algebraic/model.py:84-117): N(0, init_std) matrices, unit gains, zero sinks.
+    Kept in fp32 on `device`; `cast_params` makes the bf16 working copy."""
+    g = torch.Generator().manual_seed(seed)
+    L, d, f, V, H, D = cfg.n_layers, cfg.d_model, cfg.d_ff, cfg.vocab_size, cfg.n_heads, cfg.head_dim
+
+    def normal(*shape):
+        return (torch.randn(shape, generator=g) * cfg.init_std).to(device)
+
+    return {
+        "embed": normal(V, d), "embed_gain": torch.ones(d, device=device), "final_gain": torch.ones(d, device=device),
+        "w_q": normal(L, d, d), "w_k": normal(L, d, d), "w_v": normal(L, d, d), "w_o": normal(L, d, d),
+        "w_g": normal(L, d, f), "w_u": normal(L, d, f), "w_d": normal(L, f, d),
+        "ln1": torch.ones(L, d, device=device), "ln2": torch.ones(L, d, device=device),
+        "q_gain": torch.ones(L, D, device=device), "k_gain": torch.ones(L, D, device=device),
+        "sink": torch.zeros(L, H, device=device),
+    }
+
+
+def cast_params(params, device):
+    """bf16 copies of the matrices (the reference casts at use, model.py:167), fp32 gains."""
+    out = {}
+    for k, v in params.items():
+        v = v.to(device)
+        out[k] = v.bfloat16().contiguous() if k.startswith("w_") or k == "embed" else v.float().contiguous()
+    # q, k, v projections share their input: one GEMM with the concatenated weight
+    out["w_qkv"] = torch.cat([out["w_q"], out["w_k"], out["w_v"]], dim=2).contiguous()
+    return out
+
+
+class Prefill:
+    """Forward pass of one rank: `hidden(tokens)` and `loss(tokens, targets)`."""
+
+    def __init__(self, cfg: PrefillConfig, params, device, seq_len: int, impl: str = "auto"):
+        self.cfg, self.device, self.impl = cfg, torch.device(device), impl
+        self.p = cast_params(params, self.device)
+        self.cos, self.sin = ops.cayley_table_geometric(cfg.head_dim, seq_len, cfg.rope_base, device=self.device)
+
+    def hidden(self, tokens: torch.Tensor) -> torch.Tensor:
+        """Final normalised hidden states (B, T, d) in bf16 (model.forward_hidden, model.py:196-208)."""
+        cfg, p = self.cfg, self.p
+        B, T = tokens.shape
+        d, H, D, f = cfg.d_model, cfg.n_heads, cfg.head_dim, cfg.d_ff
+        x = ops.rms_norm(p["embed"][tokens].contiguous(), p["embed_gain"], cfg.eps).view(B * T, d)
+        attn_out = torch.empty((B, T, H, D), dtype=torch.bfloat16, device=self.device)
+        for layer in range(cfg.n_layers):
+            h = ops.rms_norm(x, p["ln1"][layer], cfg.eps)
+            qkv = torch.mm(h, p["w_qkv"][layer]).view(B, T, 3, H, D)
+            q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))          # (B,H,T,D) views
+            ops.flash_attention(q, k, v, p["sink"][layer], kind="asinh", n=cfg.attn_n, c=cfg.attn_c, block=T,
+                                range_guard=True, q_gain=p["q_gain"][layer], k_gain=p["k_gain"][layer],
+                                cos=self.cos, sin=self.sin, eps=cfg.eps, impl=self.impl,
+                                out=attn_out.transpose(1, 2))
+            x = torch.addmm(x, attn_out.view(B * T, d), p["w_o"][layer])
+            h2 = ops.rms_norm(x, p["ln2"][layer], cfg.eps)
+            gate = torch.mm(h2, p["w_g"][layer])
+            up = torch.mm(h2, p["w_u"][layer])
+            x = torch.addmm(x, ops.alu_glu(gate, up, cfg.alu_beta, out=gate), p["w_d"][layer])
+        return ops.rms_norm(x, p["final_gain"], cfg.eps).view(B, T, d)
+
+    def loss(self, tokens: torch.Tensor, targets: torch.Tensor, group=None, rank: int = 0, world: int = 1,
+             want_nll: bool = False):
+        """(objective, p_target[, nll]) over all positions (model.head_loss, model.py:211-231).
+        With `group`, `tokens` is this rank's batch slice: the hidden states of all ranks are
+        all-gathered and the head runs over this rank's vocabulary shard."""
+        cfg = self.cfg
+        hid = self.hidden(tokens).reshape(-1, cfg.d_model)
+        tgt = targets.reshape(-1).to(torch.int32)
+        if group is None or world == 1:
+            return ops.fused_head(hid, self.p["embed"], tgt, kind="alg_ce", n=cfg.head_n, c=cfg.head_c,
+                                  block_n=hid.shape[0], want_nll=want_nll, impl=self.impl)
+        import torch.distributed as dist
+        full = torch.empty((world * hid.shape[0], cfg.d_model), dtype=hid.dtype, device=hid.device)
+        dist.all_gather_into_tensor(full, hid.contiguous(), group=group)
+        all_t = torch.empty(world * tgt.shape[0], dtype=torch.int32, device=hid.device)
+        dist.all_gather_into_tensor(all_t, tgt.contiguous(), group=group)
+        lo, cnt = vocab_shard(cfg.vocab_size, rank, world)
+        return ops.fused_head(full, self.p["embed"][lo:lo + cnt], all_t, kind="alg_ce", n=cfg.head_n, c=cfg.head_c,
+                              block_n=full.shape[0], vocab_offset=lo, vocab_total=cfg.vocab_size, group=group,
+                              want_nll=want_nll, impl=self.impl)

@@ -59,60 +59,6 @@ def attn_flops(B, H, T, D):
     return 4.0 * B * H * T * T * D / 2.0
 
 
-class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
-
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, gpu_index):
-        self.gpu = gpu_index
-        self.lines = []
-        self.proc = None
-
-    def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._pump, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
-
-    def _pump(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, smax, power, reasons = [], [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            parts = [x.strip() for x in ln.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1])); smax.append(float(parts[2])); power.append(float(parts[3]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        # the busiest half of the samples is the load the kernels ran under
-        hot = sorted(zip(power, sm))[len(sm) // 2:] if sm else []
-        med = sorted(x[1] for x in hot)[len(hot) // 2] if hot else None
-        return {"sm_mhz": med, "sm_max_mhz": max(smax) if smax else None, "reasons": sorted(reasons),
-                "samples": len(sm), "power_w_max": max(power) if power else None}
-
-
 def make_attn_inputs(device, seed, B=None):
     g = torch.Generator().manual_seed(seed)
     B = B or ATTN["B"]
@@ -379,6 +325,36 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
         "frac_of_bf16_peak": 2.0 * N * d * cnt / (ms_head_k * 1e-3) / 1e12 / peak_tf,
         "collective": "none" if world == 1 else "one NCCL all-reduce of (2,N) fp32 per step",
         "logits_bytes_written": 0}
+    del h, e, t, stats
+    # ---- full prefill forward (BASELINE configs 3 and 4): batch split over ranks, hidden
+    #      states all-gathered, head vocabulary-sharded ----
+    from algebraic_transformer_b200 import prefill as PF
+    for name, size, vocab, gb, seq in (("prefill_125m", "125m", 50304, 16, 1024), ("prefill_350m", "350m", 32000, 8, 2048)):
+        if gb % world:
+            continue
+        cfg = PF.PrefillConfig.preset(size, vocab_size=vocab)
+        params = PF.init_params(cfg, seed=0)
+        model = PF.Prefill(cfg, params, dev, seq_len=seq, impl=args.kernel)
+        del params
+        gt = torch.Generator().manual_seed(2)
+        tokens = torch.randint(0, vocab, (gb, seq), generator=gt)
+        lb = gb // world
+        tok = tokens[rank * lb:(rank + 1) * lb].to(dev)
+        group = dist.group.WORLD if world > 1 else None
+
+        def prefill_step(i):
+            model.loss(tok, tok, group=group, rank=rank, world=world)
+
+        for i in range(3):
+            prefill_step(i)
+        ms_p = max_over_ranks(cuda_time(prefill_step, max(3, min(args.steps, 10)), sync))
+        fl = cfg.flops_per_token(seq) * gb * seq
+        extra[name] = {"workload": f"{size} algebraic prefill + Alg-CE head, bf16, global batch {gb} x {seq}, vocab {vocab}, "
+                                   f"random init seed 0, batch split x{world}",
+                       "tokens_per_s": gb * seq / (ms_p * 1e-3), "ms_per_step": ms_p,
+                       "tflops": fl / (ms_p * 1e-3) / 1e12, "frac_of_bf16_peak_per_gpu": fl / (ms_p * 1e-3) / 1e12 / world / peak_tf}
+        del model
+        torch.cuda.empty_cache()
     if world > 1:
         return extra
     # ---- standalone qk_rms (+ rotation): HBM bound ----

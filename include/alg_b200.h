@@ -220,6 +220,18 @@ ALG_API int alg_head_finalize(const float* l, const float* zt, int N, int n, flo
                       float* pt, float* nll, float* obj,
                       void* workspace, size_t workspace_bytes, void* stream);
 
+/* ------------------------------------------------------------------------------------
+ * Elementwise stages of the prefill body between the GEMMs (bf16 in / out, fp32 math).
+ * Replaces: model._norm = rms_norm over d_model rows   src/algebraic/model.py:141-143,
+ *                                                     src/algebraic/algebraic.py:76-83
+ *           gate * alu(up, beta) of the ALU-GLU FFN   src/algebraic/model.py:184-193,
+ *                                                     src/algebraic/algebraic.py:86-105
+ * x, y: (rows, d) bf16 contiguous, d a multiple of 8 and <= 2048; gain: (d) fp32 or NULL.
+ * gate, up, out: `count` bf16 elements (count a multiple of 8); out may alias gate or up.
+ * ---------------------------------------------------------------------------------- */
+ALG_API int alg_rms_norm_fwd(const void* x, const float* gain, void* y, int64_t rows, int d, float eps, void* stream);
+ALG_API int alg_alu_glu_fwd(const void* gate, const void* up, void* out, size_t count, float beta, void* stream);
+
 /* fp32 -> bf16 cast of the embedding shard (the reference casts E per call,
  * src/algebraic/kernels/fused_head.py:165; model.py:225). */
 ALG_API int alg_cast_f32_to_bf16(const float* src, void* dst, size_t count, void* stream);
