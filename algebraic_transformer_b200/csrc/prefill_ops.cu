@@ -68,13 +68,19 @@ __global__ void __launch_bounds__(256) rms_rows_kernel(const __nv_bfloat16* __re
   }
 }
 
+// gate, up: (rows, f) with row stride ld_in (both halves of one GEMM output qualify); out: row stride ld_out
 __global__ void __launch_bounds__(256) alu_glu_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
-                                                      __nv_bfloat16* __restrict__ out, size_t nvec, float beta) {
+                                                      __nv_bfloat16* __restrict__ out, int64_t rows, int f, int64_t ld_in,
+                                                      int64_t ld_out, float beta) {
   const size_t stride = size_t(gridDim.x) * blockDim.x;
+  const int vpr = f / 8;
+  const size_t nvec = size_t(rows) * vpr;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    const int64_t row = int64_t(i / vpr);
+    const int col = int(i % vpr) * 8;
     float g[8], u[8], o[8];
-    unpack8(reinterpret_cast<const uint4*>(gate)[i], g);
-    unpack8(reinterpret_cast<const uint4*>(up)[i], u);
+    unpack8(*reinterpret_cast<const uint4*>(gate + row * ld_in + col), g);
+    unpack8(*reinterpret_cast<const uint4*>(up + row * ld_in + col), u);
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       const float bz = beta * u[k];
@@ -85,7 +91,7 @@ __global__ void __launch_bounds__(256) alu_glu_kernel(const __nv_bfloat16* __res
       const float act = bf16_round(0.5f * u[k] * one_plus_u);
       o[k] = g[k] * act;
     }
-    reinterpret_cast<uint4*>(out)[i] = pack8(o);
+    *reinterpret_cast<uint4*>(out + row * ld_out + col) = pack8(o);
   }
 }
 
@@ -114,14 +120,15 @@ int launch_rms_rows(const void* x, const float* gain, void* y, int64_t rows, int
   return ALG_OK;
 }
 
-int launch_alu_glu(const void* gate, const void* up, void* out, size_t count, float beta, cudaStream_t stream) {
-  if (count == 0) return ALG_OK;
-  const size_t nvec = count / 8;
+int launch_alu_glu(const void* gate, const void* up, void* out, int64_t rows, int f, int64_t ld_in, int64_t ld_out,
+                   float beta, cudaStream_t stream) {
+  if (rows == 0 || f == 0) return ALG_OK;
+  const size_t nvec = size_t(rows) * (f / 8);
   size_t blocks = (nvec + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   alu_glu_kernel<<<unsigned(blocks), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate),
                                                        static_cast<const __nv_bfloat16*>(up),
-                                                       static_cast<__nv_bfloat16*>(out), nvec, beta);
+                                                       static_cast<__nv_bfloat16*>(out), rows, f, ld_in, ld_out, beta);
   ALG_CUDA_TRY(cudaGetLastError());
   count_launch();
   return ALG_OK;
@@ -138,12 +145,13 @@ extern "C" int alg_rms_norm_fwd(const void* x, const float* gain, void* y, int64
   return launch_rms_rows(x, gain, y, rows, d, eps, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int alg_alu_glu_fwd(const void* gate, const void* up, void* out, size_t count, float beta, void* stream) {
-  if (count != 0 && (gate == nullptr || up == nullptr || out == nullptr)) { set_error("alu_glu: null argument"); return ALG_ERR_INVALID; }
-  if (count % 8 != 0) { set_error("alu_glu: element count must be a multiple of 8"); return ALG_ERR_INVALID; }
+extern "C" int alg_alu_glu_fwd(const void* gate, const void* up, void* out, int64_t rows, int f, int64_t ld_in,
+                               int64_t ld_out, float beta, void* stream) {
+  if (rows < 0 || f < 0 || (rows * f != 0 && (gate == nullptr || up == nullptr || out == nullptr))) { set_error("alu_glu: bad argument"); return ALG_ERR_INVALID; }
+  if (f % 8 != 0 || ld_in % 8 != 0 || ld_out % 8 != 0 || ld_in < f || ld_out < f) { set_error("alu_glu: f and the row strides must be multiples of 8, strides >= f"); return ALG_ERR_INVALID; }
   if ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(out)) & 15) {
     set_error("alu_glu: 16-byte alignment required");
     return ALG_ERR_INVALID;
   }
-  return launch_alu_glu(gate, up, out, count, beta, static_cast<cudaStream_t>(stream));
+  return launch_alu_glu(gate, up, out, rows, f, ld_in, ld_out, beta, static_cast<cudaStream_t>(stream));
 }

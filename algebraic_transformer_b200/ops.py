@@ -155,12 +155,14 @@ def alu_glu(gate: torch.Tensor, up: torch.Tensor, beta: float = 0.5, out=None) -
     """gate * alu(up, beta), the ALU-GLU gating of the feed-forward block
     (src/algebraic/model.py:184-193, src/algebraic/algebraic.py:86-105)."""
     _require_cuda(gate, up)
-    if gate.dtype != torch.bfloat16 or up.dtype != torch.bfloat16 or gate.shape != up.shape:
-        raise ValueError("alu_glu needs two bfloat16 tensors of one shape")
-    if not (gate.is_contiguous() and up.is_contiguous()):
-        raise ValueError("alu_glu needs contiguous tensors")
-    y = torch.empty_like(gate) if out is None else out
-    L.check(L.load().alg_alu_glu_fwd(gate.data_ptr(), up.data_ptr(), y.data_ptr(), gate.numel(), float(beta), _stream()))
+    if gate.dtype != torch.bfloat16 or up.dtype != torch.bfloat16 or gate.shape != up.shape or gate.ndim != 2:
+        raise ValueError("alu_glu needs two (rows, f) bfloat16 tensors of one shape")
+    if gate.stride(1) != 1 or up.stride(1) != 1 or gate.stride(0) != up.stride(0):
+        raise ValueError("alu_glu needs unit inner stride and one row stride for gate and up")
+    rows, f = gate.shape
+    y = torch.empty((rows, f), dtype=torch.bfloat16, device=gate.device) if out is None else out
+    L.check(L.load().alg_alu_glu_fwd(gate.data_ptr(), up.data_ptr(), y.data_ptr(), rows, f, gate.stride(0), y.stride(0),
+                                     float(beta), _stream()))
     return y
 
 

@@ -89,6 +89,9 @@ def cast_params(params, device):
         out[k] = v.bfloat16().contiguous() if k.startswith("w_") or k == "embed" else v.float().contiguous()
     # q, k, v projections share their input: one GEMM with the concatenated weight
     out["w_qkv"] = torch.cat([out["w_q"], out["w_k"], out["w_v"]], dim=2).contiguous()
+    out["w_gu"] = torch.cat([out["w_g"], out["w_u"]], dim=2).contiguous()
+    for k in ("w_q", "w_k", "w_v", "w_g", "w_u"):        # only the fused copies are used
+        del out[k]
     return out
 
 
@@ -117,18 +120,53 @@ class Prefill:
                                 out=attn_out.transpose(1, 2))
             x = torch.addmm(x, attn_out.view(B * T, d), p["w_o"][layer])
             h2 = ops.rms_norm(x, p["ln2"][layer], cfg.eps)
-            gate = torch.mm(h2, p["w_g"][layer])
-            up = torch.mm(h2, p["w_u"][layer])
-            x = torch.addmm(x, ops.alu_glu(gate, up, cfg.alu_beta, out=gate), p["w_d"][layer])
+            gu = torch.mm(h2, p["w_gu"][layer])                                  # gate | up in one GEMM
+            x = torch.addmm(x, ops.alu_glu(gu[:, :f], gu[:, f:], cfg.alu_beta), p["w_d"][layer])
         return ops.rms_norm(x, p["final_gain"], cfg.eps).view(B, T, d)
+
+    def graphed_loss(self, tokens: torch.Tensor, targets: torch.Tensor, group=None, rank: int = 0, world: int = 1):
+        """Capture one `loss` step in a CUDA graph and return `(replay, outputs, how)`.
+        `replay()` re-runs the captured launches on the inputs' storage (copy new token ids
+        into `tokens` / `targets` in place before calling it); `outputs` are the tensors the
+        step writes.  The whole step is ~170 short launches, so at small per-GPU batches the
+        host cannot enqueue them as fast as the GPU retires them; a graph removes that limit.
+        If the collectives cannot be captured, only the body is captured and the head with
+        its two collectives runs eagerly after each replay (`how` says which)."""
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):                     # warm-up: attributes, workspaces, NCCL
+            for _ in range(2):
+                self.loss(tokens, targets, group=group, rank=rank, world=world)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                outputs = self.loss(tokens, targets, group=group, rank=rank, world=world)
+            return graph.replay, outputs, "whole step captured"
+        except Exception:                                  # fall back: body only
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                hid = self.hidden(tokens)
+            box = {}
+
+            def replay():
+                graph.replay()
+                box["out"] = self._head(hid.reshape(-1, self.cfg.d_model), targets, group, rank, world, False)
+                return box["out"]
+            return replay, box, "body captured, head and collectives eager"
 
     def loss(self, tokens: torch.Tensor, targets: torch.Tensor, group=None, rank: int = 0, world: int = 1,
              want_nll: bool = False):
         """(objective, p_target[, nll]) over all positions (model.head_loss, model.py:211-231).
         With `group`, `tokens` is this rank's batch slice: the hidden states of all ranks are
         all-gathered and the head runs over this rank's vocabulary shard."""
+        hid = self.hidden(tokens).reshape(-1, self.cfg.d_model)
+        return self._head(hid, targets, group, rank, world, want_nll)
+
+    def _head(self, hid, targets, group, rank, world, want_nll):
         cfg = self.cfg
-        hid = self.hidden(tokens).reshape(-1, cfg.d_model)
         tgt = targets.reshape(-1).to(torch.int32)
         if group is None or world == 1:
             return ops.fused_head(hid, self.p["embed"], tgt, kind="alg_ce", n=cfg.head_n, c=cfg.head_c,

@@ -227,10 +227,13 @@ ALG_API int alg_head_finalize(const float* l, const float* zt, int N, int n, flo
  *           gate * alu(up, beta) of the ALU-GLU FFN   src/algebraic/model.py:184-193,
  *                                                     src/algebraic/algebraic.py:86-105
  * x, y: (rows, d) bf16 contiguous, d a multiple of 8 and <= 2048; gain: (d) fp32 or NULL.
- * gate, up, out: `count` bf16 elements (count a multiple of 8); out may alias gate or up.
+ * gate, up: (rows, f) bf16 with row stride ld_in elements (the two halves of one fused
+ * gate|up GEMM output qualify); out: (rows, f) with row stride ld_out; f and the strides
+ * multiples of 8.
  * ---------------------------------------------------------------------------------- */
 ALG_API int alg_rms_norm_fwd(const void* x, const float* gain, void* y, int64_t rows, int d, float eps, void* stream);
-ALG_API int alg_alu_glu_fwd(const void* gate, const void* up, void* out, size_t count, float beta, void* stream);
+ALG_API int alg_alu_glu_fwd(const void* gate, const void* up, void* out, int64_t rows, int f, int64_t ld_in,
+                            int64_t ld_out, float beta, void* stream);
 
 /* fp32 -> bf16 cast of the embedding shard (the reference casts E per call,
  * src/algebraic/kernels/fused_head.py:165; model.py:225). */

@@ -40,9 +40,13 @@ def test_alu_glu():
     assert rel_l2(got, want) < 3e-3
     # the negative tail of the ALU survives (cancellation-free branch)
     tail = torch.full((8,), -200.0).bfloat16()
-    out = A.ops.alu_glu(torch.ones(8).bfloat16().to(DEV), tail.to(DEV), 0.5).cpu().float()
+    out = A.ops.alu_glu(torch.ones(1, 8).bfloat16().to(DEV), tail.to(DEV)[None], 0.5).cpu().float()[0]
     np.testing.assert_allclose(out, R.alu(tail, 0.5).float(), rtol=0.02)
     assert (out < 0).all()
+    # both halves of one fused gate|up GEMM output, read in place through the row stride
+    gu = torch.cat([gate, up], dim=1).to(DEV)
+    got2 = A.ops.alu_glu(gu[:, :2048], gu[:, 2048:], 0.5).cpu()
+    assert torch.equal(got2, got)
 
 
 @pytest.mark.parametrize("head_dim,T", [(64, 256), (128, 512)])
