@@ -235,6 +235,14 @@ ALG_API int alg_rms_norm_fwd(const void* x, const float* gain, void* y, int64_t 
 ALG_API int alg_alu_glu_fwd(const void* gate, const void* up, void* out, int64_t rows, int f, int64_t ld_in,
                             int64_t ld_out, float beta, void* stream);
 
+/* Failure-detection self-test (no counterpart in the reference).  Launches a one-CTA kernel
+ * whose threads wait, through the same bounded-wait helper every TMA/tcgen05 kernel here
+ * uses, on a barrier that is never signalled.  After `budget_ns` (at most 1 s) the wait
+ * gives up: `*status` (device int) becomes ALG_DEV_TIMEOUT, `*waited_ns` (device, may be
+ * NULL) the time actually spent, and the kernel returns normally. */
+ALG_API int alg_selftest_bounded_wait(int* status, unsigned long long budget_ns, unsigned long long* waited_ns,
+                                      void* stream);
+
 /* fp32 -> bf16 cast of the embedding shard (the reference casts E per call,
  * src/algebraic/kernels/fused_head.py:165; model.py:225). */
 ALG_API int alg_cast_f32_to_bf16(const float* src, void* dst, size_t count, void* stream);
