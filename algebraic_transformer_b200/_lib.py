@@ -53,6 +53,15 @@ class HeadArgs(C.Structure):
                 ("status", C.c_void_p)]
 
 
+ALG_MAX_RANKS = 16
+
+
+class HeadExchangeArgs(C.Structure):
+    _fields_ = [("rank", C.c_int), ("world", C.c_int), ("peer_region", C.c_void_p * ALG_MAX_RANKS),
+                ("N_capacity", C.c_int), ("pt", C.c_void_p), ("nll", C.c_void_p), ("obj", C.c_void_p),
+                ("wait_budget_ns", C.c_ulonglong)]
+
+
 # every symbol include/alg_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "alg_version": (C.c_int, []),
@@ -66,6 +75,8 @@ SYMBOLS = {
     "alg_head_workspace_bytes": (C.c_size_t, [C.POINTER(HeadArgs)]),
     "alg_head_fwd": (C.c_int, [C.POINTER(HeadArgs), C.c_void_p]),
     "alg_head_fwd_static": (C.c_int, [C.POINTER(HeadArgs), C.c_void_p]),
+    "alg_head_exchange_region_bytes": (C.c_size_t, [C.c_int, C.c_int]),
+    "alg_head_fwd_exchange": (C.c_int, [C.POINTER(HeadArgs), C.POINTER(HeadExchangeArgs), C.c_void_p]),
     "alg_head_finalize_workspace_bytes": (C.c_size_t, [C.c_int]),
     "alg_head_finalize": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_int,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),

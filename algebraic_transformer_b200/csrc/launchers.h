@@ -114,6 +114,29 @@ int launch_head_finalize(const float* l, const float* zt, int N, int log2n, floa
                          float* pt, float* nll, float* obj, float* block_sums, unsigned* ticket,
                          cudaStream_t stream);
 int head_finalize_blocks(int N);
+// ---- head_exchange.cu: split reduction + peer-memory exchange + telemetry in one kernel
+struct ExchangeParams {
+  const float* l_part;
+  const float* zt_part;
+  int slots, N;
+  int log2n;
+  float inv_c, clamp;
+  int rank, world;
+  float* peer_data[ALG_MAX_RANKS];       // every rank's exchange data, mapped on this device
+  unsigned* peer_flags[ALG_MAX_RANKS];   // every rank's flag table [world][128]
+  unsigned* call_counter;                // local, persists across calls
+  unsigned* ticket;
+  float* block_sums;
+  float* l_out;                          // optional: world totals
+  float* zt_out;
+  float* pt;
+  float* nll;
+  float* obj;
+  int* status;
+  unsigned long long budget_ns;
+};
+int head_exchange_blocks(int N);
+int launch_head_exchange(const ExchangeParams& p, cudaStream_t stream);
 // c_api.cu: argument checks + HeadParams derivation common to the head entry points
 extern "C" int head_fill(const alg_head_args* a, HeadParams* p, bool* use_fast);
 

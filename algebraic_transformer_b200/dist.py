@@ -57,3 +57,31 @@ def init_from_env(backend: str = None):
         kw = {"device_id": torch.device("cuda", local)} if backend == "nccl" else {}
         dist.init_process_group(backend=backend, rank=rank, world_size=world, **kw)
     return rank, world, local
+
+
+class HeadExchange:
+    """Peer-mapped exchange regions for the fused vocabulary-sharded head
+    (`alg_head_fwd_exchange`): one symmetric-memory allocation per rank, mapped on every GPU
+    of the group, into which the head's exchange kernel stores per-row partials directly over
+    NVLink.  Create it once per (group, capacity); every rank must create it collectively."""
+
+    def __init__(self, group, n_capacity: int, device):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        from . import _lib as L
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.n_capacity = int(n_capacity)
+        nbytes = L.load().alg_head_exchange_region_bytes(self.world, self.n_capacity)
+        if nbytes == 0:
+            raise ValueError("bad world size or capacity for the head exchange")
+        self.buf = symm.empty(int(nbytes), dtype=torch.uint8, device=device)
+        self.handle = symm.rendezvous(self.buf, group)
+        self.buf.zero_()                       # call counter, flags and data start at zero
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        if len(self.ptrs) != self.world:
+            raise RuntimeError("symmetric memory returned an unexpected number of peer pointers")

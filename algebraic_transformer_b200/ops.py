@@ -364,7 +364,7 @@ def head_finalize(stats, *, n: int, c: float, vocab_total: int, want_nll: bool =
 
 def fused_head(h, embed, targets, *, kind: str = "ce", n: int = 16, c: float = 16.0, block_n: int = 128,
                block_v: int = 512, vocab_offset: int = 0, vocab_total: Optional[int] = None,
-               group=None, want_nll: bool = False, impl: str = "auto"):
+               group=None, want_nll: bool = False, impl: str = "auto", exchange=None):
     """Fused tied-embedding projection and Alg-CE likelihood: returns `(objective,
     p_target)` like the reference (`want_nll=True` appends the per-token NLL).
 
@@ -391,8 +391,34 @@ def fused_head(h, embed, targets, *, kind: str = "ce", n: int = 16, c: float = 1
     e = cast_embedding(embed)
     t = targets.reshape(N).to(torch.int32).contiguous()
     V_total = int(vocab_total or embed.shape[0])
+    if exchange is not None:
+        # fused path: GEMM + statistic kernel, then one kernel that reduces the splits, exchanges
+        # the per-row partials with the peers over NVLink and forms the telemetry
+        return _fused_head_exchange(h, e, t, exchange, n=n, c=c, vocab_offset=vocab_offset, vocab_total=V_total,
+                                    want_nll=want_nll, impl=impl)
     stats = head_statistic(h, e, t, n=n, c=c, vocab_offset=vocab_offset, vocab_total=V_total, impl=impl)
     if group is not None:
         import torch.distributed as dist
         dist.all_reduce(stats, op=dist.ReduceOp.SUM, group=group)
     return head_finalize(stats, n=n, c=c, vocab_total=V_total, want_nll=want_nll)
+
+
+def _fused_head_exchange(h, e_bf16, targets, exchange, *, n, c, vocab_offset, vocab_total, want_nll, impl):
+    """`alg_head_fwd_exchange`: see include/alg_b200.h.  `exchange` is a dist.HeadExchange."""
+    N, d = h.shape
+    dev = h.device
+    pt = torch.empty(N, dtype=torch.float32, device=dev)
+    nll = torch.empty(N, dtype=torch.float32, device=dev) if want_nll else None
+    obj = torch.empty((), dtype=torch.float32, device=dev)
+    a = L.HeadArgs(h=h.data_ptr(), e=e_bf16.data_ptr(), targets=targets.data_ptr(), l_out=None, zt_out=None, N=N, d=d,
+                   V_local=e_bf16.shape[0], vocab_offset=int(vocab_offset), V_total=int(vocab_total), n=int(n),
+                   c=float(c), impl=L.IMPL[impl])
+    lib = L.load()
+    ws = _workspace(dev, lib.alg_head_workspace_bytes(a), "head")
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    x = L.HeadExchangeArgs(rank=exchange.rank, world=exchange.world, N_capacity=exchange.n_capacity,
+                           pt=pt.data_ptr(), nll=_ptr(nll), obj=obj.data_ptr(), wait_budget_ns=0)
+    for r, p in enumerate(exchange.ptrs):
+        x.peer_region[r] = p
+    L.check(lib.alg_head_fwd_exchange(a, x, _stream()))
+    return (obj, pt, nll) if want_nll else (obj, pt)

@@ -355,6 +355,25 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
         "frac_of_bf16_peak": 2.0 * N * d * cnt / (ms_head_k * 1e-3) / 1e12 / peak_tf,
         "collective": "none" if world == 1 else "one NCCL all-reduce of (2,N) fp32 per step",
         "logits_bytes_written": 0}
+    if world > 1:
+        # the same step with reduction + exchange + telemetry fused into one kernel over peer memory
+        try:
+            from algebraic_transformer_b200.dist import HeadExchange
+            ex = HeadExchange(dist.group.WORLD, N, dev)
+
+            def head_fused_step(i):
+                A.ops._fused_head_exchange(h, e, t, ex, n=HEAD["n"], c=HEAD["c"], vocab_offset=lo, vocab_total=V,
+                                           want_nll=False, impl=args.kernel)
+
+            for i in range(3):
+                head_fused_step(i)
+            ms_fx = max_over_ranks(cuda_time(head_fused_step, iters, sync))
+            extra["alg_ce_head_fused_exchange"] = {
+                "workload": extra["alg_ce_head"]["workload"], "tflops": fl / (ms_fx * 1e-3) / 1e12, "ms_per_step": ms_fx,
+                "collective": "none (one kernel: split reduction + NVLink peer stores + bounded flag wait + telemetry)"}
+            del ex
+        except Exception as err:                         # symmetric memory unavailable on this box
+            extra["alg_ce_head_fused_exchange"] = {"unavailable": repr(err)[:200]}
     del h, e, t, stats
     # ---- full prefill forward (BASELINE configs 3 and 4): batch split over ranks, hidden
     #      states all-gathered, head vocabulary-sharded ----

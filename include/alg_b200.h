@@ -210,6 +210,38 @@ ALG_API int alg_head_fwd(const alg_head_args* args, void* stream);
 #define ALG_HEAD_STATIC_SCRATCH_BYTES (4u << 20)
 ALG_API int alg_head_fwd_static(const alg_head_args* args, void* stream);
 
+/* ------------------------------------------------------------------------------------
+ * Vocabulary-sharded head with the cross-GPU exchange fused in: runs the shard's GEMM +
+ * statistic kernel, then ONE kernel that sums the split partials, writes this rank's
+ * per-row (l, zt) into every peer's exchange region over NVLink (plain peer stores; no
+ * TMA, no multicast), waits with a bound for the peers' contributions, adds them in rank
+ * order (bit-identical totals on every rank) and evaluates pt, nll and the objective.
+ * It stands in for alg_head_fwd + an all-reduce + alg_head_finalize; the reference has no
+ * multi-device head (its only collective is the trainer's gradient mean,
+ * src/algebraic/train.py:245-246).
+ *   peer_region[r]: address, valid on THIS device, of rank r's exchange region (own rank
+ *     included) of alg_head_exchange_region_bytes(world, N_capacity) bytes, 256-byte
+ *     aligned, peer-mapped (e.g. torch symmetric memory, cudaIpc, cuMemMap), zero-filled
+ *     once by every rank before the first call, with a barrier after the fill.
+ *   Every rank must call with the same N, n, c, V_total, in the same order; one rank per
+ *     GPU.  `args->l_out` / `zt_out` may be NULL; when given they receive the world totals.
+ *   A wait that runs out (a peer that never arrives) sets `args->status` to
+ *     ALG_DEV_TIMEOUT after wait_budget_ns (0 = 1 s); outputs are then undefined.
+ * ---------------------------------------------------------------------------------- */
+#define ALG_MAX_RANKS 16
+typedef struct {
+  int rank, world;
+  void* peer_region[ALG_MAX_RANKS];
+  int N_capacity;
+  float* pt;                /* (N) or NULL */
+  float* nll;               /* (N) or NULL */
+  float* obj;               /* 1 float or NULL */
+  unsigned long long wait_budget_ns;
+} alg_head_exchange_args;
+
+ALG_API size_t alg_head_exchange_region_bytes(int world, int N_capacity);
+ALG_API int alg_head_fwd_exchange(const alg_head_args* args, const alg_head_exchange_args* xargs, void* stream);
+
 /* Telemetry from the (all-reduced) statistic.
  * Replaces: _telemetry + the _inv_root finalize  src/algebraic/kernels/fused_head.py:116,219-229
  *           NLL = -log(max(pt,1e-30))            src/algebraic/train.py:239

@@ -34,6 +34,17 @@ def _worker(rank, world, port, ret):
     obj_w, pt_w = R.fused_head(h, E, t, n=8, c=2.0)
     e_head = float((nll.cpu().double() - R.nll_from_pt(pt_w).double()).norm() / R.nll_from_pt(pt_w).double().norm())
     ok_head = e_head < 1e-2 and abs(float(obj) - float(obj_w)) < 2e-3 * abs(float(obj_w))
+    # the same head with the exchange fused into one kernel over peer memory (no NCCL call):
+    # twice in a row (call parity / flag reuse) and once more with a smaller N
+    from algebraic_transformer_b200.dist import HeadExchange
+    ex = HeadExchange(dist.group.WORLD, N, dev)
+    for rows in (N, N, 384):
+        obj2, pt2, nll2 = A.fused_head(h[:rows].to(dev), E[lo:lo + cnt].to(dev), t[:rows].to(dev), kind="alg_ce",
+                                       n=8, c=2.0, vocab_offset=lo, vocab_total=V, want_nll=True, exchange=ex)
+        torch.cuda.synchronize()
+        ok_head = ok_head and torch.allclose(pt2.cpu(), pt.cpu()[:rows], rtol=1e-5, atol=1e-12)
+        ok_head = ok_head and torch.allclose(nll2.cpu(), nll.cpu()[:rows], rtol=1e-5, atol=1e-6)
+    ok_head = ok_head and abs(float(obj2) - float((1 - pt.cpu()[:384]).mean())) < 1e-6
     # ---- attention: (batch, head) units dealt out in contiguous blocks, no communication
     B, H, T, D = 1, 6, 512, 64
     q, k, v = (torch.randn((B, H, T, D), generator=g).bfloat16() for _ in range(3))
