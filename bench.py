@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Headline workload (BASELINE config 5 at the length its target is quoted on): asinh-power
+Headline workload (benchmark configuration 5 at the length its target is quoted on): asinh-power
 attention forward, bf16, causal, batch 1 x 16 heads x head_dim 128 x seq 8192 PER GPU,
 range-guarded, sink present, n=16, c=8.  Units are (batch, head) pairs; at N GPUs every
 rank runs its own 16 units (weak scaling, no collective on the attention path).
@@ -102,7 +102,7 @@ def run_reference_arm(args, rank):
 
 
 def workload_config(n_gpus):
-    return {"workload": "asinh attention forward, BASELINE config 5 @ seq 8192 (bf16, causal, range-guarded, sink)",
+    return {"workload": "asinh attention forward, benchmark configuration 5 @ seq 8192 (bf16, causal, range-guarded, sink)",
             "batch_per_gpu": ATTN["B"], "heads": ATTN["H"], "seq_len": ATTN["T"], "head_dim": ATTN["D"],
             "n": ATTN["n"], "c": ATTN["c"], "units_per_gpu": ATTN["B"] * ATTN["H"],
             "parallelism": f"(batch,head) units x{n_gpus}, no collective",
@@ -322,7 +322,7 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
     peak_tf = float(pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
     peak_bw = float(pk.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
     iters = max(5, min(args.steps, 20))
-    # ---- fused Alg-CE head: BASELINE config 2, vocabulary sharded over ranks ----
+    # ---- fused Alg-CE head: benchmark configuration 2, vocabulary sharded over ranks ----
     N, d, V = HEAD["N"], HEAD["d"], HEAD["V"]
     g = torch.Generator().manual_seed(0)
     h = torch.randn((N, d), generator=g).bfloat16().to(dev)
@@ -349,7 +349,7 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
     ms_head_k = max_over_ranks(cuda_time(head_kernel_only, iters, sync))
     fl = 2.0 * N * d * V
     extra["alg_ce_head"] = {
-        "workload": f"BASELINE config 2: N={N}, d={d}, V={V} bf16, vocab sharded x{world}",
+        "workload": f"benchmark configuration 2: N={N}, d={d}, V={V} bf16, vocab sharded x{world}",
         "tflops": fl / (ms_head * 1e-3) / 1e12, "ms_per_step": ms_head,
         "kernel_ms": ms_head_k, "kernel_tflops_per_gpu": 2.0 * N * d * cnt / (ms_head_k * 1e-3) / 1e12,
         "frac_of_bf16_peak": 2.0 * N * d * cnt / (ms_head_k * 1e-3) / 1e12 / peak_tf,
@@ -375,7 +375,7 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
         except Exception as err:                         # symmetric memory unavailable on this box
             extra["alg_ce_head_fused_exchange"] = {"unavailable": repr(err)[:200]}
     del h, e, t, stats
-    # ---- full prefill forward (BASELINE configs 3 and 4): batch split over ranks, hidden
+    # ---- full prefill forward (benchmark configurations 3 and 4): batch split over ranks, hidden
     #      states all-gathered, head vocabulary-sharded ----
     from algebraic_transformer_b200 import prefill as PF
     for name, size, vocab, gb, seq in (("prefill_125m", "125m", 50304, 16, 1024), ("prefill_350m", "350m", 32000, 8, 2048),

@@ -195,7 +195,7 @@ def test_fused_qk_prologue_layer(dtype, D, impl):
 
 
 def test_config1_single_layer_fp32():
-    """BASELINE config 1: (4,12,1024,64) fp32 causal, unit gains, Cayley over 0..1023,
+    """benchmark configuration 1: (4,12,1024,64) fp32 causal, unit gains, Cayley over 0..1023,
     n=16, c=8, sink ~ N(0, 0.02)."""
     B, H, T, D = 4, 12, 1024, 64
     q, k, v = (randn((B, H, T, D), i) for i in range(3))
@@ -214,7 +214,7 @@ def test_config1_single_layer_fp32():
 
 @pytest.mark.parametrize("impl", IMPLS)
 def test_config5_long_context_sampled(impl):
-    """BASELINE config 5 at T=8192: (1,16,8192,128) bf16.  The oracle checks two heads in
+    """benchmark configuration 5 at T=8192: (1,16,8192,128) bf16.  The oracle checks two heads in
     full (row-blocked); run-to-run determinism is checked on everything."""
     B, H, T, D = 1, 16, 8192, 128
     g = torch.Generator().manual_seed(0)
@@ -358,7 +358,7 @@ def test_head_ragged_vocab_rows_and_clamp(impl):
 
 @pytest.mark.parametrize("impl", IMPLS)
 def test_config2_full_head(impl):
-    """BASELINE config 2: hidden (8192,768) bf16 ~ N(0,1), E (50304,768) ~ N(0,0.02),
+    """benchmark configuration 2: hidden (8192,768) bf16 ~ N(0,1), E (50304,768) ~ N(0,0.02),
     targets uniform in [0, 50257); NLL rel-L2 <= 1e-2."""
     g = torch.Generator().manual_seed(0)
     h = torch.randn((8192, 768), generator=g).bfloat16()
