@@ -311,7 +311,7 @@ int launch_one(const AttnParams& p, cudaStream_t stream) {
     configured = true;
   }
   const long long items = (long long)((p.Tq + BM - 1) / BM) * p.H * p.B;
-  const int cap = 148 * 8;                             // a few resident CTAs per SM; the loop covers the rest
+  const int cap = 148 * 4;                             // a few resident CTAs per SM; the loop covers the rest
   const unsigned grid = unsigned(items < cap ? items : cap);
   kern<<<grid, NTHREADS, smem, stream>>>(p);
   ALG_CUDA_TRY(cudaGetLastError());

@@ -153,11 +153,19 @@ __global__ void __launch_bounds__(256, MODE == 0 ? 4 : 3) qk_prep_kernel(const P
       }
     }
   }
-  if (p.stat_mode != 0) {
+  if (p.stat_mode != 0) {                     // one atomic per block: warp max -> block max -> global
+    __shared__ float s_stat[8];
     stat = warp_max(stat);
     // NaN inputs must fail the guard: map NaN to +inf before the integer max.
     if (!(stat == stat)) stat = __int_as_float(0x7f800000);
-    if (lane == 0) atomicMax(p.stat_out, __float_as_uint(stat));
+    if (lane == 0) s_stat[threadIdx.x >> 5] = stat;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float m = s_stat[0];
+#pragma unroll
+      for (int w = 1; w < 8; ++w) m = fmaxf(m, s_stat[w]);
+      atomicMax(p.stat_out, __float_as_uint(m));
+    }
   }
 }
 
@@ -180,7 +188,9 @@ static int launch_t(const PrepBatch& batch, cudaStream_t stream) {
   if (positions == 0) return ALG_OK;
   const int64_t warps = (positions + RPW - 1) / RPW;
   int64_t blocks = (warps + 7) / 8;
-  const int64_t cap = 148 * 16;        // a few waves of resident CTAs; grid-stride covers the rest
+  // resident CTAs only (the grid-stride loop covers the rest): 4 per SM for the
+  // statistics-only mode, 3 for the others
+  const int64_t cap = 148 * (mode == 0 ? 4 : 3);
   if (blocks > cap) blocks = cap;
   const dim3 grid(unsigned(blocks), unsigned(batch.count));
   if (mode == 0) qk_prep_kernel<T, D, 0><<<grid, 256, 0, stream>>>(batch);
