@@ -50,7 +50,6 @@ template <> struct Vec16<__nv_bfloat16> {
   static __device__ __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 };
 
-constexpr int HEADS_PER_STEP = 4;
 
 // MODE 0: statistics only (guard maxima of ready-made q / k / v); 1: normalise (+ gain);
 // 2: normalise + rotate.  Modes 1 and 2 can also accumulate a statistic in the same pass.
@@ -61,6 +60,8 @@ __global__ void __launch_bounds__(256, MODE == 0 ? 4 : 3) qk_prep_kernel(const P
   constexpr int LPR = D / VEC;         // lanes per row
   constexpr int RPW = 32 / LPR;        // positions per warp step
   constexpr int HALF = D / 2;
+  // loads kept in flight per lane: the statistics-only pass has the registers for eight
+  constexpr int HEADS_PER_STEP = (MODE == 0) ? 8 : 4;
   const PrepParams& p = batch.t[blockIdx.y];
   const int lane = threadIdx.x & 31;
   const int lir = lane % LPR;          // lane in row
