@@ -27,42 +27,60 @@ __device__ __forceinline__ uint4 pack8(const float* v) {
 }
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
-// One warp per row; VPL 16-byte vectors per lane (d = 256 * VPL elements at most per pass).
-template <int VPL>
+// A warp owns RPW rows at a time and issues all their 16-byte loads (VPL per lane and row)
+// before using any, so that enough bytes are in flight to cover the HBM latency.
+template <int VPL, int RPW>
 __global__ void __launch_bounds__(256) rms_rows_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gain,
                                                        __nv_bfloat16* __restrict__ y, int64_t rows, int d, float eps) {
   const int lane = threadIdx.x & 31;
   const int64_t warp_global = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t warps_total = (int64_t(gridDim.x) * blockDim.x) >> 5;
   const int nvec = d / 8;
-  for (int64_t row = warp_global; row < rows; row += warps_total) {
-    const uint4* src = reinterpret_cast<const uint4*>(x + row * d);
-    uint4 raw[VPL];
+  for (int64_t row0 = warp_global * RPW; row0 < rows; row0 += warps_total * RPW) {
+    uint4 raw[RPW][VPL];
 #pragma unroll
-    for (int u = 0; u < VPL; ++u) {
-      const int vi = u * 32 + lane;
-      raw[u] = vi < nvec ? src[vi] : make_uint4(0, 0, 0, 0);
+    for (int r = 0; r < RPW; ++r) {
+      const int64_t row = row0 + r < rows ? row0 + r : rows - 1;
+      const uint4* src = reinterpret_cast<const uint4*>(x + row * d);
+#pragma unroll
+      for (int u = 0; u < VPL; ++u) {
+        const int vi = u * 32 + lane;
+        raw[r][u] = vi < nvec ? src[vi] : make_uint4(0, 0, 0, 0);
+      }
     }
-    float ss = 0.f;
 #pragma unroll
-    for (int u = 0; u < VPL; ++u) {
-      float v[8];
-      unpack8(raw[u], v);
+    for (int r = 0; r < RPW; ++r) {
+      float ss = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
-    }
-    ss = warp_sum(ss);
-    const float tau = rsqrtf(ss / float(d) + eps);
-    uint4* dst = reinterpret_cast<uint4*>(y + row * d);
-#pragma unroll
-    for (int u = 0; u < VPL; ++u) {
-      const int vi = u * 32 + lane;
-      if (vi < nvec) {
+      for (int u = 0; u < VPL; ++u) {
         float v[8];
-        unpack8(raw[u], v);
+        unpack8(raw[r][u], v);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = (v[i] * tau) * (gain != nullptr ? gain[vi * 8 + i] : 1.0f);
-        dst[vi] = pack8(v);
+        for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+      }
+      ss = warp_sum(ss);
+      const float tau = rsqrtf(ss / float(d) + eps);
+      if (row0 + r < rows) {
+        uint4* dst = reinterpret_cast<uint4*>(y + (row0 + r) * d);
+#pragma unroll
+        for (int u = 0; u < VPL; ++u) {
+          const int vi = u * 32 + lane;
+          if (vi < nvec) {
+            float v[8];
+            unpack8(raw[r][u], v);
+            if (gain != nullptr) {
+              const float4 g0 = *reinterpret_cast<const float4*>(gain + vi * 8);
+              const float4 g1 = *reinterpret_cast<const float4*>(gain + vi * 8 + 4);
+              const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = (v[i] * tau) * g[i];
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = v[i] * tau;
+            }
+            dst[vi] = pack8(v);
+          }
+        }
       }
     }
   }
@@ -100,17 +118,22 @@ __global__ void __launch_bounds__(256) alu_glu_kernel(const __nv_bfloat16* __res
 int launch_rms_rows(const void* x, const float* gain, void* y, int64_t rows, int d, float eps, cudaStream_t stream) {
   if (rows == 0) return ALG_OK;
   const int vpl = (d / 8 + 31) / 32;
-  int64_t blocks = (rows + 7) / 8;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  constexpr int RPW = 4;                               // rows per warp step (<= 4 x 4 vectors per lane in flight)
+  int64_t blocks = (rows + 8 * RPW - 1) / (8 * RPW);
+  if (blocks > 148 * 6) blocks = 148 * 6;
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
   __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
+  if ((reinterpret_cast<uintptr_t>(gain) & 15) != 0) {
+    set_error("rms_norm: gain must be 16-byte aligned");
+    return ALG_ERR_INVALID;
+  }
   switch (vpl) {
-    case 1: rms_rows_kernel<1><<<unsigned(blocks), 256, 0, stream>>>(xp, gain, yp, rows, d, eps); break;
-    case 2: rms_rows_kernel<2><<<unsigned(blocks), 256, 0, stream>>>(xp, gain, yp, rows, d, eps); break;
-    case 3: rms_rows_kernel<3><<<unsigned(blocks), 256, 0, stream>>>(xp, gain, yp, rows, d, eps); break;
-    case 4: rms_rows_kernel<4><<<unsigned(blocks), 256, 0, stream>>>(xp, gain, yp, rows, d, eps); break;
-    case 5: case 6: rms_rows_kernel<6><<<unsigned(blocks), 256, 0, stream>>>(xp, gain, yp, rows, d, eps); break;
-    case 7: case 8: rms_rows_kernel<8><<<unsigned(blocks), 256, 0, stream>>>(xp, gain, yp, rows, d, eps); break;
+    case 1: rms_rows_kernel<1, RPW><<<unsigned(blocks), 256, 0, stream>>>(xp, gain, yp, rows, d, eps); break;
+    case 2: rms_rows_kernel<2, RPW><<<unsigned(blocks), 256, 0, stream>>>(xp, gain, yp, rows, d, eps); break;
+    case 3: rms_rows_kernel<3, RPW><<<unsigned(blocks), 256, 0, stream>>>(xp, gain, yp, rows, d, eps); break;
+    case 4: rms_rows_kernel<4, RPW><<<unsigned(blocks), 256, 0, stream>>>(xp, gain, yp, rows, d, eps); break;
+    case 5: case 6: rms_rows_kernel<6, 2><<<unsigned(blocks), 256, 0, stream>>>(xp, gain, yp, rows, d, eps); break;
+    case 7: case 8: rms_rows_kernel<8, 2><<<unsigned(blocks), 256, 0, stream>>>(xp, gain, yp, rows, d, eps); break;
     default:
       set_error("rms_norm: row width %d is above the supported 2048", d);
       return ALG_ERR_UNSUPPORTED;

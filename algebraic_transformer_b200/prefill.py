@@ -98,8 +98,9 @@ def cast_params(params, device):
 class Prefill:
     """Forward pass of one rank: `hidden(tokens)` and `loss(tokens, targets)`."""
 
-    def __init__(self, cfg: PrefillConfig, params, device, seq_len: int, impl: str = "auto"):
+    def __init__(self, cfg: PrefillConfig, params, device, seq_len: int, impl: str = "auto", exchange=None):
         self.cfg, self.device, self.impl = cfg, torch.device(device), impl
+        self.exchange = exchange        # dist.HeadExchange: fuse the head's cross-GPU sum into its last kernel
         self.p = cast_params(params, self.device)
         self.cos, self.sin = ops.cayley_table_geometric(cfg.head_dim, seq_len, cfg.rope_base, device=self.device)
 
@@ -178,5 +179,6 @@ class Prefill:
         dist.all_gather_into_tensor(all_t, tgt.contiguous(), group=group)
         lo, cnt = vocab_shard(cfg.vocab_size, rank, world)
         return ops.fused_head(full, self.p["embed"][lo:lo + cnt], all_t, kind="alg_ce", n=cfg.head_n, c=cfg.head_c,
-                              block_n=full.shape[0], vocab_offset=lo, vocab_total=cfg.vocab_size, group=group,
+                              block_n=full.shape[0], vocab_offset=lo, vocab_total=cfg.vocab_size,
+                              group=None if self.exchange is not None else group, exchange=self.exchange,
                               want_nll=want_nll, impl=self.impl)

@@ -384,7 +384,14 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
             continue
         cfg = PF.PrefillConfig.preset(size, vocab_size=vocab)
         params = PF.init_params(cfg, seed=0)
-        model = PF.Prefill(cfg, params, dev, seq_len=seq, impl=args.kernel)
+        ex = None
+        if world > 1:
+            try:
+                from algebraic_transformer_b200.dist import HeadExchange
+                ex = HeadExchange(dist.group.WORLD, gb * seq, dev)
+            except Exception:
+                ex = None                               # fall back to the NCCL all-reduce
+        model = PF.Prefill(cfg, params, dev, seq_len=seq, impl=args.kernel, exchange=ex)
         del params
         gt = torch.Generator().manual_seed(2)
         tokens = torch.randint(0, vocab, (gb, seq), generator=gt)
@@ -404,8 +411,9 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
         extra[name] = {"workload": f"{size} algebraic prefill + Alg-CE head, bf16, global batch {gb} x {seq}, vocab {vocab}, "
                                    f"random init seed 0, batch split x{world}",
                        "tokens_per_s": gb * seq / (ms_p * 1e-3), "ms_per_step": ms_p, "launch": "CUDA graph: " + how,
+                       "head_exchange": "fused peer-memory kernel" if ex is not None else ("NCCL all-reduce" if world > 1 else "none"),
                        "tflops": fl / (ms_p * 1e-3) / 1e12, "frac_of_bf16_peak_per_gpu": fl / (ms_p * 1e-3) / 1e12 / world / peak_tf}
-        del replay, model
+        del replay, model, ex
         torch.cuda.empty_cache()
     if world > 1:
         return extra
