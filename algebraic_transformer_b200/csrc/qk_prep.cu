@@ -97,6 +97,10 @@ __global__ void __launch_bounds__(256, MODE == 0 ? 4 : 3) qk_prep_kernel(const P
         c[i] = V::round(cv.x); c[i + 1] = V::round(cv.y); c[i + 2] = V::round(cv.z); c[i + 3] = V::round(cv.w);
         s[i] = V::round(sv.x); s[i + 1] = V::round(sv.y); s[i + 2] = V::round(sv.z); s[i + 3] = V::round(sv.w);
       }
+      if (first) {                       // the first half subtracts x2 s
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) s[i] = -s[i];
+      }
     }
 
     for (int h0 = 0; h0 < p.H; h0 += HEADS_PER_STEP) {
@@ -124,14 +128,22 @@ __global__ void __launch_bounds__(256, MODE == 0 ? 4 : 3) qk_prep_kernel(const P
         }
         if constexpr (MODE == 2) {
 #pragma unroll
-          for (int i = 0; i < VEC; ++i) {
-            const float other = __shfl_xor_sync(0xffffffffu, v[i], LPR / 2);
-            // first half: x1 c - x2 s ; second half: x1 s + x2 c, each product rounded to T
-            const float x1 = first ? v[i] : other;
-            const float x2 = first ? other : v[i];
-            const float a = V::round(x1 * (first ? c[i] : s[i]));
-            const float bb = V::round(x2 * (first ? s[i] : c[i]));
-            v[i] = V::round(first ? a - bb : a + bb);
+          for (int i = 0; i < VEC; i += 2) {
+            // rotate-half partner values; bf16 rows hold bf16-exact values here, so a pair
+            // travels as one packed 32-bit shuffle
+            float o0, o1;
+            if constexpr (sizeof(T) == 2) {
+              const uint32_t pk = __shfl_xor_sync(0xffffffffu, pack_bf16(v[i], v[i + 1]), LPR / 2);
+              o0 = __uint_as_float(pk << 16);
+              o1 = __uint_as_float(pk & 0xffff0000u);
+            } else {
+              o0 = __shfl_xor_sync(0xffffffffu, v[i], LPR / 2);
+              o1 = __shfl_xor_sync(0xffffffffu, v[i + 1], LPR / 2);
+            }
+            // first half: x1 c - x2 s ; second half: x1 s + x2 c  ==  own * c + other * (-+ s),
+            // each product and the sum rounded to T (s[] carries the sign of this half)
+            v[i] = V::round(V::round(v[i] * c[i]) + V::round(o0 * s[i]));
+            v[i + 1] = V::round(V::round(v[i + 1] * c[i + 1]) + V::round(o1 * s[i + 1]));
           }
         }
         if (MODE >= 1 && dst0 != nullptr && on) V::store(dst0 + int64_t(h) * p.ys.h, v);

@@ -132,6 +132,8 @@ def main():
     ap.add_argument("--kernel", default="auto", choices=["auto", "mma", "tcgen05"],
                     help="attention/head kernel family (auto = tcgen05 where it applies)")
     ap.add_argument("--skip-extra", action="store_true", help="headline workload only")
+    ap.add_argument("--prefill-only", default=None, choices=["125m", "350m", "1b"],
+                    help="profiling aid: run only this prefill model in the extra section")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -380,7 +382,7 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
     from algebraic_transformer_b200 import prefill as PF
     for name, size, vocab, gb, seq in (("prefill_125m", "125m", 50304, 16, 1024), ("prefill_350m", "350m", 32000, 8, 2048),
                                        ("prefill_1b", "1b", 32000, 8, 2048)):
-        if gb % world:
+        if gb % world or (args.prefill_only is not None and args.prefill_only != size):
             continue
         cfg = PF.PrefillConfig.preset(size, vocab_size=vocab)
         params = PF.init_params(cfg, seed=0)
