@@ -22,6 +22,11 @@
 // executes one thread's MMAs in issue order, so issuing S_w(j+1) after P_w(j).V_j is what
 // protects P_w(j) from being overwritten, and S_w(j+1) complete implies P_w(j).V_j complete.
 // Key tiles above the diagonal are never loaded; only the diagonal tile evaluates a mask.
+// The kernel is persistent: one CTA per SM walks a fixed list of work items (heaviest row
+// blocks first, dealt out boustrophedon so the per-CTA sums stay level).  Barriers, tensor
+// memory and the K/V ring live across items, so the loads of the next item's first tiles
+// are in flight while the current item finishes, and its first S is issued while the
+// weight warps still write the current output.
 // Every mbarrier wait is bounded (sm100_ptx.cuh); on a timeout the kernel reports
 // ALG_DEV_TIMEOUT through the status word and returns.
 #include "common.cuh"
@@ -52,7 +57,7 @@ template <int D> struct Cfg {
 };
 
 struct __align__(16) Control {
-  uint64_t q_full, kv_full[MAX_NKV], kv_empty[MAX_NKV], s_full[2], p_full[2], o_full[2];
+  uint64_t q_full[2], q_free[2], kv_full[MAX_NKV], kv_empty[MAX_NKV], s_full[2], p_full[2], o_full[2], o_free[2];
   uint32_t tmem_base;
   int abort_flag;
   int shift_mode;
@@ -111,6 +116,28 @@ __device__ __forceinline__ void weigh_tile(uint32_t s_taddr, int r, float scale,
   tmem_st_wait();
 }
 
+// Position in the K/V ring: slot and the parity of how often the ring has wrapped.
+template <int NKV> struct RingCursor {
+  int slot = 0;
+  uint32_t phase = 0;
+  __device__ __forceinline__ void next() { if (++slot == NKV) { slot = 0; phase ^= 1u; } }
+};
+
+// The k-th work item of this CTA.  Items are numbered heaviest first (last row block of
+// every (batch, head), then the one before, ...); row k of the deal goes left to right for
+// even k and right to left for odd k.
+struct Item { int b, h, row0, n0, n1; };
+__device__ __forceinline__ bool item_at(const AttnParams& p, int k, Item& it) {
+  const int units = p.B * p.H, nblk = p.Tq / (2 * BQ), G = int(gridDim.x);
+  const int idx = k * G + ((k & 1) ? G - 1 - int(blockIdx.x) : int(blockIdx.x));
+  if (idx >= units * nblk) return false;
+  const int blk = nblk - 1 - idx / units, bh = idx % units;
+  it.b = bh / p.H; it.h = bh % p.H;
+  it.row0 = blk * 2 * BQ;
+  it.n0 = 2 * blk + 1; it.n1 = 2 * blk + 2;      // key tiles needed by query tile 0 / 1
+  return true;
+}
+
 template <int D> constexpr size_t smem_bytes() { return size_t(Cfg<D>::CTL_OFF) + sizeof(Control) + 1024; }
 
 #ifdef ALG_ATTN_TIMING   // optional instrumentation build: cycle counters written into `stat`
@@ -134,12 +161,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   if (ctl->shift_mode != 0) return;               // the guard failed: the stable kernel does this launch's work
 
   if (threadIdx.x == 0) {
-    mbar_init(&ctl->q_full, 1);
+    for (int w = 0; w < 2; ++w) { mbar_init(&ctl->q_full[w], 1); mbar_init(&ctl->q_free[w], 1); }
     for (int i = 0; i < C::NKV; ++i) { mbar_init(&ctl->kv_full[i], 1); mbar_init(&ctl->kv_empty[i], 1); }
     for (int w = 0; w < 2; ++w) {
       mbar_init(&ctl->s_full[w], 1);
       mbar_init(&ctl->p_full[w], 128);
       mbar_init(&ctl->o_full[w], 1);
+      mbar_init(&ctl->o_free[w], 128);
     }
     ctl->abort_flag = 0;
     fence_barrier_init();
@@ -155,98 +183,127 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const uint32_t tmem_base = ctl->tmem_base;
   const BoundedWait bw{&ctl->abort_flag, 1000000000ull};
 
-  // work item: heavy (late) row blocks first
-  const int units = p.B * p.H;
-  const int nblk = p.Tq / (2 * BQ);
-  const int blk = nblk - 1 - int(blockIdx.x) / units;
-  const int bh = int(blockIdx.x) % units;
-  const int b = bh / p.H, h = bh % p.H;
-  const int row0 = blk * 2 * BQ;
-  const int n0 = 2 * blk + 1, n1 = 2 * blk + 2;   // key tiles needed by query tile 0 / 1
   long long tm0 = 0, tm1 = 0, tm2 = 0;            // timing accumulators (instrumentation build only)
   (void)tm0; (void)tm1; (void)tm2;
+  Item it;
 
   if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
-      mbar_arrive_expect_tx(&ctl->q_full, 2 * C::TILE_BYTES);
-      for (int w = 0; w < 2; ++w)
-        for (int pn = 0; pn < C::PANELS; ++pn)
-          tma_load_4d(smem + C::Q_OFF + w * C::TILE_BYTES + pn * PANEL_BYTES, &tm_q, &ctl->q_full, pn * 64,
-                      row0 + w * BQ, h, b);
       bool ok = true;
-      for (int idx = 0; idx < 2 * n1 && ok; ++idx) {   // K_0, V_0, K_1, V_1, ...
-        const int buf = idx % C::NKV;
-        const uint32_t phase = (idx / C::NKV) & 1u;
-        if (!bw.wait(&ctl->kv_empty[buf], phase ^ 1u)) { ok = false; break; }
-        mbar_arrive_expect_tx(&ctl->kv_full[buf], C::TILE_BYTES);
-        const CUtensorMap* tm = (idx & 1) ? &tm_v : &tm_k;
-        for (int pn = 0; pn < C::PANELS; ++pn)
-          tma_load_4d(smem + C::KV_OFF + buf * C::TILE_BYTES + pn * PANEL_BYTES, tm, &ctl->kv_full[buf], pn * 64,
-                      (idx >> 1) * BKEY, h, b);
+      RingCursor<C::NKV> cur;                       // runs on over all items
+      for (int k = 0; ok && item_at(p, k, it); ++k) {
+        auto load_kv = [&](int idx) {               // K_0, V_0, K_1, V_1, ... of this item
+          const int buf = cur.slot;
+          if (!bw.wait(&ctl->kv_empty[buf], cur.phase ^ 1u)) return false;
+          mbar_arrive_expect_tx(&ctl->kv_full[buf], C::TILE_BYTES);
+          const CUtensorMap* tm = (idx & 1) ? &tm_v : &tm_k;
+          for (int pn = 0; pn < C::PANELS; ++pn)
+            tma_load_4d(smem + C::KV_OFF + buf * C::TILE_BYTES + pn * PANEL_BYTES, tm, &ctl->kv_full[buf], pn * 64,
+                        (idx >> 1) * BKEY, it.h, it.b);
+          cur.next();
+          return true;
+        };
+        auto load_q = [&](int w) {                  // after the previous item's last S_w has read the tile
+          if (k > 0 && !bw.wait(&ctl->q_free[w], (k - 1) & 1u)) return false;
+          mbar_arrive_expect_tx(&ctl->q_full[w], C::TILE_BYTES);
+          for (int pn = 0; pn < C::PANELS; ++pn)
+            tma_load_4d(smem + C::Q_OFF + w * C::TILE_BYTES + pn * PANEL_BYTES, &tm_q, &ctl->q_full[w], pn * 64,
+                        it.row0 + w * BQ, it.h, it.b);
+          return true;
+        };
+        // At the start nothing is resident, so what the first MMA needs goes first.  Later the
+        // K/V tiles only need ring slots the previous item drains by itself, while each Q tile
+        // has to wait for that item's last use of it.
+        if (k == 0) ok = load_q(0) && load_kv(0) && load_q(1) && load_kv(1);
+        else ok = load_kv(0) && load_q(0) && load_kv(1) && load_q(1);
+        for (int idx = 2; idx < 2 * it.n1 && ok; ++idx) ok = load_kv(idx);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t q_addr = smem_u32(smem + C::Q_OFF), kv_addr = smem_u32(smem + C::KV_OFF);
-      auto kv_wait = [&](int idx) { return bw.wait(&ctl->kv_full[idx % C::NKV], (idx / C::NKV) & 1u); };
-      auto issue_s = [&](int w, int idx) {            // S_w = Q_w K^T
-        const uint32_t qa = q_addr + w * C::TILE_BYTES, ka = kv_addr + (idx % C::NKV) * C::TILE_BYTES;
+      using Cur = RingCursor<C::NKV>;
+      Cur cur;                                      // the next K/V tile in ring order, over all items
+      int t0 = 0, t1 = 0;                           // score tiles of query tile 0 / 1 in earlier items
+      auto kv_wait = [&](const Cur& c) { return bw.wait(&ctl->kv_full[c.slot], c.phase); };
+      // descriptor low halves: Q tiles and ring slot 0 as K (K-major, LBO 16) and as V (MN-major,
+      // LBO = one panel); a slot adds slot * TILE_BYTES / 16, a K step adds a constant
+      const uint32_t q_lo0 = sw128_desc_lo(q_addr, 16), k_lo0 = sw128_desc_lo(kv_addr, 16),
+                     v_lo0 = sw128_desc_lo(kv_addr, PANEL_BYTES);
+      auto issue_s = [&](int w, int slot) {           // S_w = Q_w K^T
+        const uint32_t qa = q_lo0 + w * (C::TILE_BYTES >> 4), ka = k_lo0 + slot * (C::TILE_BYTES >> 4);
+        const uint32_t d_tmem = tmem_base + C::S_COL + w * 128;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * PANEL_BYTES + (ks & 3) * 32;
-          umma_f16_ss(tmem_base + C::S_COL + w * 128, make_sw128_desc(qa + off, 16, 1024),
-                      make_sw128_desc(ka + off, 16, 1024), C::IDESC_S, ks != 0 ? 1u : 0u);
+          const uint32_t off = ((ks >> 2) * PANEL_BYTES + (ks & 3) * 32) >> 4;
+          umma_f16_ss_parts(d_tmem, qa + off, SW128_DESC_HI, ka + off, SW128_DESC_HI, C::IDESC_S, ks != 0 ? 1u : 0u);
         }
       };
-      auto issue_pv = [&](int w, int idx, bool first) {   // O_w += P_w V, P_w from tensor memory
-        const uint32_t va = kv_addr + (idx % C::NKV) * C::TILE_BYTES;
+      auto issue_pv = [&](int w, int slot, bool first) {  // O_w += P_w V, P_w from tensor memory
+        const uint32_t va = v_lo0 + slot * (C::TILE_BYTES >> 4);
+        const uint32_t d_tmem = tmem_base + C::O_COL + w * D, p_tmem = tmem_base + C::S_COL + w * 128;
 #pragma unroll
         for (int ks = 0; ks < BKEY / 16; ++ks)        // 16 keys = 8 packed-bf16 columns of P per step
-          umma_f16_ts(tmem_base + C::O_COL + w * D, tmem_base + C::S_COL + w * 128 + ks * 8,
-                      make_sw128_desc(va + ks * 2048, PANEL_BYTES, 1024), C::IDESC_PV, (first && ks == 0) ? 0u : 1u);
+          umma_f16_ts_parts(d_tmem, p_tmem + ks * 8, va + ks * (2048 >> 4), SW128_DESC_HI, C::IDESC_PV,
+                            (first && ks == 0) ? 0u : 1u);
       };
 #ifdef ALG_ATTN_TIMING
       const long long t_begin = clock64();
 #endif
-      bool ok = bw.wait(&ctl->q_full, 0) && kv_wait(0);
-      if (ok) {
+      bool ok = true;
+      for (int k = 0; ok && item_at(p, k, it); ++k) {
+        const int n0 = it.n0, n1 = it.n1;
+        if (!bw.wait(&ctl->q_full[0], k & 1u) || !kv_wait(cur)) { ok = false; break; }
         tc_fence_after();
-        issue_s(0, 0); umma_commit(&ctl->s_full[0]);
-        issue_s(1, 0); umma_commit(&ctl->s_full[1]);
-        umma_commit(&ctl->kv_empty[0]);
-      }
-      for (int j = 0; j < n1 && ok; ++j) {
-        const int vidx = 2 * j + 1, kidx = 2 * j + 2;
-        bool k_ready = false;
-        if (!ALG_T(tm0, kv_wait(vidx))) { ok = false; break; }
-        if (j < n0) {
-          if (!ALG_T(tm1, bw.wait(&ctl->p_full[0], j & 1u))) { ok = false; break; }
-          tc_fence_after();
-          issue_pv(0, vidx, j == 0);
-          if (j + 1 < n0) {
-            if (!ALG_T(tm0, kv_wait(kidx))) { ok = false; break; }
-            k_ready = true;
+        issue_s(0, cur.slot); umma_commit(&ctl->s_full[0]);
+        if (n0 == 1) umma_commit(&ctl->q_free[0]);
+        if (!bw.wait(&ctl->q_full[1], k & 1u)) { ok = false; break; }
+        tc_fence_after();
+        issue_s(1, cur.slot); umma_commit(&ctl->s_full[1]);
+        umma_commit(&ctl->kv_empty[cur.slot]);
+        cur.next();
+        for (int j = 0; j < n1 && ok; ++j) {
+          const Cur vc = cur;                         // V_j
+          cur.next();
+          const Cur kc = cur;                         // K_{j+1}: only meaningful while j + 1 < n1
+          if (j + 1 < n1) cur.next();
+          bool k_ready = false;
+          if (!ALG_T(tm0, kv_wait(vc))) { ok = false; break; }
+          if (j < n0) {
+            if (!ALG_T(tm1, bw.wait(&ctl->p_full[0], (t0 + j) & 1u))) { ok = false; break; }
+            // the first product of an item overwrites O_0: the previous output must have been read
+            if (j == 0 && k > 0 && !bw.wait(&ctl->o_free[0], (k - 1) & 1u)) { ok = false; break; }
             tc_fence_after();
-            issue_s(0, kidx);                       // after P_0.V: may overwrite P_0
-            umma_commit(&ctl->s_full[0]);
+            issue_pv(0, vc.slot, j == 0);
+            if (j + 1 < n0) {
+              if (!ALG_T(tm0, kv_wait(kc))) { ok = false; break; }
+              k_ready = true;
+              tc_fence_after();
+              issue_s(0, kc.slot);                     // after P_0.V: may overwrite P_0
+              umma_commit(&ctl->s_full[0]);
+              if (j + 2 == n0) umma_commit(&ctl->q_free[0]);   // the item's last read of Q tile 0
+            } else {
+              umma_commit(&ctl->o_full[0]);
+            }
+          }
+          if (!ALG_T(tm2, bw.wait(&ctl->p_full[1], (t1 + j) & 1u))) { ok = false; break; }
+          if (j == 0 && k > 0 && !bw.wait(&ctl->o_free[1], (k - 1) & 1u)) { ok = false; break; }
+          tc_fence_after();
+          issue_pv(1, vc.slot, j == 0);
+          umma_commit(&ctl->kv_empty[vc.slot]);
+          if (j + 1 < n1) {
+            if (!k_ready && !ALG_T(tm0, kv_wait(kc))) { ok = false; break; }
+            tc_fence_after();
+            issue_s(1, kc.slot);
+            umma_commit(&ctl->s_full[1]);
+            umma_commit(&ctl->kv_empty[kc.slot]);
+            if (j + 2 == n1) umma_commit(&ctl->q_free[1]);     // the item's last read of Q tile 1
           } else {
-            umma_commit(&ctl->o_full[0]);
+            umma_commit(&ctl->o_full[1]);
           }
         }
-        if (!ALG_T(tm2, bw.wait(&ctl->p_full[1], j & 1u))) { ok = false; break; }
-        tc_fence_after();
-        issue_pv(1, vidx, j == 0);
-        umma_commit(&ctl->kv_empty[vidx % C::NKV]);
-        if (j + 1 < n1) {
-          if (!k_ready && !ALG_T(tm0, kv_wait(kidx))) { ok = false; break; }
-          tc_fence_after();
-          issue_s(1, kidx);
-          umma_commit(&ctl->s_full[1]);
-          umma_commit(&ctl->kv_empty[kidx % C::NKV]);
-        } else {
-          umma_commit(&ctl->o_full[1]);
-        }
+        t0 += n0; t1 += n1;
       }
 #ifdef ALG_ATTN_TIMING
       if (blockIdx.x == 0 && p.stat != nullptr) {
@@ -259,47 +316,49 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int w = (warp - 2) >> 2;                  // query tile of this weight group
     const int quarter = warp & 3;                   // TMEM lanes 32*quarter.. are this warp's
     const int r = quarter * 32 + lane;              // row inside the query tile
-    const int nk = (w == 0) ? n0 : n1;
     const uint32_t lane_sel = uint32_t(quarter * 32) << 16;
-    float l = 0.f;
-    if (p.sink != nullptr) l = pow2n<LOG2N>(rho_stable(p.sink[h] * p.inv_c));
     const uint32_t s_taddr = tmem_base + lane_sel + C::S_COL + w * 128;
-    float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
     bool ok = true;
+    int tiles_before = 0;                           // score tiles of this group in earlier items
 #ifdef ALG_ATTN_TIMING
     const long long t_begin = clock64();
 #endif
-    for (int j = 0; j < nk && ok; ++j) {
-      if (!ALG_T(tm0, bw.wait(&ctl->s_full[w], j & 1u))) { ok = false; break; }
+    for (int k = 0; ok && item_at(p, k, it); ++k) {
+      const int nk = (w == 0) ? it.n0 : it.n1;
+      float l = 0.f;                                // the sink's weight, fetched while the first scores are computed
+      if (p.sink != nullptr) l = pow2n<LOG2N>(rho_stable(p.sink[it.h] * p.inv_c));
+      float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
+      for (int j = 0; j < nk && ok; ++j) {
+        if (!ALG_T(tm0, bw.wait(&ctl->s_full[w], (tiles_before + j) & 1u))) { ok = false; break; }
+        tc_fence_after();
+#ifdef ALG_ATTN_TIMING
+        const long long tc0 = clock64();
+#endif
+        if (j == nk - 1) weigh_tile<LOG2N, true>(s_taddr, r, p.scale, la, lb);   // diagonal tile: masked
+        else weigh_tile<LOG2N, false>(s_taddr, r, p.scale, la, lb);
+        tc_fence_before();
+        mbar_arrive(&ctl->p_full[w]);
+#ifdef ALG_ATTN_TIMING
+        tm1 += clock64() - tc0;
+#endif
+      }
+      tiles_before += nk;
+      if (!ok || !bw.wait(&ctl->o_full[w], k & 1u)) { ok = false; break; }
       tc_fence_after();
-#ifdef ALG_ATTN_TIMING
-      const long long tc0 = clock64();
-#endif
-      if (j == nk - 1) weigh_tile<LOG2N, true>(s_taddr, r, p.scale, la, lb);   // diagonal tile: masked
-      else weigh_tile<LOG2N, false>(s_taddr, r, p.scale, la, lb);
-      tc_fence_before();
-      mbar_arrive(&ctl->p_full[w]);
-#ifdef ALG_ATTN_TIMING
-      tm1 += clock64() - tc0;
-#endif
-    }
-#ifdef ALG_ATTN_TIMING
-    if (blockIdx.x == 0 && r == 0 && p.stat != nullptr) {
-      float* dbg = p.stat + 8 * w;
-      dbg[0] = float(tm0); dbg[1] = 0.f; dbg[2] = float(tm1); dbg[3] = float(clock64() - t_begin); dbg[4] = float(nk);
-    }
-#endif
-    l += (la.x + la.y) + (lb.x + lb.y);
-    if (ok && bw.wait(&ctl->o_full[w], 0)) {
-      tc_fence_after();
+      item_at(p, k, it);                            // recomputed: nothing of it stays live over the tile loop
+      l += (la.x + la.y) + (lb.x + lb.y);
       const float inv = 1.0f / l;
-      const int row = row0 + w * BQ + r;
-      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + b * p.os.b + h * p.os.h + int64_t(row) * p.os.t;
+      const int row = it.row0 + w * BQ + r;
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + it.b * p.os.b + it.h * p.os.h + int64_t(row) * p.os.t;
 #pragma unroll 1
       for (int chunk = 0; chunk < D / 32; ++chunk) {
         uint32_t o[32];
         tmem_ld_32x32(tmem_base + lane_sel + C::O_COL + w * D + chunk * 32, o);
         tmem_ld_wait_for(o);
+        if (chunk == D / 32 - 1) {                  // O_w is in registers: the next item may overwrite it
+          tc_fence_before();
+          mbar_arrive(&ctl->o_free[w]);
+        }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint4 val;
@@ -311,9 +370,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
 #ifndef ALG_ATTN_TIMING
-      if (p.stat != nullptr) p.stat[(int64_t(b) * p.H + h) * p.Tq + row] = inv;
+      if (p.stat != nullptr) p.stat[(int64_t(it.b) * p.H + it.h) * p.Tq + row] = inv;
 #endif
     }
+#ifdef ALG_ATTN_TIMING
+    if (blockIdx.x == 0 && r == 0 && p.stat != nullptr) {
+      float* dbg = p.stat + 8 * w;
+      dbg[0] = float(tm0); dbg[1] = 0.f; dbg[2] = float(tm1); dbg[3] = float(clock64() - t_begin); dbg[4] = float(tiles_before);
+    }
+#endif
   }
 
   tc_fence_before();
@@ -352,7 +417,11 @@ int launch_dn(const AttnParams& p, cudaStream_t stream) {
     ALG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes<D>())));
     configured = true;
   }
-  const int grid = p.B * p.H * (p.Tq / (2 * BQ));
+  int dev = 0, sms = 148;
+  ALG_CUDA_TRY(cudaGetDevice(&dev));
+  ALG_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int items = p.B * p.H * (p.Tq / (2 * BQ));
+  const int grid = items < sms ? items : sms;
   kern<<<grid, NTHREADS, smem_bytes<D>(), stream>>>(tq, tk, tv, p);
   ALG_CUDA_TRY(cudaGetLastError());
   count_launch();

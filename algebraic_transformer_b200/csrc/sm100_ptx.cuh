@@ -177,6 +177,34 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
       "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// The same two instructions with each shared-memory descriptor passed as its 32-bit halves.
+// The issuing thread's instruction count sits on the critical path between "weights ready"
+// and "next scores ready", and in this form stepping a descriptor along K is one 32-bit add
+// to the low half (the high half is a constant; see sw128_desc_lo / SW128_DESC_HI below).
+__device__ __forceinline__ void umma_f16_ss_parts(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                  uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 da, db;\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "mov.b64 da, {%1, %2};\n"
+      "mov.b64 db, {%3, %4};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n"
+      "}\n" ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_f16_ts_parts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                                  uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 db;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n"
+      "}\n" ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 // ------------------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor, 128-byte swizzle, for a tile whose rows are 128 bytes
 // (64 bf16) and whose 8-row groups are 1024 bytes apart — exactly what a TMA box of
@@ -195,6 +223,15 @@ __device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr, uint32_t
   d |= uint64_t(1) << 46;
   d |= uint64_t(2) << 61;
   return d;
+}
+
+// The halves of the same descriptor for stride byte offset 1024: low = start address >> 4
+// and leading byte offset >> 4; high = stride offset, version bit and swizzle mode, constant.
+// Adding (bytes >> 4) to the low half moves the start address (shared-memory addresses stay
+// below 2^18, so the sum never carries out of its 14 bits).
+constexpr uint32_t SW128_DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t sw128_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return (smem_addr >> 4) | ((lbo_bytes >> 4) << 16);
 }
 
 // Instruction descriptor for kind::f16 with bf16 operands and fp32 accumulation.

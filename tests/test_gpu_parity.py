@@ -138,6 +138,32 @@ def test_guarded_attention_tail(sign, with_sink, magnitude, dtype):  # test_flas
     assert rel_l2(stat, want_stat) < 5e-3
 
 
+@pytest.mark.parametrize("which", ["q", "k", "v"])
+@pytest.mark.parametrize("row", [3, 700, 1023])
+@pytest.mark.parametrize("D", [64, 128])
+def test_guard_sees_one_bad_row_anywhere(which, row, D):
+    """A single out-of-range row of q, k or v, in any work item of the tensor-core kernel
+    (which takes the guard's maxima itself), must send the whole call down the shifted path."""
+    shape = (1, 3, 1024, D)
+    q, k, v = (randn(shape, 881 + i, torch.bfloat16) for i in range(3))
+    if which == "v":
+        v[0, 1, row, 5] = 1e9                      # above the guard's bound on |v| (1e8)
+    else:
+        (q if which == "q" else k)[0, 2, row] = 300.0
+    want = R.asinh_attention(q, k, v, n=16, c=8.0)
+    qd, kd, vd = dev(q, k, v)
+    got, stat, kind = A.flash_attention(qd, kd, vd, None, kind="asinh", n=16, c=8.0, range_guard=True,
+                                        return_stat=True)
+    assert int(kind) == 2
+    assert torch.isfinite(got).all() and torch.isfinite(stat).all()
+    assert rel_l2(got, want) < 1e-2
+    # and the same tensors without the bad row stay on the unshifted path
+    q2, k2, v2 = (randn(shape, 881 + i, torch.bfloat16) for i in range(3))
+    _, _, kind2 = A.flash_attention(*dev(q2, k2, v2), None, kind="asinh", n=16, c=8.0, range_guard=True,
+                                    return_stat=True)
+    assert int(kind2) == 1
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("seq", [512, 2048])
 @pytest.mark.parametrize("impl", IMPLS)
