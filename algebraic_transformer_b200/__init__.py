@@ -3,9 +3,10 @@ reference's Python call surface.  See `ops` for the entry points and `include/al
 for the C ABI underneath."""
 
 from .ops import (cast_embedding, cayley_powers, cayley_table_geometric, decode_attention,  # noqa: F401
-                  flash_attention, flash_clamp, fused_head, head_finalize, head_statistic, qk_rms_norm)
+                  flash_attention, flash_clamp, fused_head, glu_projection, head_finalize, head_statistic,
+                  interleave_gate_up, qk_rms_norm, qkv_projection)
 from .dist import unit_shard, vocab_shard  # noqa: F401
 
 __all__ = ["flash_attention", "fused_head", "qk_rms_norm", "decode_attention", "cayley_table_geometric",
            "cayley_powers", "cast_embedding", "head_statistic", "head_finalize", "flash_clamp",
-           "vocab_shard", "unit_shard"]
+           "vocab_shard", "unit_shard", "qkv_projection", "glu_projection", "interleave_gate_up"]

@@ -35,7 +35,21 @@ class AttnArgs(C.Structure):
                 ("D", C.c_int), ("n", C.c_int), ("c", C.c_float), ("causal", C.c_int), ("variant", C.c_int),
                 ("dtype", C.c_int), ("impl", C.c_int), ("score_clamp", C.c_float),
                 ("q_stride", I64x3), ("k_stride", I64x3), ("v_stride", I64x3), ("o_stride", I64x3),
-                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p)]
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
+                ("guard_words", C.c_void_p)]
+
+
+class QkvProjArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("w", C.c_void_p), ("qkv", C.c_void_p), ("q_gain", C.c_void_p),
+                ("k_gain", C.c_void_p), ("cos", C.c_void_p), ("sin", C.c_void_p), ("eps", C.c_float),
+                ("M", C.c_int), ("d", C.c_int), ("H", C.c_int), ("D", C.c_int), ("T", C.c_int),
+                ("ld_x", C.c_int64), ("attn_c", C.c_float), ("guard", C.c_void_p), ("status", C.c_void_p)]
+
+
+class GluProjArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("w", C.c_void_p), ("out", C.c_void_p), ("M", C.c_int), ("d", C.c_int),
+                ("f", C.c_int), ("ld_x", C.c_int64), ("ld_out", C.c_int64), ("beta", C.c_float),
+                ("status", C.c_void_p)]
 
 
 class DecodeArgs(C.Structure):
@@ -81,6 +95,8 @@ SYMBOLS = {
     "alg_head_finalize": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_int,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "alg_cast_f32_to_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "alg_qkv_proj_fwd": (C.c_int, [C.POINTER(QkvProjArgs), C.c_void_p]),
+    "alg_glu_proj_fwd": (C.c_int, [C.POINTER(GluProjArgs), C.c_void_p]),
     "alg_selftest_bounded_wait": (C.c_int, [C.c_void_p, C.c_ulonglong, C.c_void_p, C.c_void_p]),
     "alg_rms_norm_fwd":(C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_void_p]),
     "alg_alu_glu_fwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int64, C.c_int64, C.c_float,

@@ -118,8 +118,11 @@ int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
   const bool prologue = attn_has_prologue(a);
   if (prologue && ((a->cos == nullptr) != (a->sin == nullptr))) { set_error("attention: cos and sin tables come as a pair"); return ALG_ERR_INVALID; }
   if (prologue && a->Tq != a->Tk) { set_error("attention: the fused QK prologue needs Tq == Tk"); return ALG_ERR_INVALID; }
+  const bool guard_given = a->guard_words != nullptr && a->variant == ALG_VARIANT_GUARD;
+  if (guard_given && prologue) { set_error("attention: guard_words describe ready-made q, k, v; not with the fused prologue"); return ALG_ERR_INVALID; }
+  if (guard_given && !aligned16(a->guard_words)) { set_error("attention: guard_words must be 16-byte aligned"); return ALG_ERR_INVALID; }
   const size_t need = alg_attn_workspace_bytes(a);
-  const bool need_ws = prologue || a->variant == ALG_VARIANT_GUARD;
+  const bool need_ws = prologue || (a->variant == ALG_VARIANT_GUARD && !guard_given);
   if (need_ws && (a->workspace == nullptr || a->workspace_bytes < need || !aligned16(a->workspace))) {
     set_error("attention: workspace of %zu bytes (16-byte aligned) required, got %zu", need, a->workspace_bytes);
     return ALG_ERR_WORKSPACE;
@@ -147,7 +150,7 @@ int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
   p.score_clamp = a->score_clamp > 0.0f ? a->score_clamp : __int_as_float_host(0x7f800000);
 
   unsigned char* ws = static_cast<unsigned char*>(a->workspace);
-  GuardWords* guard = reinterpret_cast<GuardWords*>(ws);
+  GuardWords* guard = guard_given ? static_cast<GuardWords*>(const_cast<void*>(a->guard_words)) : reinterpret_cast<GuardWords*>(ws);
   const bool guarded = a->variant == ALG_VARIANT_GUARD;
   if (guarded) {
     // src/algebraic/kernels/flash.py:744-748, 840-849
@@ -158,9 +161,9 @@ int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
     p.guard_bound_sq = float((bound / 1.01) * (bound / 1.01));
     p.guard_sink_bound = float(bound / 1.01);
     p.guard_vmax = float(fmin(1e8, 1e37 / ((double(a->Tk) + (a->sink ? 1 : 0)) * pow(2 * bound + 1, a->n))));
-    ALG_CUDA_TRY(cudaMemsetAsync(guard, 0, sizeof(GuardWords), stream));
+    if (!guard_given) ALG_CUDA_TRY(cudaMemsetAsync(guard, 0, sizeof(GuardWords), stream));
   }
-  if (prologue || guarded) {
+  if (prologue || (guarded && !guard_given)) {
     const size_t es = elem_size(a->dtype);
     void* qn = ws + 256;
     void* kn = ws + 256 + align256(size_t(a->B) * a->H * a->Tq * a->D * es);
@@ -210,6 +213,54 @@ int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
   }
   p.run_if = 0;
   return launch_attn_mma(p, a->dtype, stream);
+}
+
+int alg_qkv_proj_fwd(const alg_qkv_proj_args* a, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a == nullptr || a->x == nullptr || a->w == nullptr || a->qkv == nullptr || a->cos == nullptr || a->sin == nullptr) {
+    set_error("qkv_proj: null argument");
+    return ALG_ERR_INVALID;
+  }
+  if (a->M < 0 || a->H < 1 || a->T < 1 || (a->D != 64 && a->D != 128) || a->d < 64 || a->d % 64 != 0 || a->ld_x < a->d ||
+      a->ld_x % 8 != 0 || !(a->eps > 0.0f) || !(a->attn_c > 0.0f)) {
+    set_error("qkv_proj: head_dim 64 or 128, d a multiple of 64, row stride a multiple of 8 and >= d, eps and c positive");
+    return ALG_ERR_INVALID;
+  }
+  if (!aligned16(a->x) || !aligned16(a->w) || !aligned16(a->qkv) || !aligned16(a->cos) || !aligned16(a->sin) ||
+      (a->guard != nullptr && !aligned16(a->guard)) || (a->q_gain != nullptr && !aligned16(a->q_gain)) ||
+      (a->k_gain != nullptr && !aligned16(a->k_gain))) {
+    set_error("qkv_proj: 16-byte alignment required");
+    return ALG_ERR_INVALID;
+  }
+  ProjParams p{};
+  p.M = a->M; p.K = a->d; p.N = 3 * a->H * a->D; p.ld_x = a->ld_x;
+  p.out = static_cast<__nv_bfloat16*>(a->qkv); p.ld_out = p.N;
+  p.q_gain = a->q_gain; p.k_gain = a->k_gain;
+  p.cos = static_cast<const __nv_bfloat16*>(a->cos); p.sin = static_cast<const __nv_bfloat16*>(a->sin);
+  p.H = a->H; p.D = a->D; p.T = a->T; p.eps = a->eps;
+  p.q_scale = float(1.0 / (sqrt(double(a->D)) * double(a->attn_c)));
+  p.guard = static_cast<GuardWords*>(a->guard);
+  p.status = a->status;
+  if (a->M == 0) return ALG_OK;
+  if (p.guard != nullptr) ALG_CUDA_TRY(cudaMemsetAsync(p.guard, 0, sizeof(GuardWords), stream));
+  return launch_proj(p, a->x, a->w, 0, stream);
+}
+
+int alg_glu_proj_fwd(const alg_glu_proj_args* a, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a == nullptr || a->x == nullptr || a->w == nullptr || a->out == nullptr) { set_error("glu_proj: null argument"); return ALG_ERR_INVALID; }
+  if (a->M < 0 || a->f < 128 || a->f % 128 != 0 || a->d < 64 || a->d % 64 != 0 || a->ld_x < a->d || a->ld_x % 8 != 0 ||
+      a->ld_out < a->f || a->ld_out % 8 != 0) {
+    set_error("glu_proj: f a multiple of 128, d a multiple of 64, row strides multiples of 8 and wide enough");
+    return ALG_ERR_INVALID;
+  }
+  if (!aligned16(a->x) || !aligned16(a->w) || !aligned16(a->out)) { set_error("glu_proj: 16-byte alignment required"); return ALG_ERR_INVALID; }
+  ProjParams p{};
+  p.M = a->M; p.K = a->d; p.N = 2 * a->f; p.ld_x = a->ld_x;
+  p.out = static_cast<__nv_bfloat16*>(a->out); p.ld_out = a->ld_out;
+  p.f = a->f; p.beta = a->beta; p.D = 64;
+  p.status = a->status;
+  return launch_proj(p, a->x, a->w, 1, stream);
 }
 
 size_t alg_decode_workspace_bytes(const alg_decode_args* a) {

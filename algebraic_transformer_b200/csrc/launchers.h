@@ -69,6 +69,27 @@ __device__ __forceinline__ bool attn_use_shift(const AttnParams& p) {
   return !ok;
 }
 
+// ---- proj_sm100.cu: projection GEMMs with fused epilogues -------------------------------
+struct ProjParams {
+  int M, K, N;             // activations (M, K), weights (N, K), both K-major bf16
+  int64_t ld_x;
+  __nv_bfloat16* out;
+  int64_t ld_out;
+  // QKV epilogue
+  const float* q_gain;
+  const float* k_gain;
+  const __nv_bfloat16* cos;
+  const __nv_bfloat16* sin;
+  int H, D, T;
+  float eps, q_scale;
+  GuardWords* guard;
+  // GLU epilogue
+  int f;
+  float beta;
+  int* status;
+};
+int launch_proj(const ProjParams& p, const void* x, const void* w, int epi, cudaStream_t stream);   // epi 0 QKV, 1 GLU
+
 // ---- decode -------------------------------------------------------------------------
 struct DecodeParams {
   const void* q;

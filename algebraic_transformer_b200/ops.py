@@ -166,6 +166,68 @@ def alu_glu(gate: torch.Tensor, up: torch.Tensor, beta: float = 0.5, out=None) -
     return y
 
 
+def qkv_projection(x: torch.Tensor, w: torch.Tensor, n_heads: int, seq_len: int, cos: torch.Tensor,
+                   sin: torch.Tensor, q_gain: Optional[torch.Tensor] = None, k_gain: Optional[torch.Tensor] = None,
+                   eps: float = 1e-5, attn_c: float = 8.0, guard_words: Optional[torch.Tensor] = None,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The q, k, v projections of a block with the QK-norm, the Cayley rotation and the range
+    guard's maxima fused into the GEMM (src/algebraic/model.py:165-174).
+
+    x: (M, d) bf16 rows in (batch, position) order, position = row % seq_len.  w: (3*H*D, d) bf16,
+    one row per output feature (q heads, k heads, v heads).  cos, sin: (>= seq_len, D/2) bf16.
+    Returns (M, 3*H*D) bf16: q and k normalised and rotated, v as projected.  `guard_words`
+    (4 int32, device) receives the maxima for `flash_attention(..., guard_words=...)`."""
+    _require_cuda(x, w, cos, sin, q_gain, k_gain, guard_words)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.ndim != 2 or w.ndim != 2 or x.stride(1) != 1:
+        raise ValueError("qkv_projection needs bf16 (M, d) activations and (3*H*D, d) weights")
+    M, d = x.shape
+    if w.shape[1] != d or w.shape[0] % (3 * n_heads) or not w.is_contiguous():
+        raise ValueError("weights must be contiguous (3*H*D, d)")
+    D = w.shape[0] // (3 * n_heads)
+    if cos.dtype != torch.bfloat16 or sin.dtype != torch.bfloat16 or cos.shape != sin.shape or cos.shape[1] != D // 2 \
+            or cos.shape[0] < seq_len or not cos.is_contiguous() or not sin.is_contiguous():
+        raise ValueError("rotation tables must be contiguous bf16 (>= seq_len, D/2)")
+    for t in (q_gain, k_gain):
+        if t is not None and (t.dtype != torch.float32 or t.shape != (D,)):
+            raise ValueError("q_gain / k_gain must be float32 of shape (D,)")
+    if guard_words is not None and (guard_words.dtype != torch.int32 or guard_words.numel() < 4):
+        raise ValueError("guard_words must hold 4 int32")
+    y = torch.empty((M, w.shape[0]), dtype=torch.bfloat16, device=x.device) if out is None else out
+    if not y.is_contiguous() or y.shape != (M, w.shape[0]):
+        raise ValueError("out must be contiguous (M, 3*H*D)")
+    a = L.QkvProjArgs(x=x.data_ptr(), w=w.data_ptr(), qkv=y.data_ptr(), q_gain=_ptr(q_gain), k_gain=_ptr(k_gain),
+                      cos=cos.data_ptr(), sin=sin.data_ptr(), eps=float(eps), M=M, d=d, H=n_heads, D=D, T=int(seq_len),
+                      ld_x=x.stride(0), attn_c=float(attn_c), guard=_ptr(guard_words), status=None)
+    L.check(L.load().alg_qkv_proj_fwd(a, _stream()))
+    return y
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """(f, d) gate and up weights (one row per output feature) -> the (2f, d) row order
+    `glu_projection` expects: blocks of 128 gate rows and the matching 128 up rows in turn."""
+    f, d = w_gate.shape
+    if w_up.shape != (f, d) or f % 128:
+        raise ValueError("gate and up weights must both be (f, d) with f a multiple of 128")
+    return torch.stack([w_gate.reshape(f // 128, 128, d), w_up.reshape(f // 128, 128, d)], dim=1).reshape(2 * f, d).contiguous()
+
+
+def glu_projection(x: torch.Tensor, w: torch.Tensor, beta: float = 0.5, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """gate * alu(up, beta) with gate = x @ w_g and up = x @ w_u computed by the same kernel
+    (src/algebraic/model.py:184-193); `w` comes from `interleave_gate_up`.  x: (M, d) bf16."""
+    _require_cuda(x, w)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.ndim != 2 or w.ndim != 2 or x.stride(1) != 1:
+        raise ValueError("glu_projection needs bf16 (M, d) activations and (2f, d) weights")
+    M, d = x.shape
+    if w.shape[1] != d or w.shape[0] % 256 or not w.is_contiguous():
+        raise ValueError("weights must be contiguous (2f, d) with f a multiple of 128")
+    f = w.shape[0] // 2
+    y = torch.empty((M, f), dtype=torch.bfloat16, device=x.device) if out is None else out
+    a = L.GluProjArgs(x=x.data_ptr(), w=w.data_ptr(), out=y.data_ptr(), M=M, d=d, f=f, ld_x=x.stride(0),
+                      ld_out=y.stride(0), beta=float(beta), status=None)
+    L.check(L.load().alg_glu_proj_fwd(a, _stream()))
+    return y
+
+
 # ------------------------------------------------------------------------ attention
 
 def flash_clamp(seq_len: int, n: int) -> float:
@@ -183,7 +245,7 @@ def flash_attention(q, k, v, sink_logit=None, *, kind: str = "softmax", n: int =
                     head_resident: Optional[bool] = None,
                     q_gain=None, k_gain=None, cos=None, sin=None, eps: float = 1e-5,
                     causal: bool = True, return_stat: bool = False, impl: str = "auto", out=None,
-                    bounded_scores: bool = False):
+                    bounded_scores: bool = False, guard_words: Optional[torch.Tensor] = None):
     """Causal asinh-power attention on (B,H,T,D); `sink_logit` broadcastable to (H,).
 
     Same keywords as the reference entry point.  TPU tiling/residency knobs (`block*`,
@@ -192,7 +254,9 @@ def flash_attention(q, k, v, sink_logit=None, *, kind: str = "softmax", n: int =
     `q_gain/k_gain/cos/sin/eps` run the QK-norm + Cayley rotation of the layer in front of
     the attention inside the same call; `return_stat=True` also returns the per-row
     statistic and which kind it is; `impl` forces a kernel family ("auto", "mma",
-    "tcgen05").  `kind="softmax"` (the reference's control arm) is not built."""
+    "tcgen05"); `guard_words` hands a guarded call the maxima `qkv_projection` took for these
+    very q, k, v, so that it skips its own pass over them.  `kind="softmax"` (the reference's
+    control arm) is not built."""
     _require_cuda(q, k, v)
     if kind == "softmax":
         raise NotImplementedError("only the algebraic (kind='asinh') arm is built for B200")
@@ -256,7 +320,8 @@ def flash_attention(q, k, v, sink_logit=None, *, kind: str = "softmax", n: int =
                    cos=_ptr(cos), sin=_ptr(sin), eps=float(eps), B=B, H=H, Tq=T, Tk=Tk, D=D, n=int(n),
                    c=float(c), causal=int(bool(causal)), variant=variant, dtype=_DTYPES[q.dtype],
                    impl=L.IMPL[impl], score_clamp=float(score_clamp), q_stride=_strides3(q),
-                   k_stride=_strides3(k), v_stride=_strides3(v), o_stride=_strides3(o))
+                   k_stride=_strides3(k), v_stride=_strides3(v), o_stride=_strides3(o),
+                   guard_words=_ptr(guard_words))
     lib = L.load()
     ws = _workspace(q.device, lib.alg_attn_workspace_bytes(a), "attn")
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()

@@ -81,15 +81,22 @@ def init_params(cfg: PrefillConfig, seed: int = 0, device="cpu"):
     }
 
 
-def cast_params(params, device):
-    """bf16 copies of the matrices (the reference casts at use, model.py:167), fp32 gains."""
+def cast_params(params, device, fused_proj: bool = False):
+    """bf16 copies of the matrices (the reference casts at use, model.py:167), fp32 gains.
+    `fused_proj` lays the q|k|v and gate|up weights out for `ops.qkv_projection` /
+    `ops.glu_projection` instead of for a plain GEMM."""
     out = {}
     for k, v in params.items():
         v = v.to(device)
         out[k] = v.bfloat16().contiguous() if k.startswith("w_") or k == "embed" else v.float().contiguous()
     # q, k, v projections share their input: one GEMM with the concatenated weight
-    out["w_qkv"] = torch.cat([out["w_q"], out["w_k"], out["w_v"]], dim=2).contiguous()
-    out["w_gu"] = torch.cat([out["w_g"], out["w_u"]], dim=2).contiguous()
+    if fused_proj:
+        # one row per output feature (K-major), gate/up rows interleaved in blocks of 128
+        out["w_qkv_t"] = torch.cat([out["w_q"], out["w_k"], out["w_v"]], dim=2).transpose(1, 2).contiguous()
+        out["w_gu_t"] = torch.stack([ops.interleave_gate_up(g.t(), u.t()) for g, u in zip(out["w_g"], out["w_u"])])
+    else:
+        out["w_qkv"] = torch.cat([out["w_q"], out["w_k"], out["w_v"]], dim=2).contiguous()
+        out["w_gu"] = torch.cat([out["w_g"], out["w_u"]], dim=2).contiguous()
     for k in ("w_q", "w_k", "w_v", "w_g", "w_u"):        # only the fused copies are used
         del out[k]
     return out
@@ -98,11 +105,20 @@ def cast_params(params, device):
 class Prefill:
     """Forward pass of one rank: `hidden(tokens)` and `loss(tokens, targets)`."""
 
-    def __init__(self, cfg: PrefillConfig, params, device, seq_len: int, impl: str = "auto", exchange=None):
+    def __init__(self, cfg: PrefillConfig, params, device, seq_len: int, impl: str = "auto", exchange=None,
+                 fused_proj: Optional[bool] = None):
         self.cfg, self.device, self.impl = cfg, torch.device(device), impl
         self.exchange = exchange        # dist.HeadExchange: fuse the head's cross-GPU sum into its last kernel
-        self.p = cast_params(params, self.device)
+        # The projections with their consumers fused in (ops.qkv_projection / glu_projection)
+        # cover the production shapes; anything else takes library GEMMs + separate kernels.
+        can_fuse = cfg.head_dim in (64, 128) and cfg.d_model % 64 == 0 and cfg.d_ff % 128 == 0 and impl != "mma"
+        if fused_proj and not can_fuse:
+            raise ValueError("fused projections need head_dim 64/128, d_model % 64 == 0, d_ff % 128 == 0")
+        self.fused_proj = can_fuse if fused_proj is None else bool(fused_proj)
+        self.p = cast_params(params, self.device, self.fused_proj)
         self.cos, self.sin = ops.cayley_table_geometric(cfg.head_dim, seq_len, cfg.rope_base, device=self.device)
+        self.cos_lp, self.sin_lp = self.cos.bfloat16().contiguous(), self.sin.bfloat16().contiguous()
+        self.guard_words = torch.zeros(4, dtype=torch.int32, device=self.device)
 
     def hidden(self, tokens: torch.Tensor) -> torch.Tensor:
         """Final normalised hidden states (B, T, d) in bf16 (model.forward_hidden, model.py:196-208)."""
@@ -113,6 +129,17 @@ class Prefill:
         attn_out = torch.empty((B, T, H, D), dtype=torch.bfloat16, device=self.device)
         for layer in range(cfg.n_layers):
             h = ops.rms_norm(x, p["ln1"][layer], cfg.eps)
+            if self.fused_proj:
+                qkv = ops.qkv_projection(h, p["w_qkv_t"][layer], H, T, self.cos_lp, self.sin_lp, p["q_gain"][layer],
+                                         p["k_gain"][layer], cfg.eps, cfg.attn_c, self.guard_words).view(B, T, 3, H, D)
+                q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))      # (B,H,T,D) views
+                ops.flash_attention(q, k, v, p["sink"][layer], kind="asinh", n=cfg.attn_n, c=cfg.attn_c, block=T,
+                                    range_guard=True, impl=self.impl, guard_words=self.guard_words,
+                                    out=attn_out.transpose(1, 2))
+                x = torch.addmm(x, attn_out.view(B * T, d), p["w_o"][layer])
+                h2 = ops.rms_norm(x, p["ln2"][layer], cfg.eps)
+                x = torch.addmm(x, ops.glu_projection(h2, p["w_gu_t"][layer], cfg.alu_beta), p["w_d"][layer])
+                continue
             qkv = torch.mm(h, p["w_qkv"][layer]).view(B, T, 3, H, D)
             q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))          # (B,H,T,D) views
             ops.flash_attention(q, k, v, p["sink"][layer], kind="asinh", n=cfg.attn_n, c=cfg.attn_c, block=T,

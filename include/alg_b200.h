@@ -129,6 +129,9 @@ typedef struct {
   void* workspace;
   size_t workspace_bytes;
   int* status;             /* device int, may be NULL */
+  const void* guard_words; /* NULL, or the 16 bytes alg_qkv_proj_fwd filled for these very q, k, v:
+                              a guarded call then skips its own statistics pass (not together
+                              with the fused prologue) */
 } alg_attn_args;
 
 ALG_API size_t alg_attn_workspace_bytes(const alg_attn_args* args);
@@ -266,6 +269,52 @@ ALG_API int alg_head_finalize(const float* l, const float* zt, int N, int n, flo
 ALG_API int alg_rms_norm_fwd(const void* x, const float* gain, void* y, int64_t rows, int d, float eps, void* stream);
 ALG_API int alg_alu_glu_fwd(const void* gate, const void* up, void* out, int64_t rows, int f, int64_t ld_in,
                             int64_t ld_out, float beta, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * The two wide projections of a prefill block, each one tcgen05 GEMM whose consumer runs in
+ * the epilogue on the accumulator tile (bf16 in / out, fp32 accumulation).
+ * alg_qkv_proj_fwd replaces, in model._block (src/algebraic/model.py:165-174): the three
+ *   projections h @ w_q, h @ w_k, h @ w_v, the QK RMS-norm (model._qk_norm, algebraic.py:76-83)
+ *   and apply_rotary (algebraic.py:172-179); it also takes the range guard's maxima
+ *   (src/algebraic/kernels/flash.py:831-849) so that alg_attn_fwd(guard_words) need not.
+ *   x: (M, d) bf16, row stride ld_x; row m is position m % T of its sequence.
+ *   w: (3*H*D, d) bf16 contiguous, one row per output feature: q heads, k heads, v heads.
+ *   qkv: (M, 3*H*D) bf16 contiguous out.  cos, sin: (T, D/2) bf16 (the reference casts its
+ *   tables to the compute dtype).  q_gain, k_gain: (D) fp32 or NULL.  D = 64 or 128,
+ *   d a multiple of 64.  guard: 16 device bytes (zeroed here, then maximised) or NULL.
+ * alg_glu_proj_fwd replaces the FFN's gate = h2 @ w_g, up = h2 @ w_u and gate * alu(up, beta)
+ *   (src/algebraic/model.py:184-193, algebraic.py:86-105).
+ *   w: (2*f, d) bf16 contiguous with the rows interleaved in blocks of 128: gate features
+ *   0..127, up features 0..127, gate 128..255, up 128..255, ...; f a multiple of 128.
+ *   out: (M, f) bf16 with row stride ld_out.
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  const void* x;
+  const void* w;
+  void* qkv;
+  const float* q_gain;
+  const float* k_gain;
+  const void* cos;
+  const void* sin;
+  float eps;
+  int M, d, H, D, T;
+  int64_t ld_x;
+  float attn_c;            /* q is scaled by 1 / (sqrt(D) attn_c) for the guard's statistic */
+  void* guard;
+  int* status;             /* device int, may be NULL */
+} alg_qkv_proj_args;
+ALG_API int alg_qkv_proj_fwd(const alg_qkv_proj_args* args, void* stream);
+
+typedef struct {
+  const void* x;
+  const void* w;
+  void* out;
+  int M, d, f;
+  int64_t ld_x, ld_out;
+  float beta;
+  int* status;             /* device int, may be NULL */
+} alg_glu_proj_args;
+ALG_API int alg_glu_proj_fwd(const alg_glu_proj_args* args, void* stream);
 
 /* Failure-detection self-test (no counterpart in the reference).  Launches a one-CTA kernel
  * whose threads wait, through the same bounded-wait helper every TMA/tcgen05 kernel here

@@ -49,8 +49,62 @@ def test_alu_glu():
     assert torch.equal(got2, got)
 
 
+def _mm(a, w):                                           # bf16 x bf16 -> fp32 accumulate -> bf16
+    return (a.float() @ w.float()).bfloat16()
+
+
+@pytest.mark.parametrize("H,D,B,T", [(6, 64, 2, 256), (2, 128, 1, 200), (12, 64, 1, 128)])
+def test_qkv_projection_fused_epilogue(H, D, B, T):
+    """Projection + QK-norm + rotation + guard maxima in one kernel (model.py:165-174) against the
+    same steps of the oracle; d = H*D gives a ragged last weight tile for H=6 and a row count
+    that is not a multiple of the tile for T=200."""
+    d = H * D
+    g = torch.Generator().manual_seed(7 + H)
+    x = torch.randn((B * T, d), generator=g).bfloat16()
+    wq, wk, wv = ((torch.randn((d, d), generator=g) * 0.05).bfloat16() for _ in range(3))
+    qg, kg = (0.75 + 0.5 * torch.rand(D, generator=g) for _ in range(2))
+    cos, sin = R.cayley_table_geometric(D, T)
+    heads = lambda y: y.reshape(B, T, H, D).transpose(1, 2)
+    want_q = R.apply_rotary(R.rms_norm(heads(_mm(x, wq)), qg, 1e-5), cos, sin)
+    want_k = R.apply_rotary(R.rms_norm(heads(_mm(x, wk)), kg, 1e-5), cos, sin)
+    want_v = heads(_mm(x, wv))
+    w = torch.cat([wq, wk, wv], dim=1).t().contiguous()                  # (3d, d): one row per feature
+    words = torch.zeros(4, dtype=torch.int32, device=DEV)
+    got = A.qkv_projection(x.to(DEV), w.to(DEV), H, T, cos.bfloat16().to(DEV), sin.bfloat16().to(DEV),
+                           qg.to(DEV), kg.to(DEV), 1e-5, 8.0, words).view(B, T, 3, H, D)
+    q, k, v = (got[:, :, i].transpose(1, 2).cpu() for i in range(3))
+    assert rel_l2(q, want_q) < 6e-3 and rel_l2(k, want_k) < 6e-3 and rel_l2(v, want_v) < 4e-3
+    # the guard maxima of exactly what was written
+    stats = words.cpu().view(torch.float32)
+    qs = (q.float() * (1.0 / (D ** 0.5 * 8.0))).bfloat16().float()
+    np.testing.assert_allclose(float(stats[0]), float((qs * qs).sum(-1).max()), rtol=1e-4)
+    np.testing.assert_allclose(float(stats[1]), float((k.float() ** 2).sum(-1).max()), rtol=1e-4)
+    assert float(stats[2]) == float(v.float().abs().max())
+    # and the attention that consumes them agrees with the one that takes its own maxima
+    qd, kd, vd = (got[:, :, i].transpose(1, 2) for i in range(3))
+    if T % 8 == 0:
+        a1 = A.flash_attention(qd, kd, vd, None, kind="asinh", n=16, c=8.0, block=T, range_guard=True, guard_words=words)
+        a2 = A.flash_attention(qd, kd, vd, None, kind="asinh", n=16, c=8.0, block=T, range_guard=True)
+        assert torch.equal(a1, a2)
+
+
+@pytest.mark.parametrize("M,d,f", [(300, 384, 256), (1024, 256, 1024)])
+def test_glu_projection_fused_epilogue(M, d, f):
+    """gate/up projections + gate * alu(up) in one kernel (model.py:184-193)."""
+    g = torch.Generator().manual_seed(f)
+    x = torch.randn((M, d), generator=g).bfloat16()
+    wg = (torch.randn((d, f), generator=g) * 0.05).bfloat16()
+    wu = (torch.randn((d, f), generator=g) * 0.4).bfloat16()
+    want = (_mm(x, wg).float() * R.alu(_mm(x, wu), 0.5).float()).bfloat16()
+    w = A.interleave_gate_up(wg.t().contiguous(), wu.t().contiguous())
+    got = A.glu_projection(x.to(DEV), w.to(DEV), 0.5).cpu()
+    assert got.shape == (M, f)
+    assert rel_l2(got, want) < 6e-3
+
+
+@pytest.mark.parametrize("fused", [True, False])
 @pytest.mark.parametrize("head_dim,T", [(64, 256), (128, 512)])
-def test_tiny_prefill_matches_reference_model(head_dim, T):
+def test_tiny_prefill_matches_reference_model(head_dim, T, fused):
     cfg = P.PrefillConfig(vocab_size=1000, d_model=2 * head_dim, n_layers=2, n_heads=2, d_ff=256)
     params = P.init_params(cfg, seed=0)
     g = torch.Generator().manual_seed(1)
@@ -60,7 +114,7 @@ def test_tiny_prefill_matches_reference_model(head_dim, T):
     tokens = torch.randint(0, cfg.vocab_size, (2, T), generator=g)
     want_h = M.forward_hidden(params, tokens, cfg)
     obj_w, pt_w = M.head_loss(params, want_h, tokens, cfg)
-    model = P.Prefill(cfg, params, DEV, seq_len=T)
+    model = P.Prefill(cfg, params, DEV, seq_len=T, fused_proj=fused)
     got_h = model.hidden(tokens.to(DEV))
     assert rel_l2(got_h, want_h) < 2e-2                  # two layers of bf16 activations
     obj, pt, nll = model.loss(tokens.to(DEV), tokens.to(DEV), want_nll=True)
