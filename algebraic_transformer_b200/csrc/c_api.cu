@@ -239,6 +239,10 @@ int alg_qkv_proj_fwd(const alg_qkv_proj_args* a, void* stream_) {
   p.cos = static_cast<const __nv_bfloat16*>(a->cos); p.sin = static_cast<const __nv_bfloat16*>(a->sin);
   p.H = a->H; p.D = a->D; p.T = a->T; p.eps = a->eps;
   p.q_scale = float(1.0 / (sqrt(double(a->D)) * double(a->attn_c)));
+  {
+    int e = 0;
+    p.q_scale_pow2 = (frexpf(p.q_scale, &e) == 0.5f && e > -60) ? 1 : 0;
+  }
   p.guard = static_cast<GuardWords*>(a->guard);
   p.status = a->status;
   if (a->M == 0) return ALG_OK;

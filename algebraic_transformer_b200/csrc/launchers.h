@@ -82,6 +82,7 @@ struct ProjParams {
   const __nv_bfloat16* sin;
   int H, D, T;
   float eps, q_scale;
+  int q_scale_pow2;        // q_scale is an exact power of two (scaling then commutes with rounding)
   GuardWords* guard;
   // GLU epilogue
   int f;

@@ -16,7 +16,11 @@
 // feeds a 4-stage shared-memory ring with TMA (128x64 activation tiles, 256x64 weight tiles,
 // 128-byte swizzle), warp 1 (one lane) issues tcgen05.mma 128x256x16 into one of two 256-column
 // TMEM accumulators, warps 2..9 drain the finished accumulator (thread = row) while the other
-// one fills.  Every wait is bounded; a wait that runs out sets ALG_DEV_TIMEOUT.
+// one fills.  The epilogues keep values as packed bf16 pairs wherever the reference's
+// arithmetic is bf16 (one conversion or one HMUL2/HADD2 per two elements) and keep the next
+// tensor-memory load in flight while the current chunk is worked on: with K of only 768..1536
+// the accumulator turns over every few microseconds and the epilogue is what has to keep up.
+// Every wait is bounded; a wait that runs out sets ALG_DEV_TIMEOUT.
 #include <cuda_bf16.h>
 
 #include "common.cuh"
@@ -39,137 +43,179 @@ struct __align__(16) Control {
   uint32_t tmem_base;
   int abort_flag;
 };
-constexpr size_t SMEM_BYTES = size_t(STAGES) * STAGE_BYTES + sizeof(Control) + 1024;
+// ring | control | one 4 KB output staging buffer per epilogue warp | slack to align the base
+constexpr int WARP_STAGE_BYTES = 32 * 128;
+constexpr size_t STAGE_OFF = size_t(STAGES) * STAGE_BYTES + 256;
+constexpr size_t SMEM_BYTES = STAGE_OFF + 8 * WARP_STAGE_BYTES + 1024;
+static_assert(sizeof(Control) <= 256, "control block outgrew its slot");
+static_assert(SMEM_BYTES + 1024 <= 232448, "shared memory budget (dynamic + the static gain table)");
 
 enum { EPI_QKV = 0, EPI_GLU = 1 };
 
-__device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 __device__ __forceinline__ __nv_bfloat162 as_bf162(uint32_t u) { return *reinterpret_cast<__nv_bfloat162*>(&u); }
 __device__ __forceinline__ uint32_t as_u32(__nv_bfloat162 h) { return *reinterpret_cast<uint32_t*>(&h); }
+// the two bf16 of a packed pair as fp32 (exact)
+__device__ __forceinline__ float pair_lo(uint32_t pk) { return __uint_as_float(pk << 16); }
+__device__ __forceinline__ float pair_hi(uint32_t pk) { return __uint_as_float(pk & 0xffff0000u); }
 
-// ---- QKV epilogue: one head (D columns starting at TMEM column `tcol`) of one row ---------
+// Where a warp's 32 rows of output go: its 4 KB staging buffer in shared memory, the global
+// address of (its first row, column 0 of the tile's output) and how many of its rows exist.
+struct WarpOut {
+  unsigned char* stage;
+  __nv_bfloat16* base;
+  int64_t ld;
+  int rows;
+};
+
+// 64 consecutive output elements (32 packed pairs) of this thread's row, starting at column
+// `col` -> global memory by way of the staging buffer.  Thread-per-row stores would hit 32
+// different 128-byte lines with 16 bytes each per instruction, and that request rate, not the
+// math, bounded these kernels; staged, every store instruction writes four whole lines.  The
+// 16-byte chunks are XOR-swizzled by row so that both the row-wise writes and the line-wise
+// reads are free of bank conflicts.  Only this warp touches its buffer: __syncwarp suffices.
+__device__ __forceinline__ void store_rows64(const WarpOut& w, int lane, const uint32_t* v, int col) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c)
+    *reinterpret_cast<uint4*>(w.stage + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+        make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+  __syncwarp();
+  const int sub = lane >> 3, ch = lane & 7;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int r = 4 * k + sub;
+    const uint4 val = *reinterpret_cast<const uint4*>(w.stage + r * 128 + ((ch ^ (r & 7)) << 4));
+    if (r < w.rows) *reinterpret_cast<uint4*>(w.base + int64_t(r) * w.ld + col + ch * 8) = val;
+  }
+  __syncwarp();
+}
+
+// ---- QKV epilogue: one head (D accumulator columns from `taddr`) of one row ----------------
 // kind 0 = q, 1 = k (normalise, rotate, statistic), 2 = v (round, statistic).
+// `tc`, `ts`: this row's cos / sin table entries as packed bf16 pairs (D/4 each), in registers.
 template <int D>
-__device__ __forceinline__ void qkv_head(const ProjParams& p, const float* s_gain, uint32_t taddr, int kind, int t,
-                                         __nv_bfloat16* dst, bool store, float& best_q, float& best_k, float& best_v) {
-  constexpr int HALF = D / 2;
-  if (kind == 2) {
-#pragma unroll 1
+__device__ __forceinline__ void qkv_head(const ProjParams& p, const float* s_gain, uint32_t taddr, int kind,
+                                         const uint32_t* tc, const uint32_t* ts, const WarpOut& wo, int lane, int col,
+                                         bool live, float& best_q, float& best_k, float& best_v) {
+  constexpr int NP = D / 2, QP = D / 4;                // packed pairs per head / per half
+  uint32_t pk[NP];                                     // the projection rounded to bf16 (the GEMM's output dtype)
+  float ss = 0.f;
+  __nv_bfloat162 vmax2 = as_bf162(0u);
+  {
+    // two chunks in flight for D = 64; for D = 128 the table already holds 64 registers, so one
+    constexpr bool DOUBLE = (D == 64);
+    uint32_t a[32], b[DOUBLE ? 32 : 1];
+    tmem_ld_32x32(taddr, a);
+#pragma unroll
     for (int c = 0; c < D / 32; ++c) {
-      uint32_t r[32];
-      tmem_ld_32x32(taddr + c * 32, r);
-      tmem_ld_wait();
-      uint32_t pk[16];
-      float m = 0.f;
+      uint32_t* cur = (DOUBLE && (c & 1)) ? b : a;
+      uint32_t* nxt = (DOUBLE && !(c & 1)) ? b : a;
+      tmem_ld_wait_for(cur);
+      if (DOUBLE && c + 1 < D / 32) tmem_ld_32x32(taddr + (c + 1) * 32, nxt);
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        pk[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-        m = fmaxf(m, fmaxf(fabsf(__uint_as_float(pk[i] << 16)), fabsf(__uint_as_float(pk[i] & 0xffff0000u))));
+        const uint32_t w = pack_bf16(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1]));
+        pk[c * 16 + i] = w;
+        if (kind == 2) {
+          vmax2 = __hmax2(vmax2, __habs2(as_bf162(w)));
+        } else {
+          const float lo = pair_lo(w), hi = pair_hi(w);
+          ss = fmaf(lo, lo, ss);
+          ss = fmaf(hi, hi, ss);
+        }
       }
-      if (store) {
-        best_v = fmaxf(best_v, m);
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
-      }
+      if (!DOUBLE && c + 1 < D / 32) tmem_ld_32x32(taddr + (c + 1) * 32, a);
     }
+  }
+  if (kind == 2) {
+    if (live) {
+      const float2 m = __bfloat1622float2(vmax2);
+      best_v = fmaxf(best_v, fmaxf(m.x, m.y));
+    }
+#pragma unroll
+    for (int h64 = 0; h64 < D / 64; ++h64) store_rows64(wo, lane, pk + 32 * h64, col + 64 * h64);
     return;
   }
-  // pass 1: mean square of the bf16-rounded projection (the GEMM's output dtype)
-  float ss = 0.f;
-#pragma unroll 1
-  for (int c = 0; c < D / 32; ++c) {
-    uint32_t r[32];
-    tmem_ld_32x32(taddr + c * 32, r);
-    tmem_ld_wait();
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const float v = bf16r(__uint_as_float(r[i]));
-      ss = fmaf(v, v, ss);
-    }
-  }
   const float tau = rsqrtf(ss * (1.0f / D) + p.eps);
-  const float* gain = s_gain + kind * 128;           // shared-memory copy: q gains, then k gains
+  const float* gain = s_gain + kind * 128;             // shared-memory copy: q gains, then k gains
+  const bool exact_scale = (kind == 1) || (p.q_scale_pow2 != 0);
   const float stat_scale = (kind == 0) ? p.q_scale : 1.0f;
   float stat = 0.f;
-  // pass 2: 32 elements of the first half with their rotate-half partners of the second half
-#pragma unroll 1
-  for (int c = 0; c < HALF / 32; ++c) {
-    uint32_t r1[32], r2[32];
-    tmem_ld_32x32(taddr + c * 32, r1);
-    tmem_ld_32x32(taddr + HALF + c * 32, r2);
-    tmem_ld_wait();
-    uint32_t o1[16], o2[16];
-    const uint4* ct = reinterpret_cast<const uint4*>(p.cos + int64_t(t) * HALF + c * 32);
-    const uint4* st = reinterpret_cast<const uint4*>(p.sin + int64_t(t) * HALF + c * 32);
 #pragma unroll
-    for (int q4 = 0; q4 < 4; ++q4) {
-      const uint4 cv = ct[q4], sv = st[q4];
-      const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, sw[4] = {sv.x, sv.y, sv.z, sv.w};
+  for (int g2i = 0; g2i < QP / 2; ++g2i) {             // two pairs = four gains of each half per step
+    const float4 ga = *reinterpret_cast<const float4*>(gain + 4 * g2i);
+    const float4 gb = *reinterpret_cast<const float4*>(gain + D / 2 + 4 * g2i);
+    const float g1v[4] = {ga.x, ga.y, ga.z, ga.w}, g2v[4] = {gb.x, gb.y, gb.z, gb.w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int i = q4 * 8 + j * 2;              // element index inside the 32-chunk
-        const float2 g1 = *reinterpret_cast<const float2*>(gain + c * 32 + i);
-        const float2 g2 = *reinterpret_cast<const float2*>(gain + HALF + c * 32 + i);
-        const float g1a = g1.x, g1b = g1.y, g2a = g2.x, g2b = g2.y;
-        // x <- round((round(acc) * tau) * gain)
-        const uint32_t x1 = pack_bf16((bf16r(__uint_as_float(r1[i])) * tau) * g1a, (bf16r(__uint_as_float(r1[i + 1])) * tau) * g1b);
-        const uint32_t x2 = pack_bf16((bf16r(__uint_as_float(r2[i])) * tau) * g2a, (bf16r(__uint_as_float(r2[i + 1])) * tau) * g2b);
-        const __nv_bfloat162 X1 = as_bf162(x1), X2 = as_bf162(x2), Cc = as_bf162(cw[j]), Ss = as_bf162(sw[j]);
-        // bf16 arithmetic, every product and sum rounded: (x1 c - x2 s, x1 s + x2 c)
-        const __nv_bfloat162 y1 = __hsub2(__hmul2(X1, Cc), __hmul2(X2, Ss));
-        const __nv_bfloat162 y2 = __hadd2(__hmul2(X1, Ss), __hmul2(X2, Cc));
-        o1[q4 * 4 + j] = as_u32(y1);
-        o2[q4 * 4 + j] = as_u32(y2);
-        const float2 f1 = __bfloat1622float2(y1), f2 = __bfloat1622float2(y2);
-        const float a = bf16r(f1.x * stat_scale), b = bf16r(f1.y * stat_scale);
-        const float cc = bf16r(f2.x * stat_scale), d = bf16r(f2.y * stat_scale);
-        stat = fmaf(a, a, stat); stat = fmaf(b, b, stat); stat = fmaf(cc, cc, stat); stat = fmaf(d, d, stat);
+    for (int jj = 0; jj < 2; ++jj) {
+      const int j = g2i * 2 + jj;                      // pair j of the first half, partner pair j + QP
+      // x <- round((x * tau) * gain)
+      const uint32_t x1 = pack_bf16((pair_lo(pk[j]) * tau) * g1v[2 * jj], (pair_hi(pk[j]) * tau) * g1v[2 * jj + 1]);
+      const uint32_t x2 = pack_bf16((pair_lo(pk[j + QP]) * tau) * g2v[2 * jj], (pair_hi(pk[j + QP]) * tau) * g2v[2 * jj + 1]);
+      const __nv_bfloat162 X1 = as_bf162(x1), X2 = as_bf162(x2), Cc = as_bf162(tc[j]), Ss = as_bf162(ts[j]);
+      // bf16 arithmetic, every product and sum rounded: (x1 c - x2 s, x1 s + x2 c)
+      const uint32_t y1 = as_u32(__hsub2(__hmul2(X1, Cc), __hmul2(X2, Ss)));
+      const uint32_t y2 = as_u32(__hadd2(__hmul2(X1, Ss), __hmul2(X2, Cc)));
+      pk[j] = y1;
+      pk[j + QP] = y2;
+      uint32_t s1 = y1, s2 = y2;
+      if (!exact_scale) {                              // the guard looks at the scaled, re-rounded q
+        s1 = pack_bf16(pair_lo(y1) * stat_scale, pair_hi(y1) * stat_scale);
+        s2 = pack_bf16(pair_lo(y2) * stat_scale, pair_hi(y2) * stat_scale);
       }
-    }
-    if (store) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) = make_uint4(o1[4 * i], o1[4 * i + 1], o1[4 * i + 2], o1[4 * i + 3]);
-        *reinterpret_cast<uint4*>(dst + HALF + c * 32 + i * 8) = make_uint4(o2[4 * i], o2[4 * i + 1], o2[4 * i + 2], o2[4 * i + 3]);
-      }
+      stat = fmaf(pair_lo(s1), pair_lo(s1), stat); stat = fmaf(pair_hi(s1), pair_hi(s1), stat);
+      stat = fmaf(pair_lo(s2), pair_lo(s2), stat); stat = fmaf(pair_hi(s2), pair_hi(s2), stat);
     }
   }
-  if (store) {
-    if (kind == 0) best_q = fmaxf(best_q, stat); else best_k = fmaxf(best_k, stat);
+  if (live) {
+    // a power-of-two scale commutes with every rounding above: apply it to the sum
+    if (kind == 0) best_q = fmaxf(best_q, exact_scale ? stat * (stat_scale * stat_scale) : stat);
+    else best_k = fmaxf(best_k, stat);
+  }
+#pragma unroll
+  for (int h64 = 0; h64 < D / 64; ++h64) store_rows64(wo, lane, pk + 32 * h64, col + 64 * h64);
+}
+
+// ---- GLU epilogue ---------------------------------------------------------------------------
+// gu[0..15] = 16 gate accumulators, gu[16..31] = the matching up accumulators -> 8 packed outputs
+__device__ __forceinline__ void glu16(const uint32_t* gu, float beta, uint32_t* out) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t gp = pack_bf16(__uint_as_float(gu[2 * i]), __uint_as_float(gu[2 * i + 1]));
+    const uint32_t up = pack_bf16(__uint_as_float(gu[16 + 2 * i]), __uint_as_float(gu[16 + 2 * i + 1]));
+    float act[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const float uv = e ? pair_hi(up) : pair_lo(up);
+      const float bz = beta * uv;
+      const float r = rsqrtf(fmaf(bz, bz, 1.0f));
+      const float uu = bz * r;
+      // for bz < 0 use 1 + u = r^2 / (1 - u) so that the negative tail survives
+      const float one_plus_u = bz < 0.f ? __fdividef(r * r, 1.0f - uu) : 1.0f + uu;
+      act[e] = 0.5f * uv * one_plus_u;
+    }
+    // gate (bf16) times the bf16-rounded activation, rounded once: a bf16 multiply
+    out[i] = as_u32(__hmul2(as_bf162(gp), as_bf162(pack_bf16(act[0], act[1]))));
   }
 }
 
-// ---- GLU epilogue: 64 output features of one row -------------------------------------------
-__device__ __forceinline__ void glu_cols(const ProjParams& p, uint32_t t_gate, uint32_t t_up, __nv_bfloat16* dst, bool store) {
-#pragma unroll 1
-  for (int c = 0; c < 2; ++c) {
-    uint32_t g[32], u[32];
-    tmem_ld_32x32(t_gate + c * 32, g);
-    tmem_ld_32x32(t_up + c * 32, u);
-    tmem_ld_wait();
-    uint32_t pk[16];
+// 64 output features of one row: gate columns from t_gate, up columns from t_up
+__device__ __forceinline__ void glu_cols(const ProjParams& p, uint32_t t_gate, uint32_t t_up, const WarpOut& wo, int lane,
+                                         int col) {
+  uint32_t a[32], b[32], o[32];
+  tmem_ld_32x16(t_gate, a);
+  tmem_ld_32x16(t_up, a + 16);
 #pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      float o[2];
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const float gv = bf16r(__uint_as_float(g[i + e])), uv = bf16r(__uint_as_float(u[i + e]));
-        const float bz = p.beta * uv;
-        const float r = rsqrtf(fmaf(bz, bz, 1.0f));
-        const float uu = bz * r;
-        // for bz < 0 use 1 + u = r^2 / (1 - u) so that the negative tail survives
-        const float one_plus_u = bz < 0.f ? __fdividef(r * r, 1.0f - uu) : 1.0f + uu;
-        o[e] = gv * bf16r(0.5f * uv * one_plus_u);
-      }
-      pk[i >> 1] = pack_bf16(o[0], o[1]);
+  for (int c = 0; c < 4; ++c) {
+    uint32_t* cur = (c & 1) ? b : a;
+    uint32_t* nxt = (c & 1) ? a : b;
+    tmem_ld_wait_for(cur);
+    if (c + 1 < 4) {
+      tmem_ld_32x16(t_gate + (c + 1) * 16, nxt);
+      tmem_ld_32x16(t_up + (c + 1) * 16, nxt + 16);
     }
-    if (store) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
-    }
+    glu16(cur, p.beta, o + 8 * c);
   }
+  store_rows64(wo, lane, o, col);
 }
 
 template <int EPI, int D>
@@ -251,32 +297,48 @@ proj_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     const int half = (warp - 2) >> 2;
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_sel = uint32_t(quarter * 32) << 16;
+    unsigned char* stage = smem + STAGE_OFF + (warp - 2) * WARP_STAGE_BYTES;
     uint32_t tile_count = 0;
     float best_q = 0.f, best_k = 0.f, best_v = 0.f;
     bool ok = true;
     for (int u = blockIdx.x; u < tiles && ok; u += gridDim.x, ++tile_count) {
       const int m = u / tiles_n, n = u % tiles_n;
       const uint32_t buf = tile_count & 1u, tphase = (tile_count >> 1) & 1u;
-      if (!bw.wait(&ctl->tfull[buf], tphase)) { ok = false; break; }
-      tc_fence_after();
       const int row = m * BM + row_in_tile;
       const bool live = row < p.M;
-      const uint32_t tbuf = tmem_base + lane_sel + buf * BN;
-      if (EPI == EPI_QKV) {
+      // QKV: this row's rotation table entries, the same for every q and k head of the tile,
+      // fetched before the wait so that their latency hides behind the accumulator filling
+      constexpr int TQ = (EPI == EPI_QKV) ? D / 4 : 1;
+      uint32_t tc[TQ], ts[TQ];
+      const int hd = p.H * D;
+      if (EPI == EPI_QKV && (n * BN + half * 128) / hd < 2) {   // kinds only grow along a tile: q/k present
         const int t = live ? row % p.T : 0;
-        const int hd = p.H * D;
+        const uint4* ct = reinterpret_cast<const uint4*>(p.cos + int64_t(t) * (D / 2));
+        const uint4* st = reinterpret_cast<const uint4*>(p.sin + int64_t(t) * (D / 2));
+#pragma unroll
+        for (int i = 0; i < TQ / 4; ++i) {
+          const uint4 cv = ct[i], sv = st[i];
+          tc[4 * i] = cv.x; tc[4 * i + 1] = cv.y; tc[4 * i + 2] = cv.z; tc[4 * i + 3] = cv.w;
+          ts[4 * i] = sv.x; ts[4 * i + 1] = sv.y; ts[4 * i + 2] = sv.z; ts[4 * i + 3] = sv.w;
+        }
+      }
+      if (!bw.wait(&ctl->tfull[buf], tphase)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t tbuf = tmem_base + lane_sel + buf * BN;
+      const int wrow = m * BM + quarter * 32;            // first row of this warp
+      const WarpOut wo{stage, p.out + int64_t(wrow) * p.ld_out, p.ld_out, min(32, max(0, p.M - wrow))};
+      if (EPI == EPI_QKV) {
 #pragma unroll 1
         for (int hh = 0; hh < 128 / D; ++hh) {
           const int lcol = half * 128 + hh * D;          // column inside the tile
           const int gcol = n * BN + lcol;                // output feature
           if (gcol >= p.N) break;
-          qkv_head<D>(p, s_gain, tbuf + lcol, gcol / hd, t, p.out + int64_t(live ? row : 0) * p.ld_out + gcol, live, best_q, best_k,
-                      best_v);
+          qkv_head<D>(p, s_gain, tbuf + lcol, gcol / hd, tc, ts, wo, lane, gcol, live, best_q, best_k, best_v);
         }
       } else {
         const int fcol = n * 128 + half * 64;            // output feature of this thread's first column
         if (fcol < p.f)
-          glu_cols(p, tbuf + half * 64, tbuf + 128 + half * 64, p.out + int64_t(live ? row : 0) * p.ld_out + fcol, live);
+          glu_cols(p, tbuf + half * 64, tbuf + 128 + half * 64, wo, lane, fcol);
       }
       tc_fence_before();
       mbar_arrive(&ctl->tempty[buf]);                    // this thread is done reading the buffer
