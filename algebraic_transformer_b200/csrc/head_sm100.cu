@@ -104,6 +104,9 @@ head_tc_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constant__
   } else if (warp == 1) {
     if (lane == 0) {
       uint32_t it = 0, tile_count = 0;
+      // descriptor low halves of stage 0 (sm100_ptx.cuh: sw128_desc_lo); a stage adds STAGE_BYTES / 16,
+      // a K step 2 — the issue loop then spends one add per operand and MMA
+      const uint32_t a_lo0 = sw128_desc_lo(smem_u32(smem), 16), b_lo0 = sw128_desc_lo(smem_u32(smem) + A_BYTES, 16);
       bool ok = true;
       for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
         const int s = u / row_blocks;
@@ -117,14 +120,11 @@ head_tc_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constant__
             const uint32_t stage = it % STAGES, phase = (it / STAGES) & 1u;
             if (!bw.wait(&ctl->full[stage], phase)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t a_addr = smem_u32(smem + size_t(stage) * STAGE_BYTES);
-            const uint32_t b_addr = a_addr + A_BYTES;
+            const uint32_t a_lo = a_lo0 + stage * (STAGE_BYTES >> 4), b_lo = b_lo0 + stage * (STAGE_BYTES >> 4);
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k) {
-              const uint64_t da = make_sw128_desc(a_addr + k * UMMA_K * 2, 16, 1024);
-              const uint64_t db = make_sw128_desc(b_addr + k * UMMA_K * 2, 16, 1024);
-              umma_f16_ss(d_tmem, da, db, IDESC, (kb | k) != 0 ? 1u : 0u);
-            }
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma_f16_ss_parts(d_tmem, a_lo + k * (UMMA_K * 2 >> 4), SW128_DESC_HI, b_lo + k * (UMMA_K * 2 >> 4),
+                                SW128_DESC_HI, IDESC, (kb | k) != 0 ? 1u : 0u);
             umma_commit(&ctl->empty[stage]);           // smem stage is free once these MMAs retire
           }
           if (ok) umma_commit(&ctl->tfull[buf]);        // accumulator tile complete
