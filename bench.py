@@ -450,7 +450,28 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
     nbytes = 2.0 * k.numel() * 2
     extra["decode"] = {"workload": f"Tq=1 vs KV cache (1,16,{T},{D}) bf16 = 268 MB", "ms": ms_d,
                        "gbs": nbytes / (ms_d * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms_d * 1e-3) / 1e9 / peak_bw}
-    del flush
+    del flush, k, v, x, y
+    # ---- the two fused projections of one 125M block (16384 tokens): tensor bound ----
+    M, dm, Hh, Dh, ff, Tt = 16384, 768, 12, 64, 2048, 1024
+    xs = torch.randn((M, dm), generator=g).bfloat16().to(dev)
+    wqkv = (torch.randn((3 * dm, dm), generator=g) * 0.05).bfloat16().to(dev)
+    wgu = (torch.randn((2 * ff, dm), generator=g) * 0.05).bfloat16().to(dev)
+    c2, s2 = A.cayley_table_geometric(Dh, Tt, device=dev)
+    c2, s2 = c2.bfloat16().contiguous(), s2.bfloat16().contiguous()
+    ones = torch.ones(Dh, device=dev)
+    words = torch.zeros(4, dtype=torch.int32, device=dev)
+    o_qkv = torch.empty((M, 3 * dm), dtype=torch.bfloat16, device=dev)
+    o_glu = torch.empty((M, ff), dtype=torch.bfloat16, device=dev)
+    for name, fn, fl in (
+            ("qkv_proj_125m", lambda i: A.qkv_projection(xs, wqkv, Hh, Tt, c2, s2, ones, ones, 1e-5, 8.0, words, out=o_qkv),
+             2.0 * M * dm * 3 * dm),
+            ("glu_proj_125m", lambda i: A.glu_projection(xs, wgu, 0.5, out=o_glu), 2.0 * M * dm * 2 * ff)):
+        for i in range(3):
+            fn(i)
+        ms_g = cuda_time(fn, iters, sync)
+        extra[name] = {"workload": f"{M} tokens, d={dm}, " + ("3 x 12 heads of 64: GEMM + QK-norm + rotation + guard maxima"
+                                                               if name.startswith("qkv") else f"f={ff}: GEMM + gate*ALU(up)"),
+                       "ms": ms_g, "tflops": fl / (ms_g * 1e-3) / 1e12, "frac_of_bf16_peak": fl / (ms_g * 1e-3) / 1e12 / peak_tf}
     return extra
 
 
