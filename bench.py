@@ -380,8 +380,14 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
     # ---- full prefill forward (benchmark configurations 3 and 4): batch split over ranks, hidden
     #      states all-gathered, head vocabulary-sharded ----
     from algebraic_transformer_b200 import prefill as PF
-    for name, size, vocab, gb, seq in (("prefill_125m", "125m", 50304, 16, 1024), ("prefill_350m", "350m", 32000, 8, 2048),
-                                       ("prefill_1b", "1b", 32000, 8, 2048)):
+    # (name, model, vocab, batch, seq, weak): the configurations' batch is taken as the GLOBAL batch and
+    # split over the ranks (strong scaling).  At N > 1 one more line gives every rank the whole batch of
+    # the 125M configuration (weak scaling), the other reading of "scales from 1 to 8 GPUs".
+    runs = [("prefill_125m", "125m", 50304, 16, 1024, False), ("prefill_350m", "350m", 32000, 8, 2048, False),
+            ("prefill_1b", "1b", 32000, 8, 2048, False)]
+    if world > 1:
+        runs.append(("prefill_125m_weak", "125m", 50304, 16 * world, 1024, True))
+    for name, size, vocab, gb, seq, weak in runs:
         if gb % world or (args.prefill_only is not None and args.prefill_only != size):
             continue
         cfg = PF.PrefillConfig.preset(size, vocab_size=vocab)
@@ -411,7 +417,7 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
         ms_p = max_over_ranks(cuda_time(prefill_step, max(3, min(args.steps, 10)), sync))
         fl = cfg.flops_per_token(seq) * gb * seq
         extra[name] = {"workload": f"{size} algebraic prefill + Alg-CE head, bf16, global batch {gb} x {seq}, vocab {vocab}, "
-                                   f"random init seed 0, batch split x{world}",
+                                   f"random init seed 0, batch split x{world}" + (" (weak: 16 sequences per GPU)" if weak else ""),
                        "tokens_per_s": gb * seq / (ms_p * 1e-3), "ms_per_step": ms_p, "launch": "CUDA graph: " + how,
                        "head_exchange": "fused peer-memory kernel" if ex is not None else ("NCCL all-reduce" if world > 1 else "none"),
                        "tflops": fl / (ms_p * 1e-3) / 1e12, "frac_of_bf16_peak_per_gpu": fl / (ms_p * 1e-3) / 1e12 / world / peak_tf}
