@@ -89,7 +89,20 @@ __global__ void __launch_bounds__(256, MODE == 0 ? 4 : 3) qk_prep_kernel(const P
     T* dst0 = (MODE >= 1 && p.y != nullptr) ? reinterpret_cast<T*>(p.y) + b * p.ys.b + int64_t(t) * p.ys.t + lir * VEC : nullptr;
 
     float c[VEC], s[VEC];              // this position's table row, cast to T, signed for the half
-    if constexpr (MODE == 2) {
+    uint32_t c2[VEC / 2], s2[VEC / 2]; // the same as packed bf16 pairs (bf16 rows only)
+    if constexpr (MODE == 2 && sizeof(T) == 2) {
+#pragma unroll
+      for (int i = 0; i < VEC; i += 4) {
+        const float4 cv = *reinterpret_cast<const float4*>(p.cos + int64_t(t) * HALF + j0 + i);
+        const float4 sv = *reinterpret_cast<const float4*>(p.sin + int64_t(t) * HALF + j0 + i);
+        c2[i / 2] = pack_bf16(cv.x, cv.y); c2[i / 2 + 1] = pack_bf16(cv.z, cv.w);
+        s2[i / 2] = pack_bf16(sv.x, sv.y); s2[i / 2 + 1] = pack_bf16(sv.z, sv.w);
+      }
+      if (first) {                       // the first half subtracts x2 s: flip both sign bits
+#pragma unroll
+        for (int i = 0; i < VEC / 2; ++i) s2[i] ^= 0x80008000u;
+      }
+    } else if constexpr (MODE == 2) {
 #pragma unroll
       for (int i = 0; i < VEC; i += 4) {
         const float4 cv = *reinterpret_cast<const float4*>(p.cos + int64_t(t) * HALF + j0 + i);
@@ -123,30 +136,43 @@ __global__ void __launch_bounds__(256, MODE == 0 ? 4 : 3) qk_prep_kernel(const P
 #pragma unroll
           for (int o = LPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
           const float tau = rsqrtf(ss * (1.0f / D) + p.eps);
+          if constexpr (MODE == 2 && sizeof(T) == 2) {
+            // bf16 rows.  The reference rotates in bf16 arithmetic (each product and the sum rounded
+            // to bf16), which is what HMUL2 / HADD2 compute, two elements per instruction; a pair
+            // also travels to its rotate-half partner lane as one 32-bit shuffle.
+            uint32_t yp[VEC / 2];
 #pragma unroll
-          for (int i = 0; i < VEC; ++i) v[i] = V::round((v[i] * tau) * gain[i]);
-        }
-        if constexpr (MODE == 2) {
-#pragma unroll
-          for (int i = 0; i < VEC; i += 2) {
-            // rotate-half partner values; bf16 rows hold bf16-exact values here, so a pair
-            // travels as one packed 32-bit shuffle
-            float o0, o1;
-            if constexpr (sizeof(T) == 2) {
-              const uint32_t pk = __shfl_xor_sync(0xffffffffu, pack_bf16(v[i], v[i + 1]), LPR / 2);
-              o0 = __uint_as_float(pk << 16);
-              o1 = __uint_as_float(pk & 0xffff0000u);
-            } else {
-              o0 = __shfl_xor_sync(0xffffffffu, v[i], LPR / 2);
-              o1 = __shfl_xor_sync(0xffffffffu, v[i + 1], LPR / 2);
+            for (int i = 0; i < VEC / 2; ++i) {
+              const uint32_t own = pack_bf16((v[2 * i] * tau) * gain[2 * i], (v[2 * i + 1] * tau) * gain[2 * i + 1]);
+              const uint32_t oth = __shfl_xor_sync(0xffffffffu, own, LPR / 2);
+              // first half: x1 c - x2 s ; second half: x2 c + x1 s  ==  own * c + other * (-+ s)
+              const __nv_bfloat162 y = __hadd2(__hmul2(*reinterpret_cast<const __nv_bfloat162*>(&own), *reinterpret_cast<const __nv_bfloat162*>(&c2[i])),
+                                               __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&oth), *reinterpret_cast<const __nv_bfloat162*>(&s2[i])));
+              yp[i] = *reinterpret_cast<const uint32_t*>(&y);
             }
-            // first half: x1 c - x2 s ; second half: x1 s + x2 c  ==  own * c + other * (-+ s),
-            // each product and the sum rounded to T (s[] carries the sign of this half)
-            v[i] = V::round(V::round(v[i] * c[i]) + V::round(o0 * s[i]));
-            v[i + 1] = V::round(V::round(v[i + 1] * c[i + 1]) + V::round(o1 * s[i + 1]));
+            if (dst0 != nullptr && on)
+              *reinterpret_cast<uint4*>(dst0 + int64_t(h) * p.ys.h) = make_uint4(yp[0], yp[1], yp[2], yp[3]);
+            if (p.stat_mode != 0) {          // the statistic below wants the written values
+#pragma unroll
+              for (int i = 0; i < VEC / 2; ++i) {
+                v[2 * i] = __uint_as_float(yp[i] << 16);
+                v[2 * i + 1] = __uint_as_float(yp[i] & 0xffff0000u);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) v[i] = V::round((v[i] * tau) * gain[i]);
           }
         }
-        if (MODE >= 1 && dst0 != nullptr && on) V::store(dst0 + int64_t(h) * p.ys.h, v);
+        if constexpr (MODE == 2 && sizeof(T) != 2) {
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) {
+            // fp32 rows: own * c + other * (-+ s), s[] carrying the sign of this half
+            const float o = __shfl_xor_sync(0xffffffffu, v[i], LPR / 2);
+            v[i] = v[i] * c[i] + o * s[i];
+          }
+        }
+        if (MODE >= 1 && !(MODE == 2 && sizeof(T) == 2) && dst0 != nullptr && on) V::store(dst0 + int64_t(h) * p.ys.h, v);
         if (p.stat_mode == 1) {          // squared row norm of the re-rounded scaled row
           float ss = 0.0f;
 #pragma unroll
