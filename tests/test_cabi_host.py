@@ -46,6 +46,25 @@ def test_invalid_arguments_fail_before_launch():
     assert lib.alg_head_fwd(h, None) == L.ALG_ERR_INVALID   # shard exceeds the vocabulary
     q = L.QkRmsArgs(x=16, y=16, eps=0.0, B=1, H=1, T=1, D=64)
     assert lib.alg_qk_rms_fwd(q, None) == L.ALG_ERR_INVALID
+    # guard words handed over by the QKV projection describe ready-made q, k, v: not with the prologue
+    a = L.AttnArgs(q=16, k=16, v=16, o=16, B=1, H=1, Tq=256, Tk=256, D=64, n=16, c=8.0, variant=L.ALG_VARIANT_GUARD,
+                   guard_words=16, q_gain=16, k_gain=16, cos=16, sin=16, eps=1e-5)
+    assert lib.alg_attn_fwd(a, None) == L.ALG_ERR_INVALID
+    assert b"guard_words" in lib.alg_last_error()
+    # the fused projections
+    assert lib.alg_qkv_proj_fwd(L.QkvProjArgs(), None) == L.ALG_ERR_INVALID
+    pj = L.QkvProjArgs(x=16, w=16, qkv=16, cos=16, sin=16, eps=1e-5, M=128, d=768, H=12, D=48, T=128, ld_x=768,
+                       attn_c=8.0)
+    assert lib.alg_qkv_proj_fwd(pj, None) == L.ALG_ERR_INVALID     # head_dim must be 64 or 128
+    pj.D, pj.d, pj.ld_x = 64, 700, 700
+    assert lib.alg_qkv_proj_fwd(pj, None) == L.ALG_ERR_INVALID     # d must be a multiple of 64
+    pj.d, pj.ld_x, pj.x = 768, 768, 8
+    assert lib.alg_qkv_proj_fwd(pj, None) == L.ALG_ERR_INVALID     # 16-byte alignment
+    assert b"alignment" in lib.alg_last_error()
+    gl = L.GluProjArgs(x=16, w=16, out=16, M=128, d=768, f=100, ld_x=768, ld_out=100, beta=0.5)
+    assert lib.alg_glu_proj_fwd(gl, None) == L.ALG_ERR_INVALID     # f must be a multiple of 128
+    gl.f, gl.ld_out = 256, 128
+    assert lib.alg_glu_proj_fwd(gl, None) == L.ALG_ERR_INVALID     # output rows narrower than f
     with pytest.raises(ValueError):
         L.check(L.ALG_ERR_INVALID)
 
