@@ -268,8 +268,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           cur.next();
           const Cur kc = cur;                         // K_{j+1}: only meaningful while j + 1 < n1
           if (j + 1 < n1) cur.next();
-          bool k_ready = false;
-          if (!ALG_T(tm0, kv_wait(vc))) { ok = false; break; }
+          // Both tiles of this step are waited for up front (they are normally long there), so
+          // that nothing stands between "weights ready" and the issue of P.V and the next S.
+          if (!ALG_T(tm0, kv_wait(vc)) || (j + 1 < n1 && !ALG_T(tm0, kv_wait(kc)))) { ok = false; break; }
           if (j < n0) {
             if (!ALG_T(tm1, bw.wait(&ctl->p_full[0], (t0 + j) & 1u))) { ok = false; break; }
             // the first product of an item overwrites O_0: the previous output must have been read
@@ -277,9 +278,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             tc_fence_after();
             issue_pv(0, vc.slot, j == 0);
             if (j + 1 < n0) {
-              if (!ALG_T(tm0, kv_wait(kc))) { ok = false; break; }
-              k_ready = true;
-              tc_fence_after();
               issue_s(0, kc.slot);                     // after P_0.V: may overwrite P_0
               umma_commit(&ctl->s_full[0]);
               if (j + 2 == n0) umma_commit(&ctl->q_free[0]);   // the item's last read of Q tile 0
@@ -293,8 +291,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           issue_pv(1, vc.slot, j == 0);
           umma_commit(&ctl->kv_empty[vc.slot]);
           if (j + 1 < n1) {
-            if (!k_ready && !ALG_T(tm0, kv_wait(kc))) { ok = false; break; }
-            tc_fence_after();
             issue_s(1, kc.slot);
             umma_commit(&ctl->s_full[1]);
             umma_commit(&ctl->kv_empty[kc.slot]);
