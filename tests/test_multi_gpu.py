@@ -1,5 +1,6 @@
 """Two-GPU checks (skipped on a single-GPU box): the vocabulary-sharded Alg-CE head with its
-NCCL all-reduce, and attention over disjoint (batch, head) unit blocks, each rank one GPU."""
+NCCL all-reduce and with the one-kernel NVLink exchange, attention over disjoint (batch, head)
+unit blocks, and the batch-split prefill against the CPU model; each rank one GPU."""
 
 import os
 import sys
@@ -54,7 +55,23 @@ def _worker(rank, world, port, ret):
                           kind="asinh", n=16, c=8.0, range_guard=True)
     want = R.asinh_attention(q[:, sl], k[:, sl], v[:, sl], n=16, c=8.0, sink_logit=torch.zeros(un))
     e_attn = float((o.cpu().double() - want.double()).norm() / want.double().norm())
-    ret[rank] = (bool(ok_head), e_head, e_attn)
+    # ---- prefill: batch split over the ranks, hidden states gathered, head vocabulary-sharded
+    #      (fused projections in the body, one-kernel exchange in the head) against the CPU model
+    from algebraic_transformer_b200 import prefill as P
+    from oracle import model_ref as M
+    cfg = P.PrefillConfig(vocab_size=1000, d_model=128, n_layers=2, n_heads=2, d_ff=256)
+    params = P.init_params(cfg, seed=0)
+    tokens = torch.randint(0, cfg.vocab_size, (2, 256), generator=g)
+    obj_w, pt_w = M.head_loss(params, M.forward_hidden(params, tokens, cfg), tokens, cfg)
+    ex2 = HeadExchange(dist.group.WORLD, tokens.numel(), dev)
+    model = P.Prefill(cfg, params, dev, seq_len=256, exchange=ex2)
+    mine = tokens[rank:rank + 1].to(dev)                               # one sequence per rank
+    obj_p, pt_p, nll_p = model.loss(mine, mine, group=dist.group.WORLD, rank=rank, world=world, want_nll=True)
+    torch.cuda.synchronize()
+    want_nll = R.nll_from_pt(pt_w).double()
+    e_prefill = float((nll_p.cpu().double() - want_nll).norm() / want_nll.norm())
+    ok_head = ok_head and e_prefill < 1e-2 and abs(float(obj_p) - float(obj_w)) < 5e-3 * abs(float(obj_w))
+    ret[rank] = (bool(ok_head), max(e_head, e_prefill), e_attn)
     dist.barrier()
     dist.destroy_process_group()
 
