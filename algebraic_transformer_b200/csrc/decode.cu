@@ -3,15 +3,14 @@
 // HBM-bound: every K and V row is read from HBM exactly once.  Keys are split over CTAs
 // (grid = splits x heads x batch); inside a CTA a producer warp streams 64-key K and V tiles
 // into a 3-stage shared-memory ring with TMA (two CTAs per SM keep ~190 KB in flight), and
-// eight consumer warps walk each tile in three short phases:
-//   A  scores: a group of D/8 lanes owns one key, 8 FMAs per lane + a shuffle reduction
-//   B  weights: one thread per key, w = (rho(x) rho(-m))^n in the max-shifted form of
-//      src/algebraic/algebraic.py:186-204 with a CTA-wide running maximum m (rescale
-//      (rho(m_old) rho(-m_new))^n applied to the accumulators when m moves)
-//   C  values: the lane groups accumulate w * V for their keys
-// so rho is evaluated once per key rather than once per lane.  Partial (acc, m, l) states
-// of the splits are merged, with the sink, by decode_combine_kernel using the same exact
-// rescale.  All mbarrier waits are bounded.
+// eight consumer warps each take 8 keys of a tile.  A group of D/8 lanes owns one key: 8 FMAs
+// per lane + a shuffle reduction give its score, w = (rho(x) rho(-m))^n is the max-shifted
+// weight of src/algebraic/algebraic.py:186-204 with the WARP's running maximum m (rescale
+// (rho(m_old) rho(-m_new))^n applied to the warp's accumulators when m moves), and every lane
+// accumulates w * V for the 8 columns it holds.  No step of the key loop involves the whole
+// CTA, so nothing but the ring's barriers paces it; the eight warp states are merged once at
+// the end with the same exact rescale, and the (acc, m, l) states of the splits are merged,
+// with the sink, by decode_combine_kernel.  All mbarrier waits are bounded.
 #include "common.cuh"
 #include "launchers.h"
 #include "sm100_ptx.cuh"
@@ -49,8 +48,6 @@ __global__ void __launch_bounds__(NTHREADS, 2)
 decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                       const DecodeParams p) {
   constexpr int LPK = D / 8;                    // lanes per key
-  constexpr int GROUPS = CONSUMERS / LPK;       // keys handled per pass
-  constexpr int PASSES = TILE / GROUPS;
   constexpr int TILE_BYTES = TILE * D * 2;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -64,6 +61,7 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], CONSUMERS / 32); }
     ctl->abort_flag = 0;
+    ctl->tile_ok = 1;
     fence_barrier_init();
   }
   __syncthreads();
@@ -82,7 +80,14 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
       }
     }
   } else {
-    const int group = threadIdx.x / LPK, lig = threadIdx.x % LPK;
+    // Consumers.  Every warp takes 8 of the tile's 64 keys and carries a state of its own (running
+    // maximum m, normaliser l, accumulator), so the key loop has no CTA-wide step at all: a
+    // key's LPK lanes form its score with shuffles, every lane evaluates the key's weight
+    // (rho(x) rho(-m))^n, and lane i of a key accumulates the 8 output columns it holds.  The
+    // eight states are merged once, after the last tile, with the exact rescale.
+    constexpr int KPW = TILE / (CONSUMERS / 32);            // keys per warp and tile
+    constexpr int KPI = 32 / LPK;                           // keys per warp instruction
+    const int lig = lane % LPK, sub = lane / LPK;
     float q[8];
     {
       const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.q) +
@@ -94,84 +99,93 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    float m_ref = -1e30f, l_part = 0.f;
+    float m_ref = -1e30f, shift = 0.f, l_part = 0.f;
     bool ok = true;
-    for (int t = 0; t < ntiles && ok; ++t) {
-      const int stage = t % STAGES, buf = t & 1;
-      // One thread performs the bounded wait and the verdict is shared through a barrier, so
-      // that all consumer warps leave the loop together if a wait ever runs out (the named
-      // barriers below must never be entered by only a part of them).
-      if (threadIdx.x == 0) ctl->tile_ok = bw.wait(&ctl->full[stage], (t / STAGES) & 1) ? 1 : 0;
-      consumer_sync();
-      if (ctl->tile_ok == 0) { ok = false; break; }
-      (void)mbar_try_wait(&ctl->full[stage], (t / STAGES) & 1);   // completed phase: acquire the tile for this thread
+    for (int t = 0; t < ntiles; ++t) {
+      const int stage = t % STAGES;
+      if (!bw.wait(&ctl->full[stage], (t / STAGES) & 1)) { ok = false; break; }
       const unsigned char* sk = smem + size_t(stage) * 2 * TILE_BYTES;
       const unsigned char* sv = sk + TILE_BYTES;
       const int key0 = k_begin + t * TILE;
-      // ---- A: scores
+      uint4 kraw[KPW / KPI], vraw[KPW / KPI];
 #pragma unroll
-      for (int ps = 0; ps < PASSES; ++ps) {
-        const int key = ps * GROUPS + group;
-        float kv[8];
-        unpack8(*reinterpret_cast<const uint4*>(sk + key * (D * 2) + lig * 16), kv);
-        float x = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) x = fmaf(q[i], kv[i], x);
-#pragma unroll
-        for (int o = LPK / 2; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
-        if (lig == 0) ctl->x[buf][key] = (key0 + key < k_end) ? x : -1e30f;
+      for (int ps = 0; ps < KPW / KPI; ++ps) {
+        const int key = warp * KPW + ps * KPI + sub;
+        kraw[ps] = *reinterpret_cast<const uint4*>(sk + key * (D * 2) + lig * 16);
+        vraw[ps] = *reinterpret_cast<const uint4*>(sv + key * (D * 2) + lig * 16);
       }
-      consumer_sync();
-      // ---- B: running maximum (every warp derives the same value) and one weight per key
-      float tmax = warp_max(fmaxf(ctl->x[buf][lane], ctl->x[buf][lane + 32]));
-      const float m_new = fmaxf(m_ref, tmax);
-      const float shift = rho_stable(-m_new);
-      if (m_new > m_ref) {
-        const float alpha = (m_ref > -1e29f) ? pow2n_rt(rho_stable(m_ref) * shift, p.log2n) : 0.f;
+      float x[KPW / KPI];
+      float tmax = -1e30f;
+#pragma unroll
+      for (int ps = 0; ps < KPW / KPI; ++ps) {
+        float kv[8];
+        unpack8(kraw[ps], kv);
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s = fmaf(q[i], kv[i], s);
+#pragma unroll
+        for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        x[ps] = (key0 + warp * KPW + ps * KPI + sub < k_end) ? s : -1e30f;
+        tmax = fmaxf(tmax, x[ps]);
+      }
+#pragma unroll
+      for (int o = LPK; o < 32; o <<= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+      if (tmax > m_ref) {                                    // warp-uniform
+        const float ns = rho_stable(-tmax);
+        const float alpha = (m_ref > -1e29f) ? pow2n_rt(rho_stable(m_ref) * ns, p.log2n) : 0.f;
         l_part *= alpha;
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] *= alpha;
-        m_ref = m_new;
+        m_ref = tmax;
+        shift = ns;
       }
-      if (threadIdx.x < TILE) {
-        const float x = ctl->x[buf][threadIdx.x];
-        const float w = (x > -1e29f) ? pow2n_rt(rho_stable(x) * shift, p.log2n) : 0.f;
-        ctl->w[buf][threadIdx.x] = w;
-        l_part += w;
-      }
-      consumer_sync();
-      // ---- C: values
 #pragma unroll
-      for (int ps = 0; ps < PASSES; ++ps) {
-        const int key = ps * GROUPS + group;
-        const float w = ctl->w[buf][key];
+      for (int ps = 0; ps < KPW / KPI; ++ps) {
+        const float w = (x[ps] > -1e29f) ? pow2n_rt(rho_stable(x[ps]) * shift, p.log2n) : 0.f;
+        l_part += w;
         float vv[8];
-        unpack8(*reinterpret_cast<const uint4*>(sv + key * (D * 2) + lig * 16), vv);
+        unpack8(vraw[ps], vv);
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = fmaf(w, vv[i], acc[i]);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl->empty[stage]);      // this warp is done with the stage
     }
-    // ---- merge the lane groups (all share m_ref) and write the split's partial state
-    consumer_sync();                                       // ring no longer read: reuse it as scratch
-    float* s_acc = reinterpret_cast<float*>(smem);         // [GROUPS][D]
+    // ---- this warp's state: add up its keys' lane groups, then merge the eight warps
 #pragma unroll
-    for (int i = 0; i < 8; ++i) s_acc[group * D + lig * 8 + i] = acc[i];
-    l_part = warp_sum(l_part);
-    if (lane == 0) ctl->red[warp] = l_part;
+    for (int o = LPK; o < 32; o <<= 1) {
+      l_part += __shfl_xor_sync(0xffffffffu, l_part, o);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+    }
+    consumer_sync();                                       // ring no longer read: reuse it as scratch
+    float* s_acc = reinterpret_cast<float*>(smem);         // [warps][D]
+    if (sub == 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s_acc[warp * D + lig * 8 + i] = acc[i];
+    }
+    if (lane == 0) { ctl->w[0][warp] = m_ref; ctl->w[1][warp] = l_part; if (!ok) ctl->tile_ok = 0; }
     consumer_sync();
     float* out = p.part + ((int64_t(b) * p.H + h) * p.splits + split) * (D + 2);
     if (threadIdx.x < D) {
-      float a = 0.f;
-      for (int g = 0; g < GROUPS; ++g) a += s_acc[g * D + threadIdx.x];
-      out[threadIdx.x] = ok ? a : 0.f;
-    }
-    if (threadIdx.x == 0) {
-      float l = 0.f;
-      for (int wv = 0; wv < CONSUMERS / 32; ++wv) l += ctl->red[wv];
-      out[D] = ok ? m_ref : -1e30f;
-      out[D + 1] = ok ? l : 0.f;
+      const bool fine = ctl->tile_ok != 0;
+      float mm = -1e30f;
+#pragma unroll
+      for (int wv = 0; wv < CONSUMERS / 32; ++wv) mm = fmaxf(mm, ctl->w[0][wv]);
+      const float ns = rho_stable(-mm);
+      float a = 0.f, l = 0.f;
+#pragma unroll
+      for (int wv = 0; wv < CONSUMERS / 32; ++wv) {
+        const float mw = ctl->w[0][wv];
+        const float f = (mw > -1e29f) ? pow2n_rt(rho_stable(mw) * ns, p.log2n) : 0.f;
+        a = fmaf(f, s_acc[wv * D + threadIdx.x], a);
+        l = fmaf(f, ctl->w[1][wv], l);
+      }
+      out[threadIdx.x] = fine ? a : 0.f;
+      if (threadIdx.x == 0) {
+        out[D] = fine ? mm : -1e30f;
+        out[D + 1] = fine ? l : 0.f;
+      }
     }
   }
   __syncthreads();
@@ -251,12 +265,13 @@ int launch_d(const DecodeParams& p, cudaStream_t stream) {
 
 }  // namespace
 
-// Splits are whole 64-key tiles; enough CTAs for two per SM on 148 SMs, never more than the
-// combine kernel's table.
+// Splits are whole 64-key tiles.  The grid is ONE wave: at most two CTAs per SM on 148 SMs (a
+// second wave would pay the ring's start-up latency again: 62 -> 56 us on a 32768-key cache),
+// never more splits than the combine kernel's table.
 int decode_splits(int B, int H, int Tk) {
   const int bh = B * H > 0 ? B * H : 1;
   const int tiles = (Tk + TILE - 1) / TILE;
-  int s = (148 * 4 + bh - 1) / bh;
+  int s = (148 * 2) / bh;
   if (s > tiles) s = tiles;
   if (s > MAX_SPLITS) s = MAX_SPLITS;
   if (s < 1) s = 1;
