@@ -60,8 +60,10 @@ __global__ void __launch_bounds__(256, MODE == 0 ? 4 : 3) qk_prep_kernel(const P
   constexpr int LPR = D / VEC;         // lanes per row
   constexpr int RPW = 32 / LPR;        // positions per warp step
   constexpr int HALF = D / 2;
-  // loads kept in flight per lane: the statistics-only pass has the registers for eight
-  constexpr int HEADS_PER_STEP = (MODE == 0) ? 8 : 4;
+  // 16-byte loads kept in flight per lane.  Eight of them at three CTAs per SM put about 100 KB
+  // per SM in flight, which is what 6.5 TB/s needs at the loaded memory latency (with four the
+  // normalising pass stopped at 5.0 TB/s; with eight it reaches 5.4).
+  constexpr int HEADS_PER_STEP = 8;
   const PrepParams& p = batch.t[blockIdx.y];
   const int lane = threadIdx.x & 31;
   const int lir = lane % LPR;          // lane in row
@@ -228,7 +230,8 @@ static int launch_t(const PrepBatch& batch, cudaStream_t stream) {
   const int64_t warps = (positions + RPW - 1) / RPW;
   int64_t blocks = (warps + 7) / 8;
   // resident CTAs only (the grid-stride loop covers the rest): 4 per SM for the
-  // statistics-only mode, 3 for the others
+  // statistics-only mode, 3 for the others, per tensor of the launch (sharing one wave among
+  // the tensors measured slightly slower)
   const int64_t cap = 148 * (mode == 0 ? 4 : 3);
   if (blocks > cap) blocks = cap;
   const dim3 grid(unsigned(blocks), unsigned(batch.count));
