@@ -39,6 +39,15 @@ class AttnArgs(C.Structure):
                 ("guard_words", C.c_void_p)]
 
 
+class AttnBwdArgs(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("d_o", C.c_void_p),
+                ("stat", C.c_void_p), ("stat_kind", C.c_void_p), ("sink", C.c_void_p), ("dq", C.c_void_p),
+                ("dk", C.c_void_p), ("dv", C.c_void_p), ("dsink", C.c_void_p), ("B", C.c_int), ("H", C.c_int),
+                ("Tq", C.c_int), ("Tk", C.c_int), ("D", C.c_int), ("n", C.c_int), ("c", C.c_float), ("causal", C.c_int),
+                ("q_stride", I64x3), ("k_stride", I64x3), ("v_stride", I64x3), ("o_stride", I64x3),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+
+
 class QkvProjArgs(C.Structure):
     _fields_ = [("x", C.c_void_p), ("w", C.c_void_p), ("qkv", C.c_void_p), ("q_gain", C.c_void_p),
                 ("k_gain", C.c_void_p), ("cos", C.c_void_p), ("sin", C.c_void_p), ("eps", C.c_float),
@@ -84,6 +93,8 @@ SYMBOLS = {
     "alg_qk_rms_fwd": (C.c_int, [C.POINTER(QkRmsArgs), C.c_void_p]),
     "alg_attn_workspace_bytes": (C.c_size_t, [C.POINTER(AttnArgs)]),
     "alg_attn_fwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
+    "alg_attn_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(AttnBwdArgs)]),
+    "alg_attn_bwd": (C.c_int, [C.POINTER(AttnBwdArgs), C.c_void_p]),
     "alg_decode_workspace_bytes": (C.c_size_t, [C.POINTER(DecodeArgs)]),
     "alg_attn_decode": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "alg_head_workspace_bytes": (C.c_size_t, [C.POINTER(HeadArgs)]),

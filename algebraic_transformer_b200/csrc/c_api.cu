@@ -267,6 +267,54 @@ int alg_glu_proj_fwd(const alg_glu_proj_args* a, void* stream_) {
   return launch_proj(p, a->x, a->w, 1, stream);
 }
 
+size_t alg_attn_bwd_workspace_bytes(const alg_attn_bwd_args* a) {
+  if (a == nullptr || a->B < 0 || a->H < 0 || a->Tq < 0) return 0;
+  return size_t(a->B) * a->H * a->Tq * sizeof(float);
+}
+
+int alg_attn_bwd(const alg_attn_bwd_args* a, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a == nullptr || a->q == nullptr || a->k == nullptr || a->v == nullptr || a->o == nullptr || a->d_o == nullptr ||
+      a->stat == nullptr || a->stat_kind == nullptr || a->dq == nullptr || a->dk == nullptr || a->dv == nullptr) {
+    set_error("attention backward: null tensor argument");
+    return ALG_ERR_INVALID;
+  }
+  if (int rc = check_common(a->D, a->n, a->c, ALG_BF16)) return rc;
+  if (a->B < 0 || a->H < 0 || a->Tq < 0 || a->Tk < 1) { set_error("attention backward: bad extents"); return ALG_ERR_INVALID; }
+  if (a->causal && a->Tk < a->Tq) { set_error("causal attention needs Tk >= Tq"); return ALG_ERR_INVALID; }
+  if ((a->sink == nullptr) != (a->dsink == nullptr)) { set_error("attention backward: sink and dsink come as a pair"); return ALG_ERR_INVALID; }
+  const size_t need = alg_attn_bwd_workspace_bytes(a);
+  if (need > 0 && (a->workspace == nullptr || a->workspace_bytes < need || !aligned16(a->workspace))) {
+    set_error("attention backward: workspace of %zu bytes (16-byte aligned) required, got %zu", need, a->workspace_bytes);
+    return ALG_ERR_WORKSPACE;
+  }
+  AttnBwdParams p{};
+  p.q = static_cast<const __nv_bfloat16*>(a->q); p.k = static_cast<const __nv_bfloat16*>(a->k);
+  p.v = static_cast<const __nv_bfloat16*>(a->v); p.o = static_cast<const __nv_bfloat16*>(a->o);
+  p.d_o = static_cast<const __nv_bfloat16*>(a->d_o);
+  p.stat = a->stat; p.stat_kind = a->stat_kind; p.sink = a->sink;
+  p.dq = static_cast<__nv_bfloat16*>(a->dq); p.dk = static_cast<__nv_bfloat16*>(a->dk); p.dv = static_cast<__nv_bfloat16*>(a->dv);
+  p.dsink = a->dsink; p.delta = static_cast<float*>(a->workspace);
+  p.B = a->B; p.H = a->H; p.Tq = a->Tq; p.Tk = a->Tk; p.D = a->D;
+  p.log2n = ilog2_exact(a->n);
+  p.scale = float(1.0 / (sqrt(double(a->D)) * double(a->c)));
+  p.inv_c = 1.0f / a->c;
+  p.n_f = float(a->n);
+  p.n_scale = p.n_f * p.scale;
+  p.causal = a->causal ? 1 : 0;
+  p.qs = strides_or_dense(a->q_stride, a->H, a->Tq, a->D);
+  p.ks = strides_or_dense(a->k_stride, a->H, a->Tk, a->D);
+  p.vs = strides_or_dense(a->v_stride, a->H, a->Tk, a->D);
+  p.os = strides_or_dense(a->o_stride, a->H, a->Tq, a->D);
+  if (!strides_ok(p.qs, ALG_BF16) || !strides_ok(p.ks, ALG_BF16) || !strides_ok(p.vs, ALG_BF16) || !strides_ok(p.os, ALG_BF16) ||
+      !aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->o) || !aligned16(a->d_o) ||
+      !aligned16(a->dq) || !aligned16(a->dk) || !aligned16(a->dv)) {
+    set_error("attention backward: rows must start on 16-byte boundaries");
+    return ALG_ERR_INVALID;
+  }
+  return launch_attn_bwd(p, stream);
+}
+
 size_t alg_decode_workspace_bytes(const alg_decode_args* a) {
   if (a == nullptr) return 0;
   return size_t(a->B) * a->H * decode_splits(a->B, a->H, a->Tk) * (a->D + 2) * sizeof(float);

@@ -69,6 +69,30 @@ __device__ __forceinline__ bool attn_use_shift(const AttnParams& p) {
   return !ok;
 }
 
+// ---- attn_bwd_mma.cu: attention backward ---------------------------------------------------
+struct AttnBwdParams {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  const __nv_bfloat16* o;
+  const __nv_bfloat16* d_o;  // strides of o
+  const float* stat;         // (B, H, Tq) saved by the forward
+  const int* stat_kind;      // device: ALG_VARIANT_NOSHIFT / ALG_VARIANT_SHIFT, as the forward wrote it
+  const float* sink;         // (H) or nullptr
+  __nv_bfloat16* dq;         // strides of q
+  __nv_bfloat16* dk;         // strides of k
+  __nv_bfloat16* dv;         // strides of v
+  float* dsink;              // (H) or nullptr
+  float* delta;              // (B, H, Tq) scratch: dO . o per row
+  int B, H, Tq, Tk, D;
+  int log2n;
+  float scale, inv_c;        // 1 / (sqrt(D) c), 1 / c
+  float n_scale, n_f;        // n * scale, n
+  int causal;
+  Strides3 qs, ks, vs, os;
+};
+int launch_attn_bwd(const AttnBwdParams& p, cudaStream_t stream);
+
 // ---- proj_sm100.cu: projection GEMMs with fused epilogues -------------------------------
 struct ProjParams {
   int M, K, N;             // activations (M, K), weights (N, K), both K-major bf16

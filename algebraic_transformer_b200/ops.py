@@ -331,6 +331,45 @@ def flash_attention(q, k, v, sink_logit=None, *, kind: str = "softmax", n: int =
     return o
 
 
+def flash_attention_backward(q, k, v, o, d_o, stat, stat_kind, sink_logit=None, *, n: int = 16, c: float = 8.0,
+                             causal: bool = True):
+    """Gradients of `flash_attention(kind="asinh", return_stat=True)`: `(dq, dk, dv, dsink)` from the
+    forward's inputs, its output `o`, the incoming gradient `d_o` and the saved `(stat, stat_kind)`
+    (the custom VJP of the reference, src/algebraic/kernels/flash.py:333-727).  bf16 tensors,
+    (B,H,T,D) with D contiguous; `dsink` is None without a sink."""
+    _require_cuda(q, k, v, o, d_o, stat, stat_kind)
+    if q.ndim != 4 or k.ndim != 4 or v.shape != k.shape or o.shape != q.shape or d_o.shape != q.shape:
+        raise ValueError("q, o, d_o must be (B, H, Tq, D) and k, v (B, H, Tk, D)")
+    if any(t.dtype != torch.bfloat16 for t in (q, k, v, o, d_o)):
+        raise ValueError("the backward kernels take bfloat16 tensors")
+    B, H, T, D = q.shape
+    Tk = k.shape[2]
+    if stat.shape != (B, H, T) or stat.dtype != torch.float32 or not stat.is_contiguous():
+        raise ValueError("stat must be the contiguous float32 (B, H, Tq) statistic of the forward")
+    if n < 2 or n & (n - 1):
+        raise ValueError("asinh kernel needs n to be a power of two")
+    if d_o.stride() != o.stride():
+        d_o = torch.empty_strided(o.shape, o.stride(), dtype=o.dtype, device=o.device).copy_(d_o)
+    sink = None
+    if sink_logit is not None:
+        s = torch.as_tensor(sink_logit, dtype=torch.float32, device=q.device).reshape(-1)
+        sink = s.expand(H).contiguous() if s.numel() == 1 else s.contiguous()
+    dq, dk, dv = (torch.empty_strided(t.shape, t.stride(), dtype=t.dtype, device=t.device) for t in (q, k, v))
+    dsink = torch.empty(H, dtype=torch.float32, device=q.device) if sink is not None else None
+    if q.numel() == 0:
+        return dq, dk, dv, dsink
+    a = L.AttnBwdArgs(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), o=o.data_ptr(), d_o=d_o.data_ptr(),
+                      stat=stat.data_ptr(), stat_kind=stat_kind.data_ptr(), sink=_ptr(sink), dq=dq.data_ptr(),
+                      dk=dk.data_ptr(), dv=dv.data_ptr(), dsink=_ptr(dsink), B=B, H=H, Tq=T, Tk=Tk, D=D, n=int(n),
+                      c=float(c), causal=int(bool(causal)), q_stride=_strides3(q), k_stride=_strides3(k),
+                      v_stride=_strides3(v), o_stride=_strides3(o))
+    lib = L.load()
+    ws = _workspace(q.device, lib.alg_attn_bwd_workspace_bytes(a), "attn_bwd")
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    L.check(lib.alg_attn_bwd(a, _stream()))
+    return dq, dk, dv, dsink
+
+
 def _attention_unshifted_unclamped(q, k, v, sink_logit=None, *, n=16, c=8.0, impl="auto", out=None):
     """The attention kernel the range guard selects when it holds, launched directly with no
     guard pre-pass (benchmarks use it to time that kernel alone)."""

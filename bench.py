@@ -478,6 +478,20 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
         extra[name] = {"workload": f"{M} tokens, d={dm}, " + ("3 x 12 heads of 64: GEMM + QK-norm + rotation + guard maxima"
                                                                if name.startswith("qkv") else f"f={ff}: GEMM + gate*ALU(up)"),
                        "ms": ms_g, "tflops": fl / (ms_g * 1e-3) / 1e12, "frac_of_bf16_peak": fl / (ms_g * 1e-3) / 1e12 / peak_tf}
+    del xs, wqkv, wgu, o_qkv, o_glu
+    # ---- attention backward (first "next" row): the 125M block's attention shape ----
+    Bb, Hb, Tb, Db = 16, 12, 1024, 64
+    qb_, kb_, vb_, dob_ = (torch.randn((Bb, Hb, Tb, Db), generator=g).bfloat16().to(dev) for _ in range(4))
+    sk = torch.zeros(Hb, device=dev)
+    ob_, stb_, kindb_ = A.flash_attention(qb_, kb_, vb_, sk, kind="asinh", n=16, c=8.0, range_guard=True, return_stat=True)
+    fnb = lambda i: A.ops.flash_attention_backward(qb_, kb_, vb_, ob_, dob_, stb_, kindb_, sk, n=16, c=8.0)  # noqa: E731
+    for i in range(3):
+        fnb(i)
+    ms_b = cuda_time(fnb, iters, sync)
+    flb = 2.5 * attn_flops(Bb, Hb, Tb, Db)
+    extra["attn_bwd"] = {"workload": f"({Bb},{Hb},{Tb},{Db}) bf16 causal: dq, dk, dv, dsink from the saved statistic (mma.sync kernels)",
+                         "ms": ms_b, "tflops": flb / (ms_b * 1e-3) / 1e12, "flop_convention": "2.5 x forward (five GEMMs)",
+                         "frac_of_bf16_peak": flb / (ms_b * 1e-3) / 1e12 / peak_tf}
     return extra
 
 

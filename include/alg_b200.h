@@ -138,6 +138,40 @@ ALG_API size_t alg_attn_workspace_bytes(const alg_attn_args* args);
 ALG_API int alg_attn_fwd(const alg_attn_args* args, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * Attention backward: dq, dk, dv and dsink from the forward's inputs, output and saved
+ * statistic.  Replaces the custom VJP of flash_attention, src/algebraic/kernels/flash.py:333-727
+ * (_dq_kernel, _dkv_kernel, _fused_bwd_kernel, _sink_mass_and_slope): the normalised weights of a
+ * tile are rebuilt from q, k and `stat`, the (T, T) matrix is never formed.
+ * bf16 tensors; q, o, d_o, dq: (B,H,Tq,D), k, v, dk, dv: (B,H,Tk,D), D contiguous, strides as in
+ * alg_attn_args (d_o uses o's strides, dq/dk/dv those of q/k/v).  stat: (B,H,Tq) fp32 and
+ * stat_kind (1 device int) exactly as alg_attn_fwd wrote them.  sink, dsink: (H) fp32 or NULL
+ * (dsink is zeroed, then accumulated).  workspace: B*H*Tq floats.
+ * ---------------------------------------------------------------------------------- */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* o;
+  const void* d_o;
+  const float* stat;
+  const int* stat_kind;
+  const float* sink;
+  void* dq;
+  void* dk;
+  void* dv;
+  float* dsink;
+  int B, H, Tq, Tk, D;
+  int n;
+  float c;
+  int causal;
+  int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3];
+  void* workspace;
+  size_t workspace_bytes;
+} alg_attn_bwd_args;
+ALG_API size_t alg_attn_bwd_workspace_bytes(const alg_attn_bwd_args* args);
+ALG_API int alg_attn_bwd(const alg_attn_bwd_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * Single-query decode against a KV cache (Tq = 1, every key visible), split over keys.
  * No reference kernel exists (the reference re-runs the full forward per token,
  * src/algebraic/benchmarking.py:250-263); semantics are asinh_power_weights with an

@@ -65,6 +65,15 @@ def test_invalid_arguments_fail_before_launch():
     assert lib.alg_glu_proj_fwd(gl, None) == L.ALG_ERR_INVALID     # f must be a multiple of 128
     gl.f, gl.ld_out = 256, 128
     assert lib.alg_glu_proj_fwd(gl, None) == L.ALG_ERR_INVALID     # output rows narrower than f
+    # attention backward
+    assert lib.alg_attn_bwd(L.AttnBwdArgs(), None) == L.ALG_ERR_INVALID
+    bw = L.AttnBwdArgs(q=16, k=16, v=16, o=16, d_o=16, stat=16, stat_kind=16, dq=16, dk=16, dv=16, B=1, H=2, Tq=64,
+                       Tk=64, D=64, n=16, c=8.0, causal=1)
+    assert lib.alg_attn_bwd_workspace_bytes(bw) == 1 * 2 * 64 * 4
+    assert lib.alg_attn_bwd(bw, None) == L.ALG_ERR_WORKSPACE         # delta scratch missing
+    bw.sink = 16                                                     # sink without dsink
+    assert lib.alg_attn_bwd(bw, None) == L.ALG_ERR_INVALID
+    assert b"pair" in lib.alg_last_error()
     with pytest.raises(ValueError):
         L.check(L.ALG_ERR_INVALID)
 

@@ -142,8 +142,8 @@ def test_guarded_attention_tail(sign, with_sink, magnitude, dtype):  # test_flas
 @pytest.mark.parametrize("row", [3, 700, 1023])
 @pytest.mark.parametrize("D", [64, 128])
 def test_guard_sees_one_bad_row_anywhere(which, row, D):
-    """A single out-of-range row of q, k or v, in any work item of the tensor-core kernel
-    (which takes the guard's maxima itself), must send the whole call down the shifted path."""
+    """A single out-of-range row of q, k or v anywhere in the tensors must send the whole call
+    down the shifted path (the guard's maxima cover every row of every head)."""
     shape = (1, 3, 1024, D)
     q, k, v = (randn(shape, 881 + i, torch.bfloat16) for i in range(3))
     if which == "v":
@@ -423,3 +423,47 @@ def test_embedding_cast_kernel():
     E = randn((1000, 72), 1, scale=0.02)
     got = A.cast_embedding(E.to(DEV)).cpu()
     assert torch.equal(got, E.bfloat16())
+
+
+# ------------------------------------------------------------------------ attention backward
+
+def _oracle_grads(q, k, v, sink, d_o, causal=True):
+    """Autograd through the CPU oracle (fp32 math on the bf16-rounded inputs)."""
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    sf = None if sink is None else sink.clone().float().requires_grad_(True)
+    out = R.asinh_attention(qf, kf, vf, n=16, c=8.0, sink_logit=sf, causal=causal)
+    out.backward(d_o.float())
+    return qf.grad, kf.grad, vf.grad, None if sf is None else sf.grad
+
+
+@pytest.mark.parametrize("shape,with_sink,causal", [((2, 3, 256, 64), True, True), ((1, 2, 512, 128), True, True),
+                                                   ((1, 2, 200, 64), False, True), ((1, 2, 192, 64), True, False)])
+def test_attention_backward_matches_oracle_autograd(shape, with_sink, causal):
+    """dq, dk, dv, dsink from the saved statistic (custom VJP of flash.py:333-727) against autograd
+    through the CPU oracle; ragged length 200 exercises the masked tails, 192 the non-causal form."""
+    q, k, v, d_o = (randn(shape, 900 + i, torch.bfloat16) for i in range(4))
+    sink = randn((shape[1],), 905) * 0.5 if with_sink else None
+    qd, kd, vd, dod, sd = dev(q, k, v, d_o, sink)
+    o, stat, kind = A.flash_attention(qd, kd, vd, sd, kind="asinh", n=16, c=8.0, block=shape[2], range_guard=True,
+                                      causal=causal, return_stat=True)
+    dq, dk, dv, ds = A.ops.flash_attention_backward(qd, kd, vd, o, dod, stat, kind, sd, n=16, c=8.0, causal=causal)
+    wq, wk, wv, ws = _oracle_grads(q, k, v, sink, d_o, causal)
+    assert rel_l2(dq, wq) < 2e-2 and rel_l2(dk, wk) < 2e-2 and rel_l2(dv, wv) < 2e-2
+    if with_sink:
+        assert rel_l2(ds, ws) < 2e-2
+
+
+def test_attention_backward_after_shifted_forward():
+    """Out-of-range inputs: the forward takes the max-shifted path and saves rho(-m) l^(-1/n); the
+    backward must rebuild the same weights from that statistic."""
+    shape = (1, 2, 256, 64)
+    q, k, v, d_o = (randn(shape, 950 + i, torch.bfloat16) for i in range(4))
+    q = (q.float() * 6).bfloat16()
+    k = (k.float() * 6).bfloat16()
+    qd, kd, vd, dod = dev(q, k, v, d_o)
+    o, stat, kind = A.flash_attention(qd, kd, vd, None, kind="asinh", n=16, c=8.0, block=256, range_guard=True,
+                                      return_stat=True)
+    assert int(kind) == 2
+    dq, dk, dv, _ = A.ops.flash_attention_backward(qd, kd, vd, o, dod, stat, kind, None, n=16, c=8.0)
+    wq, wk, wv, _ = _oracle_grads(q, k, v, None, d_o)
+    assert rel_l2(dq, wq) < 3e-2 and rel_l2(dk, wk) < 3e-2 and rel_l2(dv, wv) < 3e-2
