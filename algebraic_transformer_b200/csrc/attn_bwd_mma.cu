@@ -17,7 +17,9 @@
 //                        dP = dO V^T, dS, dQ += dS K.  Also writes delta and adds up dsink.
 //   attn_bwd_dkv_kernel  one CTA = 64 keys; for every query tile that sees them: S^T = K Q^T,
 //                        dP^T = V dO^T, dV += P^T dO, dK += dS^T Q.
-// S is therefore evaluated twice; in exchange no atomics and no transposes are needed.
+// S is therefore evaluated twice; in exchange no atomics and no transposes are needed.  The
+// tiles a CTA streams (K, V in the first kernel, Q, dO in the second) are double-buffered with
+// cp.async, so the next tile's copy runs under the current tile's MMAs.
 // bf16 tensors, fp32 accumulation.
 #include <math.h>
 
@@ -57,6 +59,23 @@ __device__ __forceinline__ void stage_tile(const __nv_bfloat16* base, int64_t ro
     *reinterpret_cast<uint4*>(s + r * LD + cv * 8) = val;
   }
 }
+
+// The same with cp.async (16-byte pieces, zero-filled past Tn): the copy of the next tile runs
+// while the current one is multiplied.  Completed with cp_async_wait<N>() + __syncthreads().
+template <int D>
+__device__ __forceinline__ void stage_tile_async(const __nv_bfloat16* base, int64_t row_stride, int row0, int Tn,
+                                                 __nv_bfloat16* s) {
+  constexpr int LD = D + 8, VPR = D / 8;
+  for (int i = threadIdx.x; i < BM * VPR; i += NTHREADS) {
+    const int r = i / VPR, cv = i % VPR;
+    const bool live = row0 + r < Tn;
+    const __nv_bfloat16* src = base + int64_t(live ? row0 + r : 0) * row_stride + cv * 8;
+    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(s + r * LD + cv * 8));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(live ? 16 : 0) : "memory");
+  }
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // c (16 x 64 per warp) = A[warp's 16 rows] . B^T, both tiles row-major [row][D] in shared memory
 template <int D>
@@ -131,8 +150,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_bwd_dq_kernel(const AttnBwdPara
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* sdO = sQ + TILE;
-  __nv_bfloat16* sK = sdO + TILE;
-  __nv_bfloat16* sV = sK + TILE;
+  __nv_bfloat16* sKV = sdO + TILE;                     // two stages of [K tile | V tile]
   __shared__ float s_delta[BM];
   __shared__ float s_sink[NTHREADS / 32];
 
@@ -193,11 +211,22 @@ __global__ void __launch_bounds__(NTHREADS) attn_bwd_dq_kernel(const AttnBwdPara
     const int last_key = min(p.Tk - 1, q0 + BM - 1 + off);
     kt_last = last_key < 0 ? -1 : min(kt_last, last_key / BN);
   }
+  if (kt_last >= 0) {
+    stage_tile_async<D>(kb, p.ks.t, 0, p.Tk, sKV);
+    stage_tile_async<D>(vb, p.vs.t, 0, p.Tk, sKV + TILE);
+  }
+  cp_async_commit();
   for (int kt = 0; kt <= kt_last; ++kt) {
     const int k0 = kt * BN;
-    __syncthreads();                                      // previous tile's reads are done
-    stage_tile<D>(kb, p.ks.t, k0, p.Tk, sK);
-    stage_tile<D>(vb, p.vs.t, k0, p.Tk, sV);
+    const __nv_bfloat16* sK = sKV + (kt & 1) * 2 * TILE;
+    const __nv_bfloat16* sV = sK + TILE;
+    if (kt < kt_last) {                                   // next tile into the other stage (its readers finished
+      __nv_bfloat16* nx = sKV + ((kt + 1) & 1) * 2 * TILE;   // at the barrier that ended the previous step)
+      stage_tile_async<D>(kb, p.ks.t, k0 + BN, p.Tk, nx);
+      stage_tile_async<D>(vb, p.vs.t, k0 + BN, p.Tk, nx + TILE);
+    }
+    cp_async_commit();
+    cp_async_wait<1>();                                   // this step's tile has landed
     __syncthreads();
     float s[BN / 8][4], dp[BN / 8][4];
     gemm_abt<D>(s, sQ, sK, warp, lane);                   // S  = Q K^T
@@ -216,6 +245,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_bwd_dq_kernel(const AttnBwdPara
         s[nt][e] = ds;
       }
     gemm_wb<D>(acc, s, sK, lane);                         // dQ += dS K
+    __syncthreads();                                      // this stage may be refilled by the next step
   }
   store_rows<D>(acc, p.dq + b * p.qs.b + h * p.qs.h, p.qs.t, row_a, p.Tq, tq);
 
@@ -240,9 +270,8 @@ __global__ void __launch_bounds__(NTHREADS) attn_bwd_dkv_kernel(const AttnBwdPar
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* sV = sK + TILE;
-  __nv_bfloat16* sQ = sV + TILE;
-  __nv_bfloat16* sdO = sQ + TILE;
-  __shared__ float s_stat[BM], s_delta[BM];
+  __nv_bfloat16* sQO = sV + TILE;                      // two stages of [Q tile | dO tile]
+  __shared__ float s_stat[2][BM], s_delta[2][BM];
 
   const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;                  // early key tiles are the heavy ones
   const int k0 = kt * BN, off = p.Tk - p.Tq;
@@ -272,17 +301,27 @@ __global__ void __launch_bounds__(NTHREADS) attn_bwd_dkv_kernel(const AttnBwdPar
     const int first_row = max(0, k0 - off);
     qt_first = first_row / BM;
   }
-  for (int qt = qt_first; qt < nqt; ++qt) {
+  auto stage_queries = [&](int qt, int stage) {           // Q, dO (asynchronously) and the rows' stat, delta
     const int q0 = qt * BM;
-    __syncthreads();                                        // previous tile's reads are done (and sK, sV visible)
-    stage_tile<D>(qb, p.qs.t, q0, p.Tq, sQ);
-    stage_tile<D>(dob, p.os.t, q0, p.Tq, sdO);
+    __nv_bfloat16* dst = sQO + stage * 2 * TILE;
+    stage_tile_async<D>(qb, p.qs.t, q0, p.Tq, dst);
+    stage_tile_async<D>(dob, p.os.t, q0, p.Tq, dst + TILE);
     if (threadIdx.x < BM) {
       const bool live = q0 + int(threadIdx.x) < p.Tq;
-      s_stat[threadIdx.x] = live ? p.stat[bh * p.Tq + q0 + threadIdx.x] : 0.f;
-      s_delta[threadIdx.x] = live ? p.delta[bh * p.Tq + q0 + threadIdx.x] : 0.f;
+      s_stat[stage][threadIdx.x] = live ? p.stat[bh * p.Tq + q0 + threadIdx.x] : 0.f;
+      s_delta[stage][threadIdx.x] = live ? p.delta[bh * p.Tq + q0 + threadIdx.x] : 0.f;
     }
-    __syncthreads();
+  };
+  if (qt_first < nqt) stage_queries(qt_first, 0);
+  cp_async_commit();
+  for (int qt = qt_first; qt < nqt; ++qt) {
+    const int q0 = qt * BM, stage = (qt - qt_first) & 1;
+    const __nv_bfloat16* sQ = sQO + stage * 2 * TILE;
+    const __nv_bfloat16* sdO = sQ + TILE;
+    if (qt + 1 < nqt) stage_queries(qt + 1, stage ^ 1);     // its readers finished at the previous step's last barrier
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();                                        // this step's tiles (and, first time, sK, sV) are visible
     float st[BN / 8][4], dpt[BN / 8][4];
     gemm_abt<D>(st, sK, sQ, warp, lane);                    // S^T  = K Q^T   (keys x queries)
     gemm_abt<D>(dpt, sV, sdO, warp, lane);                  // dP^T = V dO^T
@@ -295,14 +334,15 @@ __global__ void __launch_bounds__(NTHREADS) attn_bwd_dkv_kernel(const AttnBwdPar
         const int qc = nt * 8 + tq * 2 + (e & 1);           // query inside the tile (column of S^T)
         const int qi = q0 + qc, kj = (e < 2) ? key_a : key_b;
         float pw, slope;
-        weight_and_slope(st[nt][e], s_stat[qc], shifted, p, pw, slope);
-        float ds = slope * (dpt[nt][e] - s_delta[qc]);
+        weight_and_slope(st[nt][e], s_stat[stage][qc], shifted, p, pw, slope);
+        float ds = slope * (dpt[nt][e] - s_delta[stage][qc]);
         if (masked && !(qi < p.Tq && kj < p.Tk && (!p.causal || kj <= qi + off))) { pw = 0.f; ds = 0.f; }
         st[nt][e] = pw;
         dpt[nt][e] = ds;
       }
     gemm_wb<D>(dv, st, sdO, lane);                          // dV += P^T dO
     gemm_wb<D>(dk, dpt, sQ, lane);                          // dK += dS^T Q
+    __syncthreads();                                        // this stage may be refilled by the next step
   }
   store_rows<D>(dk, p.dk + b * p.ks.b + h * p.ks.h, p.ks.t, key_a, p.Tk, tq);
   store_rows<D>(dv, p.dv + b * p.vs.b + h * p.vs.h, p.vs.t, key_a, p.Tk, tq);
@@ -310,7 +350,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_bwd_dkv_kernel(const AttnBwdPar
 
 template <int D>
 int launch_d(const AttnBwdParams& p, cudaStream_t stream) {
-  constexpr size_t smem = size_t(4) * BM * (D + 8) * sizeof(__nv_bfloat16);
+  constexpr size_t smem = size_t(6) * BM * (D + 8) * sizeof(__nv_bfloat16);   // 2 resident tiles + 2 stages of 2
   static bool configured = false;     // idempotent attributes; benign if two threads race
   if (!configured) {
     ALG_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
