@@ -48,6 +48,12 @@ class AttnBwdArgs(C.Structure):
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
 
 
+class HeadBwdArgs(C.Structure):
+    _fields_ = [("h", C.c_void_p), ("e", C.c_void_p), ("targets", C.c_void_p), ("l", C.c_void_p), ("zt", C.c_void_p),
+                ("dz", C.c_void_p), ("N", C.c_int), ("d", C.c_int), ("V_local", C.c_int), ("vocab_offset", C.c_int),
+                ("V_total", C.c_int), ("n", C.c_int), ("c", C.c_float), ("upstream", C.c_float), ("status", C.c_void_p)]
+
+
 class QkvProjArgs(C.Structure):
     _fields_ = [("x", C.c_void_p), ("w", C.c_void_p), ("qkv", C.c_void_p), ("q_gain", C.c_void_p),
                 ("k_gain", C.c_void_p), ("cos", C.c_void_p), ("sin", C.c_void_p), ("eps", C.c_float),
@@ -95,6 +101,7 @@ SYMBOLS = {
     "alg_attn_fwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "alg_attn_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(AttnBwdArgs)]),
     "alg_attn_bwd": (C.c_int, [C.POINTER(AttnBwdArgs), C.c_void_p]),
+    "alg_head_bwd_dz": (C.c_int, [C.POINTER(HeadBwdArgs), C.c_void_p]),
     "alg_decode_workspace_bytes": (C.c_size_t, [C.POINTER(DecodeArgs)]),
     "alg_attn_decode": (C.c_int, [C.POINTER(DecodeArgs), C.c_void_p]),
     "alg_head_workspace_bytes": (C.c_size_t, [C.POINTER(HeadArgs)]),

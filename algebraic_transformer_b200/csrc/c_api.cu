@@ -315,6 +315,35 @@ int alg_attn_bwd(const alg_attn_bwd_args* a, void* stream_) {
   return launch_attn_bwd(p, stream);
 }
 
+int alg_head_bwd_dz(const alg_head_bwd_args* a, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a == nullptr || a->h == nullptr || a->e == nullptr || a->targets == nullptr || a->l == nullptr || a->zt == nullptr ||
+      a->dz == nullptr) {
+    set_error("head backward: null argument");
+    return ALG_ERR_INVALID;
+  }
+  if (a->N < 0 || a->V_local < 8 || a->V_local % 8 != 0 || a->d < 64 || a->d % 64 != 0 || a->vocab_offset < 0 ||
+      a->vocab_offset + a->V_local > a->V_total) {
+    set_error("head backward: V_local a multiple of 8 inside the vocabulary, d a multiple of 64");
+    return ALG_ERR_INVALID;
+  }
+  if (a->n < 2 || a->n > 32 || ilog2_exact(a->n) < 0 || !(a->c > 0.0f)) { set_error("head backward: n a power of two in [2, 32], c positive"); return ALG_ERR_INVALID; }
+  if (!aligned16(a->h) || !aligned16(a->e) || !aligned16(a->dz)) { set_error("head backward: 16-byte alignment required"); return ALG_ERR_INVALID; }
+  if (a->N == 0) return ALG_OK;
+  ProjParams p{};
+  p.M = a->N; p.K = a->d; p.N = a->V_local; p.ld_x = a->d;
+  p.out = static_cast<__nv_bfloat16*>(a->dz); p.ld_out = a->V_local;
+  p.targets = a->targets; p.l = a->l; p.zt = a->zt;
+  p.vocab_offset = a->vocab_offset; p.log2n = ilog2_exact(a->n);
+  p.inv_c = 1.0f / a->c;
+  p.clamp = float(0.25 * root_pow2(1e38 / double(a->V_total), a->n));       // fused_head.py:273
+  p.n_over_c = float(a->n) / a->c;
+  p.gscale = a->upstream / float(a->N);
+  p.D = 64;
+  p.status = a->status;
+  return launch_proj(p, a->h, a->e, 2, stream);
+}
+
 size_t alg_decode_workspace_bytes(const alg_decode_args* a) {
   if (a == nullptr) return 0;
   return size_t(a->B) * a->H * decode_splits(a->B, a->H, a->Tk) * (a->D + 2) * sizeof(float);

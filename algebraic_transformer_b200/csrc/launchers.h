@@ -111,9 +111,15 @@ struct ProjParams {
   // GLU epilogue
   int f;
   float beta;
+  // head-backward (dz) epilogue
+  const int* targets;      // (M) global vocabulary ids
+  const float* l;          // (M) row normaliser of the forward, summed over all shards
+  const float* zt;         // (M) target logit of the forward
+  int vocab_offset, log2n;
+  float inv_c, clamp, n_over_c, gscale;   // 1/c, logit clamp, n/c, upstream gradient / M
   int* status;
 };
-int launch_proj(const ProjParams& p, const void* x, const void* w, int epi, cudaStream_t stream);   // epi 0 QKV, 1 GLU
+int launch_proj(const ProjParams& p, const void* x, const void* w, int epi, cudaStream_t stream);   // epi 0 QKV, 1 GLU, 2 head dz
 
 // ---- decode -------------------------------------------------------------------------
 struct DecodeParams {

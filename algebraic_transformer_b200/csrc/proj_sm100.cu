@@ -7,6 +7,9 @@
 //        src/algebraic/model.py:165-174 with algebraic.py:76-83 (rms_norm), :172-179
 //        (apply_rotary) and kernels/flash.py:831-849 (guard).  The stand-alone kernels for
 //        these steps (qk_prep.cu) never run; the un-normalised projections never reach HBM.
+//   DZ   z = h . E^T once more, then the Alg-CE head's logit gradient dz from the saved row
+//        statistic (src/algebraic/kernels/fused_head.py:120-156), written as bf16 for the two
+//        library GEMMs dh = dz . E and dE = dz^T . h that follow, as the reference does.
 //   GLU  [gate | up] = x . W_gu^T, then out = gate * ALU(up) — src/algebraic/model.py:184-193
 //        with algebraic.py's alu.  The weight rows are interleaved in blocks of 128 (gate
 //        block j, up block j, ...) so that one 256-wide accumulator tile holds both operands of
@@ -50,7 +53,7 @@ constexpr size_t SMEM_BYTES = STAGE_OFF + 8 * WARP_STAGE_BYTES + 1024;
 static_assert(sizeof(Control) <= 256, "control block outgrew its slot");
 static_assert(SMEM_BYTES + 1024 <= 232448, "shared memory budget (dynamic + the static gain table)");
 
-enum { EPI_QKV = 0, EPI_GLU = 1 };
+enum { EPI_QKV = 0, EPI_GLU = 1, EPI_DZ = 2 };
 
 __device__ __forceinline__ __nv_bfloat162 as_bf162(uint32_t u) { return *reinterpret_cast<__nv_bfloat162*>(&u); }
 __device__ __forceinline__ uint32_t as_u32(__nv_bfloat162 h) { return *reinterpret_cast<uint32_t*>(&h); }
@@ -73,7 +76,8 @@ struct WarpOut {
 // math, bounded these kernels; staged, every store instruction writes four whole lines.  The
 // 16-byte chunks are XOR-swizzled by row so that both the row-wise writes and the line-wise
 // reads are free of bank conflicts.  Only this warp touches its buffer: __syncwarp suffices.
-__device__ __forceinline__ void store_rows64(const WarpOut& w, int lane, const uint32_t* v, int col) {
+// `cols` = how many of the 64 columns exist (a multiple of 8; 64 everywhere but at a ragged edge).
+__device__ __forceinline__ void store_rows64(const WarpOut& w, int lane, const uint32_t* v, int col, int cols = 64) {
 #pragma unroll
   for (int c = 0; c < 8; ++c)
     *reinterpret_cast<uint4*>(w.stage + lane * 128 + ((c ^ (lane & 7)) << 4)) =
@@ -84,9 +88,46 @@ __device__ __forceinline__ void store_rows64(const WarpOut& w, int lane, const u
   for (int k = 0; k < 8; ++k) {
     const int r = 4 * k + sub;
     const uint4 val = *reinterpret_cast<const uint4*>(w.stage + r * 128 + ((ch ^ (r & 7)) << 4));
-    if (r < w.rows) *reinterpret_cast<uint4*>(w.base + int64_t(r) * w.ld + col + ch * 8) = val;
+    if (r < w.rows && ch * 8 < cols) *reinterpret_cast<uint4*>(w.base + int64_t(r) * w.ld + col + ch * 8) = val;
   }
   __syncwarp();
+}
+
+// ---- head-backward epilogue: dz for 128 vocabulary columns of one row ------------------------
+// obj = mean_i (1 - pt_i), pt_i = w_it / l_i, w = rho(x)^n, x = min(z / c, clamp):
+//   d obj / d z_ij = a_i s_ij (p_ij - [j == t_i]),  a_i = g pt_i / N,  p = w / l,
+//   s = n / (c sqrt(1 + x^2)) where the clamp is not active, else 0
+// (src/algebraic/kernels/fused_head.py:120-156).  `a_i` and 1/l_i come in as arguments; `tgt` is
+// the target's column inside this shard (any value outside [0, V_local) when it lives elsewhere).
+__device__ __forceinline__ void dz_cols(const ProjParams& p, uint32_t taddr, const WarpOut& wo, int lane, int col0,
+                                        float a_i, float inv_l, int tgt) {
+#pragma unroll 1
+  for (int u = 0; u < 2; ++u) {                          // two units of 64 columns
+    uint32_t pk[32];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32(taddr + u * 64 + c * 32, r);
+      tmem_ld_wait();
+      const int cbase = col0 + u * 64 + c * 32;
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        float dz[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float xr = __uint_as_float(r[i + e]) * p.inv_c;
+          const float x = fminf(xr, p.clamp);
+          const float rs = rsqrtf(fmaf(x, x, 1.0f));
+          const float w = pow2n_rt(fmaf(fmaf(x, x, 1.0f), rs, x), p.log2n);      // rho_fast(x)^n
+          const float s = (xr < p.clamp) ? p.n_over_c * rs : 0.f;
+          dz[e] = a_i * s * (w * inv_l - ((cbase + i + e == tgt) ? 1.f : 0.f));
+        }
+        pk[c * 16 + (i >> 1)] = pack_bf16(dz[0], dz[1]);
+      }
+    }
+    const int first = col0 + u * 64;
+    if (first < p.N) store_rows64(wo, lane, pk, first, min(64, p.N - first));   // warp-uniform
+  }
 }
 
 // ---- QKV epilogue: one head (D accumulator columns from `taddr`) of one row ----------------
@@ -335,6 +376,17 @@ proj_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
           if (gcol >= p.N) break;
           qkv_head<D>(p, s_gain, tbuf + lcol, gcol / hd, tc, ts, wo, lane, gcol, live, best_q, best_k, best_v);
         }
+      } else if (EPI == EPI_DZ) {
+        // per-row constants of the head's backward: 1 / l_i and a_i = g pt_i / N
+        float inv_l = 0.f, a_i = 0.f;
+        int tgt = -1;
+        if (live) {
+          inv_l = 1.0f / p.l[row];
+          const float xt = fminf(p.zt[row] * p.inv_c, p.clamp);
+          a_i = p.gscale * pow2n_rt(rho_stable(xt), p.log2n) * inv_l;
+          tgt = p.targets[row] - p.vocab_offset;
+        }
+        dz_cols(p, tbuf + half * 128, wo, lane, n * BN + half * 128, a_i, inv_l, tgt);
       } else {
         const int fcol = n * 128 + half * 64;            // output feature of this thread's first column
         if (fcol < p.f)
@@ -408,6 +460,7 @@ int launch_proj(const ProjParams& p, const void* x, const void* w, int epi, cuda
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
   if (epi == 1) return launch_variant<EPI_GLU, 64>(tm_x, tm_w, p, grid, stream);
+  if (epi == 2) return launch_variant<EPI_DZ, 64>(tm_x, tm_w, p, grid, stream);
   return p.D == 64 ? launch_variant<EPI_QKV, 64>(tm_x, tm_w, p, grid, stream)
                    : launch_variant<EPI_QKV, 128>(tm_x, tm_w, p, grid, stream);
 }

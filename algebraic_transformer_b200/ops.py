@@ -507,6 +507,33 @@ def fused_head(h, embed, targets, *, kind: str = "ce", n: int = 16, c: float = 1
     return head_finalize(stats, n=n, c=c, vocab_total=V_total, want_nll=want_nll)
 
 
+def fused_head_backward(h, e_bf16, targets, stats, *, n: int = 8, c: float = 2.0, vocab_offset: int = 0,
+                        vocab_total: Optional[int] = None, upstream: float = 1.0):
+    """Gradients of the Alg-CE objective `mean(1 - pt)` with respect to the hidden states and this
+    shard's embedding rows: `(dh, de)` (src/algebraic/kernels/fused_head.py:120-156, 194-216).
+    `stats` is the forward's `(2, N)` statistic (`head_statistic`, summed over all shards).  The
+    logit gradient is rebuilt tile by tile from `stats` by one kernel and written as bf16; the two
+    products `dz . E` and `dz^T . h` are library GEMMs, as in the reference.  With several shards
+    the caller sums `dh` over them."""
+    _require_cuda(h, e_bf16, targets, stats)
+    if h.dtype != torch.bfloat16 or e_bf16.dtype != torch.bfloat16 or h.ndim != 2 or e_bf16.ndim != 2:
+        raise ValueError("fused_head_backward needs bf16 (N, d) hidden states and (V, d) embedding rows")
+    N, d = h.shape
+    V_local = e_bf16.shape[0]
+    if e_bf16.shape[1] != d or V_local % 8 or not h.is_contiguous() or not e_bf16.is_contiguous():
+        raise ValueError("contiguous operands, embedding (V_local, d) with V_local a multiple of 8")
+    if stats.shape != (2, N) or stats.dtype != torch.float32 or not stats.is_contiguous():
+        raise ValueError("stats must be the contiguous float32 (2, N) statistic of the forward")
+    V_total = V_local if vocab_total is None else int(vocab_total)
+    t = targets.to(torch.int32).contiguous()
+    dz = torch.empty((N, V_local), dtype=torch.bfloat16, device=h.device)
+    a = L.HeadBwdArgs(h=h.data_ptr(), e=e_bf16.data_ptr(), targets=t.data_ptr(), l=stats[0].data_ptr(),
+                      zt=stats[1].data_ptr(), dz=dz.data_ptr(), N=N, d=d, V_local=V_local, vocab_offset=int(vocab_offset),
+                      V_total=V_total, n=int(n), c=float(c), upstream=float(upstream), status=None)
+    L.check(L.load().alg_head_bwd_dz(a, _stream()))
+    return torch.mm(dz, e_bf16), torch.mm(dz.t(), h)
+
+
 def _fused_head_exchange(h, e_bf16, targets, exchange, *, n, c, vocab_offset, vocab_total, want_nll, impl):
     """`alg_head_fwd_exchange`: see include/alg_b200.h.  `exchange` is a dist.HeadExchange."""
     N, d = h.shape

@@ -350,6 +350,27 @@ typedef struct {
 } alg_glu_proj_args;
 ALG_API int alg_glu_proj_fwd(const alg_glu_proj_args* args, void* stream);
 
+/* Backward of the Alg-CE head, first half: the logit gradient.  Replaces fused_head._bwd_kernel
+ * (src/algebraic/kernels/fused_head.py:120-156), which also writes dz in bf16 and leaves
+ * dh = dz . E and dE = dz^T . h to library matmuls (fused_head.py:194-216).
+ * h: (N, d) bf16; e: (V_local, d) bf16; targets: (N) int32 global ids; l, zt: (N) fp32 — the
+ * forward's statistic, l summed over all vocabulary shards; dz: (N, V_local) bf16 contiguous
+ * out, V_local a multiple of 8; upstream = d loss / d objective.  obj = mean(1 - pt). */
+typedef struct {
+  const void* h;
+  const void* e;
+  const int* targets;
+  const float* l;
+  const float* zt;
+  void* dz;
+  int N, d, V_local, vocab_offset, V_total;
+  int n;
+  float c;
+  float upstream;
+  int* status;             /* device int, may be NULL */
+} alg_head_bwd_args;
+ALG_API int alg_head_bwd_dz(const alg_head_bwd_args* args, void* stream);
+
 /* Failure-detection self-test (no counterpart in the reference).  Launches a one-CTA kernel
  * whose threads wait, through the same bounded-wait helper every TMA/tcgen05 kernel here
  * uses, on a barrier that is never signalled.  After `budget_ns` (at most 1 s) the wait

@@ -453,6 +453,32 @@ def test_attention_backward_matches_oracle_autograd(shape, with_sink, causal):
         assert rel_l2(ds, ws) < 2e-2
 
 
+def test_head_backward_matches_oracle_autograd():
+    """dh and dE of the Alg-CE objective (fused_head.py:120-156, 194-216) against autograd through the
+    oracle's dense head; ragged N and V; then the same through two vocabulary shards."""
+    N, d, V = 300, 128, 1000
+    h = randn((N, d), 971).bfloat16()
+    E = (randn((V, d), 972) * 0.3).bfloat16()
+    g = torch.Generator().manual_seed(973)
+    t = torch.randint(0, V, (N,), generator=g)
+    hf, ef = h.float().requires_grad_(True), E.float().requires_grad_(True)
+    obj, _ = R.algebraic_likelihood_lean(hf @ ef.t(), t, 8, 2.0)
+    obj.backward()
+    hd, Ed, td = dev(h, E, t)
+    stats = A.head_statistic(hd, Ed, td.int(), n=8, c=2.0)
+    dh, de = A.ops.fused_head_backward(hd, Ed, td, stats, n=8, c=2.0)
+    assert rel_l2(dh, hf.grad) < 2e-2 and rel_l2(de, ef.grad) < 2e-2
+    # two shards: the statistic is summed over them, each shard returns its rows of dE and a part of dh
+    lo = 504
+    s0 = A.head_statistic(hd, Ed[:lo].contiguous(), td.int(), n=8, c=2.0, vocab_offset=0, vocab_total=V)
+    s1 = A.head_statistic(hd, Ed[lo:].contiguous(), td.int(), n=8, c=2.0, vocab_offset=lo, vocab_total=V)
+    both = s0 + s1
+    dh0, de0 = A.ops.fused_head_backward(hd, Ed[:lo].contiguous(), td, both, n=8, c=2.0, vocab_offset=0, vocab_total=V)
+    dh1, de1 = A.ops.fused_head_backward(hd, Ed[lo:].contiguous(), td, both, n=8, c=2.0, vocab_offset=lo, vocab_total=V)
+    assert rel_l2(dh0.float() + dh1.float(), hf.grad) < 2e-2
+    assert rel_l2(torch.cat([de0, de1]), ef.grad) < 2e-2
+
+
 def test_attention_backward_after_shifted_forward():
     """Out-of-range inputs: the forward takes the max-shifted path and saves rho(-m) l^(-1/n); the
     backward must rebuild the same weights from that statistic."""
