@@ -492,6 +492,21 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
     extra["attn_bwd"] = {"workload": f"({Bb},{Hb},{Tb},{Db}) bf16 causal: dq, dk, dv, dsink from the saved statistic (mma.sync kernels)",
                          "ms": ms_b, "tflops": flb / (ms_b * 1e-3) / 1e12, "flop_convention": "2.5 x forward (five GEMMs)",
                          "frac_of_bf16_peak": flb / (ms_b * 1e-3) / 1e12 / peak_tf}
+    del qb_, kb_, vb_, dob_, ob_, stb_
+    # ---- Alg-CE head backward (second "next" row): configuration 2's shape ----
+    Nh, dh_, Vh = HEAD["N"], HEAD["d"], HEAD["V"]
+    hh = torch.randn((Nh, dh_), generator=g).bfloat16().to(dev)
+    eh = (torch.randn((Vh, dh_), generator=g) * 0.02).bfloat16().to(dev)
+    th = torch.randint(0, HEAD["target_hi"], (Nh,), generator=g).to(torch.int32).to(dev)
+    sth = A.head_statistic(hh, eh, th, n=HEAD["n"], c=HEAD["c"])
+    fnh = lambda i: A.ops.fused_head_backward(hh, eh, th, sth, n=HEAD["n"], c=HEAD["c"])  # noqa: E731
+    for i in range(3):
+        fnh(i)
+    ms_hb = cuda_time(fnh, iters, sync)
+    flh = 3 * 2.0 * Nh * dh_ * Vh                          # z again, dz . E, dz^T . h
+    extra["alg_ce_head_bwd"] = {"workload": f"N={Nh}, d={dh_}, V={Vh}: dz kernel (tcgen05 GEMM + epilogue, bf16 dz to HBM) + two cuBLAS GEMMs",
+                                "ms": ms_hb, "tflops": flh / (ms_hb * 1e-3) / 1e12,
+                                "frac_of_bf16_peak": flh / (ms_hb * 1e-3) / 1e12 / peak_tf}
     return extra
 
 

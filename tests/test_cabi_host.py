@@ -65,6 +65,13 @@ def test_invalid_arguments_fail_before_launch():
     assert lib.alg_glu_proj_fwd(gl, None) == L.ALG_ERR_INVALID     # f must be a multiple of 128
     gl.f, gl.ld_out = 256, 128
     assert lib.alg_glu_proj_fwd(gl, None) == L.ALG_ERR_INVALID     # output rows narrower than f
+    # head backward
+    assert lib.alg_head_bwd_dz(L.HeadBwdArgs(), None) == L.ALG_ERR_INVALID
+    hb = L.HeadBwdArgs(h=16, e=16, targets=16, l=16, zt=16, dz=16, N=128, d=768, V_local=1001, vocab_offset=0,
+                       V_total=1001, n=8, c=2.0, upstream=1.0)
+    assert lib.alg_head_bwd_dz(hb, None) == L.ALG_ERR_INVALID        # V_local must be a multiple of 8
+    hb.V_local, hb.V_total, hb.n = 1000, 1000, 12
+    assert lib.alg_head_bwd_dz(hb, None) == L.ALG_ERR_INVALID        # n must be a power of two
     # attention backward
     assert lib.alg_attn_bwd(L.AttnBwdArgs(), None) == L.ALG_ERR_INVALID
     bw = L.AttnBwdArgs(q=16, k=16, v=16, o=16, d_o=16, stat=16, stat_kind=16, dq=16, dk=16, dv=16, B=1, H=2, Tq=64,
