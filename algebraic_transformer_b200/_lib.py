@@ -45,7 +45,8 @@ class AttnBwdArgs(C.Structure):
                 ("dk", C.c_void_p), ("dv", C.c_void_p), ("dsink", C.c_void_p), ("B", C.c_int), ("H", C.c_int),
                 ("Tq", C.c_int), ("Tk", C.c_int), ("D", C.c_int), ("n", C.c_int), ("c", C.c_float), ("causal", C.c_int),
                 ("q_stride", I64x3), ("k_stride", I64x3), ("v_stride", I64x3), ("o_stride", I64x3),
-                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
+                ("impl", C.c_int)]
 
 
 class HeadBwdArgs(C.Structure):

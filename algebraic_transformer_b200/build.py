@@ -20,7 +20,7 @@ LIBDIR = os.path.join(PKG, "lib")
 OBJDIR = os.path.join(PKG, "build")
 LIB = os.path.join(LIBDIR, "libalg_b200.so")
 
-SOURCES = ["c_api.cu", "tmap.cu", "qk_prep.cu", "attn_mma.cu", "attn_sm100.cu", "head_mma.cu", "head_sm100.cu", "head_static.cu", "decode.cu", "prefill_ops.cu", "selftest.cu", "head_exchange.cu", "proj_sm100.cu", "attn_bwd_mma.cu"]
+SOURCES = ["c_api.cu", "tmap.cu", "qk_prep.cu", "attn_mma.cu", "attn_sm100.cu", "head_mma.cu", "head_sm100.cu", "head_static.cu", "decode.cu", "prefill_ops.cu", "selftest.cu", "head_exchange.cu", "proj_sm100.cu", "attn_bwd_mma.cu", "attn_bwd_sm100.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
               "-Xptxas", "-v"]

@@ -370,6 +370,7 @@ int launch_d(const AttnBwdParams& p, cudaStream_t stream) {
 
 int launch_attn_bwd(const AttnBwdParams& p, cudaStream_t stream) {
   if (p.B == 0 || p.H == 0 || p.Tq == 0 || p.Tk == 0) return ALG_OK;
+  if (!p.force_mma && attn_bwd_tcgen05_supports(p)) return launch_attn_bwd_tcgen05(p, stream);
   if (p.dsink != nullptr) ALG_CUDA_TRY(cudaMemsetAsync(p.dsink, 0, sizeof(float) * p.H, stream));
   if (p.D == 64) return launch_d<64>(p, stream);
   if (p.D == 128) return launch_d<128>(p, stream);

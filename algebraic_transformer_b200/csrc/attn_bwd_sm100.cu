@@ -1,0 +1,373 @@
+// Asinh-power attention backward on tcgen05 tensor cores (the throughput path of alg_attn_bwd).
+//
+// Same mathematics as attn_bwd_mma.cu (reference: the custom VJP of
+// src/algebraic/kernels/flash.py:333-727): with x = q.k / (sqrt(D) c), p rebuilt from the saved
+// statistic, delta_i = dO_i . o_i and dP = dO V^T,
+//   dS = n p (dP - delta) / sqrt(1 + x^2) / (sqrt(D) c),  dQ = dS K,  dK = dS^T Q,  dV = P^T dO.
+// bf16, causal, Tq == Tk a multiple of 128, head_dim 64 or 128; everything else stays on the
+// mma.sync kernels.
+//
+// One kernel template, two modes, one CTA per 128-row tile of one (batch, head):
+//   MODE 0 (dQ, dsink)  rows = queries.  Resident: Q, dO tiles.  Streamed: K_j, V_j for every key
+//                       tile up to the diagonal.  S = Q K_j^T, dP = dO V_j^T, dQ += dS K_j.
+//   MODE 1 (dK, dV)     rows = keys.  Resident: K, V tiles.  Streamed: Q_i, dO_i for every query
+//                       tile from the diagonal on.  S^T = K Q_i^T, dP^T = V dO_i^T,
+//                       dV += P^T dO_i, dK += dS^T Q_i.
+// Roles: warp 0 (one lane) TMA producer, warp 1 (one lane) tcgen05.mma issuer, warps 2..9 the
+// element-wise stage (thread = row, two column halves of 64).  Tensor memory: the two score
+// tiles (128 columns each) and one or two D-column accumulators; the bf16 operands of the second
+// products (P^T, dS) are written back over the columns their own thread has already read — half
+// h keeps its 64 packed values in columns [64 h, 64 h + 32) — and fed to the tensor core from
+// tensor memory (TS form) with the streamed tile as an MN-major B operand, so nothing is
+// transposed or staged.  A step is serial (scores -> element-wise -> products): with both
+// accumulators of MODE 1 all 512 columns are taken and there is no room to double-buffer.
+// Every mbarrier wait is bounded; a wait that runs out reports ALG_DEV_TIMEOUT.
+#include "common.cuh"
+#include "launchers.h"
+#include "sm100_ptx.cuh"
+
+namespace alg {
+namespace {
+
+using namespace sm100;
+
+constexpr int BT = 128, NTHREADS = 320, EW_THREADS = 256;
+constexpr int PANEL_BYTES = 128 * 128;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr int MAX_STEPS = 4;
+
+template <int D> struct Cfg {
+  static constexpr int PANELS = D / 64;
+  static constexpr int TILE_BYTES = PANELS * PANEL_BYTES;
+  static constexpr int NS = (D == 128) ? 2 : 4;                 // ring depth in steps (two tiles per step)
+  static constexpr int RES_OFF = 0;
+  static constexpr int RING_OFF = 2 * TILE_BYTES;
+  static constexpr int CTL_OFF = RING_OFF + NS * 2 * TILE_BYTES;
+  static constexpr uint32_t S_COL = 0, DP_COL = 128, ACC0_COL = 256, ACC1_COL = 256 + D;
+  static constexpr uint32_t IDESC_S = make_idesc_bf16(BT, BT, 0, 0);
+  static constexpr uint32_t IDESC_TS = make_idesc_bf16(BT, D, 0, 1);
+};
+
+struct __align__(16) Control {
+  uint64_t res_full, full[MAX_STEPS], empty[MAX_STEPS], s_full, e_done, acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+  float sink_part[8];
+};
+
+template <int D> constexpr size_t smem_bytes() { return size_t(Cfg<D>::CTL_OFF) + sizeof(Control) + 1024; }
+
+// 32 scores + 32 dP values of this thread's row -> 16 packed weights and 16 packed dS.
+// `stat` / `delta` index: by row (MODE 0: one value) or by column (MODE 1: arrays of 32).
+template <bool SHIFTED, bool BY_COLUMN>
+__device__ __forceinline__ void weigh_chunk(const uint32_t* s, const uint32_t* dp, const AttnBwdParams& p, float stat_row,
+                                            float delta_row, const float* stat_col, const float* delta_col, int log2n,
+                                            bool diag, int row, int col0, bool row_is_query, uint32_t* pw_out,
+                                            uint32_t* ds_out) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    float pw[2], ds[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const float st = BY_COLUMN ? stat_col[i + e] : stat_row;
+      const float dl = BY_COLUMN ? delta_col[i + e] : delta_row;
+      const float x = __uint_as_float(s[i + e]) * p.scale;
+      const float rad = fmaf(x, x, 1.0f);
+      const float rs = rsqrt_approx(rad);
+      float w;
+      if (SHIFTED) w = pow2n_rt(rho_stable(x) * st, log2n);
+      else w = pow2n_rt(fmaf(rad, rs, x), log2n) * st;
+      // causal: key <= query.  Rows are queries in MODE 0 (mask col > row), keys in MODE 1 (mask col < row)
+      if (diag && (row_is_query ? (col0 + i + e > row) : (col0 + i + e < row))) w = 0.f;
+      pw[e] = w;
+      ds[e] = p.n_scale * w * rs * (__uint_as_float(dp[i + e]) - dl);
+    }
+    pw_out[i >> 1] = pack_bf16(pw[0], pw[1]);
+    ds_out[i >> 1] = pack_bf16(ds[0], ds[1]);
+  }
+}
+
+template <int D, int MODE>
+__global__ void __launch_bounds__(NTHREADS, 1)
+attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                   const AttnBwdParams p) {
+  using C = Cfg<D>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Control* ctl = reinterpret_cast<Control*>(smem + C::CTL_OFF);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&ctl->res_full, 1);
+    for (int i = 0; i < C::NS; ++i) { mbar_init(&ctl->full[i], 1); mbar_init(&ctl->empty[i], 1); }
+    mbar_init(&ctl->s_full, 1);
+    mbar_init(&ctl->e_done, EW_THREADS);
+    mbar_init(&ctl->acc_full, 1);
+    ctl->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&ctl->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  const BoundedWait bw{&ctl->abort_flag, 1000000000ull};
+
+  const int nt = p.Tq / BT;
+  const int h = blockIdx.x, b = blockIdx.y;
+  // heavy tiles first, over all heads: late query tiles see many keys, early key tiles are seen by many queries
+  const int tile = (MODE == 0) ? nt - 1 - int(blockIdx.z) : int(blockIdx.z);
+  const int row0 = tile * BT;
+  const int first = (MODE == 0) ? 0 : tile;                  // streamed tiles first .. last, diagonal = `tile`
+  const int last = (MODE == 0) ? tile : nt - 1;
+  const int nsteps = last - first + 1;
+  const bool shifted = *p.stat_kind == ALG_VARIANT_SHIFT;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v); tma_prefetch_desc(&tm_do);
+      const CUtensorMap* res0 = (MODE == 0) ? &tm_q : &tm_k;   // A operand of the first score product
+      const CUtensorMap* res1 = (MODE == 0) ? &tm_do : &tm_v;  // A operand of the second
+      const CUtensorMap* str0 = (MODE == 0) ? &tm_k : &tm_q;   // their streamed B operands
+      const CUtensorMap* str1 = (MODE == 0) ? &tm_v : &tm_do;
+      mbar_arrive_expect_tx(&ctl->res_full, 2 * C::TILE_BYTES);
+      for (int pn = 0; pn < C::PANELS; ++pn) {
+        tma_load_4d(smem + C::RES_OFF + pn * PANEL_BYTES, res0, &ctl->res_full, pn * 64, row0, h, b);
+        tma_load_4d(smem + C::RES_OFF + C::TILE_BYTES + pn * PANEL_BYTES, res1, &ctl->res_full, pn * 64, row0, h, b);
+      }
+      for (int j = 0; j < nsteps; ++j) {
+        const int slot = j % C::NS;
+        if (!bw.wait(&ctl->empty[slot], ((j / C::NS) & 1u) ^ 1u)) break;
+        unsigned char* dst = smem + C::RING_OFF + slot * 2 * C::TILE_BYTES;
+        mbar_arrive_expect_tx(&ctl->full[slot], 2 * C::TILE_BYTES);
+        for (int pn = 0; pn < C::PANELS; ++pn) {
+          tma_load_4d(dst + pn * PANEL_BYTES, str0, &ctl->full[slot], pn * 64, (first + j) * BT, h, b);
+          tma_load_4d(dst + C::TILE_BYTES + pn * PANEL_BYTES, str1, &ctl->full[slot], pn * 64, (first + j) * BT, h, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t res_addr = smem_u32(smem + C::RES_OFF), ring_addr = smem_u32(smem + C::RING_OFF);
+      const uint32_t a0_lo = sw128_desc_lo(res_addr, 16), a1_lo = sw128_desc_lo(res_addr + C::TILE_BYTES, 16);
+      // S-like product: d = A . B^T, both K-major tiles of D columns
+      auto issue_scores = [&](uint32_t d_tmem, uint32_t a_lo, uint32_t b_addr) {
+        const uint32_t b_lo = sw128_desc_lo(b_addr, 16);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = ((ks >> 2) * PANEL_BYTES + (ks & 3) * 32) >> 4;
+          umma_f16_ss_parts(d_tmem, a_lo + off, SW128_DESC_HI, b_lo + off, SW128_DESC_HI, C::IDESC_S, ks != 0 ? 1u : 0u);
+        }
+      };
+      // acc += W . B: W = packed bf16 in tensor memory (64 values per column half, see the header), B = a
+      // streamed [row][D] tile read as an MN-major operand
+      auto issue_product = [&](uint32_t d_tmem, uint32_t w_tmem, uint32_t b_addr, bool first_step) {
+        const uint32_t b_lo = sw128_desc_lo(b_addr, PANEL_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < BT / 16; ++ks) {
+          const uint32_t a_col = (ks < 4) ? ks * 8 : 64 + (ks - 4) * 8;
+          umma_f16_ts_parts(d_tmem, w_tmem + a_col, b_lo + ks * (2048 >> 4), SW128_DESC_HI, C::IDESC_TS,
+                            (first_step && ks == 0) ? 0u : 1u);
+        }
+      };
+      bool ok = bw.wait(&ctl->res_full, 0);
+      for (int j = 0; j < nsteps && ok; ++j) {
+        const int slot = j % C::NS;
+        if (!bw.wait(&ctl->full[slot], (j / C::NS) & 1u)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t t0 = ring_addr + slot * 2 * C::TILE_BYTES, t1 = t0 + C::TILE_BYTES;
+        issue_scores(tmem_base + C::S_COL, a0_lo, t0);      // S (or S^T)
+        issue_scores(tmem_base + C::DP_COL, a1_lo, t1);     // dP (or dP^T)
+        umma_commit(&ctl->s_full);
+        if (!bw.wait(&ctl->e_done, j & 1u)) { ok = false; break; }
+        tc_fence_after();
+        if (MODE == 0) {
+          issue_product(tmem_base + C::ACC0_COL, tmem_base + C::DP_COL, t0, j == 0);   // dQ += dS K_j
+        } else {
+          issue_product(tmem_base + C::ACC0_COL, tmem_base + C::S_COL, t1, j == 0);    // dV += P^T dO_i
+          issue_product(tmem_base + C::ACC1_COL, tmem_base + C::DP_COL, t0, j == 0);   // dK += dS^T Q_i
+        }
+        umma_commit(&ctl->empty[slot]);
+      }
+      if (ok) umma_commit(&ctl->acc_full);
+    }
+  } else {
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    const int r = quarter * 32 + lane;                        // row inside the tile
+    const int row = row0 + r;
+    const uint32_t lane_sel = uint32_t(quarter * 32) << 16;
+    const int64_t bh = int64_t(b) * p.H + h;
+    float stat_row = 0.f, delta_row = 0.f;
+    if (MODE == 0) { stat_row = p.stat[bh * p.Tq + row]; delta_row = p.delta[bh * p.Tq + row]; }
+    const uint32_t s_t = tmem_base + lane_sel + C::S_COL + half * 64, dp_t = tmem_base + lane_sel + C::DP_COL + half * 64;
+    bool ok = true;
+    for (int j = 0; j < nsteps && ok; ++j) {
+      const int other0 = (first + j) * BT;                    // first row of the streamed tile
+      const bool diag = (first + j) == tile;
+      if (!bw.wait(&ctl->s_full, j & 1u)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t s[32], dp[32], pw[16], ds[16];
+        tmem_ld_32x32(s_t + c * 32, s);
+        tmem_ld_32x32(dp_t + c * 32, dp);
+        float stc[32], dlc[32];
+        if (MODE == 1) {                                       // statistic and delta of the 32 streamed queries
+          const float4* sp = reinterpret_cast<const float4*>(p.stat + bh * p.Tq + other0 + half * 64 + c * 32);
+          const float4* dq = reinterpret_cast<const float4*>(p.delta + bh * p.Tq + other0 + half * 64 + c * 32);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 a = __ldg(sp + i), d4 = __ldg(dq + i);
+            stc[4 * i] = a.x; stc[4 * i + 1] = a.y; stc[4 * i + 2] = a.z; stc[4 * i + 3] = a.w;
+            dlc[4 * i] = d4.x; dlc[4 * i + 1] = d4.y; dlc[4 * i + 2] = d4.z; dlc[4 * i + 3] = d4.w;
+          }
+        }
+        tmem_ld_wait();
+        const int col0 = half * 64 + c * 32;                   // column inside the streamed tile
+        if (shifted) weigh_chunk<true, MODE == 1>(s, dp, p, stat_row, delta_row, stc, dlc, p.log2n, diag, r, col0, MODE == 0, pw, ds);
+        else weigh_chunk<false, MODE == 1>(s, dp, p, stat_row, delta_row, stc, dlc, p.log2n, diag, r, col0, MODE == 0, pw, ds);
+        // packed outputs over columns this thread has read already: chunk c -> [64 half + 16 c, +16)
+        if (MODE == 1) tmem_st_32x16(tmem_base + lane_sel + C::S_COL + half * 64 + c * 16, pw);
+        tmem_st_32x16(tmem_base + lane_sel + C::DP_COL + half * 64 + c * 16, ds);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&ctl->e_done);
+    }
+    if (ok && bw.wait(&ctl->acc_full, 0)) {
+      tc_fence_after();
+      constexpr int CPT = D / 2;                               // accumulator columns per thread
+      __nv_bfloat16* out0 = ((MODE == 0) ? p.dq + b * p.qs.b + h * p.qs.h + int64_t(row) * p.qs.t
+                                         : p.dv + b * p.vs.b + h * p.vs.h + int64_t(row) * p.vs.t) + half * CPT;
+      __nv_bfloat16* out1 = (MODE == 1) ? p.dk + b * p.ks.b + h * p.ks.h + int64_t(row) * p.ks.t + half * CPT : nullptr;
+#pragma unroll 1
+      for (int which = 0; which < (MODE == 0 ? 1 : 2); ++which) {
+        const uint32_t acc_t = tmem_base + lane_sel + (which == 0 ? C::ACC0_COL : C::ACC1_COL) + half * CPT;
+        __nv_bfloat16* dst = which == 0 ? out0 : out1;
+#pragma unroll 1
+        for (int c = 0; c < CPT / 32; ++c) {
+          uint32_t a[32];
+          tmem_ld_32x32(acc_t + c * 32, a);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) =
+                make_uint4(pack_bf16(__uint_as_float(a[8 * i]), __uint_as_float(a[8 * i + 1])),
+                           pack_bf16(__uint_as_float(a[8 * i + 2]), __uint_as_float(a[8 * i + 3])),
+                           pack_bf16(__uint_as_float(a[8 * i + 4]), __uint_as_float(a[8 * i + 5])),
+                           pack_bf16(__uint_as_float(a[8 * i + 6]), __uint_as_float(a[8 * i + 7])));
+        }
+      }
+    }
+    // dsink: -sum_i delta_i p_sink,i n / (c sqrt(1 + (b/c)^2)), one atomic per warp of the first column half
+    if (MODE == 0 && p.sink != nullptr && p.dsink != nullptr && half == 0) {
+      const float bs = p.sink[h] * p.inv_c;
+      const float ps = shifted ? pow2n_rt(rho_stable(bs) * stat_row, p.log2n) : pow2n_rt(rho_stable(bs), p.log2n) * stat_row;
+      float part = -delta_row * ps * p.n_f * p.inv_c * rsqrtf(fmaf(bs, bs, 1.0f));
+      part = warp_sum(part);
+      if (lane == 0) atomicAdd(p.dsink + h, part);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (ctl->abort_flag != 0) {
+    if (threadIdx.x == 0) {
+      if (p.status != nullptr) atomicExch(p.status, ALG_DEV_TIMEOUT);
+      const uint64_t t0 = global_timer_ns();                 // let issued loads land before shared memory is released
+      while (global_timer_ns() - t0 < 200000ull) { }
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// delta_i = dO_i . o_i, one row per LPR lanes
+template <int D>
+__global__ void __launch_bounds__(256) attn_delta_kernel(const AttnBwdParams p) {
+  constexpr int LPR = D / 8, RPW = 32 / LPR;
+  const int lane = threadIdx.x & 31, lir = lane % LPR, sub = lane / LPR;
+  const int64_t rows = int64_t(p.B) * p.H * p.Tq;
+  const int64_t warp_global = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t warps_total = (int64_t(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t r0 = warp_global * RPW; r0 < rows; r0 += warps_total * RPW) {
+    const int64_t row = min(r0 + sub, rows - 1);
+    const int t = int(row % p.Tq);
+    const int64_t bh = row / p.Tq;
+    const int h = int(bh % p.H);
+    const int64_t b = bh / p.H;
+    const int64_t off = b * p.os.b + h * p.os.h + int64_t(t) * p.os.t + lir * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(p.o + off), c = *reinterpret_cast<const uint4*>(p.d_o + off);
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&c);
+    float d = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 fa = __bfloat1622float2(a2[i]), fc = __bfloat1622float2(c2[i]);
+      d = fmaf(fa.x, fc.x, d);
+      d = fmaf(fa.y, fc.y, d);
+    }
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+    if (lir == 0 && r0 + sub < rows) p.delta[row] = d;
+  }
+}
+
+int make_map(CUtensorMap* tm, const void* base, const Strides3& s, int B, int H, int T, int D) {
+  const uint64_t dims[4] = {uint64_t(D), uint64_t(T), uint64_t(H), uint64_t(B)};
+  const uint64_t strides[3] = {uint64_t(s.t), uint64_t(s.h), uint64_t(s.b)};
+  const uint32_t box[4] = {64, 128, 1, 1};
+  return make_tmap_bf16(tm, base, 4, dims, strides, box, true);
+}
+
+template <int D>
+int launch_d(const AttnBwdParams& p, cudaStream_t stream) {
+  CUtensorMap tq, tk, tv, tdo;
+  if (int rc = make_map(&tq, p.q, p.qs, p.B, p.H, p.Tq, D)) return rc;
+  if (int rc = make_map(&tk, p.k, p.ks, p.B, p.H, p.Tk, D)) return rc;
+  if (int rc = make_map(&tv, p.v, p.vs, p.B, p.H, p.Tk, D)) return rc;
+  if (int rc = make_map(&tdo, p.d_o, p.os, p.B, p.H, p.Tq, D)) return rc;
+  static bool configured = false;
+  if (!configured) {
+    ALG_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_tc_kernel<D, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes<D>())));
+    ALG_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_tc_kernel<D, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes<D>())));
+    configured = true;
+  }
+  const int64_t rows = int64_t(p.B) * p.H * p.Tq;
+  int64_t blocks = (rows / (32 / (D / 8)) + 7) / 8;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  attn_delta_kernel<D><<<unsigned(blocks), 256, 0, stream>>>(p);
+  ALG_CUDA_TRY(cudaGetLastError());
+  const dim3 grid(p.H, p.B, p.Tq / BT);
+  attn_bwd_tc_kernel<D, 0><<<grid, NTHREADS, smem_bytes<D>(), stream>>>(tq, tk, tv, tdo, p);
+  ALG_CUDA_TRY(cudaGetLastError());
+  attn_bwd_tc_kernel<D, 1><<<grid, NTHREADS, smem_bytes<D>(), stream>>>(tq, tk, tv, tdo, p);
+  ALG_CUDA_TRY(cudaGetLastError());
+  count_launch(3);
+  return ALG_OK;
+}
+
+}  // namespace
+
+bool attn_bwd_tcgen05_supports(const AttnBwdParams& p) {
+  const bool strides_fit = p.qs.t > 0 && p.ks.t > 0 && p.vs.t > 0 && p.os.t > 0 && p.qs.h >= 0 && p.qs.b >= 0 &&
+                           p.ks.h >= 0 && p.ks.b >= 0 && p.vs.h >= 0 && p.vs.b >= 0 && p.os.h >= 0 && p.os.b >= 0;
+  const bool rows_fit = p.B <= 65535 && p.Tq / BT <= 65535 && (reinterpret_cast<uintptr_t>(p.stat) & 15) == 0;
+  return p.causal && p.Tq == p.Tk && p.Tq % BT == 0 && (p.D == 64 || p.D == 128) && strides_fit && rows_fit &&
+         (p.B == 1 || (p.qs.b > 0 && p.os.b > 0)) && (p.H == 1 || (p.qs.h > 0 && p.os.h > 0));
+}
+
+int launch_attn_bwd_tcgen05(const AttnBwdParams& p, cudaStream_t stream) {
+  if (p.dsink != nullptr) ALG_CUDA_TRY(cudaMemsetAsync(p.dsink, 0, sizeof(float) * p.H, stream));
+  return p.D == 64 ? launch_d<64>(p, stream) : launch_d<128>(p, stream);
+}
+
+}  // namespace alg

@@ -302,6 +302,9 @@ int alg_attn_bwd(const alg_attn_bwd_args* a, void* stream_) {
   p.n_f = float(a->n);
   p.n_scale = p.n_f * p.scale;
   p.causal = a->causal ? 1 : 0;
+  p.status = a->status;
+  p.force_mma = a->impl == 1 ? 1 : 0;
+  if (a->impl != 0 && a->impl != 1) { set_error("attention backward: impl must be 0 or 1, got %d", a->impl); return ALG_ERR_INVALID; }
   p.qs = strides_or_dense(a->q_stride, a->H, a->Tq, a->D);
   p.ks = strides_or_dense(a->k_stride, a->H, a->Tk, a->D);
   p.vs = strides_or_dense(a->v_stride, a->H, a->Tk, a->D);

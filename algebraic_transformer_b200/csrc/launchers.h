@@ -90,8 +90,14 @@ struct AttnBwdParams {
   float n_scale, n_f;        // n * scale, n
   int causal;
   Strides3 qs, ks, vs, os;
+  int* status;               // device word for ALG_DEV_TIMEOUT, or nullptr
+  int force_mma;             // 1: stay on the mma.sync kernels whatever the shape
 };
+// Dispatcher (attn_bwd_mma.cu): tcgen05 kernels when the shape fits them, else mma.sync.
 int launch_attn_bwd(const AttnBwdParams& p, cudaStream_t stream);
+// attn_bwd_sm100.cu: causal, Tq == Tk a multiple of 128, head_dim 64 or 128
+bool attn_bwd_tcgen05_supports(const AttnBwdParams& p);
+int launch_attn_bwd_tcgen05(const AttnBwdParams& p, cudaStream_t stream);
 
 // ---- proj_sm100.cu: projection GEMMs with fused epilogues -------------------------------
 struct ProjParams {

@@ -332,11 +332,15 @@ def flash_attention(q, k, v, sink_logit=None, *, kind: str = "softmax", n: int =
 
 
 def flash_attention_backward(q, k, v, o, d_o, stat, stat_kind, sink_logit=None, *, n: int = 16, c: float = 8.0,
-                             causal: bool = True):
+                             causal: bool = True, impl: str = "auto"):
     """Gradients of `flash_attention(kind="asinh", return_stat=True)`: `(dq, dk, dv, dsink)` from the
     forward's inputs, its output `o`, the incoming gradient `d_o` and the saved `(stat, stat_kind)`
     (the custom VJP of the reference, src/algebraic/kernels/flash.py:333-727).  bf16 tensors,
-    (B,H,T,D) with D contiguous; `dsink` is None without a sink."""
+    (B,H,T,D) with D contiguous; `dsink` is None without a sink.  `impl`: "auto" runs the tcgen05
+    kernels when the call is causal self-attention over a multiple of 128 positions and the mma.sync
+    kernels otherwise; "mma" always runs the latter."""
+    if impl not in ("auto", "mma"):
+        raise ValueError('impl must be "auto" or "mma"')
     _require_cuda(q, k, v, o, d_o, stat, stat_kind)
     if q.ndim != 4 or k.ndim != 4 or v.shape != k.shape or o.shape != q.shape or d_o.shape != q.shape:
         raise ValueError("q, o, d_o must be (B, H, Tq, D) and k, v (B, H, Tk, D)")
@@ -362,7 +366,7 @@ def flash_attention_backward(q, k, v, o, d_o, stat, stat_kind, sink_logit=None, 
                       stat=stat.data_ptr(), stat_kind=stat_kind.data_ptr(), sink=_ptr(sink), dq=dq.data_ptr(),
                       dk=dk.data_ptr(), dv=dv.data_ptr(), dsink=_ptr(dsink), B=B, H=H, Tq=T, Tk=Tk, D=D, n=int(n),
                       c=float(c), causal=int(bool(causal)), q_stride=_strides3(q), k_stride=_strides3(k),
-                      v_stride=_strides3(v), o_stride=_strides3(o))
+                      v_stride=_strides3(v), o_stride=_strides3(o), status=None, impl=int(impl == "mma"))
     lib = L.load()
     ws = _workspace(q.device, lib.alg_attn_bwd_workspace_bytes(a), "attn_bwd")
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()

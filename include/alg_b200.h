@@ -167,6 +167,8 @@ typedef struct {
   int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3];
   void* workspace;
   size_t workspace_bytes;
+  int* status;             /* device int, may be NULL */
+  int impl;                /* 0: tcgen05 kernels when causal, Tq == Tk, Tq % 128 == 0 (else mma.sync); 1: mma.sync */
 } alg_attn_bwd_args;
 ALG_API size_t alg_attn_bwd_workspace_bytes(const alg_attn_bwd_args* args);
 ALG_API int alg_attn_bwd(const alg_attn_bwd_args* args, void* stream);

@@ -437,16 +437,21 @@ def _oracle_grads(q, k, v, sink, d_o, causal=True):
 
 
 @pytest.mark.parametrize("shape,with_sink,causal", [((2, 3, 256, 64), True, True), ((1, 2, 512, 128), True, True),
-                                                   ((1, 2, 200, 64), False, True), ((1, 2, 192, 64), True, False)])
-def test_attention_backward_matches_oracle_autograd(shape, with_sink, causal):
+                                                   ((1, 2, 200, 64), False, True), ((1, 2, 192, 64), True, False),
+                                                   ((1, 2, 1152, 128), True, True), ((1, 1, 1152, 64), True, True)])
+@pytest.mark.parametrize("impl", ["auto", "mma"])
+def test_attention_backward_matches_oracle_autograd(shape, with_sink, causal, impl):
     """dq, dk, dv, dsink from the saved statistic (custom VJP of flash.py:333-727) against autograd
-    through the CPU oracle; ragged length 200 exercises the masked tails, 192 the non-causal form."""
+    through the CPU oracle; ragged length 200 exercises the masked tails, 192 the non-causal form,
+    1152 = 9 tiles of 128 wraps the tcgen05 kernels' tile ring several times.  "auto" takes the
+    tcgen05 kernels on the causal multiples of 128 and the mma.sync kernels elsewhere."""
     q, k, v, d_o = (randn(shape, 900 + i, torch.bfloat16) for i in range(4))
     sink = randn((shape[1],), 905) * 0.5 if with_sink else None
     qd, kd, vd, dod, sd = dev(q, k, v, d_o, sink)
     o, stat, kind = A.flash_attention(qd, kd, vd, sd, kind="asinh", n=16, c=8.0, block=shape[2], range_guard=True,
                                       causal=causal, return_stat=True)
-    dq, dk, dv, ds = A.ops.flash_attention_backward(qd, kd, vd, o, dod, stat, kind, sd, n=16, c=8.0, causal=causal)
+    dq, dk, dv, ds = A.ops.flash_attention_backward(qd, kd, vd, o, dod, stat, kind, sd, n=16, c=8.0, causal=causal,
+                                                    impl=impl)
     wq, wk, wv, ws = _oracle_grads(q, k, v, sink, d_o, causal)
     assert rel_l2(dq, wq) < 2e-2 and rel_l2(dk, wk) < 2e-2 and rel_l2(dv, wv) < 2e-2
     if with_sink:
@@ -479,7 +484,8 @@ def test_head_backward_matches_oracle_autograd():
     assert rel_l2(torch.cat([de0, de1]), ef.grad) < 2e-2
 
 
-def test_attention_backward_after_shifted_forward():
+@pytest.mark.parametrize("impl", ["auto", "mma"])
+def test_attention_backward_after_shifted_forward(impl):
     """Out-of-range inputs: the forward takes the max-shifted path and saves rho(-m) l^(-1/n); the
     backward must rebuild the same weights from that statistic."""
     shape = (1, 2, 256, 64)
@@ -490,6 +496,6 @@ def test_attention_backward_after_shifted_forward():
     o, stat, kind = A.flash_attention(qd, kd, vd, None, kind="asinh", n=16, c=8.0, block=256, range_guard=True,
                                       return_stat=True)
     assert int(kind) == 2
-    dq, dk, dv, _ = A.ops.flash_attention_backward(qd, kd, vd, o, dod, stat, kind, None, n=16, c=8.0)
+    dq, dk, dv, _ = A.ops.flash_attention_backward(qd, kd, vd, o, dod, stat, kind, None, n=16, c=8.0, impl=impl)
     wq, wk, wv, _ = _oracle_grads(q, k, v, None, d_o)
     assert rel_l2(dq, wq) < 3e-2 and rel_l2(dk, wk) < 3e-2 and rel_l2(dv, wv) < 3e-2
