@@ -57,33 +57,44 @@ struct __align__(16) Control {
 
 template <int D> constexpr size_t smem_bytes() { return size_t(Cfg<D>::CTL_OFF) + sizeof(Control) + 1024; }
 
-// 32 scores + 32 dP values of this thread's row -> 16 packed weights and 16 packed dS.
-// `stat` / `delta` index: by row (MODE 0: one value) or by column (MODE 1: arrays of 32).
+// 32 scores + 32 dP values of this thread's row -> 16 packed weights and 16 packed dS (s and dp are
+// used as scratch).  `stat` / `delta` index: by row (MODE 0: one value) or by column (MODE 1: arrays
+// of 32).  The 2^log2n-th power runs as log2n passes over the 32 values, so that every pass has 32
+// independent multiplications whatever n is (a per-element loop serialises on its own latency).
 template <bool SHIFTED, bool BY_COLUMN>
-__device__ __forceinline__ void weigh_chunk(const uint32_t* s, const uint32_t* dp, const AttnBwdParams& p, float stat_row,
+__device__ __forceinline__ void weigh_chunk(uint32_t* s, uint32_t* dp, const AttnBwdParams& p, float stat_row,
                                             float delta_row, const float* stat_col, const float* delta_col, int log2n,
                                             bool diag, int row, int col0, bool row_is_query, uint32_t* pw_out,
                                             uint32_t* ds_out) {
 #pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const float st = BY_COLUMN ? stat_col[i] : stat_row;
+    const float dl = BY_COLUMN ? delta_col[i] : delta_row;
+    const float x = __uint_as_float(s[i]) * p.scale;
+    const float rad = fmaf(x, x, 1.0f);
+    const float rs = rsqrt_approx(rad);
+    s[i] = __float_as_uint(SHIFTED ? rho_stable(x) * st : fmaf(rad, rs, x));
+    dp[i] = __float_as_uint(p.n_scale * rs * (__uint_as_float(dp[i]) - dl));   // dS = p * this
+  }
+  for (int it = 0; it < log2n; ++it) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float w = __uint_as_float(s[i]);
+      s[i] = __float_as_uint(w * w);
+    }
+  }
+#pragma unroll
   for (int i = 0; i < 32; i += 2) {
-    float pw[2], ds[2];
+    float pw[2];
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
-      const float st = BY_COLUMN ? stat_col[i + e] : stat_row;
-      const float dl = BY_COLUMN ? delta_col[i + e] : delta_row;
-      const float x = __uint_as_float(s[i + e]) * p.scale;
-      const float rad = fmaf(x, x, 1.0f);
-      const float rs = rsqrt_approx(rad);
-      float w;
-      if (SHIFTED) w = pow2n_rt(rho_stable(x) * st, log2n);
-      else w = pow2n_rt(fmaf(rad, rs, x), log2n) * st;
+      pw[e] = __uint_as_float(s[i + e]);
+      if (!SHIFTED) pw[e] *= BY_COLUMN ? stat_col[i + e] : stat_row;
       // causal: key <= query.  Rows are queries in MODE 0 (mask col > row), keys in MODE 1 (mask col < row)
-      if (diag && (row_is_query ? (col0 + i + e > row) : (col0 + i + e < row))) w = 0.f;
-      pw[e] = w;
-      ds[e] = p.n_scale * w * rs * (__uint_as_float(dp[i + e]) - dl);
+      if (diag && (row_is_query ? (col0 + i + e > row) : (col0 + i + e < row))) pw[e] = 0.f;
     }
     pw_out[i >> 1] = pack_bf16(pw[0], pw[1]);
-    ds_out[i >> 1] = pack_bf16(ds[0], ds[1]);
+    ds_out[i >> 1] = pack_bf16(pw[0] * __uint_as_float(dp[i]), pw[1] * __uint_as_float(dp[i + 1]));
   }
 }
 
