@@ -19,8 +19,13 @@
 // products (P^T, dS) are written back over the columns their own thread has already read — half
 // h keeps its 64 packed values in columns [64 h, 64 h + 32) — and fed to the tensor core from
 // tensor memory (TS form) with the streamed tile as an MN-major B operand, so nothing is
-// transposed or staged.  A step is serial (scores -> element-wise -> products): with both
-// accumulators of MODE 1 all 512 columns are taken and there is no room to double-buffer.
+// transposed or staged.  With both accumulators of MODE 1 all 512 columns are taken, so the two
+// score tiles cannot be double-buffered; instead a step has two element-wise phases and the
+// tensor core works on one region while the threads work on the other:
+//   phase 1  reads S, forms p (MODE 1 writes P^T over S) and keeps n p / sqrt(1+x^2) in registers;
+//            meanwhile: dK/dQ product of the previous step, then dP of this step;
+//   phase 2  reads dP, writes dS = (kept factor) (dP - delta) over it;
+//            meanwhile: dV product of this step (MODE 1), then S of the next step.
 // Every mbarrier wait is bounded; a wait that runs out reports ALG_DEV_TIMEOUT.
 #include "common.cuh"
 #include "launchers.h"
@@ -49,7 +54,7 @@ template <int D> struct Cfg {
 };
 
 struct __align__(16) Control {
-  uint64_t res_full, full[MAX_STEPS], empty[MAX_STEPS], s_full, e_done, acc_full;
+  uint64_t res_full, full[MAX_STEPS], empty[MAX_STEPS], s_full, dp_full, p_done, ds_done, acc_full;
   uint32_t tmem_base;
   int abort_flag;
   float sink_part[8];
@@ -57,24 +62,23 @@ struct __align__(16) Control {
 
 template <int D> constexpr size_t smem_bytes() { return size_t(Cfg<D>::CTL_OFF) + sizeof(Control) + 1024; }
 
-// 32 scores + 32 dP values of this thread's row -> 16 packed weights and 16 packed dS (s and dp are
-// used as scratch).  `stat` / `delta` index: by row (MODE 0: one value) or by column (MODE 1: arrays
-// of 32).  The 2^log2n-th power runs as log2n passes over the 32 values, so that every pass has 32
-// independent multiplications whatever n is (a per-element loop serialises on its own latency).
+// Phase 1 on 32 scores of this thread's row: the weights p, packed to bf16 in pw_out, and the factor
+// n p / (sqrt(1 + x^2) sqrt(D) c) that phase 2 multiplies (dP - delta) by, in `slope`.  `stat` comes by
+// row (MODE 0: one value) or by column (MODE 1: 32 values).  The 2^log2n-th power runs as log2n passes
+// over the 32 values, so that every pass has 32 independent multiplications whatever n is (a loop
+// per element serialises on its own latency).
 template <bool SHIFTED, bool BY_COLUMN>
-__device__ __forceinline__ void weigh_chunk(uint32_t* s, uint32_t* dp, const AttnBwdParams& p, float stat_row,
-                                            float delta_row, const float* stat_col, const float* delta_col, int log2n,
-                                            bool diag, int row, int col0, bool row_is_query, uint32_t* pw_out,
-                                            uint32_t* ds_out) {
+__device__ __forceinline__ void weights_from_scores(uint32_t* s, float* slope, const AttnBwdParams& p, float stat_row,
+                                                    const float* stat_col, int log2n, bool diag, int row, int col0,
+                                                    bool row_is_query, uint32_t* pw_out) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
     const float st = BY_COLUMN ? stat_col[i] : stat_row;
-    const float dl = BY_COLUMN ? delta_col[i] : delta_row;
     const float x = __uint_as_float(s[i]) * p.scale;
     const float rad = fmaf(x, x, 1.0f);
     const float rs = rsqrt_approx(rad);
     s[i] = __float_as_uint(SHIFTED ? rho_stable(x) * st : fmaf(rad, rs, x));
-    dp[i] = __float_as_uint(p.n_scale * rs * (__uint_as_float(dp[i]) - dl));   // dS = p * this
+    slope[i] = p.n_scale * rs;
   }
   for (int it = 0; it < log2n; ++it) {
 #pragma unroll
@@ -92,9 +96,9 @@ __device__ __forceinline__ void weigh_chunk(uint32_t* s, uint32_t* dp, const Att
       if (!SHIFTED) pw[e] *= BY_COLUMN ? stat_col[i + e] : stat_row;
       // causal: key <= query.  Rows are queries in MODE 0 (mask col > row), keys in MODE 1 (mask col < row)
       if (diag && (row_is_query ? (col0 + i + e > row) : (col0 + i + e < row))) pw[e] = 0.f;
+      slope[i + e] *= pw[e];
     }
     pw_out[i >> 1] = pack_bf16(pw[0], pw[1]);
-    ds_out[i >> 1] = pack_bf16(pw[0] * __uint_as_float(dp[i]), pw[1] * __uint_as_float(dp[i + 1]));
   }
 }
 
@@ -113,7 +117,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     mbar_init(&ctl->res_full, 1);
     for (int i = 0; i < C::NS; ++i) { mbar_init(&ctl->full[i], 1); mbar_init(&ctl->empty[i], 1); }
     mbar_init(&ctl->s_full, 1);
-    mbar_init(&ctl->e_done, EW_THREADS);
+    mbar_init(&ctl->dp_full, 1);
+    mbar_init(&ctl->p_done, EW_THREADS);
+    mbar_init(&ctl->ds_done, EW_THREADS);
     mbar_init(&ctl->acc_full, 1);
     ctl->abort_flag = 0;
     fence_barrier_init();
@@ -185,24 +191,38 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                             (first_step && ks == 0) ? 0u : 1u);
         }
       };
-      bool ok = bw.wait(&ctl->res_full, 0);
-      for (int j = 0; j < nsteps && ok; ++j) {
-        const int slot = j % C::NS;
-        if (!bw.wait(&ctl->full[slot], (j / C::NS) & 1u)) { ok = false; break; }
+      bool ok = bw.wait(&ctl->res_full, 0) && bw.wait(&ctl->full[0], 0);
+      if (ok) {
         tc_fence_after();
-        const uint32_t t0 = ring_addr + slot * 2 * C::TILE_BYTES, t1 = t0 + C::TILE_BYTES;
-        issue_scores(tmem_base + C::S_COL, a0_lo, t0);      // S (or S^T)
-        issue_scores(tmem_base + C::DP_COL, a1_lo, t1);     // dP (or dP^T)
+        issue_scores(tmem_base + C::S_COL, a0_lo, ring_addr);                       // S (or S^T) of step 0
         umma_commit(&ctl->s_full);
-        if (!bw.wait(&ctl->e_done, j & 1u)) { ok = false; break; }
+        issue_scores(tmem_base + C::DP_COL, a1_lo, ring_addr + C::TILE_BYTES);      // dP (or dP^T) of step 0
+        umma_commit(&ctl->dp_full);
+      }
+      for (int j = 0; j < nsteps && ok; ++j) {
+        const int slot = j % C::NS, nslot = (j + 1) % C::NS;
+        const bool has_next = j + 1 < nsteps;
+        const uint32_t t0 = ring_addr + slot * 2 * C::TILE_BYTES, t1 = t0 + C::TILE_BYTES;
+        const uint32_t n0 = ring_addr + nslot * 2 * C::TILE_BYTES, n1 = n0 + C::TILE_BYTES;
+        // phase 1 is over: S has been read (MODE 1: P^T stands in its place)
+        if (!bw.wait(&ctl->p_done, j & 1u)) { ok = false; break; }
         tc_fence_after();
-        if (MODE == 0) {
-          issue_product(tmem_base + C::ACC0_COL, tmem_base + C::DP_COL, t0, j == 0);   // dQ += dS K_j
-        } else {
-          issue_product(tmem_base + C::ACC0_COL, tmem_base + C::S_COL, t1, j == 0);    // dV += P^T dO_i
-          issue_product(tmem_base + C::ACC1_COL, tmem_base + C::DP_COL, t0, j == 0);   // dK += dS^T Q_i
+        if (MODE == 1) issue_product(tmem_base + C::ACC0_COL, tmem_base + C::S_COL, t1, j == 0);   // dV += P^T dO_i
+        if (has_next) {
+          if (!bw.wait(&ctl->full[nslot], ((j + 1) / C::NS) & 1u)) { ok = false; break; }
+          tc_fence_after();
+          issue_scores(tmem_base + C::S_COL, a0_lo, n0);    // after the dV product: may overwrite P^T
+          umma_commit(&ctl->s_full);
         }
+        // phase 2 is over: dS stands in place of dP
+        if (!bw.wait(&ctl->ds_done, j & 1u)) { ok = false; break; }
+        tc_fence_after();
+        issue_product(tmem_base + (MODE == 0 ? C::ACC0_COL : C::ACC1_COL), tmem_base + C::DP_COL, t0, j == 0);  // dQ += dS K_j / dK += dS^T Q_i
         umma_commit(&ctl->empty[slot]);
+        if (has_next) {
+          issue_scores(tmem_base + C::DP_COL, a1_lo, n1);   // after that product: may overwrite dS
+          umma_commit(&ctl->dp_full);
+        }
       }
       if (ok) umma_commit(&ctl->acc_full);
     }
@@ -219,35 +239,59 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     for (int j = 0; j < nsteps && ok; ++j) {
       const int other0 = (first + j) * BT;                    // first row of the streamed tile
       const bool diag = (first + j) == tile;
+      const float* col_stat = p.stat + bh * p.Tq + other0 + half * 64;     // MODE 1: of the streamed queries
+      const float* col_delta = p.delta + bh * p.Tq + other0 + half * 64;
+      float slope[2][32];
+      // ---- phase 1: scores -> weights
       if (!bw.wait(&ctl->s_full, j & 1u)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t s[32], dp[32], pw[16], ds[16];
+        uint32_t s[32], pw[16];
         tmem_ld_32x32(s_t + c * 32, s);
-        tmem_ld_32x32(dp_t + c * 32, dp);
-        float stc[32], dlc[32];
-        if (MODE == 1) {                                       // statistic and delta of the 32 streamed queries
-          const float4* sp = reinterpret_cast<const float4*>(p.stat + bh * p.Tq + other0 + half * 64 + c * 32);
-          const float4* dq = reinterpret_cast<const float4*>(p.delta + bh * p.Tq + other0 + half * 64 + c * 32);
+        float stc[32];
+        if (MODE == 1) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const float4 a = __ldg(sp + i), d4 = __ldg(dq + i);
+            const float4 a = __ldg(reinterpret_cast<const float4*>(col_stat + c * 32) + i);
             stc[4 * i] = a.x; stc[4 * i + 1] = a.y; stc[4 * i + 2] = a.z; stc[4 * i + 3] = a.w;
-            dlc[4 * i] = d4.x; dlc[4 * i + 1] = d4.y; dlc[4 * i + 2] = d4.z; dlc[4 * i + 3] = d4.w;
           }
         }
         tmem_ld_wait();
         const int col0 = half * 64 + c * 32;                   // column inside the streamed tile
-        if (shifted) weigh_chunk<true, MODE == 1>(s, dp, p, stat_row, delta_row, stc, dlc, p.log2n, diag, r, col0, MODE == 0, pw, ds);
-        else weigh_chunk<false, MODE == 1>(s, dp, p, stat_row, delta_row, stc, dlc, p.log2n, diag, r, col0, MODE == 0, pw, ds);
-        // packed outputs over columns this thread has read already: chunk c -> [64 half + 16 c, +16)
-        if (MODE == 1) tmem_st_32x16(tmem_base + lane_sel + C::S_COL + half * 64 + c * 16, pw);
-        tmem_st_32x16(tmem_base + lane_sel + C::DP_COL + half * 64 + c * 16, ds);
+        if (shifted) weights_from_scores<true, MODE == 1>(s, slope[c], p, stat_row, stc, p.log2n, diag, r, col0, MODE == 0, pw);
+        else weights_from_scores<false, MODE == 1>(s, slope[c], p, stat_row, stc, p.log2n, diag, r, col0, MODE == 0, pw);
+        // packed output over columns this thread has read already: chunk c -> [64 half + 16 c, +16)
+        if (MODE == 1) tmem_st_32x16(s_t + c * 16, pw);
+      }
+      if (MODE == 1) tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&ctl->p_done);
+      // ---- phase 2: dP -> dS
+      if (!bw.wait(&ctl->dp_full, j & 1u)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t dp[32], ds[16];
+        tmem_ld_32x32(dp_t + c * 32, dp);
+        float dlc[32];
+        if (MODE == 1) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(col_delta + c * 32) + i);
+            dlc[4 * i] = a.x; dlc[4 * i + 1] = a.y; dlc[4 * i + 2] = a.z; dlc[4 * i + 3] = a.w;
+          }
+        }
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2)
+          ds[i >> 1] = pack_bf16(slope[c][i] * (__uint_as_float(dp[i]) - (MODE == 1 ? dlc[i] : delta_row)),
+                                 slope[c][i + 1] * (__uint_as_float(dp[i + 1]) - (MODE == 1 ? dlc[i + 1] : delta_row)));
+        tmem_st_32x16(dp_t + c * 16, ds);
       }
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&ctl->e_done);
+      mbar_arrive(&ctl->ds_done);
     }
     if (ok && bw.wait(&ctl->acc_full, 0)) {
       tc_fence_after();
