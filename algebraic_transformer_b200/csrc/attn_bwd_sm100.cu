@@ -64,41 +64,50 @@ template <int D> constexpr size_t smem_bytes() { return size_t(Cfg<D>::CTL_OFF) 
 
 // Phase 1 on 32 scores of this thread's row: the weights p, packed to bf16 in pw_out, and the factor
 // n p / (sqrt(1 + x^2) sqrt(D) c) that phase 2 multiplies (dP - delta) by, in `slope`.  `stat` comes by
-// row (MODE 0: one value) or by column (MODE 1: 32 values).  The 2^log2n-th power runs as log2n passes
-// over the 32 values, so that every pass has 32 independent multiplications whatever n is (a loop
-// per element serialises on its own latency).
+// row (MODE 0: one value) or by column (MODE 1: 32 values).  Pairs of values go through the packed
+// fp32 instructions (mul.f32x2 / fma.f32x2).  The 2^log2n-th power runs as log2n passes over the 16
+// pairs, so that every pass has independent multiplications whatever n is (a loop per element
+// serialises on its own latency).
 template <bool SHIFTED, bool BY_COLUMN>
-__device__ __forceinline__ void weights_from_scores(uint32_t* s, float* slope, const AttnBwdParams& p, float stat_row,
-                                                    const float* stat_col, int log2n, bool diag, int row, int col0,
-                                                    bool row_is_query, uint32_t* pw_out) {
+__device__ __forceinline__ void weights_from_scores(const uint32_t* s, float2* slope, const AttnBwdParams& p,
+                                                    float stat_row, const float2* stat_col, int log2n, bool diag, int row,
+                                                    int col0, bool row_is_query, uint32_t* pw_out) {
+  const float2 sc = make_float2(p.scale, p.scale), one = make_float2(1.f, 1.f), ns = make_float2(p.n_scale, p.n_scale);
+  const float2 st_row = make_float2(stat_row, stat_row);
+  float2 t[16];
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    const float st = BY_COLUMN ? stat_col[i] : stat_row;
-    const float x = __uint_as_float(s[i]) * p.scale;
-    const float rad = fmaf(x, x, 1.0f);
-    const float rs = rsqrt_approx(rad);
-    s[i] = __float_as_uint(SHIFTED ? rho_stable(x) * st : fmaf(rad, rs, x));
-    slope[i] = p.n_scale * rs;
+  for (int i = 0; i < 16; ++i) {
+    const float2 x = __fmul2_rn(make_float2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), sc);
+    const float2 rad = __ffma2_rn(x, x, one);
+    const float2 rs = make_float2(rsqrt_approx(rad.x), rsqrt_approx(rad.y));
+    if (SHIFTED) {
+      const float2 st = BY_COLUMN ? stat_col[i] : st_row;
+      t[i] = make_float2(rho_stable(x.x) * st.x, rho_stable(x.y) * st.y);
+    } else {
+      t[i] = __ffma2_rn(rad, rs, x);
+    }
+    slope[i] = __fmul2_rn(ns, rs);
   }
   for (int it = 0; it < log2n; ++it) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const float w = __uint_as_float(s[i]);
-      s[i] = __float_as_uint(w * w);
+    for (int i = 0; i < 16; ++i) t[i] = __fmul2_rn(t[i], t[i]);
+  }
+  if (!SHIFTED) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) t[i] = __fmul2_rn(t[i], BY_COLUMN ? stat_col[i] : st_row);
+  }
+  if (diag) {   // causal: key <= query.  Rows are queries in MODE 0 (mask col > row), keys in MODE 1 (mask col < row)
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int c = col0 + 2 * i;
+      if (row_is_query ? (c > row) : (c < row)) t[i].x = 0.f;
+      if (row_is_query ? (c + 1 > row) : (c + 1 < row)) t[i].y = 0.f;
     }
   }
 #pragma unroll
-  for (int i = 0; i < 32; i += 2) {
-    float pw[2];
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      pw[e] = __uint_as_float(s[i + e]);
-      if (!SHIFTED) pw[e] *= BY_COLUMN ? stat_col[i + e] : stat_row;
-      // causal: key <= query.  Rows are queries in MODE 0 (mask col > row), keys in MODE 1 (mask col < row)
-      if (diag && (row_is_query ? (col0 + i + e > row) : (col0 + i + e < row))) pw[e] = 0.f;
-      slope[i + e] *= pw[e];
-    }
-    pw_out[i >> 1] = pack_bf16(pw[0], pw[1]);
+  for (int i = 0; i < 16; ++i) {
+    slope[i] = __fmul2_rn(slope[i], t[i]);
+    pw_out[i] = pack_bf16(t[i].x, t[i].y);
   }
 }
 
@@ -241,7 +250,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const bool diag = (first + j) == tile;
       const float* col_stat = p.stat + bh * p.Tq + other0 + half * 64;     // MODE 1: of the streamed queries
       const float* col_delta = p.delta + bh * p.Tq + other0 + half * 64;
-      float slope[2][32];
+      float2 slope[2][16];
       // ---- phase 1: scores -> weights
       if (!bw.wait(&ctl->s_full, j & 1u)) { ok = false; break; }
       tc_fence_after();
@@ -249,12 +258,13 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       for (int c = 0; c < 2; ++c) {
         uint32_t s[32], pw[16];
         tmem_ld_32x32(s_t + c * 32, s);
-        float stc[32];
+        float2 stc[16];
         if (MODE == 1) {
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const float4 a = __ldg(reinterpret_cast<const float4*>(col_stat + c * 32) + i);
-            stc[4 * i] = a.x; stc[4 * i + 1] = a.y; stc[4 * i + 2] = a.z; stc[4 * i + 3] = a.w;
+            stc[2 * i] = make_float2(a.x, a.y);
+            stc[2 * i + 1] = make_float2(a.z, a.w);
           }
         }
         tmem_ld_wait();
@@ -267,27 +277,35 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (MODE == 1) tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&ctl->p_done);
-      // ---- phase 2: dP -> dS
+      // ---- phase 2: dP -> dS = slope (dP - delta)
       if (!bw.wait(&ctl->dp_full, j & 1u)) { ok = false; break; }
       tc_fence_after();
+      {
+        uint32_t dp0[32], dp1[32], ds[16];
+        tmem_ld_32x32(dp_t, dp0);
+        tmem_ld_32x32(dp_t + 32, dp1);
+        const float2 minus_one = make_float2(-1.f, -1.f), dl_row = make_float2(delta_row, delta_row);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t dp[32], ds[16];
-        tmem_ld_32x32(dp_t + c * 32, dp);
-        float dlc[32];
-        if (MODE == 1) {
+        for (int c = 0; c < 2; ++c) {
+          float2 dlc[16];
+          if (MODE == 1) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float4 a = __ldg(reinterpret_cast<const float4*>(col_delta + c * 32) + i);
-            dlc[4 * i] = a.x; dlc[4 * i + 1] = a.y; dlc[4 * i + 2] = a.z; dlc[4 * i + 3] = a.w;
+            for (int i = 0; i < 8; ++i) {
+              const float4 a = __ldg(reinterpret_cast<const float4*>(col_delta + c * 32) + i);
+              dlc[2 * i] = make_float2(a.x, a.y);
+              dlc[2 * i + 1] = make_float2(a.z, a.w);
+            }
           }
-        }
-        tmem_ld_wait();
+          if (c == 0) tmem_ld_wait_for(dp0); else tmem_ld_wait_for(dp1);
+          const uint32_t* dp = c == 0 ? dp0 : dp1;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2)
-          ds[i >> 1] = pack_bf16(slope[c][i] * (__uint_as_float(dp[i]) - (MODE == 1 ? dlc[i] : delta_row)),
-                                 slope[c][i + 1] * (__uint_as_float(dp[i + 1]) - (MODE == 1 ? dlc[i + 1] : delta_row)));
-        tmem_st_32x16(dp_t + c * 16, ds);
+          for (int i = 0; i < 16; ++i) {
+            const float2 d = make_float2(__uint_as_float(dp[2 * i]), __uint_as_float(dp[2 * i + 1]));
+            const float2 v = __fmul2_rn(slope[c][i], __ffma2_rn(MODE == 1 ? dlc[i] : dl_row, minus_one, d));
+            ds[i] = pack_bf16(v.x, v.y);
+          }
+          tmem_st_32x16(dp_t + c * 16, ds);
+        }
       }
       tmem_st_wait();
       tc_fence_before();
