@@ -121,13 +121,24 @@ __device__ __forceinline__ void gemm_wb(float (*acc)[4], const float (*w)[4], co
   }
 }
 
-// normalised weight p and the factor that turns (dP - delta) into dS, for one score
-__device__ __forceinline__ void weight_and_slope(float s_raw, float stat, bool shifted, const AttnBwdParams& p, float& pw,
-                                                 float& slope) {
+// The normalised weight of a score is base^n (times the statistic on the unshifted path); the power
+// is taken afterwards for a whole fragment at once (power_passes).  Returns the base and, in `slope`,
+// n / (sqrt(1 + x^2) sqrt(D) c): weight * slope turns (dP - delta) into dS.
+__device__ __forceinline__ float weight_base(float s_raw, float stat, bool shifted, const AttnBwdParams& p, float& slope) {
   const float x = s_raw * p.scale;
   const float rs = rsqrtf(fmaf(x, x, 1.0f));           // 1 / sqrt(1 + x^2)
-  pw = shifted ? pow2n_rt(rho_stable(x) * stat, p.log2n) : pow2n_rt(rho_fast(x), p.log2n) * stat;
-  slope = p.n_scale * pw * rs;                         // n p / sqrt(1 + x^2) * 1 / (sqrt(D) c)
+  slope = p.n_scale * rs;
+  return shifted ? rho_stable(x) * stat : rho_fast(x);
+}
+// w <- w^(2^log2n) for the 32 values of a fragment: log2n passes of independent multiplications (a
+// loop per value would serialise on its own latency).
+__device__ __forceinline__ void power_passes(float (*w)[4], int log2n) {
+  for (int it = 0; it < log2n; ++it) {
+#pragma unroll
+    for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) w[nt][e] *= w[nt][e];
+  }
 }
 
 template <int D>
@@ -236,11 +247,19 @@ __global__ void __launch_bounds__(NTHREADS) attn_bwd_dq_kernel(const AttnBwdPara
     for (int nt = 0; nt < BN / 8; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
+        float slope;
+        s[nt][e] = weight_base(s[nt][e], (e < 2) ? stat_a : stat_b, shifted, p, slope);
+        dp[nt][e] = slope * (dp[nt][e] - ((e < 2) ? delta_a : delta_b));
+      }
+    power_passes(s, p.log2n);
+#pragma unroll
+    for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
         const int col = k0 + nt * 8 + tq * 2 + (e & 1);
         const int row = (e < 2) ? row_a : row_b;
-        float pw, slope;
-        weight_and_slope(s[nt][e], (e < 2) ? stat_a : stat_b, shifted, p, pw, slope);
-        float ds = slope * (dp[nt][e] - ((e < 2) ? delta_a : delta_b));
+        const float pw = shifted ? s[nt][e] : s[nt][e] * ((e < 2) ? stat_a : stat_b);
+        float ds = pw * dp[nt][e];
         if (masked && !(col < p.Tk && (!p.causal || col <= row + off))) ds = 0.f;
         s[nt][e] = ds;
       }
@@ -332,10 +351,19 @@ __global__ void __launch_bounds__(NTHREADS) attn_bwd_dkv_kernel(const AttnBwdPar
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int qc = nt * 8 + tq * 2 + (e & 1);           // query inside the tile (column of S^T)
+        float slope;
+        st[nt][e] = weight_base(st[nt][e], s_stat[stage][qc], shifted, p, slope);
+        dpt[nt][e] = slope * (dpt[nt][e] - s_delta[stage][qc]);
+      }
+    power_passes(st, p.log2n);
+#pragma unroll
+    for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int qc = nt * 8 + tq * 2 + (e & 1);
         const int qi = q0 + qc, kj = (e < 2) ? key_a : key_b;
-        float pw, slope;
-        weight_and_slope(st[nt][e], s_stat[stage][qc], shifted, p, pw, slope);
-        float ds = slope * (dpt[nt][e] - s_delta[stage][qc]);
+        float pw = shifted ? st[nt][e] : st[nt][e] * s_stat[stage][qc];
+        float ds = pw * dpt[nt][e];
         if (masked && !(qi < p.Tq && kj < p.Tk && (!p.causal || kj <= qi + off))) { pw = 0.f; ds = 0.f; }
         st[nt][e] = pw;
         dpt[nt][e] = ds;
