@@ -174,13 +174,25 @@ __global__ void __launch_bounds__(NTHREADS) attn_mma_kernel(const AttnParams p) 
     const bool masked = (k0 + BN > p.Tk) || (p.causal && (k0 + BN - 1 > q0 + off));
     float alpha[2] = {1.f, 1.f};
     if (!shift_mode) {
+      // rho^n as log2n passes over the fragment: every pass is a set of independent multiplications
+      // (a loop per value would serialise on its own latency)
+#pragma unroll
+      for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[nt][e] = rho_fast(fminf(s[nt][e] * p.scale, p.score_clamp));
+      for (int it = 0; it < p.log2n; ++it) {
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[nt][e] *= s[nt][e];
+      }
 #pragma unroll
       for (int nt = 0; nt < BN / 8; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int col = k0 + nt * 8 + tq * 2 + (e & 1);
           const int row = (e < 2) ? row_a : row_b;
-          float w = pow2n_rt(rho_fast(fminf(s[nt][e] * p.scale, p.score_clamp)), p.log2n);
+          float w = s[nt][e];
           if (masked) {
             const bool ok = col < p.Tk && (!p.causal || col <= row + off);
             w = ok ? w : 0.0f;
@@ -223,11 +235,18 @@ __global__ void __launch_bounds__(NTHREADS) attn_mma_kernel(const AttnParams p) 
         for (int e = 0; e < 4; ++e) {
           const bool ok = s[nt][e] > -1e29f;
           const float x = ok ? s[nt][e] : 0.0f;
-          float w = pow2n_rt(rho_stable(x) * shiftv[e >> 1], p.log2n);
-          w = ok ? w : 0.0f;
-          s[nt][e] = w;
-          l_run[e >> 1] += w;
+          s[nt][e] = ok ? rho_stable(x) * shiftv[e >> 1] : 0.0f;   // a masked entry stays 0 under the power
         }
+      for (int it = 0; it < p.log2n; ++it) {
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[nt][e] *= s[nt][e];
+      }
+#pragma unroll
+      for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) l_run[e >> 1] += s[nt][e];
 #pragma unroll
       for (int i = 0; i < D / 8; ++i) {
         acc[i][0] *= alpha[0]; acc[i][1] *= alpha[0];

@@ -122,13 +122,25 @@ __global__ void __launch_bounds__(NTHREADS) head_mma_kernel(const HeadParams p) 
     if (kc == kchunks - 1) {
       const int v0 = tile * BN;
       const bool tail = v0 + BN > p.V_local;
+      // rho^n as log2n passes over the fragment (independent multiplications in every pass)
+      float wt[BN / 8][4];
+#pragma unroll
+      for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) wt[nt][e] = rho_fast(fminf(acc[nt][e] * p.inv_c, p.clamp));
+      for (int it = 0; it < p.log2n; ++it) {
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) wt[nt][e] *= wt[nt][e];
+      }
 #pragma unroll
       for (int nt = 0; nt < BN / 8; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int col = v0 + nt * 8 + tq * 2 + (e & 1);
           const float z = acc[nt][e];
-          float w = pow2n_rt(rho_fast(fminf(z * p.inv_c, p.clamp)), p.log2n);
+          float w = wt[nt][e];
           if (tail && col >= p.V_local) w = 0.0f;
           l_acc[e >> 1] += w;
           if (col == tgt[e >> 1]) zt_acc[e >> 1] += z;

@@ -110,19 +110,28 @@ __device__ __forceinline__ void dz_cols(const ProjParams& p, uint32_t taddr, con
       tmem_ld_32x32(taddr + u * 64 + c * 32, r);
       tmem_ld_wait();
       const int cbase = col0 + u * 64 + c * 32;
+      // the n-th power as log2n passes over the 32 values: every pass is 32 independent
+      // multiplications (a loop per value would serialise on its own latency)
+      float w[32], sl[32];
+      const float an = a_i * p.n_over_c;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float xr = __uint_as_float(r[i]) * p.inv_c;
+        const float x = fminf(xr, p.clamp);
+        const float rad = fmaf(x, x, 1.0f);
+        const float rs = rsqrt_approx(rad);
+        w[i] = fmaf(rad, rs, x);                                                // rho_fast(x)
+        sl[i] = (xr < p.clamp) ? an * rs : 0.f;                                 // a_i s_ij
+      }
+      for (int it = 0; it < p.log2n; ++it) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) w[i] *= w[i];
+      }
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
-        float dz[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const float xr = __uint_as_float(r[i + e]) * p.inv_c;
-          const float x = fminf(xr, p.clamp);
-          const float rs = rsqrtf(fmaf(x, x, 1.0f));
-          const float w = pow2n_rt(fmaf(fmaf(x, x, 1.0f), rs, x), p.log2n);      // rho_fast(x)^n
-          const float s = (xr < p.clamp) ? p.n_over_c * rs : 0.f;
-          dz[e] = a_i * s * (w * inv_l - ((cbase + i + e == tgt) ? 1.f : 0.f));
-        }
-        pk[c * 16 + (i >> 1)] = pack_bf16(dz[0], dz[1]);
+        const float d0 = sl[i] * (w[i] * inv_l - ((cbase + i == tgt) ? 1.f : 0.f));
+        const float d1 = sl[i + 1] * (w[i + 1] * inv_l - ((cbase + i + 1 == tgt) ? 1.f : 0.f));
+        pk[c * 16 + (i >> 1)] = pack_bf16(d0, d1);
       }
     }
     const int first = col0 + u * 64;

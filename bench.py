@@ -480,19 +480,25 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
                        "ms": ms_g, "tflops": fl / (ms_g * 1e-3) / 1e12, "frac_of_bf16_peak": fl / (ms_g * 1e-3) / 1e12 / peak_tf}
     del xs, wqkv, wgu, o_qkv, o_glu
     # ---- attention backward (first "next" row): the 125M block's attention shape ----
-    Bb, Hb, Tb, Db = 16, 12, 1024, 64
-    qb_, kb_, vb_, dob_ = (torch.randn((Bb, Hb, Tb, Db), generator=g).bfloat16().to(dev) for _ in range(4))
-    sk = torch.zeros(Hb, device=dev)
-    ob_, stb_, kindb_ = A.flash_attention(qb_, kb_, vb_, sk, kind="asinh", n=16, c=8.0, range_guard=True, return_stat=True)
-    fnb = lambda i: A.ops.flash_attention_backward(qb_, kb_, vb_, ob_, dob_, stb_, kindb_, sk, n=16, c=8.0)  # noqa: E731
-    for i in range(3):
-        fnb(i)
-    ms_b = cuda_time(fnb, iters, sync)
-    flb = 2.5 * attn_flops(Bb, Hb, Tb, Db)
-    extra["attn_bwd"] = {"workload": f"({Bb},{Hb},{Tb},{Db}) bf16 causal: dq, dk, dv, dsink from the saved statistic (mma.sync kernels)",
-                         "ms": ms_b, "tflops": flb / (ms_b * 1e-3) / 1e12, "flop_convention": "2.5 x forward (five GEMMs)",
-                         "frac_of_bf16_peak": flb / (ms_b * 1e-3) / 1e12 / peak_tf}
-    del qb_, kb_, vb_, dob_, ob_, stb_
+    # and the headline attention shape; tcgen05 kernels ("auto") beside the mma.sync ones
+    for name, (Bb, Hb, Tb, Db) in (("attn_bwd", (16, 12, 1024, 64)), ("attn_bwd_seq8192", (1, 16, 8192, 128))):
+        qb_, kb_, vb_, dob_ = (torch.randn((Bb, Hb, Tb, Db), generator=g).bfloat16().to(dev) for _ in range(4))
+        sk = torch.zeros(Hb, device=dev)
+        ob_, stb_, kindb_ = A.flash_attention(qb_, kb_, vb_, sk, kind="asinh", n=16, c=8.0, range_guard=True, return_stat=True)
+        flb = 2.5 * attn_flops(Bb, Hb, Tb, Db)
+        row = {"workload": f"({Bb},{Hb},{Tb},{Db}) bf16 causal: dq, dk, dv, dsink from the saved statistic",
+               "flop_convention": "2.5 x forward (five GEMMs; the kernels run seven, S and dP twice)"}
+        for impl in ("auto", "mma"):
+            fnb = lambda i: A.ops.flash_attention_backward(qb_, kb_, vb_, ob_, dob_, stb_, kindb_, sk, n=16, c=8.0, impl=impl)  # noqa: E731
+            for i in range(3):
+                fnb(i)
+            ms_b = cuda_time(fnb, iters, sync)
+            tag = "" if impl == "auto" else "_mma_sync"
+            row["ms" + tag] = ms_b
+            row["tflops" + tag] = flb / (ms_b * 1e-3) / 1e12
+        row["frac_of_bf16_peak"] = row["tflops"] / peak_tf
+        extra[name] = row
+        del qb_, kb_, vb_, dob_, ob_, stb_
     # ---- Alg-CE head backward (second "next" row): configuration 2's shape ----
     Nh, dh_, Vh = HEAD["N"], HEAD["d"], HEAD["V"]
     hh = torch.randn((Nh, dh_), generator=g).bfloat16().to(dev)
