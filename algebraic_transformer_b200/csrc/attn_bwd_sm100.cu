@@ -49,12 +49,13 @@ template <int D> struct Cfg {
   static constexpr int RING_OFF = 2 * TILE_BYTES;
   static constexpr int CTL_OFF = RING_OFF + NS * 2 * TILE_BYTES;
   static constexpr uint32_t S_COL = 0, DP_COL = 128, ACC0_COL = 256, ACC1_COL = 256 + D;
+  static constexpr uint32_t S1_COL = 384;   // second score buffer, where the accumulators leave room for it
   static constexpr uint32_t IDESC_S = make_idesc_bf16(BT, BT, 0, 0);
   static constexpr uint32_t IDESC_TS = make_idesc_bf16(BT, D, 0, 1);
 };
 
 struct __align__(16) Control {
-  uint64_t res_full, full[MAX_STEPS], empty[MAX_STEPS], s_full, dp_full, p_done, ds_done, acc_full;
+  uint64_t res_full, full[MAX_STEPS], empty[MAX_STEPS], s_full[2], dp_full, p_done[2], ds_done, acc_full;
   uint32_t tmem_base;
   int abort_flag;
   float sink_part[8];
@@ -125,9 +126,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(&ctl->res_full, 1);
     for (int i = 0; i < C::NS; ++i) { mbar_init(&ctl->full[i], 1); mbar_init(&ctl->empty[i], 1); }
-    mbar_init(&ctl->s_full, 1);
+    mbar_init(&ctl->s_full[0], 1);
+    mbar_init(&ctl->s_full[1], 1);
     mbar_init(&ctl->dp_full, 1);
-    mbar_init(&ctl->p_done, EW_THREADS);
+    mbar_init(&ctl->p_done[0], EW_THREADS);
+    mbar_init(&ctl->p_done[1], EW_THREADS);
     mbar_init(&ctl->ds_done, EW_THREADS);
     mbar_init(&ctl->acc_full, 1);
     ctl->abort_flag = 0;
@@ -142,6 +145,12 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
   const BoundedWait bw{&ctl->abort_flag, 1000000000ull};
+  // Two score buffers where tensor memory has 128 columns to spare (one accumulator, or two of 64 columns):
+  // S of step j + 1 is then computed while the threads are still reading S of step j.
+  constexpr bool DB = (MODE == 0) || (D == 64);
+  auto sbuf = [](int j) { return DB ? (j & 1) : 0; };
+  auto sphase = [](int j) -> uint32_t { return DB ? ((j >> 1) & 1u) : (j & 1u); };
+  auto s_col = [](int j) -> uint32_t { return (DB && (j & 1)) ? C::S1_COL : C::S_COL; };
 
   const int nt = p.Tq / BT;
   const int h = blockIdx.x, b = blockIdx.y;
@@ -200,38 +209,39 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                             (first_step && ks == 0) ? 0u : 1u);
         }
       };
-      bool ok = bw.wait(&ctl->res_full, 0) && bw.wait(&ctl->full[0], 0);
-      if (ok) {
+      // S of step j goes to buffer sbuf(j); with two buffers (DB) it is issued one step earlier
+      auto tile0 = [&](int j) { return ring_addr + (j % C::NS) * 2 * C::TILE_BYTES; };
+      auto score_s = [&](int j) -> bool {               // waits for step j's tiles, then S (or S^T) of step j
+        if (!bw.wait(&ctl->full[j % C::NS], (j / C::NS) & 1u)) return false;
         tc_fence_after();
-        issue_scores(tmem_base + C::S_COL, a0_lo, ring_addr);                       // S (or S^T) of step 0
-        umma_commit(&ctl->s_full);
-        issue_scores(tmem_base + C::DP_COL, a1_lo, ring_addr + C::TILE_BYTES);      // dP (or dP^T) of step 0
+        issue_scores(tmem_base + s_col(j), a0_lo, tile0(j));
+        umma_commit(&ctl->s_full[sbuf(j)]);
+        return true;
+      };
+      bool ok = bw.wait(&ctl->res_full, 0) && score_s(0);
+      if (ok) {
+        issue_scores(tmem_base + C::DP_COL, a1_lo, tile0(0) + C::TILE_BYTES);      // dP (or dP^T) of step 0
         umma_commit(&ctl->dp_full);
+        if (DB && nsteps > 1) ok = score_s(1);
       }
       for (int j = 0; j < nsteps && ok; ++j) {
-        const int slot = j % C::NS, nslot = (j + 1) % C::NS;
         const bool has_next = j + 1 < nsteps;
-        const uint32_t t0 = ring_addr + slot * 2 * C::TILE_BYTES, t1 = t0 + C::TILE_BYTES;
-        const uint32_t n0 = ring_addr + nslot * 2 * C::TILE_BYTES, n1 = n0 + C::TILE_BYTES;
+        const uint32_t t0 = tile0(j), t1 = t0 + C::TILE_BYTES;
         // phase 1 is over: S has been read (MODE 1: P^T stands in its place)
-        if (!bw.wait(&ctl->p_done, j & 1u)) { ok = false; break; }
+        if (!bw.wait(&ctl->p_done[sbuf(j)], sphase(j))) { ok = false; break; }
         tc_fence_after();
-        if (MODE == 1) issue_product(tmem_base + C::ACC0_COL, tmem_base + C::S_COL, t1, j == 0);   // dV += P^T dO_i
-        if (has_next) {
-          if (!bw.wait(&ctl->full[nslot], ((j + 1) / C::NS) & 1u)) { ok = false; break; }
-          tc_fence_after();
-          issue_scores(tmem_base + C::S_COL, a0_lo, n0);    // after the dV product: may overwrite P^T
-          umma_commit(&ctl->s_full);
-        }
+        if (MODE == 1) issue_product(tmem_base + C::ACC0_COL, tmem_base + s_col(j), t1, j == 0);   // dV += P^T dO_i
+        if (!DB && has_next && !score_s(j + 1)) { ok = false; break; }   // after the dV product: may overwrite P^T
         // phase 2 is over: dS stands in place of dP
         if (!bw.wait(&ctl->ds_done, j & 1u)) { ok = false; break; }
         tc_fence_after();
         issue_product(tmem_base + (MODE == 0 ? C::ACC0_COL : C::ACC1_COL), tmem_base + C::DP_COL, t0, j == 0);  // dQ += dS K_j / dK += dS^T Q_i
-        umma_commit(&ctl->empty[slot]);
+        umma_commit(&ctl->empty[j % C::NS]);
         if (has_next) {
-          issue_scores(tmem_base + C::DP_COL, a1_lo, n1);   // after that product: may overwrite dS
+          issue_scores(tmem_base + C::DP_COL, a1_lo, tile0(j + 1) + C::TILE_BYTES);   // after that product: may overwrite dS
           umma_commit(&ctl->dp_full);
         }
+        if (DB && j + 2 < nsteps && !score_s(j + 2)) { ok = false; break; }   // into the buffer phase 1 of step j has left
       }
       if (ok) umma_commit(&ctl->acc_full);
     }
@@ -243,7 +253,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const int64_t bh = int64_t(b) * p.H + h;
     float stat_row = 0.f, delta_row = 0.f;
     if (MODE == 0) { stat_row = p.stat[bh * p.Tq + row]; delta_row = p.delta[bh * p.Tq + row]; }
-    const uint32_t s_t = tmem_base + lane_sel + C::S_COL + half * 64, dp_t = tmem_base + lane_sel + C::DP_COL + half * 64;
+    const uint32_t dp_t = tmem_base + lane_sel + C::DP_COL + half * 64;
     bool ok = true;
     for (int j = 0; j < nsteps && ok; ++j) {
       const int other0 = (first + j) * BT;                    // first row of the streamed tile
@@ -252,7 +262,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const float* col_delta = p.delta + bh * p.Tq + other0 + half * 64;
       float2 slope[2][16];
       // ---- phase 1: scores -> weights
-      if (!bw.wait(&ctl->s_full, j & 1u)) { ok = false; break; }
+      const uint32_t s_t = tmem_base + lane_sel + s_col(j) + half * 64;
+      if (!bw.wait(&ctl->s_full[sbuf(j)], sphase(j))) { ok = false; break; }
       tc_fence_after();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -276,7 +287,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
       if (MODE == 1) tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&ctl->p_done);
+      mbar_arrive(&ctl->p_done[sbuf(j)]);
       // ---- phase 2: dP -> dS = slope (dP - delta)
       if (!bw.wait(&ctl->dp_full, j & 1u)) { ok = false; break; }
       tc_fence_after();
