@@ -94,11 +94,13 @@ __device__ __forceinline__ void store_rows64(const WarpOut& w, int lane, const u
 }
 
 // ---- head-backward epilogue: dz for 128 vocabulary columns of one row ------------------------
-// obj = mean_i (1 - pt_i), pt_i = w_it / l_i, w = rho(x)^n, x = min(z / c, clamp):
-//   d obj / d z_ij = a_i s_ij (p_ij - [j == t_i]),  a_i = g pt_i / N,  p = w / l,
-//   s = n / (c sqrt(1 + x^2)) where the clamp is not active, else 0
-// (src/algebraic/kernels/fused_head.py:120-156).  `a_i` and 1/l_i come in as arguments; `tgt` is
-// the target's column inside this shard (any value outside [0, V_local) when it lives elsewhere).
+// The reference's custom VJP does not differentiate the primal value mean_i (1 - pt_i): it applies
+// the gradient of the negative log-likelihood,
+//   dz_ij = (g / N) (n / c) r_ij (p_ij - [j == t_i]),  p = w / l,  w = rho(x)^n,
+//   x = min(z / c, clamp),  r = 1 / sqrt(1 + x^2)  (the clamp is straight-through: r of the clamped x)
+// (src/algebraic/kernels/fused_head.py:120-145 and 236-243, src/algebraic/algebraic.py:309-316).
+// `a_i` = g / N and 1/l_i come in as arguments; `tgt` is the target's column inside this shard
+// (any value outside [0, V_local) when it lives elsewhere).
 __device__ __forceinline__ void dz_cols(const ProjParams& p, uint32_t taddr, const WarpOut& wo, int lane, int col0,
                                         float a_i, float inv_l, int tgt) {
 #pragma unroll 1
@@ -116,12 +118,11 @@ __device__ __forceinline__ void dz_cols(const ProjParams& p, uint32_t taddr, con
       const float an = a_i * p.n_over_c;
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        const float xr = __uint_as_float(r[i]) * p.inv_c;
-        const float x = fminf(xr, p.clamp);
+        const float x = fminf(__uint_as_float(r[i]) * p.inv_c, p.clamp);
         const float rad = fmaf(x, x, 1.0f);
         const float rs = rsqrt_approx(rad);
         w[i] = fmaf(rad, rs, x);                                                // rho_fast(x)
-        sl[i] = (xr < p.clamp) ? an * rs : 0.f;                                 // a_i s_ij
+        sl[i] = an * rs;                                                        // (g / N) (n / c) r_ij
       }
       for (int it = 0; it < p.log2n; ++it) {
 #pragma unroll
@@ -386,13 +387,12 @@ proj_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
           qkv_head<D>(p, s_gain, tbuf + lcol, gcol / hd, tc, ts, wo, lane, gcol, live, best_q, best_k, best_v);
         }
       } else if (EPI == EPI_DZ) {
-        // per-row constants of the head's backward: 1 / l_i and a_i = g pt_i / N
+        // per-row constants of the head's backward: 1 / l_i and the common factor g / N
         float inv_l = 0.f, a_i = 0.f;
         int tgt = -1;
         if (live) {
           inv_l = 1.0f / p.l[row];
-          const float xt = fminf(p.zt[row] * p.inv_c, p.clamp);
-          a_i = p.gscale * pow2n_rt(rho_stable(xt), p.log2n) * inv_l;
+          a_i = p.gscale;
           tgt = p.targets[row] - p.vocab_offset;
         }
         dz_cols(p, tbuf + half * 128, wo, lane, n * BN + half * 128, a_i, inv_l, tgt);

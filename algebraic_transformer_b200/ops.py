@@ -513,8 +513,11 @@ def fused_head(h, embed, targets, *, kind: str = "ce", n: int = 16, c: float = 1
 
 def fused_head_backward(h, e_bf16, targets, stats, *, n: int = 8, c: float = 2.0, vocab_offset: int = 0,
                         vocab_total: Optional[int] = None, upstream: float = 1.0):
-    """Gradients of the Alg-CE objective `mean(1 - pt)` with respect to the hidden states and this
-    shard's embedding rows: `(dh, de)` (src/algebraic/kernels/fused_head.py:120-156, 194-216).
+    """What the reference's custom VJP of the Alg-CE head returns for the hidden states and this
+    shard's embedding rows, `(dh, de)` (src/algebraic/kernels/fused_head.py:120-156, 194-216,
+    236-243): the gradient of the mean negative log-likelihood, `dz = upstream/N * (n/c) * (p - y) /
+    sqrt(1 + x^2)` with the clamp straight-through — not the derivative of the primal value
+    `mean(1 - pt)`, which the reference uses as a monotone stand-in only (algebraic.py:232-262).
     `stats` is the forward's `(2, N)` statistic (`head_statistic`, summed over all shards).  The
     logit gradient is rebuilt tile by tile from `stats` by one kernel and written as bf16; the two
     products `dz . E` and `dz^T . h` are library GEMMs, as in the reference.  With several shards

@@ -356,8 +356,12 @@ ALG_API int alg_glu_proj_fwd(const alg_glu_proj_args* args, void* stream);
  * (src/algebraic/kernels/fused_head.py:120-156), which also writes dz in bf16 and leaves
  * dh = dz . E and dE = dz^T . h to library matmuls (fused_head.py:194-216).
  * h: (N, d) bf16; e: (V_local, d) bf16; targets: (N) int32 global ids; l, zt: (N) fp32 — the
- * forward's statistic, l summed over all vocabulary shards; dz: (N, V_local) bf16 contiguous
- * out, V_local a multiple of 8; upstream = d loss / d objective.  obj = mean(1 - pt). */
+ * forward's statistic, l summed over all vocabulary shards (zt is accepted for symmetry with the
+ * forward and not read); dz: (N, V_local) bf16 contiguous out, V_local a multiple of 8;
+ * upstream = the cotangent of the objective.  As in the reference's custom VJP, the gradient is
+ * that of the negative log-likelihood, not of the primal value mean(1 - pt):
+ * dz = upstream / N * (n / c) * (p - onehot) / sqrt(1 + x^2), x = min(z / c, clamp), the clamp
+ * straight-through (fused_head.py:236-243, src/algebraic/algebraic.py:232-262, 309-316). */
 typedef struct {
   const void* h;
   const void* e;

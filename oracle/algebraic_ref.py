@@ -341,6 +341,32 @@ def algebraic_likelihood_lean(logits, targets, n: int, c: float):
     return (1.0 - pt).mean(), pt
 
 
+def algebraic_likelihood_lean_vjp(logits, targets, n: int, c: float, g: float = 1.0):
+    """The logit cotangent the reference's custom VJP returns for the Alg-CE head
+    (algebraic.py:309-316, same rule in algebraic.py:255-262 and kernels/fused_head.py:120-145,
+    236-243): `g (n/c)/N * r * (p - y)` with `r = rsqrt(1 + x^2)` of the CLAMPED x (straight-through
+    clamp).  This is the gradient of the mean negative log-likelihood, not of the primal value
+    mean(1 - pt) that `algebraic_likelihood_lean` returns, so autograd through that function does
+    NOT reproduce it."""
+    z = _acc(logits)
+    x = torch.clamp(z / c, max=likelihood_clamp(z.shape[-1], n))
+    rad = 1.0 + x * x
+    r = rsqrt(rad)
+    w = int_pow(x + rad * r, n)
+    p = w / w.sum(dim=-1, keepdim=True)
+    y = torch.zeros_like(p)
+    y.scatter_(-1, targets.long()[:, None], 1.0)
+    return (g * (n / c) / z.shape[0]) * r * (p - y)
+
+
+def head_vjp_dense(h, embed, targets, n: int = 8, c: float = 2.0, g: float = 1.0):
+    """(dh, dE) of the model's Alg-CE head under the reference's custom VJP: the logit cotangent
+    above pushed through z = h . E^T (fused_head.py:194-216: dh = dz . E, dE = dz^T . h)."""
+    e = embed.to(h.dtype).to(F32)
+    dz = algebraic_likelihood_lean_vjp(head_logits(h, embed), targets, n, c, g)
+    return dz @ e, dz.t() @ h.to(F32)
+
+
 def head_logits(h, embed):
     """z = h . bf16(E)^T with fp32 accumulation.  model.py:225."""
     e = embed.to(h.dtype)

@@ -137,6 +137,15 @@ def main():
         out[f"lik_lean_n{n}_obj"], out[f"lik_lean_n{n}_pt"] = np.array(o2), p2
         out[f"lik_lean32_n{n}_obj"], out[f"lik_lean32_n{n}_pt"] = np.array(o3), p3
         out[f"probs_n{n}"] = A.algebraic_probs(z, n, c_)
+        # the custom VJPs' backward rules, called directly (algebraic.py:255-262, 309-316): the logit
+        # cotangent for an objective cotangent of 0.75
+        out[f"lik_exact_n{n}_vjp"] = A._alg_lik_bwd(n, c_, (A.algebraic_probs(z, n, c_), z, t), (0.75, None))[0]
+        out[f"lik_lean_n{n}_vjp"] = A._lean_bwd(n, c_, (z, t), (0.75, None))[0]
+    # a row whose largest logit sits above the clamp: the lean rule is straight-through there
+    zc = z.copy()
+    zc[2, 11] = 2.0 * 8 * A.likelihood_clamp(300, 8)
+    out["lik_zclamp"] = zc
+    out["lik_lean_n8_vjp_clamped"] = A._lean_bwd(8, 2.0, (zc, t), (1.0, None))[0]
     vocabs = np.array([50304, 32768, 32000, 4096, 97])
     out["clamp_vocabs"] = vocabs
     for n in (8, 16):

@@ -458,21 +458,39 @@ def test_attention_backward_matches_oracle_autograd(shape, with_sink, causal, im
         assert rel_l2(ds, ws) < 2e-2
 
 
-def test_head_backward_matches_oracle_autograd():
-    """dh and dE of the Alg-CE objective (fused_head.py:120-156, 194-216) against autograd through the
-    oracle's dense head; ragged N and V; then the same through two vocabulary shards."""
+def test_head_backward_matches_reference_vjp():
+    """dh and dE of the Alg-CE head as the reference's custom VJP defines them (fused_head.py:120-156,
+    194-216, 236-243: the gradient of the mean negative log-likelihood, clamp straight-through)
+    against the oracle's restatement of that rule, which is pinned to the reference's own backward
+    functions; ragged N and V; a non-unit cotangent; then the same through two vocabulary shards."""
     N, d, V = 300, 128, 1000
     h = randn((N, d), 971).bfloat16()
     E = (randn((V, d), 972) * 0.3).bfloat16()
     g = torch.Generator().manual_seed(973)
     t = torch.randint(0, V, (N,), generator=g)
-    hf, ef = h.float().requires_grad_(True), E.float().requires_grad_(True)
-    obj, _ = R.algebraic_likelihood_lean(hf @ ef.t(), t, 8, 2.0)
-    obj.backward()
+    want_dh, want_de = R.head_vjp_dense(h, E, t, 8, 2.0)
+
+    class _Grad:                                          # keeps the assertions below readable
+        def __init__(self, v):
+            self.grad = v
+    hf, ef = _Grad(want_dh), _Grad(want_de)
     hd, Ed, td = dev(h, E, t)
     stats = A.head_statistic(hd, Ed, td.int(), n=8, c=2.0)
     dh, de = A.ops.fused_head_backward(hd, Ed, td, stats, n=8, c=2.0)
     assert rel_l2(dh, hf.grad) < 2e-2 and rel_l2(de, ef.grad) < 2e-2
+    dh2, de2 = A.ops.fused_head_backward(hd, Ed, td, stats, n=8, c=2.0, upstream=0.5)
+    assert rel_l2(dh2, 0.5 * hf.grad) < 2e-2 and rel_l2(de2, 0.5 * ef.grad) < 2e-2
+    # a logit far above the clamp (z / c = 57600 against a clamp of 5928): the rule is straight-through,
+    # so that entry still contributes r (p - y) n / (c N) to its row of dh and to its row of dE
+    hc, Ec, tc = h.clone(), E.clone(), t.clone()
+    hc[5], Ec[7] = 30.0, 30.0
+    tc[5] = 11
+    wc_dh, wc_de = R.head_vjp_dense(hc, Ec, tc, 8, 2.0)
+    hcd, Ecd, tcd = dev(hc, Ec, tc)
+    sc = A.head_statistic(hcd, Ecd, tcd.int(), n=8, c=2.0)
+    dhc, dec = A.ops.fused_head_backward(hcd, Ecd, tcd, sc, n=8, c=2.0)
+    assert rel_l2(dhc, wc_dh) < 2e-2 and rel_l2(dec, wc_de) < 2e-2
+    assert rel_l2(dhc[5], wc_dh[5]) < 3e-2 and rel_l2(dec[7], wc_de[7]) < 3e-2
     # two shards: the statistic is summed over them, each shard returns its rows of dE and a part of dh
     lo = 504
     s0 = A.head_statistic(hd, Ed[:lo].contiguous(), td.int(), n=8, c=2.0, vocab_offset=0, vocab_total=V)

@@ -112,6 +112,35 @@ def test_likelihoods(golden, n, c):
     close(R.algebraic_probs(z, n, c), g[f"probs_n{n}"], 1e-12, 1e-300)
 
 
+@pytest.mark.parametrize("n,c", [(16, 16.0), (8, 2.0)])
+def test_likelihood_vjp_rule(golden, n, c):
+    """The logit cotangent of the reference's custom VJPs (algebraic.py:255-262, 309-316), evaluated by
+    the reference's own backward functions, against the oracle's restatement; the exact and the lean
+    rule agree while the clamp is idle; and the rule is the gradient of the mean negative
+    log-likelihood, which autograd through the primal value mean(1 - pt) is not."""
+    g = golden
+    z, t = T(g["lik_z"]), T(g["lik_t"])
+    got = R.algebraic_likelihood_lean_vjp(z, t, n, c, 0.75)
+    close(got, g[f"lik_lean_n{n}_vjp"], 1e-11, 1e-15)
+    close(got, g[f"lik_exact_n{n}_vjp"], 1e-9, 1e-13)
+    zz = z.clone().requires_grad_(True)
+    p = R.algebraic_probs(zz, n, c)
+    nll = -torch.log(p.gather(-1, t.long()[:, None])[:, 0]).mean()
+    nll.backward()
+    close(got, 0.75 * zz.grad, 1e-9, 1e-13)
+    zp = z.clone().requires_grad_(True)
+    R.algebraic_likelihood_lean(zp, t, n, c)[0].backward()
+    assert float((0.75 * zp.grad - got).abs().max()) > 1e-3 * float(got.abs().max())
+
+
+def test_likelihood_vjp_rule_clamp_is_straight_through(golden):
+    g = golden
+    z, t = T(g["lik_zclamp"]), T(g["lik_t"])
+    got = R.algebraic_likelihood_lean_vjp(z, t, 8, 2.0, 1.0)
+    close(got, g["lik_lean_n8_vjp_clamped"], 1e-11, 1e-15)
+    assert float(got[2, 11]) > 0.0            # the clamped entry still receives (p - y) r n / (c N)
+
+
 def test_dispatch_constants(golden):
     g = golden
     for n in (8, 16):
