@@ -52,7 +52,8 @@ class AttnBwdArgs(C.Structure):
 class HeadBwdArgs(C.Structure):
     _fields_ = [("h", C.c_void_p), ("e", C.c_void_p), ("targets", C.c_void_p), ("l", C.c_void_p), ("zt", C.c_void_p),
                 ("dz", C.c_void_p), ("N", C.c_int), ("d", C.c_int), ("V_local", C.c_int), ("vocab_offset", C.c_int),
-                ("V_total", C.c_int), ("n", C.c_int), ("c", C.c_float), ("upstream", C.c_float), ("status", C.c_void_p)]
+                ("V_total", C.c_int), ("n", C.c_int), ("c", C.c_float), ("upstream", C.c_float), ("status", C.c_void_p),
+                ("kind", C.c_int)]
 
 
 class QkvProjArgs(C.Structure):
@@ -80,7 +81,10 @@ class HeadArgs(C.Structure):
                 ("zt_out", C.c_void_p), ("N", C.c_int), ("d", C.c_int), ("V_local", C.c_int),
                 ("vocab_offset", C.c_int), ("V_total", C.c_int), ("n", C.c_int), ("c", C.c_float),
                 ("impl", C.c_int), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-                ("status", C.c_void_p)]
+                ("status", C.c_void_p), ("kind", C.c_int)]
+
+
+HEAD_ALG_CE, HEAD_CE = 0, 1
 
 
 ALG_MAX_RANKS = 16
@@ -113,6 +117,8 @@ SYMBOLS = {
     "alg_head_finalize_workspace_bytes": (C.c_size_t, [C.c_int]),
     "alg_head_finalize": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_int,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "alg_head_finalize_ce": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                       C.c_void_p, C.c_size_t, C.c_void_p]),
     "alg_cast_f32_to_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "alg_qkv_proj_fwd": (C.c_int, [C.POINTER(QkvProjArgs), C.c_void_p]),
     "alg_glu_proj_fwd": (C.c_int, [C.POINTER(GluProjArgs), C.c_void_p]),

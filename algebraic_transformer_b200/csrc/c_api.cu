@@ -330,18 +330,24 @@ int alg_head_bwd_dz(const alg_head_bwd_args* a, void* stream_) {
     set_error("head backward: V_local a multiple of 8 inside the vocabulary, d a multiple of 64");
     return ALG_ERR_INVALID;
   }
-  if (a->n < 2 || a->n > 32 || ilog2_exact(a->n) < 0 || !(a->c > 0.0f)) { set_error("head backward: n a power of two in [2, 32], c positive"); return ALG_ERR_INVALID; }
+  if (a->kind != ALG_HEAD_ALG_CE && a->kind != ALG_HEAD_CE) { set_error("head backward: unknown kind %d", a->kind); return ALG_ERR_INVALID; }
+  const bool ce = a->kind == ALG_HEAD_CE;
+  if (!ce && (a->n < 2 || a->n > 32 || ilog2_exact(a->n) < 0 || !(a->c > 0.0f))) { set_error("head backward: n a power of two in [2, 32], c positive"); return ALG_ERR_INVALID; }
   if (!aligned16(a->h) || !aligned16(a->e) || !aligned16(a->dz)) { set_error("head backward: 16-byte alignment required"); return ALG_ERR_INVALID; }
   if (a->N == 0) return ALG_OK;
   ProjParams p{};
   p.M = a->N; p.K = a->d; p.N = a->V_local; p.ld_x = a->d;
   p.out = static_cast<__nv_bfloat16*>(a->dz); p.ld_out = a->V_local;
   p.targets = a->targets; p.l = a->l; p.zt = a->zt;
-  p.vocab_offset = a->vocab_offset; p.log2n = ilog2_exact(a->n);
-  p.inv_c = 1.0f / a->c;
-  p.clamp = float(0.25 * root_pow2(1e38 / double(a->V_total), a->n));       // fused_head.py:273
-  p.n_over_c = float(a->n) / a->c;
-  p.gscale = a->upstream / float(a->N);
+  p.vocab_offset = a->vocab_offset;
+  p.head_kind = a->kind;
+  if (!ce) {
+    p.log2n = ilog2_exact(a->n);
+    p.inv_c = 1.0f / a->c;
+    p.clamp = float(0.25 * root_pow2(1e38 / double(a->V_total), a->n));       // fused_head.py:273
+    p.n_over_c = float(a->n) / a->c;
+  }
+  p.gscale = a->upstream / float(a->N);                                        // ce: slope 1 (fused_head.py:240)
   p.D = 64;
   p.status = a->status;
   return launch_proj(p, a->h, a->e, 2, stream);
@@ -389,8 +395,10 @@ int head_fill(const alg_head_args* a, HeadParams* p, bool* use_fast) {
     set_error("head: null argument");
     return ALG_ERR_INVALID;
   }
-  if (a->n < 2 || a->n > 32 || ilog2_exact(a->n) < 0) { set_error("n must be a power of two"); return ALG_ERR_INVALID; }
-  if (!(a->c > 0.0f) || !isfinite(a->c)) { set_error("head scale c must be positive and finite"); return ALG_ERR_INVALID; }
+  if (a->kind != ALG_HEAD_ALG_CE && a->kind != ALG_HEAD_CE) { set_error("head: unknown kind %d", a->kind); return ALG_ERR_INVALID; }
+  const bool ce = a->kind == ALG_HEAD_CE;
+  if (!ce && (a->n < 2 || a->n > 32 || ilog2_exact(a->n) < 0)) { set_error("n must be a power of two"); return ALG_ERR_INVALID; }
+  if (!ce && (!(a->c > 0.0f) || !isfinite(a->c))) { set_error("head scale c must be positive and finite"); return ALG_ERR_INVALID; }
   if (a->N < 0 || a->d < 8 || a->d % 8 != 0 || a->V_local < 1 || a->V_total < a->V_local || a->vocab_offset < 0 ||
       a->vocab_offset + a->V_local > a->V_total) {
     set_error("head: bad extents (N=%d d=%d V_local=%d offset=%d V_total=%d)", a->N, a->d, a->V_local, a->vocab_offset, a->V_total);
@@ -400,15 +408,17 @@ int head_fill(const alg_head_args* a, HeadParams* p, bool* use_fast) {
   if (a->impl < ALG_IMPL_AUTO || a->impl > ALG_IMPL_TCGEN05) { set_error("unknown impl %d", a->impl); return ALG_ERR_INVALID; }
   p->h = a->h; p->e = a->e; p->targets = a->targets; p->l_out = a->l_out; p->zt_out = a->zt_out;
   p->N = a->N; p->d = a->d; p->V_local = a->V_local; p->vocab_offset = a->vocab_offset;
-  p->log2n = ilog2_exact(a->n);
-  p->inv_c = 1.0f / a->c;
-  p->clamp = float(0.25 * root_pow2(1e38 / double(a->V_total), a->n));   // fused_head.py:273
+  p->kind = a->kind;
+  p->log2n = ce ? -1 : ilog2_exact(a->n);
+  p->inv_c = ce ? 1.0f : 1.0f / a->c;
+  p->clamp = ce ? 0.0f : float(0.25 * root_pow2(1e38 / double(a->V_total), a->n));   // fused_head.py:273
   p->status = a->status;
   const bool fast = head_tcgen05_supports(*p);
-  if (a->impl == ALG_IMPL_TCGEN05 && !fast) {
-    set_error("head: the tcgen05 kernel needs d to be a multiple of 64");
+  if ((a->impl == ALG_IMPL_TCGEN05 || ce) && !fast) {
+    set_error("head: the tcgen05 kernel (the only one with the ce kind) needs d to be a multiple of 64");
     return ALG_ERR_UNSUPPORTED;
   }
+  if (ce && a->impl == ALG_IMPL_MMA) { set_error("head: the ce kind has no legacy-MMA kernel"); return ALG_ERR_UNSUPPORTED; }
   *use_fast = fast && a->impl != ALG_IMPL_MMA;
   p->splits = *use_fast ? head_tcgen05_splits(a->N, a->V_local) : head_mma_splits(a->N, a->V_local);
   return ALG_OK;
@@ -420,7 +430,7 @@ size_t alg_head_workspace_bytes(const alg_head_args* a) {
   int s = head_mma_splits(a->N, a->V_local);
   const int s2 = head_tcgen05_splits(a->N, a->V_local);
   if (s2 > s) s = s2;
-  return align256(size_t(2) * s * size_t(a->N > 0 ? a->N : 0) * sizeof(float));
+  return align256(size_t(3) * s * size_t(a->N > 0 ? a->N : 0) * sizeof(float));   // l, zt and (ce kind) m partials
 }
 
 int alg_head_fwd(const alg_head_args* a, void* stream_) {
@@ -429,13 +439,14 @@ int alg_head_fwd(const alg_head_args* a, void* stream_) {
   bool fast = false;
   if (int rc = head_fill(a, &p, &fast)) return rc;
   if (a->N == 0) return ALG_OK;
-  const size_t need = size_t(2) * p.splits * size_t(a->N) * sizeof(float);
+  const size_t need = size_t(p.kind == ALG_HEAD_CE ? 3 : 2) * p.splits * size_t(a->N) * sizeof(float);
   if (a->workspace == nullptr || a->workspace_bytes < need || !aligned16(a->workspace)) {
     set_error("head: workspace of %zu bytes required, got %zu", alg_head_workspace_bytes(a), a->workspace_bytes);
     return ALG_ERR_WORKSPACE;
   }
   p.l_part = static_cast<float*>(a->workspace);
   p.zt_part = p.l_part + size_t(p.splits) * a->N;
+  p.m_part = p.kind == ALG_HEAD_CE ? p.zt_part + size_t(p.splits) * a->N : nullptr;
   if (int rc = fast ? launch_head_tcgen05(p, stream) : launch_head_mma(p, stream)) return rc;
   return launch_head_reduce(p, stream);
 }
@@ -463,6 +474,25 @@ int alg_head_finalize(const float* l, const float* zt, int N, int n, float c, in
   }
   const float clamp = float(0.25 * root_pow2(1e38 / double(V_total), n));
   return launch_head_finalize(l, zt, N, ilog2_exact(n), 1.0f / c, clamp, pt, nll, obj, sums, ticket, stream);
+}
+
+int alg_head_finalize_ce(const float* lse, const float* zt, int N, float* pt, float* nll, float* obj,
+                         void* workspace, size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (lse == nullptr || zt == nullptr || N < 0) { set_error("head_finalize_ce: bad argument"); return ALG_ERR_INVALID; }
+  if (N == 0) return ALG_OK;
+  float* sums = nullptr;
+  unsigned* ticket = nullptr;
+  if (obj != nullptr) {
+    if (workspace == nullptr || workspace_bytes < alg_head_finalize_workspace_bytes(N)) {
+      set_error("head_finalize_ce: workspace of %zu bytes required", alg_head_finalize_workspace_bytes(N));
+      return ALG_ERR_WORKSPACE;
+    }
+    ticket = static_cast<unsigned*>(workspace);
+    sums = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + 16);
+    ALG_CUDA_TRY(cudaMemsetAsync(ticket, 0, sizeof(unsigned), stream));
+  }
+  return launch_head_finalize(lse, zt, N, /*log2n=*/-1, 1.0f, 0.0f, pt, nll, obj, sums, ticket, stream);
 }
 
 int alg_cast_f32_to_bf16(const float* src, void* dst, size_t count, void* stream) {

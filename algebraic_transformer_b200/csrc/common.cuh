@@ -38,6 +38,14 @@ __device__ __forceinline__ float rsqrt_approx(float x) {
   return y;
 }
 
+// 2^x on the special-function unit (the softmax cross-entropy head only; the algebraic paths use
+// no exponential)
+__device__ __forceinline__ float exp2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // rho(x) = x + sqrt(1 + x^2), summation form (relative cancellation O(eps x^2) for x << 0).
 // src/algebraic/kernels/flash.py:84-88.
 __device__ __forceinline__ float rho_fast(float x) {

@@ -167,6 +167,7 @@ extern "C" int alg_head_fwd_exchange(const alg_head_args* a, const alg_head_exch
   HeadParams p{};
   bool fast = false;
   if (int rc = head_fill(&tmp, &p, &fast)) return rc;
+  if (p.kind != ALG_HEAD_ALG_CE) { set_error("head exchange: only the alg_ce kind (ce shards combine by logsumexp)"); return ALG_ERR_UNSUPPORTED; }
   if (a->N == 0) return ALG_OK;
   const size_t need = size_t(2) * p.splits * size_t(a->N) * sizeof(float);
   if (a->workspace == nullptr || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 15)) {

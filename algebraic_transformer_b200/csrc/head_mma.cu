@@ -160,16 +160,30 @@ __global__ void __launch_bounds__(NTHREADS) head_mma_kernel(const HeadParams p) 
   }
 }
 
+// Sums the split partials of a row.  With `m_part` (softmax cross-entropy) a partial is the pair
+// (m, sum exp(z - m)) and the result written to l_out is the row's logsumexp m + log l
+// (src/algebraic/kernels/fused_head.py:87-94, 113-114).
 __global__ void head_reduce_kernel(const float* __restrict__ l_part, const float* __restrict__ zt_part,
-                                   int N, int splits, float* __restrict__ l_out, float* __restrict__ zt_out) {
+                                   const float* __restrict__ m_part, int N, int splits, float* __restrict__ l_out,
+                                   float* __restrict__ zt_out) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= N) return;
   float l = 0.f, z = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    l += l_part[int64_t(s) * N + i];
-    z += zt_part[int64_t(s) * N + i];
+  if (m_part == nullptr) {
+    for (int s = 0; s < splits; ++s) {
+      l += l_part[int64_t(s) * N + i];
+      z += zt_part[int64_t(s) * N + i];
+    }
+    l_out[i] = l;
+  } else {
+    float m = -1e30f;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, m_part[int64_t(s) * N + i]);
+    for (int s = 0; s < splits; ++s) {
+      l += l_part[int64_t(s) * N + i] * expf(m_part[int64_t(s) * N + i] - m);
+      z += zt_part[int64_t(s) * N + i];
+    }
+    l_out[i] = m + logf(l);
   }
-  l_out[i] = l;
   zt_out[i] = z;
 }
 
@@ -186,7 +200,14 @@ __global__ void __launch_bounds__(FIN_THREADS) head_finalize_kernel(
   __shared__ bool last;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   float miss = 0.f;
-  if (i < N) {
+  if (i < N && log2n < 0) {
+    // softmax cross-entropy: l holds the logsumexp; nll = lse - zt, objective = mean nll
+    // (src/algebraic/kernels/fused_head.py:221-223, src/algebraic/standard.py:41-47)
+    const float nll = l[i] - zt[i];
+    if (pt_out != nullptr) pt_out[i] = expf(-nll);
+    if (nll_out != nullptr) nll_out[i] = nll;
+    miss = nll;
+  } else if (i < N) {
     const float x = fminf(zt[i] * inv_c, clamp);
     const float ptv = pow2n_rt(rho_stable(x) * inv_root_rt(l[i], log2n), log2n);
     if (pt_out != nullptr) pt_out[i] = ptv;
@@ -226,6 +247,10 @@ int head_mma_splits(int N, int V_local) {
 }
 
 int launch_head_mma(const HeadParams& p, cudaStream_t stream) {
+  if (p.kind != ALG_HEAD_ALG_CE) {
+    set_error("head (legacy MMA path): only the alg_ce kind; softmax cross-entropy needs d to be a multiple of 64");
+    return ALG_ERR_UNSUPPORTED;
+  }
   if (p.d % BK != 0) {
     set_error("head (legacy MMA path): d must be a multiple of %d, got %d", BK, p.d);
     return ALG_ERR_UNSUPPORTED;
@@ -243,7 +268,8 @@ int launch_head_mma(const HeadParams& p, cudaStream_t stream) {
 }
 
 int launch_head_reduce(const HeadParams& p, cudaStream_t stream) {
-  head_reduce_kernel<<<(p.N + 255) / 256, 256, 0, stream>>>(p.l_part, p.zt_part, p.N, p.splits, p.l_out, p.zt_out);
+  head_reduce_kernel<<<(p.N + 255) / 256, 256, 0, stream>>>(p.l_part, p.zt_part, p.kind == ALG_HEAD_CE ? p.m_part : nullptr,
+                                                            p.N, p.splits, p.l_out, p.zt_out);
   ALG_CUDA_TRY(cudaGetLastError());
   count_launch();
   return ALG_OK;

@@ -54,6 +54,11 @@ Plan make_plan(int N, int V_local) {
   return pl;
 }
 
+// LOG2N = log2 of the power of the algebraic likelihood, or LOG2N_CE for the softmax cross-entropy
+// kind: the same GEMM and partial layout, with an online logsumexp (running maximum m, sum of
+// exp(z - m) rescaled when m grows; src/algebraic/kernels/fused_head.py:87-94) in place of rho^n.
+constexpr int LOG2N_CE = -1;
+
 template <int LOG2N>
 __global__ void __launch_bounds__(NTHREADS, 1)
 head_tc_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constant__ CUtensorMap tm_e,
@@ -143,6 +148,7 @@ head_tc_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constant__
       const int row = m * BM + row_in_tile;
       const int tgt = (row < p.N) ? (p.targets[row] - p.vocab_offset) : -0x40000000;
       float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f, zt = 0.f;
+      float m_run = -1e30f;                                // ce kind: running maximum of this thread's logits
       for (int t = t0; t < t1 && ok; ++t, ++tile_count) {
         const uint32_t buf = tile_count & 1u, tphase = (tile_count >> 1) & 1u;
         if (!bw.wait(&ctl->tfull[buf], tphase)) { ok = false; break; }
@@ -159,6 +165,29 @@ head_tc_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constant__
           if (dt < 32u) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) zt += (unsigned(j) == dt) ? __uint_as_float(r[j]) : 0.f;
+          }
+          if (LOG2N == LOG2N_CE) {
+            if (c0 >= p.V_local) continue;                 // nothing but zero-filled columns (same for the whole warp)
+            constexpr float LOG2E = 1.4426950408889634f;
+            float cmax = -1e30f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (tail && c0 + j >= p.V_local) r[j] = __float_as_uint(-1e30f);   // exp -> 0 below
+              cmax = fmaxf(cmax, __uint_as_float(r[j]));
+            }
+            const float m_new = fmaxf(m_run, cmax);
+            const float resc = exp2_approx((m_run - m_new) * LOG2E);   // 0 on the first chunk, where the sums are 0
+            const float off = -m_new * LOG2E;
+            l0 *= resc; l1 *= resc; l2 *= resc; l3 *= resc;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              l0 += exp2_approx(fmaf(__uint_as_float(r[j]), LOG2E, off));
+              l1 += exp2_approx(fmaf(__uint_as_float(r[j + 1]), LOG2E, off));
+              l2 += exp2_approx(fmaf(__uint_as_float(r[j + 2]), LOG2E, off));
+              l3 += exp2_approx(fmaf(__uint_as_float(r[j + 3]), LOG2E, off));
+            }
+            m_run = m_new;
+            continue;
           }
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
@@ -179,6 +208,7 @@ head_tc_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constant__
         const int slot = s * 2 + half;
         p.l_part[int64_t(slot) * p.N + row] = (l0 + l1) + (l2 + l3);
         p.zt_part[int64_t(slot) * p.N + row] = zt;
+        if (LOG2N == LOG2N_CE) p.m_part[int64_t(slot) * p.N + row] = m_run;   // (-1e30, 0) when the slot saw no column
       }
     }
   }
@@ -218,7 +248,9 @@ int launch_log2n(const CUtensorMap& tm_h, const CUtensorMap& tm_e, const HeadPar
 
 }  // namespace
 
-bool head_tcgen05_supports(const HeadParams& p) { return p.d >= BK && p.d % BK == 0 && p.log2n >= 1 && p.log2n <= 5; }
+bool head_tcgen05_supports(const HeadParams& p) {
+  return p.d >= BK && p.d % BK == 0 && (p.kind == ALG_HEAD_CE || (p.log2n >= 1 && p.log2n <= 5));
+}
 
 int head_tcgen05_splits(int N, int V_local) {
   if (N <= 0 || V_local <= 0) return 2;
@@ -244,6 +276,7 @@ int launch_head_tcgen05(const HeadParams& p, cudaStream_t stream) {
   ALG_CUDA_TRY(cudaGetDevice(&dev));
   ALG_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const int grid = pl.units < sms ? pl.units : sms;
+  if (p.kind == ALG_HEAD_CE) return launch_log2n<LOG2N_CE>(tm_h, tm_e, p, pl, grid, stream);
   switch (p.log2n) {
     case 1: return launch_log2n<1>(tm_h, tm_e, p, pl, grid, stream);
     case 2: return launch_log2n<2>(tm_h, tm_e, p, pl, grid, stream);

@@ -60,6 +60,7 @@ extern "C" int alg_head_fwd_static(const alg_head_args* a, void* stream_) {
   HeadParams p{};
   bool fast = false;
   if (int rc = head_fill(a, &p, &fast)) return rc;
+  if (p.kind != ALG_HEAD_ALG_CE) { set_error("alg_head_fwd_static: only the alg_ce kind"); return ALG_ERR_UNSUPPORTED; }
   if (a->N == 0) return ALG_OK;
   const size_t need = size_t(2) * size_t(p.splits) * size_t(a->N);      // floats: l and zt partials
   if (need > kScratchFloats) {

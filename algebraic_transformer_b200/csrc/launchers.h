@@ -123,6 +123,7 @@ struct ProjParams {
   const float* zt;         // (M) target logit of the forward
   int vocab_offset, log2n;
   float inv_c, clamp, n_over_c, gscale;   // 1/c, logit clamp, n/c, upstream gradient / M
+  int head_kind;                          // ALG_HEAD_ALG_CE, or ALG_HEAD_CE: `l` holds the rows' logsumexp
   int* status;
 };
 int launch_proj(const ProjParams& p, const void* x, const void* w, int epi, cudaStream_t stream);   // epi 0 QKV, 1 GLU, 2 head dz
@@ -161,6 +162,8 @@ struct HeadParams {
   float* l_part;           // (splits, N)
   float* zt_part;          // (splits, N)
   int* status;
+  int kind;                // ALG_HEAD_ALG_CE, or ALG_HEAD_CE: softmax cross-entropy, l_out = logsumexp
+  float* m_part;           // (splits, N) running maxima of the partial sums, ALG_HEAD_CE only
 };
 int head_mma_splits(int N, int V_local);
 int launch_head_mma(const HeadParams& p, cudaStream_t stream);

@@ -112,6 +112,20 @@ __device__ __forceinline__ void dz_cols(const ProjParams& p, uint32_t taddr, con
       tmem_ld_32x32(taddr + u * 64 + c * 32, r);
       tmem_ld_wait();
       const int cbase = col0 + u * 64 + c * 32;
+      if (p.head_kind == ALG_HEAD_CE) {
+        // softmax cross-entropy: dz = (g / N) (exp(z - lse) - y), `inv_l` carries the row's logsumexp
+        // (src/algebraic/kernels/fused_head.py:134-135)
+        constexpr float LOG2E = 1.4426950408889634f;
+        const float off = -inv_l * LOG2E;
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = exp2_approx(fmaf(__uint_as_float(r[i]), LOG2E, off));
+          const float p1 = exp2_approx(fmaf(__uint_as_float(r[i + 1]), LOG2E, off));
+          pk[c * 16 + (i >> 1)] = pack_bf16(a_i * (p0 - ((cbase + i == tgt) ? 1.f : 0.f)),
+                                            a_i * (p1 - ((cbase + i + 1 == tgt) ? 1.f : 0.f)));
+        }
+        continue;
+      }
       // the n-th power as log2n passes over the 32 values: every pass is 32 independent
       // multiplications (a loop per value would serialise on its own latency)
       float w[32], sl[32];
@@ -391,7 +405,7 @@ proj_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
         float inv_l = 0.f, a_i = 0.f;
         int tgt = -1;
         if (live) {
-          inv_l = 1.0f / p.l[row];
+          inv_l = p.head_kind == ALG_HEAD_CE ? p.l[row] : 1.0f / p.l[row];   // ce: the logsumexp itself
           a_i = p.gscale;
           tgt = p.targets[row] - p.vocab_offset;
         }

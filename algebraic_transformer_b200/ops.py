@@ -422,18 +422,23 @@ def cast_embedding(embed: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def head_statistic(h, e_bf16, targets, *, n: int, c: float, vocab_offset: int = 0,
-                   vocab_total: Optional[int] = None, impl: str = "auto", out=None):
+def head_statistic(h, e_bf16, targets, *, n: int = 16, c: float = 16.0, vocab_offset: int = 0,
+                   vocab_total: Optional[int] = None, impl: str = "auto", out=None, kind: str = "alg_ce"):
     """Per-row (l, zt) of one vocabulary shard as a (2, N) fp32 tensor: row 0 the partial
-    normaliser, row 1 the target logit (0 where the target is not in the shard)."""
+    normaliser, row 1 the target logit (0 where the target is not in the shard).  With
+    `kind="ce"` row 0 is the logsumexp of the shard's logits instead (n and c are unused)."""
     N, d = h.shape
     V_local = e_bf16.shape[0]
     stats = torch.empty((2, N), dtype=torch.float32, device=h.device) if out is None else out
     if V_local == 0:                                   # a rank that owns no vocabulary tile
-        return stats.zero_()
+        stats.zero_()
+        if kind == "ce":
+            stats[0].fill_(-1e30)                      # the logsumexp of nothing
+        return stats
     a = L.HeadArgs(h=h.data_ptr(), e=e_bf16.data_ptr(), targets=targets.data_ptr(), l_out=stats[0].data_ptr(),
                    zt_out=stats[1].data_ptr(), N=N, d=d, V_local=V_local, vocab_offset=int(vocab_offset),
-                   V_total=int(vocab_total or V_local), n=int(n), c=float(c), impl=L.IMPL[impl])
+                   V_total=int(vocab_total or V_local), n=int(n), c=float(c), impl=L.IMPL[impl],
+                   kind=L.HEAD_CE if kind == "ce" else L.HEAD_ALG_CE)
     lib = L.load()
     ws = _workspace(h.device, lib.alg_head_workspace_bytes(a), "head")
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
@@ -456,15 +461,22 @@ def head_statistic_no_alloc(h, e_bf16, targets, out, *, n: int, c: float, vocab_
     return out
 
 
-def head_finalize(stats, *, n: int, c: float, vocab_total: int, want_nll: bool = False):
-    """(objective, p_target[, nll]) from the (all-reduced) (2, N) statistic."""
+def head_finalize(stats, *, n: int = 16, c: float = 16.0, vocab_total: int = 0, want_nll: bool = False,
+                  kind: str = "alg_ce"):
+    """(objective, p_target[, nll]) from the (all-reduced) (2, N) statistic.  `kind="ce"`: row 0
+    is the logsumexp; returns (mean nll, nll) like the reference's "ce" arm (`want_nll=True`
+    appends the nll once more, so that both kinds unpack alike)."""
     N = stats.shape[1]
     dev = stats.device
     pt = torch.empty(N, dtype=torch.float32, device=dev)
-    nll = torch.empty(N, dtype=torch.float32, device=dev) if want_nll else None
+    nll = torch.empty(N, dtype=torch.float32, device=dev) if (want_nll or kind == "ce") else None
     obj = torch.empty((), dtype=torch.float32, device=dev)
     lib = L.load()
     ws = _workspace(dev, lib.alg_head_finalize_workspace_bytes(N), "head_fin")
+    if kind == "ce":
+        L.check(lib.alg_head_finalize_ce(stats[0].data_ptr(), stats[1].data_ptr(), N, pt.data_ptr(), nll.data_ptr(),
+                                         obj.data_ptr(), ws.data_ptr(), ws.numel(), _stream()))
+        return (obj, nll, nll) if want_nll else (obj, nll)
     L.check(lib.alg_head_finalize(stats[0].data_ptr(), stats[1].data_ptr(), N, int(n), float(c), int(vocab_total),
                                   pt.data_ptr(), _ptr(nll), obj.data_ptr(), ws.data_ptr(), ws.numel(), _stream()))
     return (obj, pt, nll) if want_nll else (obj, pt)
@@ -479,14 +491,16 @@ def fused_head(h, embed, targets, *, kind: str = "ce", n: int = 16, c: float = 1
     `embed` is this rank's vocabulary shard: rows [vocab_offset, vocab_offset + V_local) of a
     `vocab_total`-row embedding (defaults: the whole thing).  With a `torch.distributed`
     `group`, the per-row partials (normaliser, target logit) of all shards are summed with one
-    all-reduce before the telemetry is formed.  `kind="ce"` (softmax control arm) is not built."""
+    all-reduce before the telemetry is formed.  `kind="ce"` (the reference's softmax control arm)
+    returns `(mean nll, nll)`; its shards combine by logsumexp (a MAX and a SUM all-reduce), and
+    it is not offered through `exchange`."""
     _require_cuda(h, embed, targets)
     if kind not in ("ce", "alg_ce"):
         raise ValueError(kind)
-    if kind == "ce":
-        raise NotImplementedError("only the algebraic (kind='alg_ce') head is built for B200")
-    if n & (n - 1):
+    if kind == "alg_ce" and n & (n - 1):
         raise ValueError("n must be a power of two")
+    if kind == "ce" and exchange is not None:
+        raise NotImplementedError("the one-kernel exchange is built for kind='alg_ce' only")
     if h.ndim != 2 or embed.ndim != 2 or h.shape[1] != embed.shape[1]:
         raise ValueError("h must be (N, d) and embed (V, d)")
     N = h.shape[0]
@@ -504,15 +518,31 @@ def fused_head(h, embed, targets, *, kind: str = "ce", n: int = 16, c: float = 1
         # the per-row partials with the peers over NVLink and forms the telemetry
         return _fused_head_exchange(h, e, t, exchange, n=n, c=c, vocab_offset=vocab_offset, vocab_total=V_total,
                                     want_nll=want_nll, impl=impl)
-    stats = head_statistic(h, e, t, n=n, c=c, vocab_offset=vocab_offset, vocab_total=V_total, impl=impl)
+    stats = head_statistic(h, e, t, n=n, c=c, vocab_offset=vocab_offset, vocab_total=V_total, impl=impl, kind=kind)
     if group is not None:
         import torch.distributed as dist
-        dist.all_reduce(stats, op=dist.ReduceOp.SUM, group=group)
-    return head_finalize(stats, n=n, c=c, vocab_total=V_total, want_nll=want_nll)
+        if kind == "ce":
+            combine_ce_statistics(stats, group)
+        else:
+            dist.all_reduce(stats, op=dist.ReduceOp.SUM, group=group)
+    return head_finalize(stats, n=n, c=c, vocab_total=V_total, want_nll=want_nll, kind=kind)
+
+
+def combine_ce_statistics(stats, group):
+    """In place: the (2, N) statistics of the "ce" kind over the vocabulary shards of `group` —
+    row 0 (per-shard logsumexp) by logsumexp (one MAX all-reduce for the common shift, then the
+    shifted exponentials ride the SUM all-reduce of row 1), row 1 (target logit) by a sum."""
+    import torch.distributed as dist
+    top = stats[0].clone()
+    dist.all_reduce(top, op=dist.ReduceOp.MAX, group=group)
+    stats[0] = torch.exp(stats[0] - top)
+    dist.all_reduce(stats, op=dist.ReduceOp.SUM, group=group)
+    stats[0] = top + torch.log(stats[0])
+    return stats
 
 
 def fused_head_backward(h, e_bf16, targets, stats, *, n: int = 8, c: float = 2.0, vocab_offset: int = 0,
-                        vocab_total: Optional[int] = None, upstream: float = 1.0):
+                        vocab_total: Optional[int] = None, upstream: float = 1.0, kind: str = "alg_ce"):
     """What the reference's custom VJP of the Alg-CE head returns for the hidden states and this
     shard's embedding rows, `(dh, de)` (src/algebraic/kernels/fused_head.py:120-156, 194-216,
     236-243): the gradient of the mean negative log-likelihood, `dz = upstream/N * (n/c) * (p - y) /
@@ -521,7 +551,10 @@ def fused_head_backward(h, e_bf16, targets, stats, *, n: int = 8, c: float = 2.0
     `stats` is the forward's `(2, N)` statistic (`head_statistic`, summed over all shards).  The
     logit gradient is rebuilt tile by tile from `stats` by one kernel and written as bf16; the two
     products `dz . E` and `dz^T . h` are library GEMMs, as in the reference.  With several shards
-    the caller sums `dh` over them."""
+    the caller sums `dh` over them.  `kind="ce"`: `stats` is the "ce" statistic (row 0 the
+    logsumexp over all shards) and `dz = upstream/N * (softmax - y)` (fused_head.py:134-135)."""
+    if kind not in ("ce", "alg_ce"):
+        raise ValueError(kind)
     _require_cuda(h, e_bf16, targets, stats)
     if h.dtype != torch.bfloat16 or e_bf16.dtype != torch.bfloat16 or h.ndim != 2 or e_bf16.ndim != 2:
         raise ValueError("fused_head_backward needs bf16 (N, d) hidden states and (V, d) embedding rows")
@@ -536,7 +569,8 @@ def fused_head_backward(h, e_bf16, targets, stats, *, n: int = 8, c: float = 2.0
     dz = torch.empty((N, V_local), dtype=torch.bfloat16, device=h.device)
     a = L.HeadBwdArgs(h=h.data_ptr(), e=e_bf16.data_ptr(), targets=t.data_ptr(), l=stats[0].data_ptr(),
                       zt=stats[1].data_ptr(), dz=dz.data_ptr(), N=N, d=d, V_local=V_local, vocab_offset=int(vocab_offset),
-                      V_total=V_total, n=int(n), c=float(c), upstream=float(upstream), status=None)
+                      V_total=V_total, n=int(n), c=float(c), upstream=float(upstream), status=None,
+                      kind=L.HEAD_CE if kind == "ce" else L.HEAD_ALG_CE)
     L.check(L.load().alg_head_bwd_dz(a, _stream()))
     return torch.mm(dz, e_bf16), torch.mm(dz.t(), h)
 

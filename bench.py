@@ -509,6 +509,14 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
     for i in range(3):
         fnh(i)
     ms_hb = cuda_time(fnh, iters, sync)
+    # the reference's control arm on the same kernel: softmax cross-entropy (online logsumexp epilogue)
+    fnc = lambda i: A.head_statistic(hh, eh, th, kind="ce")  # noqa: E731
+    for i in range(3):
+        fnc(i)
+    ms_ce = cuda_time(fnc, iters, sync)
+    extra["ce_head"] = {"workload": f"N={Nh}, d={dh_}, V={Vh}: kind='ce' (logsumexp + target logit, no logits to HBM)",
+                        "ms": ms_ce, "tflops": 2.0 * Nh * dh_ * Vh / (ms_ce * 1e-3) / 1e12,
+                        "frac_of_bf16_peak": 2.0 * Nh * dh_ * Vh / (ms_ce * 1e-3) / 1e12 / peak_tf}
     flh = 3 * 2.0 * Nh * dh_ * Vh                          # z again, dz . E, dz^T . h
     extra["alg_ce_head_bwd"] = {"workload": f"N={Nh}, d={dh_}, V={Vh}: dz kernel (tcgen05 GEMM + epilogue, bf16 dz to HBM) + two cuBLAS GEMMs",
                                 "ms": ms_hb, "tflops": flh / (ms_hb * 1e-3) / 1e12,

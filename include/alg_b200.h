@@ -58,6 +58,10 @@ enum { ALG_VARIANT_GUARD = 0, ALG_VARIANT_NOSHIFT = 1, ALG_VARIANT_SHIFT = 2 };
  * fail with ALG_ERR_UNSUPPORTED if it cannot run the request. */
 enum { ALG_IMPL_AUTO = 0, ALG_IMPL_MMA = 1, ALG_IMPL_TCGEN05 = 2 };
 
+/* The two kinds of the reference's fused head (src/algebraic/kernels/fused_head.py:260-275):
+ * "alg_ce" (the algebraic likelihood) and "ce" (softmax cross-entropy, the control arm). */
+enum { ALG_HEAD_ALG_CE = 0, ALG_HEAD_CE = 1 };
+
 ALG_API int alg_version(void);
 ALG_API const char* alg_last_error(void);
 /* Number of kernels this library has launched in this process so far (diagnostics: lets a
@@ -208,6 +212,10 @@ ALG_API int alg_attn_decode(const alg_decode_args* args, void* stream);
  *   zt_out = the target's logit if the target lies in this shard, else 0
  * with clamp = 0.25 (1e38 / V_total)^(1/n).  No (N x V) logits are written anywhere.
  * Summing l_out and zt_out over shards (one all-reduce) gives the full statistic.
+ * kind = ALG_HEAD_CE (fused_head's kind="ce", _fwd_kernel :87-94, 113-114): n and c are ignored and
+ *   l_out = logsumexp of the shard's logits (running maximum + rescaled sum, as the reference);
+ * shards then combine by logsumexp, not by a sum.  This kind runs on the tcgen05 kernel only
+ * (d a multiple of 64) and is not offered by alg_head_fwd_static / alg_head_fwd_exchange.
  * ---------------------------------------------------------------------------------- */
 typedef struct {
   const void* h;
@@ -222,6 +230,7 @@ typedef struct {
   void* workspace;
   size_t workspace_bytes;
   int* status;
+  int kind;                /* ALG_HEAD_ALG_CE (0) or ALG_HEAD_CE */
 } alg_head_args;
 
 ALG_API size_t alg_head_workspace_bytes(const alg_head_args* args);
@@ -290,6 +299,11 @@ ALG_API size_t alg_head_finalize_workspace_bytes(int N);
 ALG_API int alg_head_finalize(const float* l, const float* zt, int N, int n, float c, int V_total,
                       float* pt, float* nll, float* obj,
                       void* workspace, size_t workspace_bytes, void* stream);
+/* The same for kind "ce" (_telemetry, fused_head.py:221-223; standard.cross_entropy,
+ * src/algebraic/standard.py:41-47): lse = the (shard-combined) logsumexp that alg_head_fwd wrote to
+ * l_out; nll = lse - zt, pt = exp(-nll), obj = mean(nll).  Same workspace. */
+ALG_API int alg_head_finalize_ce(const float* lse, const float* zt, int N, float* pt, float* nll, float* obj,
+                                 void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------
  * Elementwise stages of the prefill body between the GEMMs (bf16 in / out, fp32 math).
@@ -374,6 +388,8 @@ typedef struct {
   float c;
   float upstream;
   int* status;             /* device int, may be NULL */
+  int kind;                /* ALG_HEAD_ALG_CE (0), or ALG_HEAD_CE: l = the rows' logsumexp from alg_head_fwd,
+                              dz = upstream / N * (exp(z - l) - onehot)  (fused_head.py:134-135); n, c ignored */
 } alg_head_bwd_args;
 ALG_API int alg_head_bwd_dz(const alg_head_bwd_args* args, void* stream);
 

@@ -367,6 +367,17 @@ def head_vjp_dense(h, embed, targets, n: int = 8, c: float = 2.0, g: float = 1.0
     return dz @ e, dz.t() @ h.to(F32)
 
 
+def cross_entropy(logits, targets):
+    """The "ce" head: (mean cross-entropy, per-token nll), nll = logsumexp(z) - z_target in fp32.
+    src/algebraic/standard.py:41-47; the fused kernel's telemetry is the same quantity
+    (kernels/fused_head.py:113-114, 221-223)."""
+    z = logits.to(F32) if logits.dtype != torch.float64 else logits
+    lse = torch.logsumexp(z, dim=-1)
+    zt = z.gather(-1, targets.long()[:, None])[:, 0]
+    nll = lse - zt
+    return nll.mean(), nll
+
+
 def head_logits(h, embed):
     """z = h . bf16(E)^T with fp32 accumulation.  model.py:225."""
     e = embed.to(h.dtype)

@@ -77,6 +77,23 @@ def install():
     lax.rsqrt = _rsqrt
     lax.stop_gradient = lambda x: x
 
+    # what src/algebraic/standard.py calls (the "ce" head and its neighbours)
+    for name in ("exp", "log", "cos", "sin"):
+        setattr(jnp, name, getattr(np, name))
+    nn = types.ModuleType("jax.nn")
+
+    def _logsumexp(a, axis=None):
+        a = np.asarray(a)
+        top = np.max(a, axis=axis, keepdims=True)
+        out = np.log(np.sum(np.exp(a - top), axis=axis, keepdims=True)) + top
+        return np.squeeze(out, axis=axis).astype(a.dtype)
+
+    nn.logsumexp = _logsumexp
+    nn.sigmoid = lambda x: (1.0 / (1.0 + np.exp(-np.asarray(x)))).astype(np.asarray(x).dtype)
+    nn.softmax = lambda x, axis=-1: np.exp(np.asarray(x) - np.expand_dims(_logsumexp(x, axis=axis), axis))
+    jax.nn = nn
+    sys.modules["jax.nn"] = nn
+
     jax.Array = np.ndarray
     jax.custom_vjp = _CustomVjp
     jax.numpy = jnp

@@ -38,6 +38,11 @@ def main():
     from algebraic import algebraic as A
     from algebraic.kernels import flash as FK
     from algebraic.kernels import fused_head as FH
+    from algebraic import standard as S
+    import jax                                            # the stand-in installed above
+
+    def jax_logsumexp(a):
+        return jax.nn.logsumexp(a, axis=-1)
 
     f32, f64 = np.float32, np.float64
     out = {}
@@ -146,6 +151,18 @@ def main():
     zc[2, 11] = 2.0 * 8 * A.likelihood_clamp(300, 8)
     out["lik_zclamp"] = zc
     out["lik_lean_n8_vjp_clamped"] = A._lean_bwd(8, 2.0, (zc, t), (1.0, None))[0]
+    # the "ce" head (standard.py:41-47) and the fused kernel's telemetry for it (fused_head.py:221-223),
+    # on the same logits and on a copy with one huge logit per row sign (the shift must absorb it)
+    zh = z.copy()
+    zh[1, 4], zh[3, 200] = 3.0e4, -3.0e4
+    out["ce_zhuge"] = zh
+    for tag, zz in (("", z), ("_huge", zh)):
+        o_ce, nll_ce = S.cross_entropy(zz.astype(f32), t)
+        out[f"ce{tag}_obj"], out[f"ce{tag}_nll"] = np.array(o_ce), nll_ce
+        lse = jax_logsumexp(zz.astype(f32))
+        zt_ = np.take_along_axis(zz.astype(f32), t[:, None], axis=-1)[:, 0]
+        tel, tobj = FH._telemetry(lse, zt_, "ce", 16, 16.0, 0.0)
+        out[f"ce{tag}_tel_nll"], out[f"ce{tag}_tel_obj"] = tel, np.array(tobj)
     vocabs = np.array([50304, 32768, 32000, 4096, 97])
     out["clamp_vocabs"] = vocabs
     for n in (8, 16):

@@ -458,6 +458,48 @@ def test_attention_backward_matches_oracle_autograd(shape, with_sink, causal, im
         assert rel_l2(ds, ws) < 2e-2
 
 
+@pytest.mark.parametrize("V", [32768, 4096, 6280])
+def test_fused_head_ce_kind_matches_dense(V):                        # test_fused_head_tpu.py:14-43, kind "ce"
+    """The softmax cross-entropy kind: objective, per-token nll and both gradients against the dense
+    definition (standard.py:41-47) with the reference test's tolerances; 6280 is off the 256-column
+    tile grid (zero-filled columns must not add exp(0)); then a logit of 3e4 (the running maximum
+    must absorb it) and the statistic combined over two vocabulary shards by logsumexp."""
+    N, d = 1024, 256
+    h, E, t = head_inputs(N, d, V, 0.15)
+    hf, ef = h.float().requires_grad_(True), E.bfloat16().float().requires_grad_(True)
+    want_obj, want_nll = R.cross_entropy(hf @ ef.t(), t)
+    want_obj.backward()
+    want_obj = want_obj.detach()
+    hd, Ed, td = dev(h, E, t)
+    obj, nll = A.fused_head(hd, Ed, td, kind="ce", block_n=256, block_v=1024)
+    np.testing.assert_allclose(float(obj), float(want_obj), rtol=2e-3, atol=2e-4)
+    np.testing.assert_allclose(nll.cpu(), want_nll.detach(), rtol=2e-2, atol=2e-4)
+    eb = A.ops.cast_embedding(Ed)
+    stats = A.head_statistic(hd, eb, td.int(), kind="ce")
+    dh, de = A.ops.fused_head_backward(hd, eb, td, stats, kind="ce")
+    for got, want in ((dh, hf.grad), (de, ef.grad)):
+        a, b = got.float().cpu().numpy(), want.numpy()
+        scale = np.abs(b).max() + 1e-12
+        np.testing.assert_allclose(a / scale, b / scale, atol=2e-2)
+        assert (a * b).sum() / np.sqrt((a * a).sum() * (b * b).sum()) > 0.999
+    # two shards: per-shard logsumexp, combined by logsumexp; target logits add
+    lo = (V // 2) // 8 * 8 + 8
+    s0 = A.head_statistic(hd, eb[:lo].contiguous(), td.int(), kind="ce", vocab_offset=0, vocab_total=V)
+    s1 = A.head_statistic(hd, eb[lo:].contiguous(), td.int(), kind="ce", vocab_offset=lo, vocab_total=V)
+    both = torch.stack([torch.logsumexp(torch.stack([s0[0], s1[0]]), dim=0), s0[1] + s1[1]])
+    obj2, nll2 = A.ops.head_finalize(both, kind="ce")
+    np.testing.assert_allclose(nll2.cpu(), want_nll.detach(), rtol=2e-2, atol=2e-4)
+    np.testing.assert_allclose(float(obj2), float(want_obj), rtol=2e-3, atol=2e-4)
+    # one very large logit: h row 3 and E row 9 aligned
+    h2, E2 = h.clone(), E.clone()
+    h2[3], E2[9] = 12.0, 10.0                                         # z[3, 9] = 256 * 120 = 30720
+    w_obj, w_nll = R.cross_entropy(R.head_logits(h2, E2), t)
+    obj3, nll3 = A.fused_head(*dev(h2, E2, t), kind="ce", block_n=256)
+    assert torch.isfinite(nll3).all()
+    np.testing.assert_allclose(nll3.cpu(), w_nll, rtol=2e-2, atol=2e-3)
+    np.testing.assert_allclose(float(obj3), float(w_obj), rtol=2e-3)
+
+
 def test_head_backward_matches_reference_vjp():
     """dh and dE of the Alg-CE head as the reference's custom VJP defines them (fused_head.py:120-156,
     194-216, 236-243: the gradient of the mean negative log-likelihood, clamp straight-through)

@@ -133,6 +133,17 @@ def test_likelihood_vjp_rule(golden, n, c):
     assert float((0.75 * zp.grad - got).abs().max()) > 1e-3 * float(got.abs().max())
 
 
+@pytest.mark.parametrize("tag,zkey", [("", "lik_z"), ("_huge", "ce_zhuge")])
+def test_cross_entropy_head(golden, tag, zkey):
+    """The "ce" kind: the reference's dense definition (standard.py:41-47) and the fused kernel's
+    telemetry from (logsumexp, target logit) (fused_head.py:221-223) against the oracle."""
+    g = golden
+    z, t = T(g[zkey]).float(), T(g["lik_t"])
+    obj, nll = R.cross_entropy(z, t)
+    close(nll, g[f"ce{tag}_nll"], 2e-6, 2e-6); close(obj, g[f"ce{tag}_obj"], 2e-6)
+    close(nll, g[f"ce{tag}_tel_nll"], 2e-6, 2e-6); close(obj, g[f"ce{tag}_tel_obj"], 2e-6)
+
+
 def test_likelihood_vjp_rule_clamp_is_straight_through(golden):
     g = golden
     z, t = T(g["lik_zclamp"]), T(g["lik_t"])

@@ -33,6 +33,19 @@ def _worker(rank, world, port, ret):
     pt, obj = R.fused_head_telemetry(stats[0], stats[1], 8, 2.0, R.likelihood_clamp(V, 8))
     obj0, pt0 = R.head_loss_dense(h, E, t, 8, 2.0)
     ok = torch.allclose(pt, pt0, rtol=2e-5, atol=1e-9) and abs(float(obj) - float(obj0)) < 1e-5
+    # the "ce" kind: per-shard logsumexp and target logit, combined by the product's own host routine
+    # (a MAX and a SUM all-reduce), against the unsharded cross-entropy; one shard holds a logit of 3e4
+    from algebraic_transformer_b200.ops import combine_ce_statistics
+    E2 = E.clone()
+    E2[700] = 40.0 * torch.sign(h[5].float())               # z[5, 700] ~ 40 * sum |h_5| >> 88
+    z = R.head_logits(h, E2)
+    zs = z[:, lo:lo + cnt]
+    in_shard = (t >= lo) & (t < lo + cnt)
+    zt_s = torch.where(in_shard, zs.gather(-1, (t - lo).clamp(0, cnt - 1)[:, None])[:, 0], torch.zeros(N))
+    ce_stats = torch.stack([torch.logsumexp(zs, dim=-1), zt_s])
+    combine_ce_statistics(ce_stats, dist.group.WORLD)
+    obj_ce, nll_ce = R.cross_entropy(z, t)
+    ok = ok and torch.allclose(ce_stats[0] - ce_stats[1], nll_ce, rtol=1e-5, atol=1e-4) and float(z.max()) > 1000.0
     ret[rank] = bool(ok)
     dist.barrier()
     dist.destroy_process_group()
