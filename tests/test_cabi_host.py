@@ -44,6 +44,15 @@ def test_invalid_arguments_fail_before_launch():
     h = L.HeadArgs(h=16, e=16, targets=16, l_out=16, zt_out=16, N=128, d=64, V_local=10, vocab_offset=5,
                    V_total=12, n=8, c=2.0)
     assert lib.alg_head_fwd(h, None) == L.ALG_ERR_INVALID   # shard exceeds the vocabulary
+    h = L.HeadArgs(h=16, e=16, targets=16, l_out=16, zt_out=16, N=128, d=64, V_local=8, V_total=8, n=8, c=2.0, kind=7)
+    assert lib.alg_head_fwd(h, None) == L.ALG_ERR_INVALID and b"kind" in lib.alg_last_error()
+    h.kind, h.n, h.c, h.d = L.HEAD_CE, 0, 0.0, 72            # the ce kind ignores n and c, but has no kernel for d % 64 != 0
+    assert lib.alg_head_fwd(h, None) == L.ALG_ERR_UNSUPPORTED
+    h.d, h.impl = 64, L.IMPL["mma"]
+    assert lib.alg_head_fwd(h, None) == L.ALG_ERR_UNSUPPORTED
+    h.impl = L.IMPL["auto"]
+    assert lib.alg_head_fwd_static(h, None) == L.ALG_ERR_UNSUPPORTED
+    assert lib.alg_head_finalize_ce(None, None, 4, None, None, None, None, 0, None) == L.ALG_ERR_INVALID
     q = L.QkRmsArgs(x=16, y=16, eps=0.0, B=1, H=1, T=1, D=64)
     assert lib.alg_qk_rms_fwd(q, None) == L.ALG_ERR_INVALID
     # guard words handed over by the QKV projection describe ready-made q, k, v: not with the prologue
@@ -72,6 +81,8 @@ def test_invalid_arguments_fail_before_launch():
     assert lib.alg_head_bwd_dz(hb, None) == L.ALG_ERR_INVALID        # V_local must be a multiple of 8
     hb.V_local, hb.V_total, hb.n = 1000, 1000, 12
     assert lib.alg_head_bwd_dz(hb, None) == L.ALG_ERR_INVALID        # n must be a power of two
+    hb.n, hb.kind = 8, 5
+    assert lib.alg_head_bwd_dz(hb, None) == L.ALG_ERR_INVALID and b"kind" in lib.alg_last_error()
     # attention backward
     assert lib.alg_attn_bwd(L.AttnBwdArgs(), None) == L.ALG_ERR_INVALID
     bw = L.AttnBwdArgs(q=16, k=16, v=16, o=16, d_o=16, stat=16, stat_kind=16, dq=16, dk=16, dv=16, B=1, H=2, Tq=64,
