@@ -189,16 +189,27 @@ head_tc_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constant__
             m_run = m_new;
             continue;
           }
+          // pairs of columns through the packed fp32 instructions (mul.f32x2 / fma.f32x2 / add.f32x2)
+          const float2 ic2 = make_float2(p.inv_c, p.inv_c), one2 = make_float2(1.f, 1.f);
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
-            float w[4];
+            float2 xa = __fmul2_rn(make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), ic2);
+            float2 xb = __fmul2_rn(make_float2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])), ic2);
+            xa.x = fminf(xa.x, p.clamp); xa.y = fminf(xa.y, p.clamp);
+            xb.x = fminf(xb.x, p.clamp); xb.y = fminf(xb.y, p.clamp);
+            const float2 ra = __ffma2_rn(xa, xa, one2), rb = __ffma2_rn(xb, xb, one2);
+            float2 wa = __ffma2_rn(ra, make_float2(rsqrt_approx(ra.x), rsqrt_approx(ra.y)), xa);   // rho_fast
+            float2 wb = __ffma2_rn(rb, make_float2(rsqrt_approx(rb.x), rsqrt_approx(rb.y)), xb);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const float x = fminf(__uint_as_float(r[j + q]) * p.inv_c, p.clamp);
-              w[q] = pow2n<LOG2N>(rho_fast(x));
-              if (tail && c0 + j + q >= p.V_local) w[q] = 0.f;   // zero-filled columns must not add rho(0)^n
+            for (int k = 0; k < LOG2N; ++k) { wa = __fmul2_rn(wa, wa); wb = __fmul2_rn(wb, wb); }
+            if (tail) {                                    // zero-filled columns must not add rho(0)^n
+              if (c0 + j >= p.V_local) wa.x = 0.f;
+              if (c0 + j + 1 >= p.V_local) wa.y = 0.f;
+              if (c0 + j + 2 >= p.V_local) wb.x = 0.f;
+              if (c0 + j + 3 >= p.V_local) wb.y = 0.f;
             }
-            l0 += w[0]; l1 += w[1]; l2 += w[2]; l3 += w[3];
+            const float2 la = __fadd2_rn(make_float2(l0, l1), wa), lb = __fadd2_rn(make_float2(l2, l3), wb);
+            l0 = la.x; l1 = la.y; l2 = lb.x; l3 = lb.y;
           }
         }
         tc_fence_before();
