@@ -128,25 +128,30 @@ __device__ __forceinline__ void dz_cols(const ProjParams& p, uint32_t taddr, con
       }
       // the n-th power as log2n passes over the 32 values: every pass is 32 independent
       // multiplications (a loop per value would serialise on its own latency)
-      float w[32], sl[32];
+      // (pairs of columns through the packed fp32 instructions)
+      float2 w[16], sl[16];
       const float an = a_i * p.n_over_c;
+      const float2 an2 = make_float2(an, an), ic2 = make_float2(p.inv_c, p.inv_c), one2 = make_float2(1.f, 1.f);
+      const float2 il2 = make_float2(inv_l, inv_l);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float x = fminf(__uint_as_float(r[i]) * p.inv_c, p.clamp);
-        const float rad = fmaf(x, x, 1.0f);
-        const float rs = rsqrt_approx(rad);
-        w[i] = fmaf(rad, rs, x);                                                // rho_fast(x)
-        sl[i] = an * rs;                                                        // (g / N) (n / c) r_ij
+      for (int i = 0; i < 16; ++i) {
+        float2 x = __fmul2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), ic2);
+        x.x = fminf(x.x, p.clamp);
+        x.y = fminf(x.y, p.clamp);
+        const float2 rad = __ffma2_rn(x, x, one2);
+        const float2 rs = make_float2(rsqrt_approx(rad.x), rsqrt_approx(rad.y));
+        w[i] = __ffma2_rn(rad, rs, x);                                          // rho_fast(x)
+        sl[i] = __fmul2_rn(an2, rs);                                            // (g / N) (n / c) r_ij
       }
       for (int it = 0; it < p.log2n; ++it) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) w[i] *= w[i];
+        for (int i = 0; i < 16; ++i) w[i] = __fmul2_rn(w[i], w[i]);
       }
 #pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        const float d0 = sl[i] * (w[i] * inv_l - ((cbase + i == tgt) ? 1.f : 0.f));
-        const float d1 = sl[i + 1] * (w[i + 1] * inv_l - ((cbase + i + 1 == tgt) ? 1.f : 0.f));
-        pk[c * 16 + (i >> 1)] = pack_bf16(d0, d1);
+      for (int i = 0; i < 16; ++i) {
+        const float2 negy = make_float2((cbase + 2 * i == tgt) ? -1.f : 0.f, (cbase + 2 * i + 1 == tgt) ? -1.f : 0.f);
+        const float2 d = __fmul2_rn(sl[i], __ffma2_rn(w[i], il2, negy));
+        pk[c * 16 + i] = pack_bf16(d.x, d.y);
       }
     }
     const int first = col0 + u * 64;
@@ -247,19 +252,21 @@ __device__ __forceinline__ void glu16(const uint32_t* gu, float beta, uint32_t* 
   for (int i = 0; i < 8; ++i) {
     const uint32_t gp = pack_bf16(__uint_as_float(gu[2 * i]), __uint_as_float(gu[2 * i + 1]));
     const uint32_t up = pack_bf16(__uint_as_float(gu[16 + 2 * i]), __uint_as_float(gu[16 + 2 * i + 1]));
-    float act[2];
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const float uv = e ? pair_hi(up) : pair_lo(up);
-      const float bz = beta * uv;
-      const float r = rsqrtf(fmaf(bz, bz, 1.0f));
-      const float uu = bz * r;
-      // for bz < 0 use 1 + u = r^2 / (1 - u) so that the negative tail survives
-      const float one_plus_u = bz < 0.f ? __fdividef(r * r, 1.0f - uu) : 1.0f + uu;
-      act[e] = 0.5f * uv * one_plus_u;
-    }
+    // both values of the pair through the packed fp32 instructions
+    const float2 uv = make_float2(pair_lo(up), pair_hi(up));
+    const float2 one = make_float2(1.f, 1.f);
+    const float2 bz = __fmul2_rn(uv, make_float2(beta, beta));
+    const float2 rad = __ffma2_rn(bz, bz, one);
+    const float2 r = make_float2(rsqrt_approx(rad.x), rsqrt_approx(rad.y));
+    const float2 uu = __fmul2_rn(bz, r);
+    // for bz < 0 use 1 + u = r^2 / (1 - u) so that the negative tail survives
+    const float2 den = __ffma2_rn(uu, make_float2(-1.f, -1.f), one);
+    const float2 neg = __fmul2_rn(__fmul2_rn(r, r), make_float2(__fdividef(1.0f, den.x), __fdividef(1.0f, den.y)));
+    const float2 pos = __fadd2_rn(uu, one);
+    const float2 opu = make_float2(bz.x < 0.f ? neg.x : pos.x, bz.y < 0.f ? neg.y : pos.y);
+    const float2 act = __fmul2_rn(__fmul2_rn(uv, make_float2(0.5f, 0.5f)), opu);
     // gate (bf16) times the bf16-rounded activation, rounded once: a bf16 multiply
-    out[i] = as_u32(__hmul2(as_bf162(gp), as_bf162(pack_bf16(act[0], act[1]))));
+    out[i] = as_u32(__hmul2(as_bf162(gp), as_bf162(pack_bf16(act.x, act.y))));
   }
 }
 
