@@ -545,6 +545,27 @@ def test_head_backward_matches_reference_vjp():
 
 
 @pytest.mark.parametrize("impl", ["auto", "mma"])
+def test_attention_backward_on_views_of_a_fused_projection(impl):
+    """q, k, v as the (B,H,T,D) views of one (B,T,3,H,D) projection output, d_o a view of a
+    (B,T,H,D) tensor: strides reach the kernels (tensor maps for the tcgen05 path) unchanged, and the
+    gradients come back in the layout of their inputs."""
+    B, H, T, D = 2, 2, 384, 64
+    qkv = randn((B, T, 3, H, D), 990, torch.bfloat16)
+    q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+    d_o = randn((B, T, H, D), 991, torch.bfloat16).transpose(1, 2)
+    sink = randn((H,), 992) * 0.5
+    qkvd = qkv.to(DEV)
+    qd, kd, vd = (qkvd[:, :, i].transpose(1, 2) for i in range(3))
+    dod, sd = d_o.to(DEV), sink.to(DEV)
+    assert not qd.is_contiguous()
+    o, stat, kind = A.flash_attention(qd, kd, vd, sd, kind="asinh", n=16, c=8.0, range_guard=True, return_stat=True)
+    dq, dk, dv, ds = A.ops.flash_attention_backward(qd, kd, vd, o, dod, stat, kind, sd, n=16, c=8.0, impl=impl)
+    assert dq.stride() == qd.stride() and dv.stride() == vd.stride()
+    wq, wk, wv, ws = _oracle_grads(q.contiguous(), k.contiguous(), v.contiguous(), sink, d_o.contiguous())
+    assert rel_l2(dq, wq) < 2e-2 and rel_l2(dk, wk) < 2e-2 and rel_l2(dv, wv) < 2e-2 and rel_l2(ds, ws) < 2e-2
+
+
+@pytest.mark.parametrize("impl", ["auto", "mma"])
 def test_attention_backward_after_shifted_forward(impl):
     """Out-of-range inputs: the forward takes the max-shifted path and saves rho(-m) l^(-1/n); the
     backward must rebuild the same weights from that statistic."""
