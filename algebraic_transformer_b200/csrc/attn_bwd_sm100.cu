@@ -64,7 +64,7 @@ struct __align__(16) Control {
 template <int D> constexpr size_t smem_bytes() { return size_t(Cfg<D>::CTL_OFF) + sizeof(Control) + 1024; }
 
 // Phase 1 on 32 scores of this thread's row: the weights p, packed to bf16 in pw_out, and the factor
-// n p / (sqrt(1 + x^2) sqrt(D) c) that phase 2 multiplies (dP - delta) by, in `slope`.  `stat` comes by
+// p / sqrt(1 + x^2) that phase 2 multiplies (dP - delta) by, in `slope`.  `stat` comes by
 // row (MODE 0: one value) or by column (MODE 1: 32 values).  Pairs of values go through the packed
 // fp32 instructions (mul.f32x2 / fma.f32x2).  The 2^log2n-th power runs as log2n passes over the 16
 // pairs, so that every pass has independent multiplications whatever n is (a loop per element
@@ -73,7 +73,11 @@ template <bool SHIFTED, bool BY_COLUMN>
 __device__ __forceinline__ void weights_from_scores(const uint32_t* s, float2* slope, const AttnBwdParams& p,
                                                     float stat_row, const float2* stat_col, int log2n, bool diag, int row,
                                                     int col0, bool row_is_query, uint32_t* pw_out) {
-  const float2 sc = make_float2(p.scale, p.scale), one = make_float2(1.f, 1.f), ns = make_float2(p.n_scale, p.n_scale);
+  // Two factors that are constant over a row of the accumulator are left to the kernel's epilogue instead
+  // of being multiplied into every score: n / (sqrt(D) c) always, and the row's statistic when it is a
+  // plain factor of the weight (rows = queries, unshifted forward).  What is written to tensor memory is
+  // then an unnormalised dS, as the forward's P is unnormalised.
+  const float2 sc = make_float2(p.scale, p.scale), one = make_float2(1.f, 1.f);
   const float2 st_row = make_float2(stat_row, stat_row);
   float2 t[16];
 #pragma unroll
@@ -87,15 +91,15 @@ __device__ __forceinline__ void weights_from_scores(const uint32_t* s, float2* s
     } else {
       t[i] = __ffma2_rn(rad, rs, x);
     }
-    slope[i] = __fmul2_rn(ns, rs);
+    slope[i] = rs;
   }
   for (int it = 0; it < log2n; ++it) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) t[i] = __fmul2_rn(t[i], t[i]);
   }
-  if (!SHIFTED) {
+  if (!SHIFTED && BY_COLUMN) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) t[i] = __fmul2_rn(t[i], BY_COLUMN ? stat_col[i] : st_row);
+    for (int i = 0; i < 16; ++i) t[i] = __fmul2_rn(t[i], stat_col[i]);
   }
   if (diag) {   // causal: key <= query.  Rows are queries in MODE 0 (mask col > row), keys in MODE 1 (mask col < row)
 #pragma unroll
@@ -332,11 +336,16 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       for (int which = 0; which < (MODE == 0 ? 1 : 2); ++which) {
         const uint32_t acc_t = tmem_base + lane_sel + (which == 0 ? C::ACC0_COL : C::ACC1_COL) + half * CPT;
         __nv_bfloat16* dst = which == 0 ? out0 : out1;
+        // the row factors phase 1 left out: n / (sqrt(D) c) on dQ and dK, and on dQ the row's statistic
+        // where it is a plain factor of the weight (dV carries none)
+        const float fac = (MODE == 0) ? (shifted ? p.n_scale : p.n_scale * stat_row) : (which == 1 ? p.n_scale : 1.0f);
 #pragma unroll 1
         for (int c = 0; c < CPT / 32; ++c) {
           uint32_t a[32];
           tmem_ld_32x32(acc_t + c * 32, a);
           tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) a[i] = __float_as_uint(__uint_as_float(a[i]) * fac);
 #pragma unroll
           for (int i = 0; i < 4; ++i)
             *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) =
