@@ -26,6 +26,8 @@ struct PrepParams {
 struct PrepBatch {         // up to three tensors (q, k, v) of one dtype / head_dim in one launch
   PrepParams t[3];
   int count;
+  int lean;                // statistics-only launches: CTAs of 128 threads (8192 registers), small enough to
+                           // share an SM with a resident attention CTA when the pass runs beside that kernel
 };
 int launch_prep(const PrepParams& p, int dtype, cudaStream_t stream);
 int launch_prep_batch(const PrepBatch& batch, int dtype, cudaStream_t stream);

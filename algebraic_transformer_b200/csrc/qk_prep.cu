@@ -203,8 +203,7 @@ __global__ void __launch_bounds__(256, MODE == 0 ? 4 : 3) qk_prep_kernel(const P
     __syncthreads();
     if (threadIdx.x == 0) {
       float m = s_stat[0];
-#pragma unroll
-      for (int w = 1; w < 8; ++w) m = fmaxf(m, s_stat[w]);
+      for (int w = 1; w < int(blockDim.x >> 5); ++w) m = fmaxf(m, s_stat[w]);
       atomicMax(p.stat_out, __float_as_uint(m));
     }
   }
@@ -227,15 +226,16 @@ static int launch_t(const PrepBatch& batch, cudaStream_t stream) {
     if (batch.t[i].H == 0) return ALG_OK;
   }
   if (positions == 0) return ALG_OK;
+  const int threads = (mode == 0 && batch.lean) ? 128 : 256;
   const int64_t warps = (positions + RPW - 1) / RPW;
-  int64_t blocks = (warps + 7) / 8;
+  int64_t blocks = (warps + threads / 32 - 1) / (threads / 32);
   // resident CTAs only (the grid-stride loop covers the rest): 4 per SM for the
   // statistics-only mode, 3 for the others, per tensor of the launch (sharing one wave among
   // the tensors measured slightly slower)
   const int64_t cap = 148 * (mode == 0 ? 4 : 3);
   if (blocks > cap) blocks = cap;
   const dim3 grid(unsigned(blocks), unsigned(batch.count));
-  if (mode == 0) qk_prep_kernel<T, D, 0><<<grid, 256, 0, stream>>>(batch);
+  if (mode == 0) qk_prep_kernel<T, D, 0><<<grid, threads, 0, stream>>>(batch);
   else if (mode == 1) qk_prep_kernel<T, D, 1><<<grid, 256, 0, stream>>>(batch);
   else qk_prep_kernel<T, D, 2><<<grid, 256, 0, stream>>>(batch);
   ALG_CUDA_TRY(cudaGetLastError());

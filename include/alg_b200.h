@@ -138,6 +138,14 @@ typedef struct {
                               with the fused prologue) */
 } alg_attn_args;
 
+/* A guarded call (variant = ALG_VARIANT_GUARD) without guard_words and without the fused prologue, on a
+ * shape the tcgen05 kernel covers, runs its pass over q, k, v on a stream owned by the library, beside
+ * the attention kernel, which is launched for the unshifted form at once; the stable kernel follows
+ * both and redoes the work only if the guard failed.  The caller sees one ordered operation on
+ * `stream` (fork and join by events; legal inside stream capture once the per-device stream and events
+ * exist — they are created on the first such call outside capture; a first call made during capture
+ * keeps everything on `stream`).  Until the call's work has completed o, stat and stat_kind may hold
+ * the speculative result.  ALG_ATTN_SERIAL_GUARD=1 in the environment keeps everything on `stream`. */
 ALG_API size_t alg_attn_workspace_bytes(const alg_attn_args* args);
 ALG_API int alg_attn_fwd(const alg_attn_args* args, void* stream);
 

@@ -138,6 +138,34 @@ def test_guarded_attention_tail(sign, with_sink, magnitude, dtype):  # test_flas
     assert rel_l2(stat, want_stat) < 5e-3
 
 
+def test_guarded_call_replays_from_a_cuda_graph():
+    """A stand-alone guarded call forks its statistics pass onto the library's own stream beside the
+    attention kernel; captured into a CUDA graph (after one eager call, which creates that stream)
+    the fork and join become graph edges, and replays on fresh inputs — in range, then out of range —
+    give the eager results."""
+    shape = (1, 2, 512, 64)
+    q, k, v = (randn(shape, 871 + i, torch.bfloat16) for i in range(3))
+    qd, kd, vd = dev(q, k, v)
+    sink = torch.zeros(2, device=DEV)
+    out = torch.empty_like(qd)
+    A.flash_attention(qd, kd, vd, sink, kind="asinh", n=16, c=8.0, range_guard=True, out=out)   # eager, warms up
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        A.flash_attention(qd, kd, vd, sink, kind="asinh", n=16, c=8.0, range_guard=True, out=out)
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    want = R.asinh_attention(q, k, v, n=16, c=8.0, sink_logit=torch.zeros(2))
+    assert rel_l2(out, want) < 1e-2
+    big = (q.float() * 40).bfloat16()                      # the same graph, inputs that fail the guard
+    qd.copy_(big.to(DEV))
+    graph.replay()
+    torch.cuda.synchronize()
+    want2 = R.asinh_attention(big, k, v, n=16, c=8.0, sink_logit=torch.zeros(2))
+    assert torch.isfinite(out).all() and rel_l2(out, want2) < 1e-2
+
+
 @pytest.mark.parametrize("which", ["q", "k", "v"])
 @pytest.mark.parametrize("row", [3, 700, 1023])
 @pytest.mark.parametrize("D", [64, 128])
