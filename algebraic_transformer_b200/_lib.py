@@ -27,6 +27,13 @@ class QkRmsArgs(C.Structure):
                 ("D", C.c_int), ("dtype", C.c_int), ("x_stride", I64x3), ("y_stride", I64x3)]
 
 
+class QkRmsBwdArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("dy", C.c_void_p), ("gain", C.c_void_p), ("dx", C.c_void_p),
+                ("dgain", C.c_void_p), ("eps", C.c_float), ("B", C.c_int), ("H", C.c_int), ("T", C.c_int),
+                ("D", C.c_int), ("dtype", C.c_int), ("x_stride", I64x3), ("dy_stride", I64x3), ("dx_stride", I64x3),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+
+
 class AttnArgs(C.Structure):
     _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p),
                 ("stat", C.c_void_p), ("stat_kind", C.c_void_p), ("sink", C.c_void_p),
@@ -102,6 +109,8 @@ SYMBOLS = {
     "alg_last_error": (C.c_char_p, []),
     "alg_kernel_launches": (C.c_ulonglong, []),
     "alg_qk_rms_fwd": (C.c_int, [C.POINTER(QkRmsArgs), C.c_void_p]),
+    "alg_qk_rms_bwd_workspace_bytes": (C.c_size_t, [C.c_int]),
+    "alg_qk_rms_bwd": (C.c_int, [C.POINTER(QkRmsBwdArgs), C.c_void_p]),
     "alg_attn_workspace_bytes": (C.c_size_t, [C.POINTER(AttnArgs)]),
     "alg_attn_fwd": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "alg_attn_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(AttnBwdArgs)]),

@@ -134,6 +134,37 @@ int alg_qk_rms_fwd(const alg_qk_rms_args* a, void* stream) {
   return launch_prep(p, a->dtype, static_cast<cudaStream_t>(stream));
 }
 
+size_t alg_qk_rms_bwd_workspace_bytes(int D) {
+  return (D == 64 || D == 128) ? size_t(rms_bwd_max_blocks()) * size_t(D) * sizeof(float) : 0;
+}
+
+int alg_qk_rms_bwd(const alg_qk_rms_bwd_args* a, void* stream) {
+  if (a == nullptr || a->x == nullptr || a->dy == nullptr || a->dx == nullptr) { set_error("qk_rms backward: null argument"); return ALG_ERR_INVALID; }
+  if (a->dtype != ALG_BF16 && a->dtype != ALG_F32) { set_error("QK RMS kernel needs float32/BF16 input"); return ALG_ERR_INVALID; }
+  if (a->D != 64 && a->D != 128) { set_error("QK RMS kernel needs D=64 or D=128, got %d", a->D); return ALG_ERR_UNSUPPORTED; }
+  if (!(a->eps > 0.0f)) { set_error("QK RMS epsilon must be positive"); return ALG_ERR_INVALID; }
+  if (a->B < 0 || a->H < 0 || a->T < 0) { set_error("qk_rms backward: negative extent"); return ALG_ERR_INVALID; }
+  if (a->dgain != nullptr && a->gain == nullptr) { set_error("qk_rms backward: dgain without gain"); return ALG_ERR_INVALID; }
+  const size_t need = alg_qk_rms_bwd_workspace_bytes(a->D);
+  if (a->dgain != nullptr && (a->workspace == nullptr || a->workspace_bytes < need || !aligned16(a->workspace))) {
+    set_error("qk_rms backward: workspace of %zu bytes (16-byte aligned) required, got %zu", need, a->workspace_bytes);
+    return ALG_ERR_WORKSPACE;
+  }
+  RmsBwdParams p{};
+  p.x = a->x; p.dy = a->dy; p.gain = a->gain; p.dx = a->dx; p.dgain = a->dgain;
+  p.partials = static_cast<float*>(a->workspace);
+  p.eps = a->eps; p.B = a->B; p.H = a->H; p.T = a->T; p.D = a->D;
+  p.xs = strides_or_dense(a->x_stride, a->H, a->T, a->D);
+  p.gs = strides_or_dense(a->dy_stride, a->H, a->T, a->D);
+  p.ds = strides_or_dense(a->dx_stride, a->H, a->T, a->D);
+  if (!strides_ok(p.xs, a->dtype) || !strides_ok(p.gs, a->dtype) || !strides_ok(p.ds, a->dtype) || !aligned16(a->x) ||
+      !aligned16(a->dy) || !aligned16(a->dx) || (a->gain != nullptr && !aligned16(a->gain))) {
+    set_error("qk_rms backward: rows must start on 16-byte boundaries");
+    return ALG_ERR_INVALID;
+  }
+  return launch_rms_bwd(p, a->dtype, static_cast<cudaStream_t>(stream));
+}
+
 size_t alg_attn_workspace_bytes(const alg_attn_args* a) {
   if (a == nullptr) return 0;
   size_t bytes = 256;                                   // guard words

@@ -29,6 +29,20 @@ struct PrepBatch {         // up to three tensors (q, k, v) of one dtype / head_
   int lean;                // statistics-only launches: CTAs of 128 threads (8192 registers), small enough to
                            // share an SM with a resident attention CTA when the pass runs beside that kernel
 };
+// backward of the QK RMS-norm (qk_prep.cu): dx, and the gain gradient as per-CTA partial rows summed in order
+struct RmsBwdParams {
+  const void* x;
+  const void* dy;
+  const float* gain;       // (D) or nullptr (no gain: dgain is not produced)
+  void* dx;
+  float* dgain;            // (D) or nullptr
+  float* partials;         // (rms_bwd_max_blocks(), D) scratch
+  float eps;
+  int B, H, T, D;
+  Strides3 xs, gs, ds;     // of x, dy, dx
+};
+int rms_bwd_max_blocks();
+int launch_rms_bwd(const RmsBwdParams& p, int dtype, cudaStream_t stream);
 int launch_prep(const PrepParams& p, int dtype, cudaStream_t stream);
 int launch_prep_batch(const PrepBatch& batch, int dtype, cudaStream_t stream);
 int launch_cast(const float* src, void* dst, size_t count, cudaStream_t stream);

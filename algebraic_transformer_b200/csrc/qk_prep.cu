@@ -267,6 +267,140 @@ int launch_prep(const PrepParams& p, int dtype, cudaStream_t stream) {
   return launch_prep_batch(batch, dtype, stream);
 }
 
+// ---- backward of the QK RMS-norm --------------------------------------------------------------
+// y = x tau g with tau = rsqrt(mean(x^2) + eps).  With u = g dy (all in fp32, one rounding to the
+// I/O dtype at the end):
+//   dx      = tau (u - x tau^2 mean(u x))        the input gradient of src/algebraic/algebraic.py:76-83
+//   dgain_j = sum over rows of dy_j x_j tau      src/algebraic/kernels/qk_norm.py:20-26
+// The reference reduces the gain gradient in row blocks and sums the block partials afterwards
+// (qk_norm.py:47-56); here every CTA writes one partial row and a second kernel adds the rows in
+// block order, so the result does not depend on scheduling.  Same lane layout as the forward pass.
+constexpr int RMS_BWD_BLOCKS = 148 * 4;
+int rms_bwd_max_blocks() { return RMS_BWD_BLOCKS; }
+
+template <typename T, int D>
+__global__ void __launch_bounds__(256) qk_rms_bwd_kernel(const RmsBwdParams p) {
+  using V = Vec16<T>;
+  constexpr int VEC = V::N;
+  constexpr int LPR = D / VEC;         // lanes per row
+  constexpr int RPW = 32 / LPR;        // rows per warp step
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int lir = lane % LPR, sub = lane / LPR;
+  const int64_t rows = int64_t(p.B) * p.H * p.T;
+  const int64_t warp_global = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t warps_total = (int64_t(gridDim.x) * blockDim.x) >> 5;
+  float g[VEC], dg[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    g[i] = (p.gain != nullptr) ? p.gain[lir * VEC + i] : 1.0f;
+    dg[i] = 0.f;
+  }
+  // four row groups per step, all eight 16-byte loads issued before any is used (memory-level parallelism)
+  constexpr int U = 4;
+  for (int64_t base = warp_global * RPW; base < rows; base += warps_total * RPW * U) {
+    typename V::Raw rx[U], rd[U];
+    int64_t off_dx[U];
+    bool alive[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t row = base + int64_t(u) * warps_total * RPW + sub;
+      alive[u] = row < rows;
+      const int64_t rr = alive[u] ? row : rows - 1;
+      const int t = int(rr % p.T);
+      const int64_t bh = rr / p.T;
+      const int h = int(bh % p.H);
+      const int64_t b = bh / p.H;
+      rx[u] = V::load(reinterpret_cast<const T*>(p.x) + b * p.xs.b + h * p.xs.h + int64_t(t) * p.xs.t + lir * VEC);
+      rd[u] = V::load(reinterpret_cast<const T*>(p.dy) + b * p.gs.b + h * p.gs.h + int64_t(t) * p.gs.t + lir * VEC);
+      off_dx[u] = b * p.ds.b + h * p.ds.h + int64_t(t) * p.ds.t + lir * VEC;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+    const bool live = alive[u];
+    float x[VEC], d[VEC];
+    V::unpack(rx[u], x);
+    V::unpack(rd[u], d);
+    float ss = 0.f, su = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      ss = fmaf(x[i], x[i], ss);
+      su = fmaf(g[i] * d[i], x[i], su);
+    }
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) {
+      ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      su += __shfl_xor_sync(0xffffffffu, su, o);
+    }
+    const float tau = rsqrtf(ss * (1.0f / D) + p.eps);
+    const float coef = tau * tau * su * (1.0f / D);
+    float out[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      out[i] = tau * (g[i] * d[i] - x[i] * coef);
+      if (live) dg[i] = fmaf(d[i] * x[i], tau, dg[i]);
+    }
+    if (live) V::store(reinterpret_cast<T*>(p.dx) + off_dx[u], out);
+    }
+  }
+  if (p.dgain == nullptr) return;
+  // the rows a warp handled side by side, then the warps of the CTA, in a fixed order
+#pragma unroll
+  for (int i = 0; i < VEC; ++i)
+    for (int o = LPR; o < 32; o <<= 1) dg[i] += __shfl_xor_sync(0xffffffffu, dg[i], o);
+  __shared__ float s_dg[8][D];
+  if (sub == 0) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) s_dg[warp][lir * VEC + i] = dg[i];
+  }
+  __syncthreads();
+  if (threadIdx.x < D) {
+    float s = 0.f;
+    for (int w = 0; w < int(blockDim.x >> 5); ++w) s += s_dg[w][threadIdx.x];
+    p.partials[int64_t(blockIdx.x) * D + threadIdx.x] = s;
+  }
+}
+
+__global__ void qk_rms_dgain_kernel(const float* __restrict__ partials, int blocks, int D, float* __restrict__ dgain) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= D) return;
+  float s = 0.f;
+  for (int b = 0; b < blocks; ++b) s += partials[int64_t(b) * D + j];
+  dgain[j] = s;
+}
+
+template <typename T, int D>
+static int launch_rms_bwd_t(const RmsBwdParams& p, cudaStream_t stream) {
+  constexpr int RPW = 32 / (D * int(sizeof(T)) / 16);
+  const int64_t rows = int64_t(p.B) * p.H * p.T;
+  if (rows == 0) {
+    if (p.dgain != nullptr) ALG_CUDA_TRY(cudaMemsetAsync(p.dgain, 0, sizeof(float) * D, stream));
+    return ALG_OK;
+  }
+  int64_t blocks = ((rows + RPW - 1) / RPW + 7) / 8;
+  if (blocks > RMS_BWD_BLOCKS) blocks = RMS_BWD_BLOCKS;
+  qk_rms_bwd_kernel<T, D><<<unsigned(blocks), 256, 0, stream>>>(p);
+  ALG_CUDA_TRY(cudaGetLastError());
+  count_launch();
+  if (p.dgain != nullptr) {
+    qk_rms_dgain_kernel<<<1, 128, 0, stream>>>(p.partials, int(blocks), D, p.dgain);
+    ALG_CUDA_TRY(cudaGetLastError());
+    count_launch();
+  }
+  return ALG_OK;
+}
+
+int launch_rms_bwd(const RmsBwdParams& p, int dtype, cudaStream_t stream) {
+  if (p.D != 64 && p.D != 128) {
+    set_error("QK RMS backward needs head_dim 64 or 128, got %d", p.D);
+    return ALG_ERR_UNSUPPORTED;
+  }
+  if (dtype == ALG_BF16)
+    return p.D == 64 ? launch_rms_bwd_t<__nv_bfloat16, 64>(p, stream) : launch_rms_bwd_t<__nv_bfloat16, 128>(p, stream);
+  if (dtype == ALG_F32) return p.D == 64 ? launch_rms_bwd_t<float, 64>(p, stream) : launch_rms_bwd_t<float, 128>(p, stream);
+  set_error("unknown dtype %d", dtype);
+  return ALG_ERR_INVALID;
+}
+
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
                                      size_t count) {
   const size_t stride = size_t(gridDim.x) * blockDim.x * 8;

@@ -138,6 +138,37 @@ def qk_rms_norm(x: torch.Tensor, gain: Optional[torch.Tensor], eps: float = 1e-5
     return y.view(x.shape)
 
 
+def qk_rms_norm_backward(x: torch.Tensor, gain: Optional[torch.Tensor], dy: torch.Tensor, eps: float = 1e-5):
+    """`(dx, dgain)` of `qk_rms_norm(x, gain, eps)` (no rotation) for the output gradient `dy`: what
+    the reference's custom VJP returns (src/algebraic/kernels/qk_norm.py:29-56) — the autodiff input
+    gradient of `rms_norm` and the gain gradient reduced over row blocks.  `dgain` is None without a
+    gain.  Same shapes, dtypes and layouts as the forward; `dx` comes back in the layout of `x`."""
+    _require_cuda(x, gain, dy)
+    if x.ndim < 2 or x.shape[-1] not in (64, 128) or (gain is not None and gain.shape != (x.shape[-1],)):
+        raise ValueError("QK RMS kernel needs D=64 or D=128 and a one-dimensional gain")
+    if x.dtype not in _DTYPES or dy.dtype != x.dtype or (gain is not None and gain.dtype != torch.float32):
+        raise ValueError("QK RMS kernel needs float32/BF16 input and float32 gain")
+    if dy.shape != x.shape:
+        raise ValueError("dy must have the shape of x")
+    if eps <= 0:
+        raise ValueError("QK RMS epsilon must be positive")
+    D = x.shape[-1]
+    x4 = x.reshape(1, 1, -1, D) if x.ndim != 4 else x
+    dy4 = dy.reshape(1, 1, -1, D) if dy.ndim != 4 else dy
+    dx = torch.empty_strided(x4.shape, x4.stride(), dtype=x.dtype, device=x.device)
+    dgain = torch.empty(D, dtype=torch.float32, device=x.device) if gain is not None else None
+    if x4.numel() == 0:
+        return dx.view(x.shape), (dgain.zero_() if dgain is not None else None)
+    lib = L.load()
+    ws = _workspace(x.device, lib.alg_qk_rms_bwd_workspace_bytes(D), "qk_rms_bwd")
+    a = L.QkRmsBwdArgs(x=x4.data_ptr(), dy=dy4.data_ptr(), gain=_ptr(gain), dx=dx.data_ptr(), dgain=_ptr(dgain),
+                       eps=float(eps), B=x4.shape[0], H=x4.shape[1], T=x4.shape[2], D=D, dtype=_DTYPES[x.dtype],
+                       x_stride=_strides3(x4), dy_stride=_strides3(dy4), dx_stride=_strides3(dx),
+                       workspace=ws.data_ptr(), workspace_bytes=ws.numel())
+    L.check(lib.alg_qk_rms_bwd(a, _stream()))
+    return (dx if x.ndim == 4 else dx.view(x.shape)), dgain
+
+
 def rms_norm(x: torch.Tensor, gain: Optional[torch.Tensor], eps: float = 1e-5, out=None) -> torch.Tensor:
     """RMS normalisation over the last axis of a contiguous bf16 tensor (the model's `_norm`,
     src/algebraic/model.py:141-143): fp32 math, one rounding to bf16."""

@@ -441,6 +441,14 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
         extra["qk_rms_rot" if rot else "qk_rms"] = {
             "workload": f"(1,16,{T},{D}) bf16 (134 MB in + 134 MB out, > L2)", "ms": ms_r,
             "gbs": nbytes / (ms_r * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms_r * 1e-3) / 1e9 / peak_bw}
+    # backward of the same normalisation: reads x and dy, writes dx (+ the gain gradient)
+    fnb = lambda i: A.ops.qk_rms_norm_backward(x, gain, y, 1e-5)  # noqa: E731
+    for i in range(3):
+        fnb(i)
+    ms_rb = cuda_time(fnb, iters, sync)
+    nbytes_b = 3.0 * x.numel() * 2
+    extra["qk_rms_bwd"] = {"workload": f"(1,16,{T},{D}) bf16: x and dy in, dx out (3 x 134 MB) + dgain", "ms": ms_rb,
+                           "gbs": nbytes_b / (ms_rb * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes_b / (ms_rb * 1e-3) / 1e9 / peak_bw}
     # ---- single-query decode against a 32768-token KV cache: HBM bound ----
     k = x
     v = torch.randn((B, H, T, D), generator=g).bfloat16().to(dev)

@@ -93,6 +93,33 @@ typedef struct {
 
 ALG_API int alg_qk_rms_fwd(const alg_qk_rms_args* args, void* stream);
 
+/* Backward of the QK RMS normalisation (no rotation): dx and the learned-gain gradient.
+ * Replaces: the custom VJP of qk_rms_norm      src/algebraic/kernels/qk_norm.py:29-56
+ *           (_gain_kernel :20-26 reduces dy * x * tau over row blocks, the partials are summed
+ *           afterwards; the input gradient is the autodiff gradient of rms_norm,
+ *           src/algebraic/algebraic.py:76-83).
+ * x, dy, dx: (B, H, T, D) of one dtype, D contiguous, strides as above (dx may alias dy).
+ * gain: (D) fp32 or NULL; dgain: (D) fp32, or NULL when gain is NULL.  workspace:
+ * alg_qk_rms_bwd_workspace_bytes(D) bytes (per-CTA partial rows of the gain gradient, added in
+ * block order: the result does not depend on scheduling). */
+typedef struct {
+  const void* x;
+  const void* dy;
+  const float* gain;
+  void* dx;
+  float* dgain;
+  float eps;
+  int B, H, T, D;
+  int dtype;               /* ALG_BF16 | ALG_F32 (x, dy and dx) */
+  int64_t x_stride[3];
+  int64_t dy_stride[3];
+  int64_t dx_stride[3];
+  void* workspace;
+  size_t workspace_bytes;
+} alg_qk_rms_bwd_args;
+ALG_API size_t alg_qk_rms_bwd_workspace_bytes(int D);
+ALG_API int alg_qk_rms_bwd(const alg_qk_rms_bwd_args* args, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * Asinh-power attention forward.
  * Replaces: flash_attention(q,k,v,sink_logit,kind="asinh",n,c,range_guard=...)

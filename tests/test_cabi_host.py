@@ -55,6 +55,14 @@ def test_invalid_arguments_fail_before_launch():
     assert lib.alg_head_finalize_ce(None, None, 4, None, None, None, None, 0, None) == L.ALG_ERR_INVALID
     q = L.QkRmsArgs(x=16, y=16, eps=0.0, B=1, H=1, T=1, D=64)
     assert lib.alg_qk_rms_fwd(q, None) == L.ALG_ERR_INVALID
+    assert lib.alg_qk_rms_bwd(L.QkRmsBwdArgs(), None) == L.ALG_ERR_INVALID
+    qb = L.QkRmsBwdArgs(x=16, dy=16, dx=16, dgain=16, eps=1e-5, B=1, H=1, T=8, D=64, dtype=L.ALG_BF16)
+    assert lib.alg_qk_rms_bwd(qb, None) == L.ALG_ERR_INVALID and b"dgain without gain" in lib.alg_last_error()
+    qb.gain = 16
+    assert lib.alg_qk_rms_bwd(qb, None) == L.ALG_ERR_WORKSPACE
+    qb.D = 96
+    assert lib.alg_qk_rms_bwd(qb, None) == L.ALG_ERR_UNSUPPORTED
+    assert lib.alg_qk_rms_bwd_workspace_bytes(128) == 148 * 4 * 128 * 4 and lib.alg_qk_rms_bwd_workspace_bytes(96) == 0
     # guard words handed over by the QKV projection describe ready-made q, k, v: not with the prologue
     a = L.AttnArgs(q=16, k=16, v=16, o=16, B=1, H=1, Tq=256, Tk=256, D=64, n=16, c=8.0, variant=L.ALG_VARIANT_GUARD,
                    guard_words=16, q_gain=16, k_gain=16, cos=16, sin=16, eps=1e-5)

@@ -63,6 +63,36 @@ def test_qk_rms_with_rotation_and_strided_view(dtype, D):
     assert rel_l2(got, want) < (2e-6 if dtype == torch.float32 else 6e-3)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("D", [64, 128])
+def test_qk_rms_backward_matches_oracle_autograd(dtype, D):
+    """dx and dgain of the QK RMS-norm (custom VJP of qk_norm.py:29-56: autodiff input gradient, gain
+    gradient reduced over row blocks) against autograd through the oracle's rms_norm; a strided view
+    of a projection output, a zero row, and the call without a gain."""
+    B, H, T = 2, 3, 300
+    proj = randn((B, T, H * D), 281, dtype, 2.0)
+    proj[0, 7] = 0
+    x = proj.view(B, T, H, D).transpose(1, 2)                # (B,H,T,D) view, not contiguous
+    dy = randn((B, H, T, D), 282, dtype)
+    g = torch.Generator().manual_seed(283)
+    gain = 0.25 + 2 * torch.rand(D, generator=g)
+    xf, gf = x.float().clone().requires_grad_(True), gain.clone().requires_grad_(True)
+    R.rms_norm(xf, gf, 1e-5).backward(dy.float())
+    xd = proj.to(DEV).view(B, T, H, D).transpose(1, 2)
+    dx, dgain = A.ops.qk_rms_norm_backward(xd, gain.to(DEV), dy.to(DEV), 1e-5)
+    assert dx.stride() == xd.stride()
+    tol = 2e-5 if dtype == torch.float32 else 1e-2
+    assert rel_l2(dx, xf.grad) < tol and rel_l2(dgain, gf.grad) < tol
+    assert torch.isfinite(dx).all()
+    x2 = x.float().clone().requires_grad_(True)
+    R.rms_norm(x2, None, 1e-5).backward(dy.float())
+    dx2, none = A.ops.qk_rms_norm_backward(xd, None, dy.to(DEV), 1e-5)
+    assert none is None and rel_l2(dx2, x2.grad) < tol
+    # the same call twice gives the same bits (partials are added in block order)
+    dx3, dgain3 = A.ops.qk_rms_norm_backward(xd, gain.to(DEV), dy.to(DEV), 1e-5)
+    assert torch.equal(dgain, dgain3) and torch.equal(dx, dx3)
+
+
 def test_qk_rms_golden(golden):
     x, gain = torch.from_numpy(golden["rms_x"]), torch.from_numpy(golden["rms_gain"])
     got = A.qk_rms_norm(*dev(x, gain), 1e-5).cpu()
