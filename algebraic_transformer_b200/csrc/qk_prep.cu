@@ -279,7 +279,7 @@ constexpr int RMS_BWD_BLOCKS = 148 * 4;
 int rms_bwd_max_blocks() { return RMS_BWD_BLOCKS; }
 
 template <typename T, int D>
-__global__ void __launch_bounds__(256) qk_rms_bwd_kernel(const RmsBwdParams p) {
+__global__ void __launch_bounds__(256, 3) qk_rms_bwd_kernel(const RmsBwdParams p) {
   using V = Vec16<T>;
   constexpr int VEC = V::N;
   constexpr int LPR = D / VEC;         // lanes per row
@@ -377,7 +377,7 @@ static int launch_rms_bwd_t(const RmsBwdParams& p, cudaStream_t stream) {
     return ALG_OK;
   }
   int64_t blocks = ((rows + RPW - 1) / RPW + 7) / 8;
-  if (blocks > RMS_BWD_BLOCKS) blocks = RMS_BWD_BLOCKS;
+  if (blocks > 148 * 3) blocks = 148 * 3;               // one resident wave: three CTAs per SM (<= RMS_BWD_BLOCKS rows of scratch)
   qk_rms_bwd_kernel<T, D><<<unsigned(blocks), 256, 0, stream>>>(p);
   ALG_CUDA_TRY(cudaGetLastError());
   count_launch();
