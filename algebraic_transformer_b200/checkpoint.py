@@ -62,26 +62,35 @@ def config_from_meta(meta: dict) -> Tuple[PrefillConfig, int]:
     return cfg, int(c.get("seq_len", 1024))
 
 
+def _parse_key(key: str) -> Tuple[str, ...]:
+    """`['layers']['w_q']` -> ("layers", "w_q") (the reference flattens its tree with keystr)."""
+    return tuple(re.findall(r"\['([^']+)'\]", key))
+
+
 def load_checkpoint(run_dir: str):
-    """`(cfg, seq_len, params)` of a run directory, validated as the reference validates it:
-    unknown, duplicate, mis-shaped, non-finite or missing parameters raise ValueError
-    (benchmarking.py:118-145).  `params` uses this package's flat layout (`prefill.init_params`)."""
+    """`(cfg, seq_len, params)` of a run directory.  The archive is checked as a whole before any
+    tensor is kept, against the same rules the reference applies (benchmarking.py:118-145):
+    every stored name must be one of the model's parameters and occur once, every parameter must
+    be stored, and every array must have the model's shape and hold finite values only; each
+    failure raises ValueError.  `params` uses this package's flat layout (`prefill.init_params`)."""
     with open(os.path.join(run_dir, "meta.json")) as f:
         cfg, seq_len = config_from_meta(json.load(f))
-    expected = _expected_shapes(cfg)
-    params, seen = {}, set()
-    with np.load(os.path.join(run_dir, "params.npz"), allow_pickle=False) as flat:
-        for key in flat.files:
-            parts = tuple(re.findall(r"\['([^']+)'\]", key))
-            if parts not in expected or parts in seen:
-                raise ValueError(f"unexpected checkpoint parameter: {key}")
-            value = flat[key]
-            if value.shape != expected[parts] or not np.isfinite(value).all():
-                raise ValueError(f"invalid checkpoint parameter: {key}")
-            params[parts[-1]] = torch.from_numpy(np.ascontiguousarray(value, dtype=np.float32))
-            seen.add(parts)
-    if seen != set(expected):
-        raise ValueError(f"missing checkpoint parameters: {sorted(set(expected) - seen)}")
+    shapes = _expected_shapes(cfg)
+    with np.load(os.path.join(run_dir, "params.npz"), allow_pickle=False) as archive:
+        names = list(archive.files)
+        paths = [_parse_key(name) for name in names]
+        strangers = [name for name, path in zip(names, paths) if path not in shapes]
+        repeated = [name for name, path in zip(names, paths) if paths.count(path) > 1]
+        if strangers or repeated:
+            raise ValueError(f"unexpected checkpoint parameter: {(strangers + repeated)[0]}")
+        absent = sorted(set(shapes) - set(paths))
+        if absent:
+            raise ValueError(f"missing checkpoint parameters: {absent}")
+        arrays = {path: archive[name] for name, path in zip(names, paths)}
+    bad = [path for path, value in arrays.items() if value.shape != shapes[path] or not np.isfinite(value).all()]
+    if bad:
+        raise ValueError("invalid checkpoint parameter: " + "".join(f"['{part}']" for part in bad[0]))
+    params = {path[-1]: torch.from_numpy(np.ascontiguousarray(value, dtype=np.float32)) for path, value in arrays.items()}
     return cfg, seq_len, params
 
 
@@ -111,6 +120,7 @@ class Scorer:
             raise ValueError("batch must be positive")
         self.cfg, self.params, self.device, self.T, self.batch = cfg, params, torch.device(device), int(seq_len), batch
         self._models = {}
+        self.truncated_pairs = 0
 
     def _bucket(self, n: int) -> int:
         if n > self.T:
@@ -130,27 +140,43 @@ class Scorer:
         _, _, nll = self._model(T).loss(tokens.to(self.device), targets.to(self.device), want_nll=True)
         return (-nll).view(B, T)
 
-    def score_token_pairs(self, pairs: Sequence[Tuple[List[int], List[int]]]) -> List[float]:
-        """Sum of `log p` over each continuation given its context, one float per (context ids,
-        continuation ids) pair.  Sequences are right-padded to a power-of-two bucket; only the
-        continuation positions are projected through the head."""
+    def score_token_pairs(self, pairs: Sequence[Tuple[List[int], List[int]]], *, allow_truncation: bool = False):
+        """`(mean log p, greedy hit)` per (context ids, continuation ids) pair, as the reference's
+        `Scorer.score_token_pairs` returns them (benchmarking.py:196-240): the mean of
+        `log p(cont[j] | context, cont[:j])` over the continuation, and whether the arg-max token
+        equals the target at every continuation position (for a causal model that is the greedy
+        generation reproducing the continuation).  The model is fed `context + cont[:-1]`; a
+        context too long for the trained length is an error unless `allow_truncation`, which
+        keeps its tail and counts the pair in `truncated_pairs`.  Only the continuation positions
+        go through the head: `log p` comes from the fused Alg-CE kernel (no logits in HBM for it);
+        the arg-max needs the logits of those few rows, one small GEMM.  `log p` is floored at
+        log(1e-30) by the kernel's telemetry; non-finite values raise ValueError."""
         from . import ops
-        out = [0.0] * len(pairs)
-        order = sorted(range(len(pairs)), key=lambda i: len(pairs[i][0]) + len(pairs[i][1]))
+        encoded = []
+        for context, continuation in pairs:
+            ctx, cont = list(context), list(continuation)
+            if not ctx or not cont or len(cont) > self.T:
+                raise ValueError("need nonempty context/target and target length <= context")
+            room = self.T + 1 - len(cont)
+            if len(ctx) > room:
+                if not allow_truncation:
+                    raise ValueError("recall scoring would truncate its evidence")
+                ctx = ctx[-room:]
+                self.truncated_pairs += 1
+            encoded.append((ctx + cont[:-1], len(ctx) - 1, cont))
+        lps: List[float] = [0.0] * len(encoded)
+        hits: List[bool] = [False] * len(encoded)
+        order = sorted(range(len(encoded)), key=lambda i: len(encoded[i][0]))
         for lo in range(0, len(order), self.batch):
             idx = order[lo:lo + self.batch]
-            longest = max(len(pairs[i][0]) + len(pairs[i][1]) for i in idx)
-            bucket = self._bucket(longest)
+            bucket = self._bucket(max(len(encoded[i][0]) for i in idx))
             x = torch.zeros((len(idx), bucket), dtype=torch.long)
             rows, cols, tgt = [], [], []
             for r, i in enumerate(idx):
-                ctx, cont = pairs[i]
-                if not ctx or not cont:
-                    raise ValueError("context and continuation must both be non-empty")
-                seq = list(ctx) + list(cont)
+                seq, start, cont = encoded[i]
                 x[r, :len(seq)] = torch.tensor(seq)
-                for j, t in enumerate(cont):                    # position len(ctx)-1+j predicts cont[j]
-                    rows.append(r); cols.append(len(ctx) - 1 + j); tgt.append(t)
+                for j, t in enumerate(cont):                    # position start + j predicts cont[j]
+                    rows.append(r); cols.append(start + j); tgt.append(t)
             model = self._model(bucket)
             hid = model.hidden(x.to(self.device))
             sel = hid[torch.tensor(rows, device=self.device), torch.tensor(cols, device=self.device)].contiguous()
@@ -158,11 +184,19 @@ class Scorer:
             pad = (-n_sel) % 8                                   # keep the row count friendly to 16-byte rows
             if pad:
                 sel = torch.cat([sel, sel[:1].expand(pad, -1)]).contiguous()
-                tgt = tgt + [0] * pad
-            tg = torch.tensor(tgt, dtype=torch.int32, device=self.device)
+            tg = torch.tensor(tgt + [0] * pad, dtype=torch.int32, device=self.device)
             _, _, nll = ops.fused_head(sel, model.p["embed"], tg, kind="alg_ce", n=self.cfg.head_n, c=self.cfg.head_c,
                                        block_n=sel.shape[0], want_nll=True)
-            lp = (-nll[:n_sel]).cpu()
-            for r_i, v in zip(rows, lp.tolist()):
-                out[idx[r_i]] += v
-        return out
+            lp = (-nll[:n_sel]).double().cpu()
+            if not bool(torch.isfinite(lp).all()):
+                raise ValueError("non-finite evaluation log-probabilities")
+            # the head's weight is monotone in the logit, so the arg-max of the logits is the arg-max of p
+            top = torch.matmul(sel[:n_sel], model.p["embed"].t()).float().argmax(-1).cpu()
+            want = torch.tensor(tgt)
+            at = 0
+            for r, i in enumerate(idx):
+                m = len(encoded[i][2])
+                lps[i] = float(lp[at:at + m].mean())
+                hits[i] = bool(torch.equal(top[at:at + m], want[at:at + m]))
+                at += m
+        return lps, hits

@@ -379,12 +379,11 @@ __global__ void __launch_bounds__(NTHREADS) attn_bwd_dkv_kernel(const AttnBwdPar
 template <int D>
 int launch_d(const AttnBwdParams& p, cudaStream_t stream) {
   constexpr size_t smem = size_t(6) * BM * (D + 8) * sizeof(__nv_bfloat16);   // 2 resident tiles + 2 stages of 2
-  static bool configured = false;     // idempotent attributes; benign if two threads race
-  if (!configured) {
-    ALG_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    ALG_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_dkv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  if (int rc = configured.run([&] {
+        cudaError_t e = cudaFuncSetAttribute(attn_bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        return e != cudaSuccess ? e : cudaFuncSetAttribute(attn_bwd_dkv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+      })) return rc;
   const dim3 gq((p.Tq + BM - 1) / BM, p.H, p.B), gk((p.Tk + BN - 1) / BN, p.H, p.B);
   attn_bwd_dq_kernel<D><<<gq, NTHREADS, smem, stream>>>(p);
   ALG_CUDA_TRY(cudaGetLastError());

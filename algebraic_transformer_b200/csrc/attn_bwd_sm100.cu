@@ -428,15 +428,15 @@ int launch_d(const AttnBwdParams& p, cudaStream_t stream) {
   if (int rc = make_map(&tk, p.k, p.ks, p.B, p.H, p.Tk, D)) return rc;
   if (int rc = make_map(&tv, p.v, p.vs, p.B, p.H, p.Tk, D)) return rc;
   if (int rc = make_map(&tdo, p.d_o, p.os, p.B, p.H, p.Tq, D)) return rc;
-  static bool configured = false;
-  if (!configured) {
-    ALG_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_tc_kernel<D, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes<D>())));
-    ALG_CUDA_TRY(cudaFuncSetAttribute(attn_bwd_tc_kernel<D, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes<D>())));
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  int sms = 0;
+  if (int rc = configured.run([&] {
+        cudaError_t e = cudaFuncSetAttribute(attn_bwd_tc_kernel<D, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes<D>()));
+        return e != cudaSuccess ? e : cudaFuncSetAttribute(attn_bwd_tc_kernel<D, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes<D>()));
+      }, &sms)) return rc;
   const int64_t rows = int64_t(p.B) * p.H * p.Tq;
   int64_t blocks = (rows / (32 / (D / 8)) + 7) / 8;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > sms * 8) blocks = sms * 8;
   attn_delta_kernel<D><<<unsigned(blocks), 256, 0, stream>>>(p);
   ALG_CUDA_TRY(cudaGetLastError());
   const dim3 grid(p.H, p.B, p.Tq / BT);

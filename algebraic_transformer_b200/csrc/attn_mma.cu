@@ -324,13 +324,11 @@ int launch_one(const AttnParams& p, cudaStream_t stream) {
   constexpr int NS = SPLIT ? 2 : 1;
   constexpr size_t smem = size_t(3) * NS * BM * (D + 8) * sizeof(__nv_bfloat16);
   auto kern = attn_mma_kernel<T, D, SPLIT>;
-  static bool configured = false;     // idempotent attribute; benign if two threads race
-  if (!configured) {
-    ALG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  int sms = 0;
+  if (int rc = configured.run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); }, &sms)) return rc;
   const long long items = (long long)((p.Tq + BM - 1) / BM) * p.H * p.B;
-  const int cap = 148 * 4;                             // a few resident CTAs per SM; the loop covers the rest
+  const int cap = sms * 4;                             // a few resident CTAs per SM; the loop covers the rest
   const unsigned grid = unsigned(items < cap ? items : cap);
   kern<<<grid, NTHREADS, smem, stream>>>(p);
   ALG_CUDA_TRY(cudaGetLastError());

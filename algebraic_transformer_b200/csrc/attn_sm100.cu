@@ -8,37 +8,59 @@
 //
 // One CTA owns 256 consecutive query rows of one (batch, head): two 128-row tiles.
 //   warp 0 (one lane)  TMA: both Q tiles once, then K_j / V_j tiles through a ring
-//   warp 1 (one lane)  tcgen05.mma: S_w = Q_w K_j^T (both operands in shared memory) and
-//                      O_w += P_w V_j with P_w read from TENSOR MEMORY (the A operand) and
-//                      V_j from shared memory as an MN-major B operand
-//   warps 2..5         weights for query tile 0: tcgen05.ld S_0 (one thread = one row),
+//   warp 1             tcgen05.mma (the whole warp runs the loop, one elected lane issues):
+//                      S_w = Q_w K_j^T (both operands in shared memory) and O_w += P_w V_j with P_w
+//                      read from TENSOR MEMORY (the A operand) and V_j from shared memory as an
+//                      MN-major B operand
+//   warps 2, 3         scale Q tile 0 / 1 in shared memory by a power of two (see below)
+//   weight group 0     weights for query tile 0: tcgen05.ld S_0 (one thread = one row),
 //                      x -> rho_fast(x)^n in packed fp32, row sum, bf16 P_0 written back
-//                      with tcgen05.st over the columns S_0 occupied
-//   warps 6..9         the same for query tile 1
-// The two tiles run out of phase, so the tensor pipe works for one while the other
-// evaluates rho.  TMEM (512 columns): S_0, S_1 (128 each; P_w aliases the first 64 columns
-// of S_w as packed bf16) + O_0, O_1 (head_dim each).  P never touches shared memory, which
-// leaves the tensor core's shared-memory operand path to Q, K and V alone.  The tensor pipe
-// executes one thread's MMAs in issue order, so issuing S_w(j+1) after P_w(j).V_j is what
-// protects P_w(j) from being overwritten, and S_w(j+1) complete implies P_w(j).V_j complete.
-// Key tiles above the diagonal are never loaded; only the diagonal tile evaluates a mask.
+//                      with tcgen05.st over columns S_0 occupied
+//   weight group 1     the same for query tile 1
+// A weight group is 4 * SPLIT warps.  With SPLIT = 2 two warps share each 32-lane quarter of
+// tensor memory and take 64 of the tile's 128 key columns each.
+//
+// The score scale.  x = s / (sqrt(D) c) with 1 / (sqrt(D) c) = 2^e m, 1 <= m < 2.  The factor
+// 2^e goes onto Q in shared memory (an exact exponent shift of bf16 values), so tensor memory
+// holds y = x / m, and with kappa = 1 / m^2
+//     t' = y + sqrt(kappa + y^2) = rho(x) / m
+// costs one multiplication less per score than scaling s first.  Every weight is then short of
+// the reference's by the constant m^n, which cancels in o = sum(p v) / l; the sink's weight and
+// the saved statistic carry the constant explicitly.
+//
+// Tensor-memory layout (512 columns): S_0, S_1 (128 each) + O_0, O_1 (head_dim each).  The bf16
+// weights of S columns [32 g, 32 g + 32) are written over columns [32 g, 32 g + 16) of the same
+// block, so a thread only ever overwrites scores it has already read and two warps working on
+// different 32-column blocks never touch each other's columns.  P never touches shared memory,
+// which leaves the tensor core's shared-memory operand path to Q, K and V alone.
+//
+// Hand-overs.  The tensor pipe executes one thread's MMAs in issue order, so issuing S_w(j+1)
+// after P_w(j).V_j is what protects P_w(j) from being overwritten.  P_w V_j is issued in two
+// halves of 64 keys: the weight warps signal after the first 64 keys of a tile, and the first
+// half of the product runs while they evaluate the second.  Key tiles above the diagonal are
+// never loaded; only the diagonal tile evaluates a mask, and it skips the 32-column blocks that
+// lie wholly above the diagonal for its rows.
 // The kernel is persistent: one CTA per SM walks a fixed list of work items (heaviest row
 // blocks first, dealt out boustrophedon so the per-CTA sums stay level).  Barriers, tensor
 // memory and the K/V ring live across items, so the loads of the next item's first tiles
-// are in flight while the current item finishes, and its first S is issued while the
-// weight warps still write the current output.
+// are in flight while the current item finishes.
 // Every mbarrier wait is bounded (sm100_ptx.cuh); on a timeout the kernel reports
 // ALG_DEV_TIMEOUT through the status word and returns.
 #include "common.cuh"
 #include "launchers.h"
 #include "sm100_ptx.cuh"
 
+#include <math.h>
+#include <stdlib.h>
+
 namespace alg {
 namespace {
 
 using namespace sm100;
 
-constexpr int BQ = 128, BKEY = 128, NTHREADS = 320;
+constexpr int BQ = 128, BKEY = 128;
+constexpr int FIRST_WEIGHT_WARP = 4;            // warps 0..3: TMA, MMA, two Q scalers
+template <int SPLIT> constexpr int nthreads() { return FIRST_WEIGHT_WARP * 32 + 2 * 4 * SPLIT * 32; }
 constexpr int PANEL_BYTES = 128 * 128;          // 128 rows x 64 bf16, one swizzle-128B panel
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int MAX_NKV = 10;
@@ -50,33 +72,44 @@ template <int D> struct Cfg {
   static constexpr int Q_OFF = 0;
   static constexpr int KV_OFF = 2 * TILE_BYTES;
   static constexpr int CTL_OFF = KV_OFF + NKV * TILE_BYTES;
-  static constexpr uint32_t S_COL = 0;                      // S_w at S_COL + 128 w; P_w = its first 64 columns
+  static constexpr uint32_t S_COL = 0;                      // S_w at S_COL + 128 w; P_w inside it
   static constexpr uint32_t O_COL = 256;                    // O_w at O_COL + D w
   static constexpr uint32_t IDESC_S = make_idesc_bf16(BQ, BKEY, 0, 0);
   static constexpr uint32_t IDESC_PV = make_idesc_bf16(BQ, D, 0, 1);   // V is [key][d]: MN-major B
 };
 
 struct __align__(16) Control {
-  uint64_t q_full[2], q_free[2], kv_full[MAX_NKV], kv_empty[MAX_NKV], s_full[2], p_full[2], o_full[2], o_free[2];
+  uint64_t q_full[2], q_ready[2], q_free[2], kv_full[MAX_NKV], kv_empty[MAX_NKV];
+  uint64_t s_full[2], p_half[2], p_full[2], o_full[2], o_free[2];
+  uint64_t l_part[2], l_total[2];   // split weight groups: hand-over of the row sums between the column halves
   uint32_t tmem_base;
   int abort_flag;
   int shift_mode;
+  float row_sum[2][BQ];       // [query tile][row]: half 1's partial row sum, then the row's total
 };
 
-// 32 scores -> 32 weights rho_fast(s * scale)^n, two at a time on the packed fp32 pipe
-// (fma.f32x2 / mul.f32x2); row-sum partials in `la`, `lb`; bf16 pairs in `packed`.
-template <int LOG2N, bool DIAG>
-__device__ __forceinline__ void weigh32(const uint32_t* s, float scale, int col0, int r, float2& la, float2& lb,
-                                        uint32_t* packed) {
-  const float2 sc = make_float2(scale, scale), one = make_float2(1.f, 1.f);
+// Tensor-memory column (relative to the S block) of the packed weights of S column `scol`.
+__device__ __forceinline__ constexpr uint32_t p_col_of(uint32_t scol) { return 32u * (scol >> 5) + ((scol & 31u) >> 1); }
+
+// W (16 or 32) scores y -> W weights (y + sqrt(kappa + y^2))^n, two at a time on the packed fp32
+// pipe (fma.f32x2 / mul.f32x2); row-sum partials in `la`, `lb`; bf16 pairs in `packed`.
+template <int LOG2N, bool DIAG, int W>
+__device__ __forceinline__ void weigh(const uint32_t* s, float kappa, int col0, int r, float2& la, float2& lb,
+                                      uint32_t* packed) {
+  if (DIAG && col0 > (r | 31)) {                    // warp-uniform: the block lies above the diagonal for all 32 rows
 #pragma unroll
-  for (int i = 0; i < 32; i += 4) {
-    float2 x0 = __fmul2_rn(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc);
-    float2 x1 = __fmul2_rn(make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), sc);
-    const float2 rad0 = __ffma2_rn(x0, x0, one), rad1 = __ffma2_rn(x1, x1, one);
+    for (int i = 0; i < W / 2; ++i) packed[i] = 0u;
+    return;
+  }
+  const float2 kp = make_float2(kappa, kappa);
+#pragma unroll
+  for (int i = 0; i < W; i += 4) {
+    const float2 y0 = make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+    const float2 y1 = make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+    const float2 rad0 = __ffma2_rn(y0, y0, kp), rad1 = __ffma2_rn(y1, y1, kp);
     const float2 rs0 = make_float2(rsqrt_approx(rad0.x), rsqrt_approx(rad0.y));
     const float2 rs1 = make_float2(rsqrt_approx(rad1.x), rsqrt_approx(rad1.y));
-    float2 t0 = __ffma2_rn(rad0, rs0, x0), t1 = __ffma2_rn(rad1, rs1, x1);
+    float2 t0 = __ffma2_rn(rad0, rs0, y0), t1 = __ffma2_rn(rad1, rs1, y1);
 #pragma unroll
     for (int k = 0; k < LOG2N; ++k) { t0 = __fmul2_rn(t0, t0); t1 = __fmul2_rn(t1, t1); }
     if (DIAG) {                                     // causal mask inside the diagonal tile
@@ -90,30 +123,74 @@ __device__ __forceinline__ void weigh32(const uint32_t* s, float scale, int col0
   }
 }
 
-// One 128-key score tile of this thread's row: S from TMEM -> weights -> packed bf16 P back
-// into TMEM over the same columns.  Columns 32c..32c+31 of S become columns 16c..16c+15 of
-// P, always at or below what has already been read, and the load of the next 32 columns is
-// in flight while the current 32 are evaluated.
+// "The first 64 keys of this tile are weighed": stores complete, then one arrival per thread.
+__device__ __forceinline__ void signal_weights(uint64_t* bar) {
+  tmem_st_wait();
+  tc_fence_before();
+  mbar_arrive(bar);
+}
+
+// One 128-key score tile of this thread's row (one warp per tensor-memory quarter): S from
+// tensor memory -> weights -> packed bf16 P back over the block the scores came from.  The load
+// of the next 32 columns is in flight while the current 32 are evaluated.
 template <int LOG2N, bool DIAG>
-__device__ __forceinline__ void weigh_tile(uint32_t s_taddr, int r, float scale, float2& la, float2& lb) {
+__device__ __forceinline__ void weigh_tile(uint32_t s_taddr, int r, float kappa, float2& la, float2& lb,
+                                           uint64_t* p_half, uint64_t* p_full) {
   uint32_t a[32], b[32], packed[16];
   tmem_ld_32x32(s_taddr, a);
   tmem_ld_wait_for(a);
   tmem_ld_32x32(s_taddr + 32, b);
-  weigh32<LOG2N, DIAG>(a, scale, 0, r, la, lb, packed);
-  tmem_st_32x16(s_taddr, packed);
+  weigh<LOG2N, DIAG, 32>(a, kappa, 0, r, la, lb, packed);
+  tmem_st_32x16(s_taddr + p_col_of(0), packed);
   tmem_ld_wait_for(b);
   tmem_ld_32x32(s_taddr + 64, a);
-  weigh32<LOG2N, DIAG>(b, scale, 32, r, la, lb, packed);
-  tmem_st_32x16(s_taddr + 16, packed);
+  weigh<LOG2N, DIAG, 32>(b, kappa, 32, r, la, lb, packed);
+  tmem_st_32x16(s_taddr + p_col_of(32), packed);
+  signal_weights(p_half);
   tmem_ld_wait_for(a);
   tmem_ld_32x32(s_taddr + 96, b);
-  weigh32<LOG2N, DIAG>(a, scale, 64, r, la, lb, packed);
-  tmem_st_32x16(s_taddr + 32, packed);
+  weigh<LOG2N, DIAG, 32>(a, kappa, 64, r, la, lb, packed);
+  tmem_st_32x16(s_taddr + p_col_of(64), packed);
   tmem_ld_wait_for(b);
-  weigh32<LOG2N, DIAG>(b, scale, 96, r, la, lb, packed);
-  tmem_st_32x16(s_taddr + 48, packed);
-  tmem_st_wait();
+  weigh<LOG2N, DIAG, 32>(b, kappa, 96, r, la, lb, packed);
+  tmem_st_32x16(s_taddr + p_col_of(96), packed);
+  signal_weights(p_full);
+}
+
+// The same for a warp that shares its tensor-memory quarter with a second one (`half` 0 or 1): it
+// owns S columns [32 half, 32 half + 32) of the tile's first 64 keys and the same block of the
+// second 64.  Sixteen columns at a time: a thread has 96 registers here (requesting both blocks
+// at once, for more independent chains in flight, spilled and measured 7 % slower).
+template <int LOG2N, bool DIAG>
+__device__ __forceinline__ void weigh_half_tile(uint32_t s_taddr, int half, int r, float kappa, float2& la, float2& lb,
+                                                uint64_t* p_half, uint64_t* p_full) {
+  uint32_t a[16], b[16], packed[8];
+  const int c0 = 32 * half;
+  const uint32_t base = s_taddr + c0;
+  tmem_ld_32x16(base, a);
+  tmem_ld_wait_for16(a);
+  tmem_ld_32x16(base + 16, b);
+  weigh<LOG2N, DIAG, 16>(a, kappa, c0, r, la, lb, packed);
+  tmem_st_32x8(base, packed);                       // p_col_of(32 half) = 32 half
+  tmem_ld_wait_for16(b);
+  tmem_ld_32x16(base + 64, a);
+  weigh<LOG2N, DIAG, 16>(b, kappa, c0 + 16, r, la, lb, packed);
+  tmem_st_32x8(base + 8, packed);
+  signal_weights(p_half);
+  tmem_ld_wait_for16(a);
+  tmem_ld_32x16(base + 80, b);
+  weigh<LOG2N, DIAG, 16>(a, kappa, c0 + 64, r, la, lb, packed);
+  tmem_st_32x8(base + 64, packed);
+  tmem_ld_wait_for16(b);
+  weigh<LOG2N, DIAG, 16>(b, kappa, c0 + 80, r, la, lb, packed);
+  tmem_st_32x8(base + 72, packed);
+  signal_weights(p_full);
+}
+
+__device__ __forceinline__ bool elect_one() {       // one lane of a converged warp
+  uint32_t pred = 0;
+  asm volatile("{\n.reg .pred P;\nelect.sync _|P, 0xffffffff;\nselp.u32 %0, 1, 0, P;\n}\n" : "=r"(pred));
+  return pred != 0;
 }
 
 // Position in the K/V ring: slot and the parity of how often the ring has wrapped.
@@ -139,6 +216,14 @@ __device__ __forceinline__ bool item_at(const AttnParams& p, int k, Item& it) {
 }
 
 template <int D> constexpr size_t smem_bytes() { return size_t(Cfg<D>::CTL_OFF) + sizeof(Control) + 1024; }
+static_assert(smem_bytes<128>() <= 232448 && smem_bytes<64>() <= 232448, "shared memory budget of one CTA");
+
+// The constants of the score scale 1 / (sqrt(D) c) = 2^e m (see the head of the file).
+struct ScaleSplit {
+  float pow2;      // 2^e: applied to Q in shared memory
+  float kappa;     // 1 / m^2
+  float inv_mn;    // 1 / m^n: the factor every weight is short of the reference's
+};
 
 #ifdef ALG_ATTN_TIMING   // optional instrumentation build: cycle counters written into `stat`
 #define ALG_T(acc, expr) [&] { const long long t_ = clock64(); const bool r_ = (expr); acc += clock64() - t_; return r_; }()
@@ -146,10 +231,10 @@ template <int D> constexpr size_t smem_bytes() { return size_t(Cfg<D>::CTL_OFF) 
 #define ALG_T(acc, expr) (expr)
 #endif
 
-template <int D, int LOG2N>
-__global__ void __launch_bounds__(NTHREADS, 1)
+template <int D, int LOG2N, int SPLIT>
+__global__ void __launch_bounds__(nthreads<SPLIT>(), 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-               const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+               const __grid_constant__ CUtensorMap tm_v, const AttnParams p, const ScaleSplit sc) {
   using C = Cfg<D>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -161,15 +246,19 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   if (ctl->shift_mode != 0) return;               // the guard failed: the stable kernel does this launch's work
 
   if (threadIdx.x == 0) {
-    for (int w = 0; w < 2; ++w) { mbar_init(&ctl->q_full[w], 1); mbar_init(&ctl->q_free[w], 1); }
+    for (int w = 0; w < 2; ++w) { mbar_init(&ctl->q_full[w], 1); mbar_init(&ctl->q_ready[w], 1); mbar_init(&ctl->q_free[w], 1); }
     for (int i = 0; i < C::NKV; ++i) { mbar_init(&ctl->kv_full[i], 1); mbar_init(&ctl->kv_empty[i], 1); }
     for (int w = 0; w < 2; ++w) {
       mbar_init(&ctl->s_full[w], 1);
-      mbar_init(&ctl->p_full[w], 128);
+      mbar_init(&ctl->p_half[w], 128 * SPLIT);
+      mbar_init(&ctl->p_full[w], 128 * SPLIT);
       mbar_init(&ctl->o_full[w], 1);
-      mbar_init(&ctl->o_free[w], 128);
+      mbar_init(&ctl->o_free[w], 128 * SPLIT);
+      mbar_init(&ctl->l_part[w], 128);
+      mbar_init(&ctl->l_total[w], 128);
     }
     ctl->abort_flag = 0;
+   
     fence_barrier_init();
     if (blockIdx.x == 0 && p.stat_kind != nullptr) *p.stat_kind = ALG_VARIANT_NOSHIFT;
   }
@@ -221,137 +310,221 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t q_addr = smem_u32(smem + C::Q_OFF), kv_addr = smem_u32(smem + C::KV_OFF);
-      using Cur = RingCursor<C::NKV>;
-      Cur cur;                                      // the next K/V tile in ring order, over all items
-      int t0 = 0, t1 = 0;                           // score tiles of query tile 0 / 1 in earlier items
-      auto kv_wait = [&](const Cur& c) { return bw.wait(&ctl->kv_full[c.slot], c.phase); };
-      // descriptor low halves: Q tiles and ring slot 0 as K (K-major, LBO 16) and as V (MN-major,
-      // LBO = one panel); a slot adds slot * TILE_BYTES / 16, a K step adds a constant
-      const uint32_t q_lo0 = sw128_desc_lo(q_addr, 16), k_lo0 = sw128_desc_lo(kv_addr, 16),
-                     v_lo0 = sw128_desc_lo(kv_addr, PANEL_BYTES);
-      auto issue_s = [&](int w, int slot) {           // S_w = Q_w K^T
-        const uint32_t qa = q_lo0 + w * (C::TILE_BYTES >> 4), ka = k_lo0 + slot * (C::TILE_BYTES >> 4);
-        const uint32_t d_tmem = tmem_base + C::S_COL + w * 128;
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = ((ks >> 2) * PANEL_BYTES + (ks & 3) * 32) >> 4;
-          umma_f16_ss_parts(d_tmem, qa + off, SW128_DESC_HI, ka + off, SW128_DESC_HI, C::IDESC_S, ks != 0 ? 1u : 0u);
-        }
-      };
-      auto issue_pv = [&](int w, int slot, bool first) {  // O_w += P_w V, P_w from tensor memory
-        const uint32_t va = v_lo0 + slot * (C::TILE_BYTES >> 4);
-        const uint32_t d_tmem = tmem_base + C::O_COL + w * D, p_tmem = tmem_base + C::S_COL + w * 128;
-#pragma unroll
-        for (int ks = 0; ks < BKEY / 16; ++ks)        // 16 keys = 8 packed-bf16 columns of P per step
-          umma_f16_ts_parts(d_tmem, p_tmem + ks * 8, va + ks * (2048 >> 4), SW128_DESC_HI, C::IDESC_PV,
-                            (first && ks == 0) ? 0u : 1u);
-      };
+    // The MMA warp.  Its own instruction time is the scarce resource: an issue costs the issuing
+    // thread 30 to 50 cycles (the lower figure when the whole warp runs the loop and one elected
+    // lane issues, as here) and a commit about 90, against 64 cycles of tensor-pipe time per
+    // 128x128x16 product.  So it commits only what nobody else can signal (scores ready, output
+    // ready); the K/V slots and the Q tiles are released by the weight warps, which learn of an
+    // MMA's completion through those same two barriers.  Serving the two query tiles in turn also
+    // keeps their weight groups half a step apart, so that one evaluates while the other's
+    // products run.
+    const uint32_t q_addr = smem_u32(smem + C::Q_OFF), kv_addr = smem_u32(smem + C::KV_OFF);
+    using Cur = RingCursor<C::NKV>;
+    Cur cur;                                        // the next K/V tile in ring order, over all items
+    int t0 = 0, t1 = 0;                             // score tiles of query tile 0 / 1 in earlier items
+    auto wait_all = [&](uint64_t* bar, uint32_t parity) { return __all_sync(0xffffffffu, bw.wait(bar, parity)) != 0; };
+    auto kv_wait = [&](const Cur& c) { return wait_all(&ctl->kv_full[c.slot], c.phase); };
+    // descriptor low halves: Q tiles and ring slot 0 as K (K-major, LBO 16) and as V (MN-major,
+    // LBO = one panel); a slot adds slot * TILE_BYTES / 16, a K step adds a constant
+    const uint32_t q_lo0 = sw128_desc_lo(q_addr, 16), k_lo0 = sw128_desc_lo(kv_addr, 16),
+                   v_lo0 = sw128_desc_lo(kv_addr, PANEL_BYTES);
 #ifdef ALG_ATTN_TIMING
-      const long long t_begin = clock64();
+    long long tm3 = 0;
+#define ALG_TI0 const long long ti_ = clock64();
+#define ALG_TI1 tm3 += clock64() - ti_;
+#else
+#define ALG_TI0
+#define ALG_TI1
 #endif
-      bool ok = true;
-      for (int k = 0; ok && item_at(p, k, it); ++k) {
-        const int n0 = it.n0, n1 = it.n1;
-        if (!bw.wait(&ctl->q_full[0], k & 1u) || !kv_wait(cur)) { ok = false; break; }
-        tc_fence_after();
-        issue_s(0, cur.slot); umma_commit(&ctl->s_full[0]);
-        if (n0 == 1) umma_commit(&ctl->q_free[0]);
-        if (!bw.wait(&ctl->q_full[1], k & 1u)) { ok = false; break; }
-        tc_fence_after();
-        issue_s(1, cur.slot); umma_commit(&ctl->s_full[1]);
-        umma_commit(&ctl->kv_empty[cur.slot]);
+    auto issue_s = [&](int w, int slot) {           // S_w = Q_w K^T
+      ALG_TI0
+      const uint32_t qa = q_lo0 + w * (C::TILE_BYTES >> 4), ka = k_lo0 + slot * (C::TILE_BYTES >> 4);
+      const uint32_t d_tmem = tmem_base + C::S_COL + w * 128;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const uint32_t off = ((ks >> 2) * PANEL_BYTES + (ks & 3) * 32) >> 4;
+        umma_f16_ss_parts(d_tmem, qa + off, SW128_DESC_HI, ka + off, SW128_DESC_HI, C::IDESC_S, ks != 0 ? 1u : 0u);
+      }
+      ALG_TI1
+    };
+    // O_w += P_w V for the first (h64 = 0) or second 64 keys of the tile, P_w from tensor memory
+    auto issue_pv = [&](int w, int slot, int h64, bool first) {
+      ALG_TI0
+      const uint32_t va = v_lo0 + slot * (C::TILE_BYTES >> 4);
+      const uint32_t d_tmem = tmem_base + C::O_COL + w * D, p_tmem = tmem_base + C::S_COL + w * 128;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {                 // 16 keys = 8 packed-bf16 columns of P per step
+        const int ks = 4 * h64 + i;
+        umma_f16_ts_parts(d_tmem, p_tmem + p_col_of(16 * ks), va + ks * (2048 >> 4), SW128_DESC_HI, C::IDESC_PV,
+                          (first && ks == 0) ? 0u : 1u);
+      }
+      ALG_TI1
+    };
+#ifdef ALG_ATTN_TIMING
+    const long long t_begin = clock64();
+#endif
+    bool ok = true;
+    for (int k = 0; ok && item_at(p, k, it); ++k) {
+      const int n0 = it.n0, n1 = it.n1;
+      if (!wait_all(&ctl->q_ready[0], k & 1u) || !kv_wait(cur)) { ok = false; break; }
+      tc_fence_after();
+      if (elect_one()) { issue_s(0, cur.slot); umma_commit(&ctl->s_full[0]); }
+      __syncwarp();
+      if (!wait_all(&ctl->q_ready[1], k & 1u)) { ok = false; break; }
+      tc_fence_after();
+      if (elect_one()) { issue_s(1, cur.slot); umma_commit(&ctl->s_full[1]); }
+      __syncwarp();
+      cur.next();
+      for (int j = 0; j < n1 && ok; ++j) {
+        const Cur vc = cur;                         // V_j
         cur.next();
-        for (int j = 0; j < n1 && ok; ++j) {
-          const Cur vc = cur;                         // V_j
-          cur.next();
-          const Cur kc = cur;                         // K_{j+1}: only meaningful while j + 1 < n1
-          if (j + 1 < n1) cur.next();
-          // Both tiles of this step are waited for up front (they are normally long there), so
-          // that nothing stands between "weights ready" and the issue of P.V and the next S.
-          if (!ALG_T(tm0, kv_wait(vc)) || (j + 1 < n1 && !ALG_T(tm0, kv_wait(kc)))) { ok = false; break; }
-          if (j < n0) {
-            if (!ALG_T(tm1, bw.wait(&ctl->p_full[0], (t0 + j) & 1u))) { ok = false; break; }
-            // the first product of an item overwrites O_0: the previous output must have been read
-            if (j == 0 && k > 0 && !bw.wait(&ctl->o_free[0], (k - 1) & 1u)) { ok = false; break; }
-            tc_fence_after();
-            issue_pv(0, vc.slot, j == 0);
-            if (j + 1 < n0) {
-              issue_s(0, kc.slot);                     // after P_0.V: may overwrite P_0
-              umma_commit(&ctl->s_full[0]);
-              if (j + 2 == n0) umma_commit(&ctl->q_free[0]);   // the item's last read of Q tile 0
-            } else {
-              umma_commit(&ctl->o_full[0]);
-            }
-          }
-          if (!ALG_T(tm2, bw.wait(&ctl->p_full[1], (t1 + j) & 1u))) { ok = false; break; }
-          if (j == 0 && k > 0 && !bw.wait(&ctl->o_free[1], (k - 1) & 1u)) { ok = false; break; }
+        const Cur kc = cur;                         // K_{j+1}: only meaningful while j + 1 < n1
+        if (j + 1 < n1) cur.next();
+        // Both tiles of this step are waited for up front (they are normally long there), so
+        // that nothing stands between "weights ready" and the issue of P.V and the next S.
+        if (!ALG_T(tm0, kv_wait(vc)) || (j + 1 < n1 && !ALG_T(tm0, kv_wait(kc)))) { ok = false; break; }
+        if (j < n0) {
+          if (!ALG_T(tm1, wait_all(&ctl->p_half[0], (t0 + j) & 1u))) { ok = false; break; }
+          // the first product of an item overwrites O_0: the previous output must have been read
+          if (j == 0 && k > 0 && !wait_all(&ctl->o_free[0], (k - 1) & 1u)) { ok = false; break; }
           tc_fence_after();
-          issue_pv(1, vc.slot, j == 0);
-          umma_commit(&ctl->kv_empty[vc.slot]);
-          if (j + 1 < n1) {
-            issue_s(1, kc.slot);
-            umma_commit(&ctl->s_full[1]);
-            umma_commit(&ctl->kv_empty[kc.slot]);
-            if (j + 2 == n1) umma_commit(&ctl->q_free[1]);     // the item's last read of Q tile 1
-          } else {
-            umma_commit(&ctl->o_full[1]);
+          if (elect_one()) issue_pv(0, vc.slot, 0, j == 0);
+          __syncwarp();
+          if (!ALG_T(tm1, wait_all(&ctl->p_full[0], (t0 + j) & 1u))) { ok = false; break; }
+          tc_fence_after();
+          if (elect_one()) {
+            issue_pv(0, vc.slot, 1, false);
+            if (j + 1 < n0) { issue_s(0, kc.slot); umma_commit(&ctl->s_full[0]); }   // after P_0.V: may overwrite P_0
+            else umma_commit(&ctl->o_full[0]);
           }
+          __syncwarp();
         }
-        t0 += n0; t1 += n1;
+        if (!ALG_T(tm2, wait_all(&ctl->p_half[1], (t1 + j) & 1u))) { ok = false; break; }
+        if (j == 0 && k > 0 && !wait_all(&ctl->o_free[1], (k - 1) & 1u)) { ok = false; break; }
+        tc_fence_after();
+        if (elect_one()) issue_pv(1, vc.slot, 0, j == 0);
+        __syncwarp();
+        if (!ALG_T(tm2, wait_all(&ctl->p_full[1], (t1 + j) & 1u))) { ok = false; break; }
+        tc_fence_after();
+        if (elect_one()) {
+          issue_pv(1, vc.slot, 1, false);
+          if (j + 1 < n1) { issue_s(1, kc.slot); umma_commit(&ctl->s_full[1]); }
+          else umma_commit(&ctl->o_full[1]);
+        }
+        __syncwarp();
       }
+      t0 += n0; t1 += n1;
+    }
 #ifdef ALG_ATTN_TIMING
-      if (blockIdx.x == 0 && p.stat != nullptr) {
-        float* dbg = p.stat + 16;
-        dbg[0] = float(tm0); dbg[1] = float(tm1); dbg[2] = float(tm2); dbg[3] = float(clock64() - t_begin);
-      }
+    if (blockIdx.x == 0 && lane == 0 && p.stat != nullptr) {
+      float* dbg = p.stat + 16;
+      dbg[0] = float(tm0); dbg[1] = float(tm1); dbg[2] = float(tm2); dbg[3] = float(clock64() - t_begin); dbg[4] = float(tm3);
+    }
 #endif
+  } else if (warp < FIRST_WEIGHT_WARP) {
+    // Q scalers (warp 2: tile 0, warp 3: tile 1): once a Q tile has landed, multiply it by 2^e
+    // where it lies (element-wise, so the swizzled layout does not matter), make the result
+    // visible to the tensor core's reads and release the tile to the MMA warp.
+    const int w = warp - 2;
+    const __nv_bfloat162 f2 = __float2bfloat162_rn(sc.pow2);
+    uint4* tile = reinterpret_cast<uint4*>(smem + C::Q_OFF + w * C::TILE_BYTES);
+    bool ok = true;
+    for (int k = 0; ok && item_at(p, k, it); ++k) {
+      if (!bw.wait(&ctl->q_full[w], k & 1u)) { ok = false; break; }
+      if (sc.pow2 != 1.0f) {
+#pragma unroll 4
+        for (int i = lane; i < C::TILE_BYTES / 16; i += 32) {
+          uint4 v = tile[i];
+          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+          h[0] = __hmul2(h[0], f2); h[1] = __hmul2(h[1], f2); h[2] = __hmul2(h[2], f2); h[3] = __hmul2(h[3], f2);
+          tile[i] = v;
+        }
+        fence_async_shared();
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->q_ready[w]);
     }
   } else {
-    const int w = (warp - 2) >> 2;                  // query tile of this weight group
+    const int ww = warp - FIRST_WEIGHT_WARP;
+    const int w = ww / (4 * SPLIT);                 // query tile of this weight group
+    const int half = (ww >> 2) & (SPLIT - 1);       // which 32-column blocks (split groups)
     const int quarter = warp & 3;                   // TMEM lanes 32*quarter.. are this warp's
     const int r = quarter * 32 + lane;              // row inside the query tile
     const uint32_t lane_sel = uint32_t(quarter * 32) << 16;
     const uint32_t s_taddr = tmem_base + lane_sel + C::S_COL + w * 128;
     bool ok = true;
     int tiles_before = 0;                           // score tiles of this group in earlier items
+    // One thread per group passes on what the arrival of scores implies.  The tensor pipe runs the
+    // MMA thread's instructions in order, so "S_w(j) is there" means every product issued before it
+    // has finished reading its operands: for query tile 1 (served second in every step) that is all
+    // of step j - 1, hence V_{j-1} and K_j can be overwritten; for either tile, the last scores of
+    // an item mean its Q tile can be.  The releasing thread walks the K/V ring in load order.
+    const bool releaser = (ww % (4 * SPLIT)) == 0 && lane == 0;
+    RingCursor<C::NKV> rel;
 #ifdef ALG_ATTN_TIMING
     const long long t_begin = clock64();
 #endif
     for (int k = 0; ok && item_at(p, k, it); ++k) {
       const int nk = (w == 0) ? it.n0 : it.n1;
       float l = 0.f;                                // the sink's weight, fetched while the first scores are computed
-      if (p.sink != nullptr) l = pow2n<LOG2N>(rho_stable(p.sink[it.h] * p.inv_c));
+      if (p.sink != nullptr) l = pow2n<LOG2N>(rho_stable(p.sink[it.h] * p.inv_c)) * sc.inv_mn;
       float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
       for (int j = 0; j < nk && ok; ++j) {
         if (!ALG_T(tm0, bw.wait(&ctl->s_full[w], (tiles_before + j) & 1u))) { ok = false; break; }
         tc_fence_after();
+        if (releaser) {
+          if (w == 1) {
+            if (j > 0) { mbar_arrive(&ctl->kv_empty[rel.slot]); rel.next(); }    // V_{j-1}
+            mbar_arrive(&ctl->kv_empty[rel.slot]); rel.next();                   // K_j
+          }
+          if (j == nk - 1) mbar_arrive(&ctl->q_free[w]);
+        }
 #ifdef ALG_ATTN_TIMING
         const long long tc0 = clock64();
 #endif
-        if (j == nk - 1) weigh_tile<LOG2N, true>(s_taddr, r, p.scale, la, lb);   // diagonal tile: masked
-        else weigh_tile<LOG2N, false>(s_taddr, r, p.scale, la, lb);
-        tc_fence_before();
-        mbar_arrive(&ctl->p_full[w]);
+        if (SPLIT == 2) {
+          if (j == nk - 1) weigh_half_tile<LOG2N, true>(s_taddr, half, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);   // diagonal tile: masked
+          else weigh_half_tile<LOG2N, false>(s_taddr, half, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
+        } else {
+          if (j == nk - 1) weigh_tile<LOG2N, true>(s_taddr, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
+          else weigh_tile<LOG2N, false>(s_taddr, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
+        }
 #ifdef ALG_ATTN_TIMING
         tm1 += clock64() - tc0;
 #endif
       }
       tiles_before += nk;
+      float part = (la.x + la.y) + (lb.x + lb.y);
+      if (SPLIT == 2 && half == 1) {                // row sums of the two column halves meet in shared memory:
+        ctl->row_sum[w][r] = part;                  // half 1 hands its partial to half 0 ...
+        mbar_arrive(&ctl->l_part[w]);
+      }
       if (!ok || !bw.wait(&ctl->o_full[w], k & 1u)) { ok = false; break; }
+      if (releaser && w == 1) { mbar_arrive(&ctl->kv_empty[rel.slot]); rel.next(); }   // the item's last V tile
+      if (SPLIT == 2) {
+        if (half == 0) {                            // ... which returns the row's total through the same word
+          if (!bw.wait(&ctl->l_part[w], k & 1u)) { ok = false; break; }
+          part += ctl->row_sum[w][r];
+          ctl->row_sum[w][r] = part;
+          mbar_arrive(&ctl->l_total[w]);
+        } else {
+          if (!bw.wait(&ctl->l_total[w], k & 1u)) { ok = false; break; }
+          part = ctl->row_sum[w][r];
+        }
+      }
       tc_fence_after();
       item_at(p, k, it);                            // recomputed: nothing of it stays live over the tile loop
-      l += (la.x + la.y) + (lb.x + lb.y);
+      l += part;
       const float inv = 1.0f / l;
       const int row = it.row0 + w * BQ + r;
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + it.b * p.os.b + it.h * p.os.h + int64_t(row) * p.os.t;
+      constexpr int CHUNKS = D / 32 / SPLIT;         // a split group divides the output columns as well
 #pragma unroll 1
-      for (int chunk = 0; chunk < D / 32; ++chunk) {
+      for (int chunk = half * CHUNKS; chunk < (half + 1) * CHUNKS; ++chunk) {
         uint32_t o[32];
         tmem_ld_32x32(tmem_base + lane_sel + C::O_COL + w * D + chunk * 32, o);
         tmem_ld_wait_for(o);
-        if (chunk == D / 32 - 1) {                  // O_w is in registers: the next item may overwrite it
+        if (chunk == (half + 1) * CHUNKS - 1) {     // O_w is in registers: the next item may overwrite it
           tc_fence_before();
           mbar_arrive(&ctl->o_free[w]);
         }
@@ -366,11 +539,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
 #ifndef ALG_ATTN_TIMING
-      if (p.stat != nullptr) p.stat[(int64_t(it.b) * p.H + it.h) * p.Tq + row] = inv;
+      // 1 / l of the reference = 1 / (l' m^n)
+      if (p.stat != nullptr && half == 0) p.stat[(int64_t(it.b) * p.H + it.h) * p.Tq + row] = inv * sc.inv_mn;
 #endif
     }
 #ifdef ALG_ATTN_TIMING
-    if (blockIdx.x == 0 && r == 0 && p.stat != nullptr) {
+    if (blockIdx.x == 0 && r == 0 && half == 0 && p.stat != nullptr) {
       float* dbg = p.stat + 8 * w;
       dbg[0] = float(tm0); dbg[1] = 0.f; dbg[2] = float(tm1); dbg[3] = float(clock64() - t_begin); dbg[4] = float(tiles_before);
     }
@@ -401,27 +575,43 @@ int make_qkv_map(CUtensorMap* tm, const void* base, const Strides3& s, int B, in
   return make_tmap_bf16(tm, base, 4, dims, strides, box, true);
 }
 
-template <int D, int LOG2N>
-int launch_dn(const AttnParams& p, cudaStream_t stream) {
+template <int D, int LOG2N, int SPLIT>
+int launch_dns(const AttnParams& p, cudaStream_t stream) {
   CUtensorMap tq, tk, tv;
   if (int rc = make_qkv_map(&tq, p.q, p.qs, p.B, p.H, p.Tq, D)) return rc;
   if (int rc = make_qkv_map(&tk, p.k, p.ks, p.B, p.H, p.Tk, D)) return rc;
   if (int rc = make_qkv_map(&tv, p.v, p.vs, p.B, p.H, p.Tk, D)) return rc;
-  auto kern = attn_tc_kernel<D, LOG2N>;
-  static bool configured = false;
-  if (!configured) {
-    ALG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes<D>())));
-    configured = true;
+  // 1 / (sqrt(D) c) = 2^e m with 1 <= m < 2
+  ScaleSplit sc;
+  {
+    int ex = 0;
+    const double f = frexp(double(p.scale), &ex);         // scale = f 2^ex, 0.5 <= f < 1
+    const double m = 2.0 * f;
+    sc.pow2 = float(ldexp(1.0, ex - 1));
+    sc.kappa = float(1.0 / (m * m));
+    sc.inv_mn = float(pow(m, -double(1 << LOG2N)));
   }
-  int dev = 0, sms = 148;
-  ALG_CUDA_TRY(cudaGetDevice(&dev));
-  ALG_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  auto kern = attn_tc_kernel<D, LOG2N, SPLIT>;
+  static PerDeviceOnce configured;
+  int sms = 0;
+  if (int rc = configured.run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes<D>())); }, &sms)) return rc;
   const int items = p.B * p.H * (p.Tq / (2 * BQ));
   const int grid = items < sms ? items : sms;
-  kern<<<grid, NTHREADS, smem_bytes<D>(), stream>>>(tq, tk, tv, p);
+  kern<<<grid, nthreads<SPLIT>(), smem_bytes<D>(), stream>>>(tq, tk, tv, p, sc);
   ALG_CUDA_TRY(cudaGetLastError());
   count_launch();
   return ALG_OK;
+}
+
+// How many warps weigh a score tile.  Four (one per tensor-memory quarter) are fastest at head_dim
+// 128, where the tensor pipe has as much to do per tile as the weight warps; eight (two per
+// quarter, half the key columns each) are 10 to 14 % faster at head_dim 64, where the weights
+// dominate.  ALG_ATTN_SPLIT = 1 or 2 in the environment overrides the choice (measurement aid).
+template <int D, int LOG2N>
+int launch_dn(const AttnParams& p, cudaStream_t stream) {
+  static const int forced = [] { const char* e = getenv("ALG_ATTN_SPLIT"); return e != nullptr ? atoi(e) : 0; }();
+  const int split = forced == 1 || forced == 2 ? forced : (D == 64 ? 2 : 1);
+  return split == 1 ? launch_dns<D, LOG2N, 1>(p, stream) : launch_dns<D, LOG2N, 2>(p, stream);
 }
 
 template <int D>

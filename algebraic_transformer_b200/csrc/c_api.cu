@@ -28,6 +28,24 @@ int cuda_fail(cudaError_t e, const char* what) {
   return ALG_ERR_CUDA;
 }
 
+int sm_count() {
+  static std::atomic<int> cached[PerDeviceOnce::kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= PerDeviceOnce::kMaxDevices) {
+    cudaGetLastError();
+    return 148;
+  }
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      return 148;
+    }
+    cached[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
+
 static std::atomic<unsigned long long> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 

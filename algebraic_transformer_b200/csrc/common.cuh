@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/alg_b200.h"
 
 namespace alg {
@@ -21,6 +23,35 @@ void count_launch(int n = 1);   // bumps the process-wide kernel-launch counter 
     cudaError_t _e = (expr);                                   \
     if (_e != cudaSuccess) return ::alg::cuda_fail(_e, #expr); \
   } while (0)
+
+// Number of SMs of the current device (cached per device ordinal).  Grids and split counts are
+// sized from it; 148 (B200) stands in when no device can be queried, which only happens when a
+// workspace-size function is called on a machine without a GPU.
+int sm_count();
+
+// One-time per-DEVICE set-up of a kernel: function attributes such as the dynamic shared-memory
+// opt-in belong to the device that was current when they were set, so a process that drives
+// several GPUs has to repeat them on each.  `run` performs `setup` once for the current device
+// and reports that device's SM count.
+struct PerDeviceOnce {
+  static constexpr int kMaxDevices = 64;
+  std::atomic<int> done[kMaxDevices];
+  template <class F>
+  int run(F&& setup, int* sms = nullptr) {
+    int dev = 0;
+    ALG_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) {
+      set_error("device ordinal %d is outside the supported range [0, %d)", dev, kMaxDevices);
+      return ALG_ERR_UNSUPPORTED;
+    }
+    if (done[dev].load(std::memory_order_acquire) == 0) {   // idempotent: a race repeats it harmlessly
+      ALG_CUDA_TRY(setup());
+      done[dev].store(1, std::memory_order_release);
+    }
+    if (sms != nullptr) *sms = sm_count();
+    return ALG_OK;
+  }
+};
 
 struct Strides3 {
   int64_t b, h, t;

@@ -250,11 +250,8 @@ int launch_d(const DecodeParams& p, cudaStream_t stream) {
   if (int rc = make_kv_map(&tk, p.k, p.ks, p.B, p.H, p.Tk, D)) return rc;
   if (int rc = make_kv_map(&tv, p.v, p.vs, p.B, p.H, p.Tk, D)) return rc;
   auto kern = decode_partial_kernel<D>;
-  static bool configured = false;
-  if (!configured) {
-    ALG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(decode_smem<D>())));
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  if (int rc = configured.run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(decode_smem<D>())); })) return rc;
   kern<<<dim3(p.splits, p.H, p.B), NTHREADS, decode_smem<D>(), stream>>>(tk, tv, p);
   ALG_CUDA_TRY(cudaGetLastError());
   decode_combine_kernel<D><<<p.B * p.H, D, 0, stream>>>(p);
@@ -265,13 +262,13 @@ int launch_d(const DecodeParams& p, cudaStream_t stream) {
 
 }  // namespace
 
-// Splits are whole 64-key tiles.  The grid is ONE wave: at most two CTAs per SM on 148 SMs (a
+// Splits are whole 64-key tiles.  The grid is ONE wave: at most two CTAs per SM (a
 // second wave would pay the ring's start-up latency again: 62 -> 56 us on a 32768-key cache),
 // never more splits than the combine kernel's table.
 int decode_splits(int B, int H, int Tk) {
   const int bh = B * H > 0 ? B * H : 1;
   const int tiles = (Tk + TILE - 1) / TILE;
-  int s = (148 * 2) / bh;
+  int s = (sm_count() * 2) / bh;
   if (s > tiles) s = tiles;
   if (s > MAX_SPLITS) s = MAX_SPLITS;
   if (s < 1) s = 1;

@@ -240,7 +240,7 @@ __global__ void __launch_bounds__(FIN_THREADS) head_finalize_kernel(
 int head_mma_splits(int N, int V_local) {
   const int row_blocks = (N + BM - 1) / BM;
   const int ntiles = (V_local + BN - 1) / BN;
-  int s = (2 * 148 + row_blocks - 1) / (row_blocks > 0 ? row_blocks : 1);
+  int s = (2 * sm_count() + row_blocks - 1) / (row_blocks > 0 ? row_blocks : 1);
   if (s > ntiles) s = ntiles;
   if (s > 64) s = 64;
   return s < 1 ? 1 : s;
@@ -255,11 +255,8 @@ int launch_head_mma(const HeadParams& p, cudaStream_t stream) {
     set_error("head (legacy MMA path): d must be a multiple of %d, got %d", BK, p.d);
     return ALG_ERR_UNSUPPORTED;
   }
-  static bool configured = false;
-  if (!configured) {
-    ALG_CUDA_TRY(cudaFuncSetAttribute(head_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * STAGE_BYTES));
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  if (int rc = configured.run([&] { return cudaFuncSetAttribute(head_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * STAGE_BYTES); })) return rc;
   dim3 grid((p.N + BM - 1) / BM, p.splits);
   head_mma_kernel<<<grid, NTHREADS, 2 * STAGE_BYTES, stream>>>(p);
   ALG_CUDA_TRY(cudaGetLastError());

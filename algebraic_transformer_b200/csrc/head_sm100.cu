@@ -45,7 +45,7 @@ Plan make_plan(int N, int V_local) {
   pl.row_blocks = (N + BM - 1) / BM;
   pl.ntiles = (V_local + BN - 1) / BN;
   const long long total = (long long)pl.row_blocks * pl.ntiles;
-  long long tps = total / (148 * 8);
+  long long tps = total / (sm_count() * 8);
   if (tps < 1) tps = 1;
   if (tps > 8) tps = 8;
   pl.tps = int(tps);
@@ -246,11 +246,8 @@ template <int LOG2N>
 int launch_log2n(const CUtensorMap& tm_h, const CUtensorMap& tm_e, const HeadParams& p, const Plan& pl, int grid,
                  cudaStream_t stream) {
   auto kern = head_tc_kernel<LOG2N>;
-  static bool configured = false;
-  if (!configured) {
-    ALG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES)));
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  if (int rc = configured.run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES)); })) return rc;
   kern<<<grid, NTHREADS, SMEM_BYTES, stream>>>(tm_h, tm_e, p, pl.S, pl.tps, pl.units, pl.row_blocks);
   ALG_CUDA_TRY(cudaGetLastError());
   count_launch();
@@ -283,9 +280,7 @@ int launch_head_tcgen05(const HeadParams& p, cudaStream_t stream) {
     const uint32_t box[2] = {BK, BN};
     if (int rc = make_tmap_bf16(&tm_e, p.e, 2, dims, strides, box, true)) return rc;
   }
-  int dev = 0, sms = 148;
-  ALG_CUDA_TRY(cudaGetDevice(&dev));
-  ALG_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int sms = sm_count();
   const int grid = pl.units < sms ? pl.units : sms;
   if (p.kind == ALG_HEAD_CE) return launch_log2n<LOG2N_CE>(tm_h, tm_e, p, pl, grid, stream);
   switch (p.log2n) {

@@ -120,7 +120,7 @@ int launch_rms_rows(const void* x, const float* gain, void* y, int64_t rows, int
   const int vpl = (d / 8 + 31) / 32;
   constexpr int RPW = 4;                               // rows per warp step (<= 4 x 4 vectors per lane in flight)
   int64_t blocks = (rows + 8 * RPW - 1) / (8 * RPW);
-  if (blocks > 148 * 6) blocks = 148 * 6;
+  if (blocks > sm_count() * 6) blocks = sm_count() * 6;
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
   __nv_bfloat16* yp = static_cast<__nv_bfloat16*>(y);
   if ((reinterpret_cast<uintptr_t>(gain) & 15) != 0) {
@@ -148,7 +148,7 @@ int launch_alu_glu(const void* gate, const void* up, void* out, int64_t rows, in
   if (rows == 0 || f == 0) return ALG_OK;
   const size_t nvec = size_t(rows) * (f / 8);
   size_t blocks = (nvec + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > size_t(sm_count()) * 16) blocks = size_t(sm_count()) * 16;
   alu_glu_kernel<<<unsigned(blocks), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate),
                                                        static_cast<const __nv_bfloat16*>(up),
                                                        static_cast<__nv_bfloat16*>(out), rows, f, ld_in, ld_out, beta);

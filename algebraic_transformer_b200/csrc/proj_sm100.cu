@@ -456,11 +456,8 @@ proj_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
 template <int EPI, int D>
 int launch_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const ProjParams& p, int grid, cudaStream_t stream) {
   auto kern = proj_tc_kernel<EPI, D>;
-  static bool configured = false;
-  if (!configured) {
-    ALG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES)));
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  if (int rc = configured.run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES)); })) return rc;
   kern<<<grid, NTHREADS, SMEM_BYTES, stream>>>(tm_x, tm_w, p);
   ALG_CUDA_TRY(cudaGetLastError());
   count_launch();
@@ -484,9 +481,7 @@ int launch_proj(const ProjParams& p, const void* x, const void* w, int epi, cuda
     const uint32_t box[2] = {BK, BN};
     if (int rc = make_tmap_bf16(&tm_w, w, 2, dims, strides, box, true)) return rc;
   }
-  int dev = 0, sms = 148;
-  ALG_CUDA_TRY(cudaGetDevice(&dev));
-  ALG_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int sms = sm_count();
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
   if (epi == 1) return launch_variant<EPI_GLU, 64>(tm_x, tm_w, p, grid, stream);

@@ -232,7 +232,7 @@ static int launch_t(const PrepBatch& batch, cudaStream_t stream) {
   // resident CTAs only (the grid-stride loop covers the rest): 4 per SM for the
   // statistics-only mode, 3 for the others, per tensor of the launch (sharing one wave among
   // the tensors measured slightly slower)
-  const int64_t cap = 148 * (mode == 0 ? 4 : 3);
+  const int64_t cap = int64_t(sm_count()) * (mode == 0 ? 4 : 3);
   if (blocks > cap) blocks = cap;
   const dim3 grid(unsigned(blocks), unsigned(batch.count));
   if (mode == 0) qk_prep_kernel<T, D, 0><<<grid, threads, 0, stream>>>(batch);
@@ -275,7 +275,7 @@ int launch_prep(const PrepParams& p, int dtype, cudaStream_t stream) {
 // The reference reduces the gain gradient in row blocks and sums the block partials afterwards
 // (qk_norm.py:47-56); here every CTA writes one partial row and a second kernel adds the rows in
 // block order, so the result does not depend on scheduling.  Same lane layout as the forward pass.
-constexpr int RMS_BWD_BLOCKS = 148 * 4;
+constexpr int RMS_BWD_BLOCKS = 1024;    // rows of scratch: an upper bound on the CTAs of one launch
 int rms_bwd_max_blocks() { return RMS_BWD_BLOCKS; }
 
 template <typename T, int D>
@@ -377,7 +377,9 @@ static int launch_rms_bwd_t(const RmsBwdParams& p, cudaStream_t stream) {
     return ALG_OK;
   }
   int64_t blocks = ((rows + RPW - 1) / RPW + 7) / 8;
-  if (blocks > 148 * 3) blocks = 148 * 3;               // one resident wave: three CTAs per SM (<= RMS_BWD_BLOCKS rows of scratch)
+  const int64_t wave = int64_t(sm_count()) * 3;         // one resident wave: three CTAs per SM
+  if (blocks > wave) blocks = wave;
+  if (blocks > RMS_BWD_BLOCKS) blocks = RMS_BWD_BLOCKS;
   qk_rms_bwd_kernel<T, D><<<unsigned(blocks), 256, 0, stream>>>(p);
   ALG_CUDA_TRY(cudaGetLastError());
   count_launch();
@@ -421,7 +423,7 @@ __global__ void cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat1
 int launch_cast(const float* src, void* dst, size_t count, cudaStream_t stream) {
   if (count == 0) return ALG_OK;
   size_t blocks = (count / 8 + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > size_t(sm_count()) * 16) blocks = size_t(sm_count()) * 16;
   if (blocks == 0) blocks = 1;
   cast_f32_bf16_kernel<<<unsigned(blocks), 256, 0, stream>>>(src, reinterpret_cast<__nv_bfloat16*>(dst), count);
   ALG_CUDA_TRY(cudaGetLastError());

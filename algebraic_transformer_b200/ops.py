@@ -11,6 +11,7 @@ streams here.  Every op runs a hand-written sm_100a kernel from
 raised as `ValueError` where the reference raises them.
 """
 
+import functools
 import math
 from typing import Optional
 
@@ -44,6 +45,28 @@ def _require_cuda(*tensors):
     for t in tensors:
         if t is not None and not t.is_cuda:
             raise ValueError("algebraic_transformer_b200 ops need CUDA tensors (there is no CPU path)")
+
+
+def _on_tensor_device(fn):
+    """Every op launches on the device that holds its tensors, on that device's current stream.
+    All tensor arguments must sit on one device (ValueError otherwise): the C side builds TMA maps
+    and launches on the current device, so a tensor from another GPU would be addressed from the
+    wrong one.  When the tensors' device is not the current one, the call runs under
+    `torch.cuda.device(...)`."""
+    @functools.wraps(fn)
+    def call(*args, **kwargs):
+        dev = None
+        for a in list(args) + list(kwargs.values()):
+            if isinstance(a, torch.Tensor) and a.device.type == "cuda":
+                if dev is None:
+                    dev = a.device
+                elif a.device != dev:
+                    raise ValueError(f"{fn.__name__}: tensors on different devices ({dev} and {a.device})")
+        if dev is None or dev.index == torch.cuda.current_device():
+            return fn(*args, **kwargs)
+        with torch.cuda.device(dev):
+            return fn(*args, **kwargs)
+    return call
 
 
 def _strides3(t: torch.Tensor):
@@ -107,6 +130,7 @@ def cayley_table_geometric(head_dim: int, seq_len: int, base: float = 10000.0, w
 
 # --------------------------------------------------------------------------- qk_rms
 
+@_on_tensor_device
 def qk_rms_norm(x: torch.Tensor, gain: Optional[torch.Tensor], eps: float = 1e-5, *, block: int = 1024,
                 cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -138,6 +162,7 @@ def qk_rms_norm(x: torch.Tensor, gain: Optional[torch.Tensor], eps: float = 1e-5
     return y.view(x.shape)
 
 
+@_on_tensor_device
 def qk_rms_norm_backward(x: torch.Tensor, gain: Optional[torch.Tensor], dy: torch.Tensor, eps: float = 1e-5):
     """`(dx, dgain)` of `qk_rms_norm(x, gain, eps)` (no rotation) for the output gradient `dy`: what
     the reference's custom VJP returns (src/algebraic/kernels/qk_norm.py:29-56) — the autodiff input
@@ -169,6 +194,7 @@ def qk_rms_norm_backward(x: torch.Tensor, gain: Optional[torch.Tensor], dy: torc
     return (dx if x.ndim == 4 else dx.view(x.shape)), dgain
 
 
+@_on_tensor_device
 def rms_norm(x: torch.Tensor, gain: Optional[torch.Tensor], eps: float = 1e-5, out=None) -> torch.Tensor:
     """RMS normalisation over the last axis of a contiguous bf16 tensor (the model's `_norm`,
     src/algebraic/model.py:141-143): fp32 math, one rounding to bf16."""
@@ -182,6 +208,7 @@ def rms_norm(x: torch.Tensor, gain: Optional[torch.Tensor], eps: float = 1e-5, o
     return y
 
 
+@_on_tensor_device
 def alu_glu(gate: torch.Tensor, up: torch.Tensor, beta: float = 0.5, out=None) -> torch.Tensor:
     """gate * alu(up, beta), the ALU-GLU gating of the feed-forward block
     (src/algebraic/model.py:184-193, src/algebraic/algebraic.py:86-105)."""
@@ -197,6 +224,7 @@ def alu_glu(gate: torch.Tensor, up: torch.Tensor, beta: float = 0.5, out=None) -
     return y
 
 
+@_on_tensor_device
 def qkv_projection(x: torch.Tensor, w: torch.Tensor, n_heads: int, seq_len: int, cos: torch.Tensor,
                    sin: torch.Tensor, q_gain: Optional[torch.Tensor] = None, k_gain: Optional[torch.Tensor] = None,
                    eps: float = 1e-5, attn_c: float = 8.0, guard_words: Optional[torch.Tensor] = None,
@@ -242,6 +270,7 @@ def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor
     return torch.stack([w_gate.reshape(f // 128, 128, d), w_up.reshape(f // 128, 128, d)], dim=1).reshape(2 * f, d).contiguous()
 
 
+@_on_tensor_device
 def glu_projection(x: torch.Tensor, w: torch.Tensor, beta: float = 0.5, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """gate * alu(up, beta) with gate = x @ w_g and up = x @ w_u computed by the same kernel
     (src/algebraic/model.py:184-193); `w` comes from `interleave_gate_up`.  x: (M, d) bf16."""
@@ -267,6 +296,7 @@ def flash_clamp(seq_len: int, n: int) -> float:
     return 0.5 * (t - 1.0 / t)
 
 
+@_on_tensor_device
 def flash_attention(q, k, v, sink_logit=None, *, kind: str = "softmax", n: int = 16, c: float = 16.0,
                     block: int = 512, block_q: Optional[int] = None, block_k: Optional[int] = None,
                     shift: Optional[bool] = None, fast_rho: Optional[bool] = None,
@@ -362,6 +392,7 @@ def flash_attention(q, k, v, sink_logit=None, *, kind: str = "softmax", n: int =
     return o
 
 
+@_on_tensor_device
 def flash_attention_backward(q, k, v, o, d_o, stat, stat_kind, sink_logit=None, *, n: int = 16, c: float = 8.0,
                              causal: bool = True, impl: str = "auto"):
     """Gradients of `flash_attention(kind="asinh", return_stat=True)`: `(dq, dk, dv, dsink)` from the
@@ -412,6 +443,7 @@ def _attention_unshifted_unclamped(q, k, v, sink_logit=None, *, n=16, c=8.0, imp
                            impl=impl, out=out)
 
 
+@_on_tensor_device
 def decode_attention(q, k, v, sink_logit=None, *, n: int = 16, c: float = 8.0, out=None):
     """One query per (batch, head) against a (B,H,Tk,D) bf16 KV cache, every key visible.
     The reference has no decode kernel; semantics follow its dense weights with an all-true
@@ -442,6 +474,7 @@ def decode_attention(q, k, v, sink_logit=None, *, n: int = 16, c: float = 8.0, o
 
 # ----------------------------------------------------------------------------- head
 
+@_on_tensor_device
 def cast_embedding(embed: torch.Tensor) -> torch.Tensor:
     """fp32 (V,d) -> bf16 with the library's cast kernel (the reference casts per call)."""
     _require_cuda(embed)
@@ -453,6 +486,7 @@ def cast_embedding(embed: torch.Tensor) -> torch.Tensor:
     return out
 
 
+@_on_tensor_device
 def head_statistic(h, e_bf16, targets, *, n: int = 16, c: float = 16.0, vocab_offset: int = 0,
                    vocab_total: Optional[int] = None, impl: str = "auto", out=None, kind: str = "alg_ce"):
     """Per-row (l, zt) of one vocabulary shard as a (2, N) fp32 tensor: row 0 the partial
@@ -477,6 +511,7 @@ def head_statistic(h, e_bf16, targets, *, n: int = 16, c: float = 16.0, vocab_of
     return stats
 
 
+@_on_tensor_device
 def head_statistic_no_alloc(h, e_bf16, targets, out, *, n: int, c: float, vocab_offset: int = 0,
                             vocab_total: Optional[int] = None, impl: str = "auto"):
     """`head_statistic` through `alg_head_fwd_static`: the same (2, N) statistic, written
@@ -492,6 +527,7 @@ def head_statistic_no_alloc(h, e_bf16, targets, out, *, n: int, c: float, vocab_
     return out
 
 
+@_on_tensor_device
 def head_finalize(stats, *, n: int = 16, c: float = 16.0, vocab_total: int = 0, want_nll: bool = False,
                   kind: str = "alg_ce"):
     """(objective, p_target[, nll]) from the (all-reduced) (2, N) statistic.  `kind="ce"`: row 0
@@ -513,6 +549,7 @@ def head_finalize(stats, *, n: int = 16, c: float = 16.0, vocab_total: int = 0, 
     return (obj, pt, nll) if want_nll else (obj, pt)
 
 
+@_on_tensor_device
 def fused_head(h, embed, targets, *, kind: str = "ce", n: int = 16, c: float = 16.0, block_n: int = 128,
                block_v: int = 512, vocab_offset: int = 0, vocab_total: Optional[int] = None,
                group=None, want_nll: bool = False, impl: str = "auto", exchange=None):
@@ -572,6 +609,7 @@ def combine_ce_statistics(stats, group):
     return stats
 
 
+@_on_tensor_device
 def fused_head_backward(h, e_bf16, targets, stats, *, n: int = 8, c: float = 2.0, vocab_offset: int = 0,
                         vocab_total: Optional[int] = None, upstream: float = 1.0, kind: str = "alg_ce"):
     """What the reference's custom VJP of the Alg-CE head returns for the hidden states and this
@@ -606,6 +644,7 @@ def fused_head_backward(h, e_bf16, targets, stats, *, n: int = 8, c: float = 2.0
     return torch.mm(dz, e_bf16), torch.mm(dz.t(), h)
 
 
+@_on_tensor_device
 def _fused_head_exchange(h, e_bf16, targets, exchange, *, n, c, vocab_offset, vocab_total, want_nll, impl):
     """`alg_head_fwd_exchange`: see include/alg_b200.h.  `exchange` is a dist.HeadExchange."""
     N, d = h.shape

@@ -13,17 +13,19 @@ from . import algebraic_ref as R
 
 
 def _mm(a, w):
-    """bf16 x bf16 -> fp32 accumulate -> bf16 (model.py:167-169, 183, 186-187, 193)."""
-    return (a.float() @ w.bfloat16().float()).bfloat16()
+    """The activations' dtype x the weight cast to it -> fp32 accumulate -> that dtype
+    (model.py:167-169, 183, 186-187, 193)."""
+    return (a.float() @ w.to(a.dtype).float()).to(a.dtype)
 
 
-def forward_hidden(params, tokens, cfg):
-    """model.forward_hidden (model.py:196-208) + model._block (model.py:162-193)."""
+def forward_hidden(params, tokens, cfg, dtype=torch.bfloat16):
+    """model.forward_hidden (model.py:196-208) + model._block (model.py:162-193).
+    `dtype` is the reference's `cfg.dtype` (bfloat16 in every preset)."""
     B, T = tokens.shape
     d, H = cfg.d_model, cfg.n_heads
     D = d // H
     cos, sin = R.cayley_table_geometric(D, T, cfg.rope_base)
-    x = params["embed"][tokens].bfloat16()
+    x = params["embed"][tokens].to(dtype)
     x = R.rms_norm(x, params["embed_gain"], cfg.eps)
     for l in range(cfg.n_layers):
         h = R.rms_norm(x, params["ln1"][l], cfg.eps)
@@ -34,12 +36,12 @@ def forward_hidden(params, tokens, cfg):
         k = R.apply_rotary(R.rms_norm(k, params["k_gain"][l], cfg.eps), cos, sin)
         a = R.asinh_attention(q, k, v, n=cfg.attn_n, c=cfg.attn_c, sink_logit=params["sink"][l])
         a = a.transpose(1, 2).reshape(B, T, d)
-        x = (x.float() + _mm(a, params["w_o"][l]).float()).bfloat16()
+        x = (x.float() + _mm(a, params["w_o"][l]).float()).to(dtype)
         h2 = R.rms_norm(x, params["ln2"][l], cfg.eps)
         gate = _mm(h2, params["w_g"][l])
         up = _mm(h2, params["w_u"][l])
         act = R.alu(up, cfg.alu_beta)
-        x = (x.float() + _mm((gate.float() * act.float()).bfloat16(), params["w_d"][l]).float()).bfloat16()
+        x = (x.float() + _mm((gate.float() * act.float()).to(dtype), params["w_d"][l]).float()).to(dtype)
     return R.rms_norm(x, params["final_gain"], cfg.eps)
 
 

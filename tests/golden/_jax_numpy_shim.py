@@ -10,7 +10,11 @@ up in the golden files is evaluated by the reference's unmodified code.
 Covered API: `jax.numpy` array functions used by `src/algebraic/algebraic.py`,
 `src/algebraic/kernels/flash.py` (host-side helpers only) and
 `src/algebraic/kernels/fused_head.py` (host-side helpers only); `jax.lax.rsqrt`,
-`jax.lax.stop_gradient`; `jax.custom_vjp` as a primal pass-through.
+`jax.lax.stop_gradient`; `jax.custom_vjp` as a primal pass-through.  For
+`src/algebraic/model.py` (the forward pass only): `jax.lax.scan` as a Python loop over the
+leading axis, `jax.checkpoint` as the identity, `jax.random.PRNGKey/split/normal` on
+NumPy generators, bfloat16 through `ml_dtypes`, and an ndarray subclass (`XlaArray`) whose
+`@` multiplies with float32 accumulation and rounds to the operands' dtype as XLA does.
 """
 
 import sys
@@ -45,6 +49,33 @@ class _CustomVjp:
 
     def __call__(self, *a, **k):
         return self.fn(*a, **k)
+
+
+def _xla_matmul(a, b):
+    a, b = np.asarray(a), np.asarray(b)
+    out = np.promote_types(a.dtype, b.dtype)
+    acc = np.float64 if out == np.float64 else np.float32
+    return np.matmul(a.astype(acc), b.astype(acc)).astype(out).view(XlaArray)
+
+
+class XlaArray(np.ndarray):
+    """ndarray whose `@` follows XLA's dot: accumulate in float32, round to the promoted
+    operand dtype (NumPy would return float32 for two bfloat16 operands)."""
+
+    def __matmul__(self, other):
+        return _xla_matmul(self, other)
+
+    def __rmatmul__(self, other):
+        return _xla_matmul(other, self)
+
+
+def _scan(body, carry, xs):
+    """`lax.scan` over the leading axis of every leaf of the dict `xs`; outputs are dropped
+    (model.py's body returns None for them)."""
+    length = len(next(iter(xs.values())))
+    for i in range(length):
+        carry, _ = body(carry, {k: v[i] for k, v in xs.items()})
+    return carry, None
 
 
 def _rsqrt(x):
@@ -93,6 +124,21 @@ def install():
     nn.softmax = lambda x, axis=-1: np.exp(np.asarray(x) - np.expand_dims(_logsumexp(x, axis=axis), axis))
     jax.nn = nn
     sys.modules["jax.nn"] = nn
+
+    # what src/algebraic/model.py needs on top (forward pass only)
+    import ml_dtypes                                      # registers the NumPy dtype "bfloat16"
+    jnp.bfloat16 = ml_dtypes.bfloat16
+    lax.scan = _scan
+    jax.checkpoint = lambda fn, **kw: fn
+    random = types.ModuleType("jax.random")
+    random.PRNGKey = lambda seed: int(seed)
+    random.split = lambda key, num=2: [int(key) * 1000003 + i + 1 for i in range(num)]
+    random.normal = lambda key, shape, dtype=np.float32: (
+        np.random.default_rng(int(key)).standard_normal(shape).astype(dtype).view(XlaArray))
+    jax.random = random
+    jax.tree_util = types.ModuleType("jax.tree_util")
+    sys.modules["jax.random"] = random
+    sys.modules["jax.tree_util"] = jax.tree_util
 
     jax.Array = np.ndarray
     jax.custom_vjp = _CustomVjp

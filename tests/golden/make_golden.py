@@ -193,6 +193,39 @@ def main():
     pt, obj = FH._telemetry(FH._inv_root(lrow, 8), zt, "alg_ce", 8, 2.0, clamp8)
     out["tel_zt"], out["tel_l"], out["tel_pt"], out["tel_obj"] = zt, lrow, pt, np.array(obj)
 
+    # --- the model's forward pass (model.py:162-231): two tiny algebraic configurations, one in
+    #     float32 (pins the structure to 1e-5) and one in bfloat16 (pins the rounding points) ---
+    from algebraic import config as CFG
+    from algebraic import model as M
+    for tag, dtype in (("f32", "float32"), ("bf16", "bfloat16")):
+        cfg = CFG.algebraic("proxy", vocab_size=384, d_model=128, n_layers=2, n_heads=2, d_ff=256, seq_len=48,
+                            dtype=dtype, attn_impl="dense", head_impl="dense")
+        params = M.init_params(cfg, jax.random.PRNGKey(7))
+        rng = np.random.default_rng(70)
+        params["embed"] = (params["embed"] * 5).astype(f32)      # logits of order one, so that pt is not flat
+        for name in ("embed_gain", "final_gain"):                 # non-trivial gains and sinks: a swapped or
+            params[name] = (params[name] + 0.2 * rng.standard_normal(params[name].shape)).astype(f32)
+        for name in ("ln1", "ln2", "q_gain", "k_gain", "sink"):   # dropped one must show
+            leaf = params["layers"][name]
+            params["layers"][name] = (leaf + 0.2 * rng.standard_normal(leaf.shape)).astype(f32)
+        for name in ("w_q", "w_k", "w_v", "w_o", "w_g", "w_u", "w_d"):
+            params["layers"][name] = (params["layers"][name] * 3).astype(f32)
+        tokens = rng.integers(0, cfg.vocab_size, (2, cfg.seq_len))
+        targets = rng.integers(0, cfg.vocab_size, (2, cfg.seq_len))
+        targets[0] = tokens[0]                                    # likely targets in one sequence, unlikely in the other
+        tables = M.position_tables(cfg)
+        hidden = M.forward_hidden(params, tokens, cfg, tables)
+        obj, pt = M.head_loss(params, hidden, targets, cfg)
+        if tag == "f32":
+            out["model_tokens"], out["model_targets"] = tokens.astype(np.int64), targets.astype(np.int64)
+            out["model_embed"] = np.asarray(params["embed"])
+            out["model_embed_gain"], out["model_final_gain"] = np.asarray(params["embed_gain"]), np.asarray(params["final_gain"])
+            for name, leaf in params["layers"].items():
+                out[f"model_layers_{name}"] = np.asarray(leaf)
+        assert str(np.asarray(hidden).dtype) == dtype, hidden.dtype
+        out[f"model_{tag}_hidden"] = np.asarray(hidden).astype(f32)
+        out[f"model_{tag}_obj"], out[f"model_{tag}_pt"] = np.asarray(obj, f32), np.asarray(pt, f32)
+
     np.savez_compressed(args.out, **{k_: np.asarray(v_) for k_, v_ in out.items()})
     print(f"wrote {args.out}: {len(out)} arrays, {os.path.getsize(args.out)} bytes")
 

@@ -62,7 +62,7 @@ def test_invalid_arguments_fail_before_launch():
     assert lib.alg_qk_rms_bwd(qb, None) == L.ALG_ERR_WORKSPACE
     qb.D = 96
     assert lib.alg_qk_rms_bwd(qb, None) == L.ALG_ERR_UNSUPPORTED
-    assert lib.alg_qk_rms_bwd_workspace_bytes(128) == 148 * 4 * 128 * 4 and lib.alg_qk_rms_bwd_workspace_bytes(96) == 0
+    assert lib.alg_qk_rms_bwd_workspace_bytes(128) == 1024 * 128 * 4 and lib.alg_qk_rms_bwd_workspace_bytes(96) == 0
     # guard words handed over by the QKV projection describe ready-made q, k, v: not with the prologue
     a = L.AttnArgs(q=16, k=16, v=16, o=16, B=1, H=1, Tq=256, Tk=256, D=64, n=16, c=8.0, variant=L.ALG_VARIANT_GUARD,
                    guard_words=16, q_gain=16, k_gain=16, cos=16, sin=16, eps=1e-5)
@@ -125,6 +125,18 @@ def test_python_surface_validation_matches_reference_errors():
         def is_cuda(self):
             return True
     xf = x.as_subclass(FakeCuda)
+
+    # tensors of one call must share a device; checked before anything touches CUDA
+    def on(index):
+        class Placed(FakeCuda):
+            @property
+            def device(self):
+                return torch.device("cuda", index)
+        return x.as_subclass(Placed)
+    with pytest.raises(ValueError, match="different devices"):
+        A.flash_attention(on(0), on(1), on(0), kind="asinh")
+    with pytest.raises(ValueError, match="different devices"):
+        A.qk_rms_norm(on(1), on(0))
     with pytest.raises(ValueError, match="divisible by blocks"):
         A.flash_attention(xf[:, :, :500], xf[:, :, :500], xf[:, :, :500], kind="asinh", block=128)
     with pytest.raises(ValueError, match="power of two"):

@@ -79,17 +79,30 @@ def test_scoring_matches_oracle(tmp_path):
     want = torch.log(pt).view(2, 256)
     got = scorer.eval_logprobs(tokens, targets).cpu()
     assert float((got - want).abs().max()) < 0.08 and float((got - want).norm() / want.norm()) < 1e-2
-    # continuation scoring: contexts and continuations of different lengths, bucketed and padded
+    # continuation scoring with the reference's semantics (benchmarking.py:196-240): the model sees
+    # context + cont[:-1]; the score is the MEAN log p over the continuation plus the greedy-match flag
     pairs = [(tokens[0, :40].tolist(), tokens[0, 40:47].tolist()), (tokens[1, :100].tolist(), tokens[1, 100:103].tolist()),
-             (tokens[0, :5].tolist(), tokens[0, 5:6].tolist())]
-    scores = scorer.score_token_pairs(pairs)
-    for (ctx, cont), s in zip(pairs, scores):
-        seq = torch.tensor([ctx + cont])
+             (tokens[0, :5].tolist(), tokens[0, 5:6].tolist()),
+             (tokens[1, :250].tolist(), tokens[1, 250:256].tolist() + [7])]    # context + continuation == T + 1 tokens
+    scores, hits = scorer.score_token_pairs(pairs)
+    assert len(scores) == len(hits) == len(pairs)
+    for (ctx, cont), s, hit in zip(pairs, scores, hits):
+        seq = torch.tensor([ctx + cont[:-1]])
         n = seq.shape[1]
         bucket = min(256, max(128, 1 << (n - 1).bit_length()))
         x = torch.zeros((1, bucket), dtype=torch.long)
         x[0, :n] = seq
-        h = M.forward_hidden(params, x, cfg)[0, len(ctx) - 1:n - 1]
+        h = M.forward_hidden(params, x, cfg)[0, len(ctx) - 1:n]
         _, pt_c = R.head_loss_dense(h, params["embed"], torch.tensor(cont), cfg.head_n, cfg.head_c)
-        want_s = float(torch.log(pt_c).sum())
+        want_s = float(torch.log(pt_c).mean())
         assert abs(s - want_s) < 0.05 * max(1.0, abs(want_s))
+        z = R.head_logits(h, params["embed"])
+        top2 = z.topk(2, dim=-1).values
+        if float((top2[:, 0] - top2[:, 1]).min()) > 0.05:       # unambiguous arg-max rows only
+            assert hit == bool(torch.equal(z.argmax(-1), torch.tensor(cont)))
+    # a context that does not fit is an error unless truncation is allowed
+    long_pair = [(tokens[0].tolist() + tokens[1, :10].tolist(), tokens[1, 10:13].tolist())]
+    with pytest.raises(ValueError, match="truncate"):
+        scorer.score_token_pairs(long_pair)
+    s_trunc, _ = scorer.score_token_pairs(long_pair, allow_truncation=True)
+    assert scorer.truncated_pairs == 1 and np.isfinite(s_trunc[0])

@@ -90,3 +90,55 @@ def test_two_gpu_sharded_head_and_unit_parallel_attention():
         ok_head, e_head, e_attn = ret[r]
         assert ok_head, (r, e_head)
         assert e_attn < 1e-2, (r, e_attn)
+
+
+def _second_device_child(ret):
+    """One process, two GPUs: the very first kernels of the process run on cuda:1 while cuda:0 is
+    the current device (function attributes and grids are per device), then the same ops on cuda:0."""
+    sys.path.insert(0, ROOT)
+    import algebraic_transformer_b200 as A
+    from oracle import algebraic_ref as R
+    torch.cuda.set_device(0)
+    g = torch.Generator().manual_seed(5)
+    B, H, T, D = 1, 2, 512, 128
+    q, k, v = (torch.randn((B, H, T, D), generator=g).bfloat16() for _ in range(3))
+    want = R.asinh_attention(q, k, v, n=16, c=8.0, sink_logit=torch.zeros(H)).double()
+    N, d, V = 256, 256, 4096
+    h = torch.randn((N, d), generator=g).bfloat16()
+    E = (torch.randn((V, d), generator=g) * 0.1).bfloat16()
+    t = torch.randint(0, V, (N,), generator=g).int()
+    l_w, zt_w = R.fused_head_stats(h, E, t, 8, 2.0)
+    errs = {}
+    for dev in ("cuda:1", "cuda:0"):
+        o = A.flash_attention(q.to(dev), k.to(dev), v.to(dev), torch.zeros(H, device=dev), kind="asinh", n=16, c=8.0,
+                              range_guard=True)
+        st = A.head_statistic(h.to(dev), E.to(dev), t.to(dev), n=8, c=2.0)
+        kd = torch.randn((B, H, 1, D), generator=g).bfloat16()
+        od = A.decode_attention(kd.to(dev), k.to(dev), v.to(dev), None, n=16, c=8.0)
+        torch.cuda.synchronize(dev)
+        errs[dev] = (float((o.cpu().double() - want).norm() / want.norm()),
+                     float((st[0].cpu().double() - l_w.double()).norm() / l_w.double().norm()),
+                     bool(torch.isfinite(od.float()).all()))
+    mixed = None
+    try:
+        A.flash_attention(q.to("cuda:0"), k.to("cuda:1"), v.to("cuda:0"), None, kind="asinh", n=16, c=8.0, shift=True)
+    except ValueError as e:
+        mixed = str(e)
+    ret["errs"], ret["mixed"], ret["current"] = errs, mixed, torch.cuda.current_device()
+
+
+@pytest.mark.timeout(300)
+def test_one_process_two_devices():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    ctx = mp.get_context("spawn")
+    proc = ctx.Process(target=_second_device_child, args=(ret,))
+    proc.start()
+    proc.join(240)
+    assert proc.exitcode == 0
+    for dev, (e_attn, e_head, finite) in ret["errs"].items():
+        assert e_attn < 1e-2 and e_head < 1e-3 and finite, (dev, e_attn, e_head, finite)
+    assert ret["mixed"] is not None and "different devices" in ret["mixed"]
+    assert ret["current"] == 0                      # the ops leave the caller's current device alone

@@ -176,3 +176,30 @@ def test_kernel_side_forms(golden):
     pt, obj = R.fused_head_telemetry(T(g["tel_l"]), T(g["tel_zt"]), 8, 2.0, float(clamp8))
     close(pt, g["tel_pt"], 2e-5, 1e-30)
     close(obj, g["tel_obj"], 1e-6)
+
+
+@pytest.mark.parametrize("tag,dtype,tol_hidden,tol_nll", [("f32", torch.float32, 2e-5, 2e-5), ("bf16", torch.bfloat16, 1e-2, 1e-2)])
+def test_model_forward_matches_reference_model(golden, tag, dtype, tol_hidden, tol_nll):
+    """oracle/model_ref.py against the reference's own model.forward_hidden + head_loss
+    (src/algebraic/model.py:162-231, executed by tests/golden/make_golden.py) on a two-layer
+    algebraic configuration with random gains and sinks: in float32, where only summation order
+    differs, and in bfloat16, where every rounding point has to sit where the reference's does."""
+    from algebraic_transformer_b200.prefill import PrefillConfig
+    from oracle import model_ref as MR
+    g = golden
+    cfg = PrefillConfig(vocab_size=384, d_model=128, n_layers=2, n_heads=2, d_ff=256)
+    params = {"embed": T(g["model_embed"]), "embed_gain": T(g["model_embed_gain"]), "final_gain": T(g["model_final_gain"])}
+    for name in ("w_q", "w_k", "w_v", "w_o", "w_g", "w_u", "w_d", "ln1", "ln2", "q_gain", "k_gain", "sink"):
+        params[name] = T(g[f"model_layers_{name}"])
+    tokens, targets = T(g["model_tokens"]), T(g["model_targets"])
+    hidden = MR.forward_hidden(params, tokens, cfg, dtype=dtype)
+    assert hidden.dtype == dtype
+    want = T(g[f"model_{tag}_hidden"])
+    rel = float((hidden.float() - want).norm() / want.norm())
+    assert rel <= tol_hidden, rel
+    obj, pt = MR.head_loss(params, hidden, targets, cfg)
+    want_nll = -torch.log(T(g[f"model_{tag}_pt"]).clamp_min(1e-30))
+    nll = -torch.log(pt.float().clamp_min(1e-30))
+    rel_nll = float((nll - want_nll).norm() / want_nll.norm())
+    assert rel_nll <= tol_nll, rel_nll
+    close(obj, g[f"model_{tag}_obj"], 1e-4 if tag == "f32" else 2e-2)
