@@ -85,7 +85,10 @@ __global__ void __launch_bounds__(NTHREADS) attn_mma_kernel(const AttnParams p) 
   __nv_bfloat16* sV = sK + NS * TILE;
   __shared__ int s_shift;
 
-  if (threadIdx.x == 0) s_shift = attn_use_shift(p) ? 1 : 0;
+  if (threadIdx.x < 32) {
+    const bool sh = attn_use_shift(p, threadIdx.x);
+    if (threadIdx.x == 0) s_shift = sh ? 1 : 0;
+  }
   __syncthreads();
   const bool shift_mode = s_shift != 0;
   if ((p.run_if == 1 && shift_mode) || (p.run_if == 2 && !shift_mode)) return;

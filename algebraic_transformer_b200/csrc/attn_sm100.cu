@@ -12,7 +12,9 @@
 //                      S_w = Q_w K_j^T (both operands in shared memory) and O_w += P_w V_j with P_w
 //                      read from TENSOR MEMORY (the A operand) and V_j from shared memory as an
 //                      MN-major B operand
-//   warps 2, 3         scale Q tile 0 / 1 in shared memory by a power of two (see below)
+//   warp 2             scales the Q tiles in shared memory by a power of two (see below)
+//   warp 3             on request, takes the range guard's maxima of q, k, v beside the attention
+//                      work, so that a guarded call needs no separate pass over its inputs
 //   weight group 0     weights for query tile 0: tcgen05.ld S_0 (one thread = one row),
 //                      x -> rho_fast(x)^n in packed fp32, row sum, bf16 P_0 written back
 //                      with tcgen05.st over columns S_0 occupied
@@ -200,19 +202,107 @@ template <int NKV> struct RingCursor {
   __device__ __forceinline__ void next() { if (++slot == NKV) { slot = 0; phase ^= 1u; } }
 };
 
-// The k-th work item of this CTA.  Items are numbered heaviest first (last row block of
-// every (batch, head), then the one before, ...); row k of the deal goes left to right for
-// even k and right to left for odd k.
+// Which work items a CTA takes, in which order.  Items are numbered heaviest first (last row block
+// of every (batch, head), then the one before, ...).  Up to MAX_LISTED items the host deals them
+// out greedily - every item, heaviest first, to the CTA with the least work so far - and passes the
+// lists as a kernel argument: per-CTA sums then differ by about one key tile, where dealing the items
+// out in rows, left to right and back, left 9 % between the lightest and the heaviest CTA at 512
+// items over 148 CTAs.  Larger problems use the row-wise deal (many items per CTA level it out).
+constexpr int MAX_LISTED = 1024, MAX_LIST_CTAS = 160;
+struct ItemLists {
+  uint16_t start[MAX_LIST_CTAS + 1];   // CTA c owns item[start[c] .. start[c + 1])
+  uint16_t item[MAX_LISTED];
+  int listed;                          // 0: row-wise deal
+};
+
+// The k-th work item of this CTA.
 struct Item { int b, h, row0, n0, n1; };
-__device__ __forceinline__ bool item_at(const AttnParams& p, int k, Item& it) {
+__device__ __forceinline__ bool item_at(const AttnParams& p, const ItemLists& lists, int k, Item& it) {
   const int units = p.B * p.H, nblk = p.Tq / (2 * BQ), G = int(gridDim.x);
-  const int idx = k * G + ((k & 1) ? G - 1 - int(blockIdx.x) : int(blockIdx.x));
-  if (idx >= units * nblk) return false;
+  int idx;
+  if (lists.listed) {
+    const int at = int(lists.start[blockIdx.x]) + k;
+    if (at >= int(lists.start[blockIdx.x + 1])) return false;
+    idx = lists.item[at];
+  } else {
+    // row k of the deal goes left to right for even k and right to left for odd k
+    idx = k * G + ((k & 1) ? G - 1 - int(blockIdx.x) : int(blockIdx.x));
+    if (idx >= units * nblk) return false;
+  }
   const int blk = nblk - 1 - idx / units, bh = idx % units;
   it.b = bh / p.H; it.h = bh % p.H;
   it.row0 = blk * 2 * BQ;
   it.n0 = 2 * blk + 1; it.n1 = 2 * blk + 2;      // key tiles needed by query tile 0 / 1
   return true;
+}
+
+// The range guard's three maxima (src/algebraic/kernels/flash.py:834-849) taken by one otherwise idle
+// warp while the CTA does its attention work: the largest squared row norm of q in score units, the
+// largest squared row norm of k, the largest |v|, each over the rows this CTA looks at (the reader
+// takes the largest over the CTAs' records).  A lane owns a row (all of its 16-byte loads in
+// flight at once, no shuffles); the rows of the whole problem are dealt over all CTAs.  The
+// reference takes the norm of q after re-rounding q / (sqrt(D) c) to the input dtype; here the
+// unrounded norm is multiplied by (1 + 2^-8), an upper bound on what that rounding can add, so the
+// guard can only err towards the shifted (always valid) form.  NaN anywhere fails the guard.
+template <int D>
+__device__ __forceinline__ void guard_statistics(const AttnParams& p, GuardWords* out, int lane) {
+  constexpr int NV = D / 8;                       // 16-byte vectors per row
+  const int64_t step = int64_t(gridDim.x) * 32;
+  float best[2] = {0.f, 0.f};
+  for (int which = 0; which < 2; ++which) {
+    const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(which == 0 ? p.q : p.k);
+    const Strides3& st = which == 0 ? p.qs : p.ks;
+    const int T = which == 0 ? p.Tq : p.Tk;
+    const int64_t rows = int64_t(p.B) * p.H * T;
+    float m = 0.f;
+    for (int64_t r = int64_t(blockIdx.x) * 32 + lane; r < rows; r += step) {
+      const int t = int(r % T);
+      const int64_t bh = r / T;
+      const uint4* src = reinterpret_cast<const uint4*>(base + (bh / p.H) * st.b + (bh % p.H) * st.h + int64_t(t) * st.t);
+      uint4 raw[NV];
+#pragma unroll
+      for (int i = 0; i < NV; ++i) raw[i] = __ldg(src + i);
+      float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); acc = __ffma2_rn(f, f, acc); }
+      }
+      const float ss = acc.x + acc.y;
+      m = (ss > m || ss != ss) ? ss : m;          // a NaN sticks
+    }
+    best[which] = m;
+  }
+  __nv_bfloat162 vm2 = __float2bfloat162_rn(0.f);
+  {
+    const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(p.v);
+    const int64_t rows = int64_t(p.B) * p.H * p.Tk;
+    for (int64_t r = int64_t(blockIdx.x) * 32 + lane; r < rows; r += step) {
+      const int t = int(r % p.Tk);
+      const int64_t bh = r / p.Tk;
+      const uint4* src = reinterpret_cast<const uint4*>(base + (bh / p.H) * p.vs.b + (bh % p.H) * p.vs.h + int64_t(t) * p.vs.t);
+      uint4 raw[NV];
+#pragma unroll
+      for (int i = 0; i < NV; ++i) raw[i] = __ldg(src + i);
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) vm2 = __hmax2_nan(vm2, __habs2(h[e]));
+      }
+    }
+  }
+  const float2 vm = __bfloat1622float2(vm2);
+  float stat[3] = {best[0] * (p.scale * p.scale * 1.00390625f), best[1], (vm.x > vm.y || vm.x != vm.x) ? vm.x : vm.y};
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    float x = stat[i];
+    if (!(x == x)) x = __int_as_float(0x7f800000);  // NaN -> +inf, which orders above everything as an unsigned word
+    stat[i] = warp_max(x);
+  }
+  // one record per CTA, plain stores: nothing to zero beforehand, nothing to contend for
+  if (lane == 0) *reinterpret_cast<uint4*>(out + blockIdx.x) = make_uint4(__float_as_uint(stat[0]), __float_as_uint(stat[1]), __float_as_uint(stat[2]), 0u);
 }
 
 template <int D> constexpr size_t smem_bytes() { return size_t(Cfg<D>::CTL_OFF) + sizeof(Control) + 1024; }
@@ -234,14 +324,18 @@ struct ScaleSplit {
 template <int D, int LOG2N, int SPLIT>
 __global__ void __launch_bounds__(nthreads<SPLIT>(), 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-               const __grid_constant__ CUtensorMap tm_v, const AttnParams p, const ScaleSplit sc) {
+               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p, const ScaleSplit sc,
+               const __grid_constant__ ItemLists lists) {
   using C = Cfg<D>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Control* ctl = reinterpret_cast<Control*>(smem + C::CTL_OFF);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  if (threadIdx.x == 0) ctl->shift_mode = attn_use_shift(p) ? 1 : 0;
+  if (warp == 0) {
+    const bool sh = attn_use_shift(p, lane);
+    if (lane == 0) ctl->shift_mode = sh ? 1 : 0;
+  }
   __syncthreads();
   if (ctl->shift_mode != 0) return;               // the guard failed: the stable kernel does this launch's work
 
@@ -281,7 +375,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
       bool ok = true;
       RingCursor<C::NKV> cur;                       // runs on over all items
-      for (int k = 0; ok && item_at(p, k, it); ++k) {
+      for (int k = 0; ok && item_at(p, lists, k, it); ++k) {
         auto load_kv = [&](int idx) {               // K_0, V_0, K_1, V_1, ... of this item
           const int buf = cur.slot;
           if (!bw.wait(&ctl->kv_empty[buf], cur.phase ^ 1u)) return false;
@@ -364,7 +458,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const long long t_begin = clock64();
 #endif
     bool ok = true;
-    for (int k = 0; ok && item_at(p, k, it); ++k) {
+    for (int k = 0; ok && item_at(p, lists, k, it); ++k) {
       const int n0 = it.n0, n1 = it.n1;
       if (!wait_all(&ctl->q_ready[0], k & 1u) || !kv_wait(cur)) { ok = false; break; }
       tc_fence_after();
@@ -421,29 +515,38 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       dbg[0] = float(tm0); dbg[1] = float(tm1); dbg[2] = float(tm2); dbg[3] = float(clock64() - t_begin); dbg[4] = float(tm3);
     }
 #endif
-  } else if (warp < FIRST_WEIGHT_WARP) {
-    // Q scalers (warp 2: tile 0, warp 3: tile 1): once a Q tile has landed, multiply it by 2^e
-    // where it lies (element-wise, so the swizzled layout does not matter), make the result
-    // visible to the tensor core's reads and release the tile to the MMA warp.
-    const int w = warp - 2;
+  } else if (warp == 2) {
+    // Q scaler: once a Q tile has landed, multiply it by 2^e where it lies (element-wise, so
+    // the swizzled layout does not matter), make the result visible to the tensor core's reads
+    // and release the tile to the MMA warp.
     const __nv_bfloat162 f2 = __float2bfloat162_rn(sc.pow2);
-    uint4* tile = reinterpret_cast<uint4*>(smem + C::Q_OFF + w * C::TILE_BYTES);
     bool ok = true;
-    for (int k = 0; ok && item_at(p, k, it); ++k) {
-      if (!bw.wait(&ctl->q_full[w], k & 1u)) { ok = false; break; }
-      if (sc.pow2 != 1.0f) {
+    for (int k = 0; ok && item_at(p, lists, k, it); ++k) {
+      for (int w = 0; w < 2 && ok; ++w) {
+        if (!bw.wait(&ctl->q_full[w], k & 1u)) { ok = false; break; }
+        if (sc.pow2 != 1.0f) {
+          uint4* tile = reinterpret_cast<uint4*>(smem + C::Q_OFF + w * C::TILE_BYTES);
 #pragma unroll 4
-        for (int i = lane; i < C::TILE_BYTES / 16; i += 32) {
-          uint4 v = tile[i];
-          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
-          h[0] = __hmul2(h[0], f2); h[1] = __hmul2(h[1], f2); h[2] = __hmul2(h[2], f2); h[3] = __hmul2(h[3], f2);
-          tile[i] = v;
+          for (int i = lane; i < C::TILE_BYTES / 16; i += 32) {
+            uint4 v = tile[i];
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+            h[0] = __hmul2(h[0], f2); h[1] = __hmul2(h[1], f2); h[2] = __hmul2(h[2], f2); h[3] = __hmul2(h[3], f2);
+            tile[i] = v;
+          }
+          fence_async_shared();
         }
-        fence_async_shared();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->q_ready[w]);
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl->q_ready[w]);
     }
+  } else if (warp == 3) {
+#ifdef ALG_ATTN_TIMING
+    const long long tg0 = clock64();
+#endif
+    if (p.guard_out != nullptr) guard_statistics<D>(p, p.guard_out, lane);
+#ifdef ALG_ATTN_TIMING
+    if (lane == 0 && p.stat != nullptr) p.stat[40 + 2 * blockIdx.x] = float(clock64() - tg0);
+#endif
   } else {
     const int ww = warp - FIRST_WEIGHT_WARP;
     const int w = ww / (4 * SPLIT);                 // query tile of this weight group
@@ -464,7 +567,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #ifdef ALG_ATTN_TIMING
     const long long t_begin = clock64();
 #endif
-    for (int k = 0; ok && item_at(p, k, it); ++k) {
+    for (int k = 0; ok && item_at(p, lists, k, it); ++k) {
       const int nk = (w == 0) ? it.n0 : it.n1;
       float l = 0.f;                                // the sink's weight, fetched while the first scores are computed
       if (p.sink != nullptr) l = pow2n<LOG2N>(rho_stable(p.sink[it.h] * p.inv_c)) * sc.inv_mn;
@@ -513,7 +616,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
       tc_fence_after();
-      item_at(p, k, it);                            // recomputed: nothing of it stays live over the tile loop
+      item_at(p, lists, k, it);                            // recomputed: nothing of it stays live over the tile loop
       l += part;
       const float inv = 1.0f / l;
       const int row = it.row0 + w * BQ + r;
@@ -544,6 +647,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #endif
     }
 #ifdef ALG_ATTN_TIMING
+    if (w == 1 && r == 0 && half == 0 && p.stat != nullptr) p.stat[41 + 2 * blockIdx.x] = float(clock64() - t_begin);
     if (blockIdx.x == 0 && r == 0 && half == 0 && p.stat != nullptr) {
       float* dbg = p.stat + 8 * w;
       dbg[0] = float(tm0); dbg[1] = 0.f; dbg[2] = float(tm1); dbg[3] = float(clock64() - t_begin); dbg[4] = float(tiles_before);
@@ -566,6 +670,29 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+// Greedy deal of the items (cost of row block blk: its 4 blk + 3 score tiles) over `grid` CTAs.
+void deal_items(ItemLists* out, int units, int nblk, int grid) {
+  const int items = units * nblk;
+  out->listed = 0;
+  if (items > MAX_LISTED || grid > MAX_LIST_CTAS) return;
+  int load[MAX_LIST_CTAS] = {0}, count[MAX_LIST_CTAS] = {0};
+  uint16_t owner[MAX_LISTED];
+  for (int i = 0; i < items; ++i) {                      // items are already in order of falling cost
+    int best = 0;
+    for (int c = 1; c < grid; ++c)
+      if (load[c] < load[best]) best = c;
+    owner[i] = uint16_t(best);
+    load[best] += 4 * (nblk - 1 - i / units) + 3;
+    ++count[best];
+  }
+  out->start[0] = 0;
+  for (int c = 0; c < grid; ++c) out->start[c + 1] = uint16_t(out->start[c] + count[c]);
+  int fill[MAX_LIST_CTAS];
+  for (int c = 0; c < grid; ++c) fill[c] = out->start[c];
+  for (int i = 0; i < items; ++i) out->item[fill[owner[i]]++] = uint16_t(i);
+  out->listed = 1;
 }
 
 int make_qkv_map(CUtensorMap* tm, const void* base, const Strides3& s, int B, int H, int T, int D) {
@@ -595,9 +722,17 @@ int launch_dns(const AttnParams& p, cudaStream_t stream) {
   static PerDeviceOnce configured;
   int sms = 0;
   if (int rc = configured.run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes<D>())); }, &sms)) return rc;
-  const int items = p.B * p.H * (p.Tq / (2 * BQ));
-  const int grid = items < sms ? items : sms;
-  kern<<<grid, nthreads<SPLIT>(), smem_bytes<D>(), stream>>>(tq, tk, tv, p, sc);
+  const int grid = attn_tcgen05_grid(p);
+  (void)sms;
+  // the deal depends on three integers only: keep the last one (a launch path must stay cheap)
+  struct Dealt { int units, nblk, grid; ItemLists lists; };
+  static thread_local Dealt dealt = {-1, -1, -1, {}};
+  const int units = p.B * p.H, nblk = p.Tq / (2 * BQ);
+  if (dealt.units != units || dealt.nblk != nblk || dealt.grid != grid) {
+    deal_items(&dealt.lists, units, nblk, grid);
+    dealt.units = units; dealt.nblk = nblk; dealt.grid = grid;
+  }
+  kern<<<grid, nthreads<SPLIT>(), smem_bytes<D>(), stream>>>(tq, tk, tv, p, sc, dealt.lists);
   ALG_CUDA_TRY(cudaGetLastError());
   count_launch();
   return ALG_OK;
@@ -634,6 +769,16 @@ bool attn_tcgen05_supports(const AttnParams& p, int dtype) {
          p.log2n >= 3 && p.log2n <= 5 && p.variant != ALG_VARIANT_SHIFT && strides_fit &&
          (p.B == 1 || p.qs.b > 0) && (p.H == 1 || p.qs.h > 0);
 }
+
+// One warp per SM streams 6 B H T D bytes at about 5 GB/s per SM while the kernel needs time in
+// proportion to B H T^2 D: from T D = 3/4 Mi elements per head on, the statistics are ready well
+// before the attention is (T >= 6144 at head_dim 128).
+int attn_tcgen05_grid(const AttnParams& p) {
+  const int items = p.B * p.H * (p.Tq / (2 * BQ)), sms = sm_count();
+  return items < sms ? items : sms;
+}
+
+bool attn_tcgen05_takes_guard_statistics(const AttnParams& p) { return int64_t(p.Tq) * p.D >= 786432; }
 
 int launch_attn_tcgen05(const AttnParams& p, cudaStream_t stream) {
   return p.D == 64 ? launch_d<64>(p, stream) : launch_d<128>(p, stream);

@@ -1,6 +1,6 @@
 // The C ABI declared in include/alg_b200.h: argument validation, workspace carving and
-// kernel selection.  Nothing here allocates device memory or synchronises; the one set of objects
-// the library creates by itself is a side stream with two events per device (side_stream_for).
+// kernel selection.  Nothing here allocates device memory, creates streams or events, or
+// synchronises: every call only enqueues work on the caller's stream.
 #include <math.h>
 #include <atomic>
 #include <mutex>
@@ -52,6 +52,7 @@ void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memo
 namespace {
 
 const int64_t kDense[3] = {0, 0, 0};
+constexpr size_t kGuardBytes = 8192;                    // 512 guard records of 16 bytes
 inline float __int_as_float_host(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
 inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 inline size_t elem_size(int dtype) { return dtype == ALG_BF16 ? 2 : 4; }
@@ -77,44 +78,6 @@ int check_common(int D, int n, float c, int dtype) {
   }
   if (!(c > 0.0f) || !isfinite(c)) { set_error("asinh scale c must be positive and finite"); return ALG_ERR_INVALID; }
   return ALG_OK;
-}
-
-// A stream and two events per device, created on first use and kept for the life of the process:
-// the guarded attention call forks the guard's pass over q, k, v onto it (see alg_attn_fwd).
-// Returns nullptr — the caller then keeps everything on its own stream — when the environment
-// variable ALG_ATTN_SERIAL_GUARD is set, or when the objects do not exist yet and cannot be
-// created because the caller's stream is being captured into a graph.
-struct SideStream {
-  cudaStream_t stream = nullptr;
-  cudaEvent_t fork = nullptr, join = nullptr;
-};
-constexpr int kMaxDevices = 64;
-SideStream g_side[kMaxDevices];
-std::mutex g_side_mutex;
-
-SideStream* side_stream_for(cudaStream_t user_stream) {
-  static const bool serial = getenv("ALG_ATTN_SERIAL_GUARD") != nullptr;
-  if (serial) return nullptr;
-  int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return nullptr; }
-  std::lock_guard<std::mutex> lock(g_side_mutex);
-  SideStream& s = g_side[dev];
-  if (s.stream == nullptr) {
-    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(user_stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
-      cudaGetLastError();
-      return nullptr;
-    }
-    SideStream t;
-    if (cudaStreamCreateWithFlags(&t.stream, cudaStreamNonBlocking) != cudaSuccess ||
-        cudaEventCreateWithFlags(&t.fork, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&t.join, cudaEventDisableTiming) != cudaSuccess) {
-      cudaGetLastError();
-      return nullptr;
-    }
-    s = t;
-  }
-  return &s;
 }
 
 bool attn_has_prologue(const alg_attn_args* a) {
@@ -185,7 +148,7 @@ int alg_qk_rms_bwd(const alg_qk_rms_bwd_args* a, void* stream) {
 
 size_t alg_attn_workspace_bytes(const alg_attn_args* a) {
   if (a == nullptr) return 0;
-  size_t bytes = 256;                                   // guard words
+  size_t bytes = kGuardBytes;                           // guard words: one record, or one per CTA of the tcgen05 kernel
   if (attn_has_prologue(a)) {
     const size_t es = elem_size(a->dtype);
     bytes += align256(size_t(a->B) * a->H * a->Tq * a->D * es);
@@ -242,25 +205,13 @@ int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
   unsigned char* ws = static_cast<unsigned char*>(a->workspace);
   GuardWords* guard = guard_given ? static_cast<GuardWords*>(const_cast<void*>(a->guard_words)) : reinterpret_cast<GuardWords*>(ws);
   const bool guarded = a->variant == ALG_VARIANT_GUARD;
-  // Speculation: when the guard's maxima still have to be measured (a pass over q, k, v) and the
-  // tcgen05 kernel is the one that will run if the guard holds, that kernel is launched at once, for
-  // the unshifted form, while the pass runs beside it on a stream of the library's own; the stable
-  // kernel follows, after both, and does its work (overwriting o, stat and stat_kind) only if the
-  // guard failed.  In-range inputs — the case the guard exists to make fast — no longer wait for
-  // the pass; out-of-range inputs pay for a discarded kernel.
-  SideStream* side = nullptr;
-  if (guarded && !guard_given && !prologue && a->impl != ALG_IMPL_MMA && !(a->score_clamp > 0.0f) &&
-      attn_tcgen05_supports(p, a->dtype))
-    side = side_stream_for(stream);
-  cudaStream_t gstream = side != nullptr ? side->stream : stream;     // where the guard's memset and pass go
-  if (side != nullptr) {
-    ALG_CUDA_TRY(cudaEventRecord(side->fork, stream));
-    ALG_CUDA_TRY(cudaStreamWaitEvent(side->stream, side->fork, 0));
-    AttnParams ps = p;                                  // enqueued first, so that its CTAs take the SMs first
-    ps.variant = ALG_VARIANT_NOSHIFT;
-    ps.run_if = 0;
-    if (int rc = launch_attn_tcgen05(ps, stream)) return rc;
-  }
+  // Speculation: when the guard's maxima still have to be measured and the sequences are long, the
+  // tcgen05 kernel runs at once, for the unshifted form, and one of its warps takes the maxima of
+  // q, k, v beside the attention work; the stable kernel follows and does its work (overwriting o,
+  // stat and stat_kind) only if the guard failed.  In-range inputs - the case the guard exists to
+  // make fast - then cost no pass over q, k, v at all; out-of-range inputs pay for a discarded kernel.
+  const bool speculate = guarded && !guard_given && !prologue && a->impl != ALG_IMPL_MMA && !(a->score_clamp > 0.0f) &&
+                         attn_tcgen05_supports(p, a->dtype) && attn_tcgen05_takes_guard_statistics(p);
   if (guarded) {
     // src/algebraic/kernels/flash.py:744-748, 840-849
     const double t = root_pow2(1e37 / (double(a->Tk) + 1.0), a->n);
@@ -270,14 +221,24 @@ int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
     p.guard_bound_sq = float((bound / 1.01) * (bound / 1.01));
     p.guard_sink_bound = float(bound / 1.01);
     p.guard_vmax = float(fmin(1e8, 1e37 / ((double(a->Tk) + (a->sink ? 1 : 0)) * pow(2 * bound + 1, a->n))));
-    if (!guard_given) ALG_CUDA_TRY(cudaMemsetAsync(guard, 0, sizeof(GuardWords), gstream));
   }
+  if (speculate) {
+    AttnParams ps = p;
+    ps.variant = ALG_VARIANT_NOSHIFT;
+    ps.run_if = 0;
+    ps.guard_out = guard;                               // one record per CTA: no memset, no atomics
+    p.guard_slots = attn_tcgen05_grid(p);
+    if (size_t(p.guard_slots) * sizeof(GuardWords) > kGuardBytes) { set_error("attention: more CTAs than guard records"); return ALG_ERR_UNSUPPORTED; }
+    if (int rc = launch_attn_tcgen05(ps, stream)) return rc;
+    p.run_if = 2;                                       // the stable path runs only if the guard failed
+    return launch_attn_mma(p, a->dtype, stream);
+  }
+  if (guarded && !guard_given) ALG_CUDA_TRY(cudaMemsetAsync(guard, 0, sizeof(GuardWords), stream));
   if (prologue || (guarded && !guard_given)) {
     const size_t es = elem_size(a->dtype);
-    void* qn = ws + 256;
-    void* kn = ws + 256 + align256(size_t(a->B) * a->H * a->Tq * a->D * es);
+    void* qn = ws + kGuardBytes;
+    void* kn = ws + kGuardBytes + align256(size_t(a->B) * a->H * a->Tq * a->D * es);
     PrepBatch batch{};
-    batch.lean = side != nullptr ? 1 : 0;               // beside the attention kernel: CTAs that fit next to its own
     PrepParams pp{};
     pp.eps = a->eps; pp.B = a->B; pp.H = a->H; pp.D = a->D;
     pp.cos = prologue ? a->cos : nullptr; pp.sin = prologue ? a->sin : nullptr;
@@ -301,7 +262,7 @@ int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
       pp.normalise = 0; pp.stat_mode = 2; pp.stat_out = &guard->vmax;
       batch.t[batch.count++] = pp;
     }
-    if (int rc = launch_prep_batch(batch, a->dtype, gstream)) return rc;  // statistics-only tensors share a launch
+    if (int rc = launch_prep_batch(batch, a->dtype, stream)) return rc;  // statistics-only tensors share a launch
     if (prologue) {
       p.q = qn; p.k = kn;
       p.qs = strides_or_dense(kDense, a->H, a->Tq, a->D);
@@ -313,12 +274,6 @@ int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
   if (a->impl == ALG_IMPL_TCGEN05 && !fast_ok) {
     set_error("attention: the tcgen05 kernel covers bf16, causal Tq == Tk multiple of 128, unshifted or guarded");
     return ALG_ERR_UNSUPPORTED;
-  }
-  if (side != nullptr) {                                // the tcgen05 kernel is already running
-    ALG_CUDA_TRY(cudaEventRecord(side->join, side->stream));
-    ALG_CUDA_TRY(cudaStreamWaitEvent(stream, side->join, 0));
-    p.run_if = 2;                                       // the stable path runs only if the guard failed
-    return launch_attn_mma(p, a->dtype, stream);
   }
   if (fast_ok && a->impl != ALG_IMPL_MMA) {
     p.run_if = guarded ? 1 : 0;

@@ -26,8 +26,6 @@ struct PrepParams {
 struct PrepBatch {         // up to three tensors (q, k, v) of one dtype / head_dim in one launch
   PrepParams t[3];
   int count;
-  int lean;                // statistics-only launches: CTAs of 128 threads (8192 registers), small enough to
-                           // share an SM with a resident attention CTA when the pass runs beside that kernel
 };
 // backward of the QK RMS-norm (qk_prep.cu): dx, and the gain gradient as per-CTA partial rows summed in order
 struct RmsBwdParams {
@@ -64,22 +62,45 @@ struct AttnParams {
   int variant;             // ALG_VARIANT_*
   Strides3 qs, ks, vs, os;
   const GuardWords* guard; // required when variant == GUARD
+  int guard_slots;         // 0: `guard` is one record; n > 0: n records (one per CTA of the kernel that
+                           // took the maxima), the guard's maxima being the largest of each word
   float guard_bound_sq;    // (bound/1.01)^2
   float guard_sink_bound;  // bound/1.01
   float guard_vmax;
   float score_clamp;       // unshifted path: x <- min(x, score_clamp); +inf when off
   int run_if;              // 0 always, 1 only when the guard holds, 2 only when it fails
   int* status;
+  GuardWords* guard_out;   // tcgen05 kernel only: CTA i writes the maxima of the rows it looked at to guard_out[i]
 };
 int launch_attn_mma(const AttnParams& p, int dtype, cudaStream_t stream);
 bool attn_tcgen05_supports(const AttnParams& p, int dtype);
+// Long enough sequences leave one warp of the tcgen05 kernel time to take the guard's maxima itself.
+bool attn_tcgen05_takes_guard_statistics(const AttnParams& p);
+int attn_tcgen05_grid(const AttnParams& p);          // CTAs of that kernel = records it writes to guard_out
 int launch_attn_tcgen05(const AttnParams& p, cudaStream_t stream);
 
-// Shared by both attention kernels: does this launch use the max-shifted form?
-__device__ __forceinline__ bool attn_use_shift(const AttnParams& p) {
+// Shared by both attention kernels: does this launch use the max-shifted form?  Called by all 32
+// lanes of one warp; every lane gets the answer.
+__device__ __forceinline__ bool attn_use_shift(const AttnParams& p, int lane) {
   if (p.variant == ALG_VARIANT_NOSHIFT) return false;
   if (p.variant == ALG_VARIANT_SHIFT) return true;
-  bool ok = guard_in_range(p.guard, p.guard_bound_sq, p.guard_vmax);
+  bool ok;
+  if (p.guard_slots > 0) {                              // per-CTA records: the words order as unsigned integers
+    unsigned q2 = 0, k2 = 0, vm = 0;
+    for (int i = lane; i < p.guard_slots; i += 32) {
+      const uint4 r = *reinterpret_cast<const uint4*>(p.guard + i);
+      q2 = max(q2, r.x); k2 = max(k2, r.y); vm = max(vm, r.z);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      q2 = max(q2, __shfl_xor_sync(0xffffffffu, q2, o));
+      k2 = max(k2, __shfl_xor_sync(0xffffffffu, k2, o));
+      vm = max(vm, __shfl_xor_sync(0xffffffffu, vm, o));
+    }
+    ok = (__uint_as_float(q2) * __uint_as_float(k2) <= p.guard_bound_sq) && (__uint_as_float(vm) <= p.guard_vmax);
+  } else {
+    ok = guard_in_range(p.guard, p.guard_bound_sq, p.guard_vmax);
+  }
   if (p.sink != nullptr)
     for (int h = 0; h < p.H; ++h) ok = ok && (fabsf(p.sink[h] * p.inv_c) <= p.guard_sink_bound);
   return !ok;

@@ -226,7 +226,7 @@ static int launch_t(const PrepBatch& batch, cudaStream_t stream) {
     if (batch.t[i].H == 0) return ALG_OK;
   }
   if (positions == 0) return ALG_OK;
-  const int threads = (mode == 0 && batch.lean) ? 128 : 256;
+  const int threads = 256;
   const int64_t warps = (positions + RPW - 1) / RPW;
   int64_t blocks = (warps + threads / 32 - 1) / (threads / 32);
   // resident CTAs only (the grid-stride loop covers the rest): 4 per SM for the

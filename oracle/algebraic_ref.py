@@ -276,10 +276,12 @@ def range_guard_in_range(q, k, v, sink_logit, *, n: int, c: float) -> bool:
 def attention_row_stat(q, k, *, n: int, c: float, sink_logit=None, shifted: bool):
     """Per-row statistic the forward kernels save for a backward pass
     (flash.py:271-284): unshifted 1/l with l = rho(b')^n + sum_j rho_fast(x_ij)^n;
-    shifted rho(-m) l^(-1/n) with the max-shifted l."""
+    shifted rho(-m) l^(-1/n) with the max-shifted l.  With fewer query rows than keys the
+    queries are the last rows of the square problem, as in `asinh_attention`."""
     B, H, T, D = q.shape
+    Tk = k.shape[-2]
     x = torch.matmul(q.to(F32), k.to(F32).transpose(-1, -2)) * (1.0 / (math.sqrt(D) * c))
-    mask = torch.tril(torch.ones((T, T), dtype=torch.bool))[None, None]
+    mask = (torch.arange(Tk)[None, :] <= torch.arange(T)[:, None] + (Tk - T))[None, None]
     sink = _sink4(sink_logit, H, F32)
     if not shifted:
         w = torch.where(mask, int_pow(rho_fast(x), n), torch.zeros(()))

@@ -107,9 +107,9 @@ def test_invalid_arguments_fail_before_launch():
 def test_workspace_sizes():
     lib = L.load()
     a = L.AttnArgs(B=2, H=3, Tq=512, Tk=512, D=64, dtype=L.ALG_BF16)
-    assert lib.alg_attn_workspace_bytes(a) == 256
+    assert lib.alg_attn_workspace_bytes(a) == 8192
     a.cos = 16
-    assert lib.alg_attn_workspace_bytes(a) == 256 + 2 * (2 * 3 * 512 * 64 * 2)
+    assert lib.alg_attn_workspace_bytes(a) == 8192 + 2 * (2 * 3 * 512 * 64 * 2)
     h = L.HeadArgs(N=8192, d=768, V_local=50304)
     assert lib.alg_head_workspace_bytes(h) >= 2 * 8192 * 4
     assert lib.alg_head_finalize_workspace_bytes(8192) >= 32 * 4 + 16

@@ -169,9 +169,8 @@ def test_guarded_attention_tail(sign, with_sink, magnitude, dtype):  # test_flas
 
 
 def test_guarded_call_replays_from_a_cuda_graph():
-    """A stand-alone guarded call forks its statistics pass onto the library's own stream beside the
-    attention kernel; captured into a CUDA graph (after one eager call, which creates that stream)
-    the fork and join become graph edges, and replays on fresh inputs — in range, then out of range —
+    """A stand-alone guarded call only enqueues kernels and a 16-byte memset on the caller's stream, so
+    it can be captured into a CUDA graph; replays on fresh inputs — in range, then out of range —
     give the eager results."""
     shape = (1, 2, 512, 64)
     q, k, v = (randn(shape, 871 + i, torch.bfloat16) for i in range(3))
@@ -313,6 +312,62 @@ def test_config5_long_context_sampled(impl):
         want = R.asinh_attention(q[:, h:h + 1], k[:, h:h + 1], v[:, h:h + 1], n=16, c=8.0,
                                  sink_logit=torch.zeros(1), row_block=1024)
         assert rel_l2(got[:, h:h + 1], want) < 1e-2
+
+
+@pytest.mark.parametrize("T", [16384, 32768])
+def test_config5_longer_sequences_sampled(T):
+    """benchmark configuration 5 at T = 16384 and 32768: (1,16,T,128) bf16 through the guarded public
+    call.  The dense (T,T) oracle does not fit, so it is evaluated on a deterministic sample of 256-row
+    blocks (the first, one in mid-sequence, the last: rows r0:r1 of the square problem are the causal
+    problem of q[r0:r1] against the first r1 keys) of two heads; all heads are checked for run-to-run
+    bit equality, which also exercises the kernel's ring and phase arithmetic at 64 to 128 key tiles
+    per item."""
+    B, H, D = 1, 16, 128
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn((B, H, T, D), generator=g).bfloat16() for _ in range(3))
+    qd, kd, vd = dev(q, k, v)
+    sink = torch.zeros(H, device=DEV)
+    got, stat, kind = A.flash_attention(qd, kd, vd, sink, kind="asinh", n=16, c=8.0, range_guard=True, return_stat=True)
+    again = A.flash_attention(qd, kd, vd, sink, kind="asinh", n=16, c=8.0, range_guard=True)
+    assert int(kind) == 1 and torch.equal(got, again)
+    assert torch.isfinite(got).all() and torch.isfinite(stat).all()
+    for h in (3, 15):
+        for r0 in (0, (T // 2 // 256) * 256 + 256, T - 256):
+            r1 = r0 + 256
+            want = R.asinh_attention(q[:, h:h + 1, r0:r1], k[:, h:h + 1, :r1], v[:, h:h + 1, :r1], n=16, c=8.0,
+                                     sink_logit=torch.zeros(1))
+            assert rel_l2(got[:, h:h + 1, r0:r1], want) < 1e-2, (h, r0)
+            want_stat = R.attention_row_stat(q[:, h:h + 1, r0:r1], k[:, h:h + 1, :r1], n=16, c=8.0,
+                                             sink_logit=torch.zeros(1), shifted=False)
+            assert rel_l2(stat[:, h:h + 1, r0:r1], want_stat) < 2e-3, (h, r0)
+
+
+@pytest.mark.parametrize("which", ["none", "q", "k", "v", "v_nan"])
+def test_guard_inside_the_attention_kernel(which):
+    """From T * head_dim = 3/4 Mi on, a guarded stand-alone call takes the guard's maxima of q, k, v
+    with one warp of the attention kernel itself instead of a pass of its own.  In range the result is
+    the unshifted kernel's; one out-of-range row anywhere (here in the last head, far from row 0) must
+    still send the whole call down the shifted path."""
+    B, H, T, D = 1, 2, 6144, 128
+    q, k, v = (randn((B, H, T, D), 901 + i, torch.bfloat16) for i in range(3))
+    if which == "q":
+        q[0, 1, 5000] = 300.0
+    elif which == "k":
+        k[0, 1, 4097] = 300.0
+    elif which == "v":
+        v[0, 1, 6143, 77] = 1e9
+    elif which == "v_nan":
+        v[0, 0, 3000, 1] = float("nan")
+    qd, kd, vd = dev(q, k, v)
+    got, stat, kind = A.flash_attention(qd, kd, vd, None, kind="asinh", n=16, c=8.0, range_guard=True, return_stat=True)
+    assert int(kind) == (1 if which == "none" else 2)
+    if which == "v_nan":
+        return                                         # the output carries the NaN either way
+    assert torch.isfinite(got).all() and torch.isfinite(stat).all()
+    for h, r0 in ((0, 0), (1, 4864), (1, T - 256)):
+        r1 = r0 + 256
+        want = R.asinh_attention(q[:, h:h + 1, r0:r1], k[:, h:h + 1, :r1], v[:, h:h + 1, :r1], n=16, c=8.0)
+        assert rel_l2(got[:, h:h + 1, r0:r1], want) < 1e-2, (h, r0)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
