@@ -22,8 +22,13 @@ from . import ops
 class _Attention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, sink, n, c, causal, range_guard):
+        # Without the guard the reference's default would be the unshifted form with a score clamp, whose
+        # backward zeroes the slope of clamped scores (flash.py:346, 357-360, 698-704); the backward
+        # kernels here rebuild weights from unclamped scores.  So the unguarded differentiable call takes
+        # the max-shifted form, which needs no clamp and is exact for any input.
         o, stat, kind = ops.flash_attention(q, k, v, sink, kind="asinh", n=n, c=c, causal=causal,
-                                            range_guard=range_guard, return_stat=True)
+                                            range_guard=range_guard, shift=None if range_guard else True,
+                                            return_stat=True)
         ctx.save_for_backward(q, k, v, o, stat, kind, sink if sink is not None else q.new_empty(0))
         ctx.has_sink, ctx.n, ctx.c, ctx.causal = sink is not None, n, c, causal
         return o
@@ -41,7 +46,8 @@ def attention(q, k, v, sink_logit: Optional[torch.Tensor] = None, *, n: int = 16
               causal: bool = True, range_guard: bool = True):
     """Differentiable asinh-power attention on bf16 (B,H,T,D) tensors; `sink_logit` is a float32 (H,)
     tensor or None.  Forward: `ops.flash_attention`; backward: `ops.flash_attention_backward` fed with
-    the statistic the forward saved."""
+    the statistic the forward saved.  `range_guard=False` runs the max-shifted form (never the
+    clamped unshifted one, whose clamp the backward kernels do not model)."""
     if sink_logit is not None and (sink_logit.dtype != torch.float32 or sink_logit.shape != (q.shape[1],)):
         raise ValueError("sink_logit must be a float32 tensor of shape (H,)")
     return _Attention.apply(q, k, v, sink_logit, int(n), float(c), bool(causal), bool(range_guard))

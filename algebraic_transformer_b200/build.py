@@ -80,7 +80,32 @@ def build(force=False, verbose=False):
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    build_xla_ffi(verbose)
     return LIB
+
+
+def build_xla_ffi(verbose=False):
+    """`lib/libalg_b200_xla.so`: the XLA typed-FFI handlers of csrc/xla_ffi.cc, linked against
+    libalg_b200.so.  Needs the jaxlib headers (`jax.ffi.include_dir()`); returns None, leaving the
+    rest of the package untouched, where JAX is not installed."""
+    try:
+        import jax
+        inc = jax.ffi.include_dir()
+    except Exception:
+        return None
+    src = os.path.join(CSRC, "xla_ffi.cc")
+    out = os.path.join(LIBDIR, "libalg_b200_xla.so")
+    if not _stale(out, [src, LIB] + _headers()):
+        return out
+    cuda_inc = os.path.join(os.path.dirname(os.path.dirname(_nvcc())), "include") if os.path.isabs(_nvcc()) else "/usr/local/cuda/include"
+    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-I", inc, "-I", cuda_inc, src, "-o", out,
+           "-L", LIBDIR, "-lalg_b200", "-Wl,-rpath,$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"xla_ffi.cc failed to build:\n{r.stdout}\n{r.stderr}")
+    if verbose:
+        print(r.stderr)
+    return out
 
 
 if __name__ == "__main__":

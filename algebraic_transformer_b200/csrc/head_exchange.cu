@@ -44,7 +44,9 @@ __global__ void __launch_bounds__(XT) head_exchange_kernel(const ExchangeParams 
   if (threadIdx.x == 0) s_call = *reinterpret_cast<volatile unsigned*>(p.call_counter) + 1u;
   __syncthreads();
   const unsigned call = s_call;
-  const size_t plane = size_t(2) * p.N;                            // one rank's (l, zt) pair
+  // Planes are laid out by the region's CAPACITY, not by this call's N: consecutive calls may differ
+  // in N, and the two parities must never overlap while a slow peer still reads the previous call's.
+  const size_t plane = size_t(2) * p.N_capacity;                   // one rank's (l, zt) pair
   const size_t parity_off = size_t(call & 1u) * p.world * plane;
 
   // ---- 1. reduce my slots, push to every peer
@@ -179,7 +181,7 @@ extern "C" int alg_head_fwd_exchange(const alg_head_args* a, const alg_head_exch
   if (int rc = fast ? launch_head_tcgen05(p, stream) : launch_head_mma(p, stream)) return rc;
 
   ExchangeParams e{};
-  e.l_part = p.l_part; e.zt_part = p.zt_part; e.slots = p.splits; e.N = a->N;
+  e.l_part = p.l_part; e.zt_part = p.zt_part; e.slots = p.splits; e.N = a->N; e.N_capacity = x->N_capacity;
   e.log2n = p.log2n; e.inv_c = p.inv_c; e.clamp = p.clamp;
   e.rank = x->rank; e.world = x->world;
   for (int r = 0; r < x->world; ++r) {

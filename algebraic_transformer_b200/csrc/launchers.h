@@ -217,6 +217,7 @@ struct ExchangeParams {
   const float* l_part;
   const float* zt_part;
   int slots, N;
+  int N_capacity;                        // rows the exchange region was sized for (layout of its planes)
   int log2n;
   float inv_c, clamp;
   int rank, world;

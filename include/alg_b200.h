@@ -165,14 +165,14 @@ typedef struct {
                               with the fused prologue) */
 } alg_attn_args;
 
-/* A guarded call (variant = ALG_VARIANT_GUARD) without guard_words and without the fused prologue, on a
- * shape the tcgen05 kernel covers, runs its pass over q, k, v on a stream owned by the library, beside
- * the attention kernel, which is launched for the unshifted form at once; the stable kernel follows
- * both and redoes the work only if the guard failed.  The caller sees one ordered operation on
- * `stream` (fork and join by events; legal inside stream capture once the per-device stream and events
- * exist — they are created on the first such call outside capture; a first call made during capture
- * keeps everything on `stream`).  Until the call's work has completed o, stat and stat_kind may hold
- * the speculative result.  ALG_ATTN_SERIAL_GUARD=1 in the environment keeps everything on `stream`. */
+/* A guarded call (variant = ALG_VARIANT_GUARD) without guard_words and without the fused prologue has to
+ * take the guard's maxima of q, k, v itself.  On long sequences that the tcgen05 kernel covers
+ * (Tq * D >= 786432) that kernel is launched at once for the unshifted form and takes the maxima
+ * with one of its own warps, into per-CTA records in the workspace; the stable kernel follows and
+ * redoes the work only if the guard failed, so until the call's work has completed o, stat and
+ * stat_kind may hold the speculative result.  Otherwise a statistics pass runs first.  Either way
+ * the call only enqueues kernels (and at most a 16-byte memset) on `stream`: it creates no stream or
+ * event of its own and can be captured into a CUDA graph. */
 ALG_API size_t alg_attn_workspace_bytes(const alg_attn_args* args);
 ALG_API int alg_attn_fwd(const alg_attn_args* args, void* stream);
 

@@ -1,6 +1,8 @@
 """Prefill body (PyTorch-hosted GEMMs + this package's kernels) against the CPU restatement
 of the reference model, and the elementwise kernels against the oracle."""
 
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -119,4 +121,27 @@ def test_tiny_prefill_matches_reference_model(head_dim, T, fused):
     assert rel_l2(got_h, want_h) < 2e-2                  # two layers of bf16 activations
     obj, pt, nll = model.loss(tokens.to(DEV), tokens.to(DEV), want_nll=True)
     assert rel_l2(nll, R.nll_from_pt(pt_w)) < 1e-2
+    np.testing.assert_allclose(float(obj), float(obj_w), rtol=5e-3)
+
+
+@pytest.mark.parametrize("size,vocab,T", [("125m", 50304, 1024), ("350m", 32000, 2048)])
+def test_prefill_at_the_benchmark_shapes(size, vocab, T):
+    """Benchmark configurations 3 and 4 at their real widths and depths (125M: 12 layers, d 768,
+    12 heads of 64, vocabulary 50304; 350M: 24 layers, d 1024, 16 heads of 64, vocabulary 32000), one
+    sequence each so that the CPU model finishes in seconds: per-token NLL within rel-L2 1e-2 of
+    oracle/model_ref.py (itself pinned to the reference's model.py)."""
+    cfg = P.PrefillConfig.preset(size, vocab_size=vocab)
+    params = P.init_params(cfg, seed=0)
+    g = torch.Generator().manual_seed(3)
+    tokens = torch.randint(0, vocab, (1, T), generator=g)
+    torch.set_num_threads(max(1, (os.cpu_count() or 1)))
+    want_h = M.forward_hidden(params, tokens, cfg)
+    obj_w, pt_w = M.head_loss(params, want_h, tokens, cfg)
+    model = P.Prefill(cfg, params, DEV, seq_len=T)
+    got_h = model.hidden(tokens.to(DEV))
+    obj, pt, nll = model.loss(tokens.to(DEV), tokens.to(DEV), want_nll=True)
+    e_h, e_nll = rel_l2(got_h, want_h), rel_l2(nll, R.nll_from_pt(pt_w))
+    print(f"{size}: hidden rel-L2 {e_h:.2e}, NLL rel-L2 {e_nll:.2e}")
+    assert e_nll < 1e-2, (e_h, e_nll)
+    assert e_h < 6e-2, e_h                               # bf16 activations through every layer, summation order differs
     np.testing.assert_allclose(float(obj), float(obj_w), rtol=5e-3)

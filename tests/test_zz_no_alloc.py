@@ -6,7 +6,9 @@ memory plan.  They cannot give alg_head_fwd its workspace, so alg_head_fwd_stati
 the scratch in an array compiled into the library.  This test drives both entry points
 through the C ABI on the same inputs and expects the same per-row statistic — twice in a
 row with different inputs, because the second call finds the first call's partials still
-sitting in the shared array and must not be affected by them.
+sitting in the shared array and must not be affected by them.  The expected values come from
+the CPU oracle (`fused_head_stats`), so the two entry points are not merely checked against
+each other.
 
 Collected last on purpose (file name), so a run that stops at the first failure has already
 covered every other test; it also passes when run alone in a fresh process.
@@ -19,6 +21,7 @@ import pytest
 import torch
 
 from algebraic_transformer_b200 import _lib as L
+from oracle import algebraic_ref as R
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -58,6 +61,12 @@ def test_static_scratch_head_matches_workspace_head_twice(impl):
         torch.cuda.synchronize()
         assert torch.isfinite(got).all()
         np.testing.assert_allclose(got.cpu(), want.cpu(), rtol=1e-6, atol=0)
+        # both against the oracle: row normaliser l and target logit zt of the fused kernel
+        l_ref, zt_ref = R.fused_head_stats(h.cpu(), e.cpu(), t.cpu(), 8, 2.0)
+        for name, res in (("alg_head_fwd_static", got), ("alg_head_fwd", want)):
+            l, zt = res[0].cpu().double(), res[1].cpu().double()
+            assert float((l - l_ref.double()).norm() / l_ref.double().norm()) < 1e-3, name
+            np.testing.assert_allclose(zt, zt_ref.double(), rtol=2e-3, atol=2e-3, err_msg=name)
 
 
 def test_static_scratch_head_rejects_oversized_problem():
