@@ -67,13 +67,20 @@ class QkvProjArgs(C.Structure):
     _fields_ = [("x", C.c_void_p), ("w", C.c_void_p), ("qkv", C.c_void_p), ("q_gain", C.c_void_p),
                 ("k_gain", C.c_void_p), ("cos", C.c_void_p), ("sin", C.c_void_p), ("eps", C.c_float),
                 ("M", C.c_int), ("d", C.c_int), ("H", C.c_int), ("D", C.c_int), ("T", C.c_int),
-                ("ld_x", C.c_int64), ("attn_c", C.c_float), ("guard", C.c_void_p), ("status", C.c_void_p)]
+                ("ld_x", C.c_int64), ("attn_c", C.c_float), ("guard", C.c_void_p), ("status", C.c_void_p),
+                ("row_ss", C.c_void_p), ("ss_slots", C.c_int), ("row_eps", C.c_float)]
 
 
 class GluProjArgs(C.Structure):
     _fields_ = [("x", C.c_void_p), ("w", C.c_void_p), ("out", C.c_void_p), ("M", C.c_int), ("d", C.c_int),
                 ("f", C.c_int), ("ld_x", C.c_int64), ("ld_out", C.c_int64), ("beta", C.c_float),
-                ("status", C.c_void_p)]
+                ("status", C.c_void_p), ("row_ss", C.c_void_p), ("ss_slots", C.c_int), ("row_eps", C.c_float)]
+
+
+class ResidProjArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("w", C.c_void_p), ("resid", C.c_void_p), ("out", C.c_void_p),
+                ("ss_out", C.c_void_p), ("M", C.c_int), ("K", C.c_int), ("N", C.c_int), ("ld_x", C.c_int64),
+                ("ld_resid", C.c_int64), ("ld_out", C.c_int64), ("status", C.c_void_p)]
 
 
 class DecodeArgs(C.Structure):
@@ -131,6 +138,9 @@ SYMBOLS = {
     "alg_cast_f32_to_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "alg_qkv_proj_fwd": (C.c_int, [C.POINTER(QkvProjArgs), C.c_void_p]),
     "alg_glu_proj_fwd": (C.c_int, [C.POINTER(GluProjArgs), C.c_void_p]),
+    "alg_resid_proj_fwd": (C.c_int, [C.POINTER(ResidProjArgs), C.c_void_p]),
+    "alg_resid_proj_ss_slots": (C.c_int, [C.c_int, C.c_int]),
+    "alg_row_sumsq": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_int64, C.c_void_p, C.c_void_p]),
     "alg_selftest_bounded_wait": (C.c_int, [C.c_void_p, C.c_ulonglong, C.c_void_p, C.c_void_p]),
     "alg_rms_norm_fwd":(C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_void_p]),
     "alg_alu_glu_fwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int64, C.c_int64, C.c_float,

@@ -189,10 +189,106 @@ __device__ __forceinline__ void weigh_half_tile(uint32_t s_taddr, int half, int 
   signal_weights(p_full);
 }
 
-__device__ __forceinline__ bool elect_one() {       // one lane of a converged warp
-  uint32_t pred = 0;
-  asm volatile("{\n.reg .pred P;\nelect.sync _|P, 0xffffffff;\nselp.u32 %0, 1, 0, P;\n}\n" : "=r"(pred));
-  return pred != 0;
+// ---- max-shifted form (src/algebraic/kernels/flash.py:235-259): p = (rho(x) rho(-m'))^n with the
+// running row maximum m', so that no weight exceeds 1 whatever the inputs.  rho is taken in its
+// cancellation-free form: T = |x| + sqrt(1 + x^2) >= 1, rho(x) = T for x >= 0 and 1/T below, which
+// costs a reciprocal per score on top of the rsqrt (the MUFU then bounds this form: about twice
+// the unshifted time per tile).  Scores are scaled explicitly here (Q is not pre-scaled).
+
+// First pass over a tile: the row's largest score in kernel units (masked entries excluded).
+template <bool DIAG>
+__device__ __forceinline__ float tile_row_max(uint32_t s_taddr, int r, float scale) {
+  uint32_t a[32], b[32];
+  float m0 = -3.0e38f, m1 = -3.0e38f, m2 = -3.0e38f, m3 = -3.0e38f;
+  auto scan = [&](const uint32_t* s, int col0) {
+    if (DIAG && col0 > (r | 31)) return;
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      float x0 = __uint_as_float(s[i]) * scale, x1 = __uint_as_float(s[i + 1]) * scale;
+      float x2 = __uint_as_float(s[i + 2]) * scale, x3 = __uint_as_float(s[i + 3]) * scale;
+      if (DIAG) {
+        x0 = (col0 + i <= r) ? x0 : -3.0e38f;     x1 = (col0 + i + 1 <= r) ? x1 : -3.0e38f;
+        x2 = (col0 + i + 2 <= r) ? x2 : -3.0e38f; x3 = (col0 + i + 3 <= r) ? x3 : -3.0e38f;
+      }
+      m0 = fmaxf(m0, x0); m1 = fmaxf(m1, x1); m2 = fmaxf(m2, x2); m3 = fmaxf(m3, x3);
+    }
+  };
+  tmem_ld_32x32(s_taddr, a);
+  tmem_ld_wait_for(a);
+  tmem_ld_32x32(s_taddr + 32, b);
+  scan(a, 0);
+  tmem_ld_wait_for(b);
+  tmem_ld_32x32(s_taddr + 64, a);
+  scan(b, 32);
+  tmem_ld_wait_for(a);
+  tmem_ld_32x32(s_taddr + 96, b);
+  scan(a, 64);
+  tmem_ld_wait_for(b);
+  scan(b, 96);
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+
+// 32 scores -> 32 shifted weights (rho(x) sigma)^n; NaN scores give NaN weights (as the reference's do).
+template <int LOG2N, bool DIAG>
+__device__ __forceinline__ void weigh_shifted(const uint32_t* s, float scale, float sigma, int col0, int r, float2& la,
+                                              float2& lb, uint32_t* packed) {
+  if (DIAG && col0 > (r | 31)) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) packed[i] = 0u;
+    return;
+  }
+  const float2 sc = make_float2(scale, scale), one = make_float2(1.f, 1.f), sg = make_float2(sigma, sigma);
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    const float2 x0 = __fmul2_rn(make_float2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), sc);
+    const float2 x1 = __fmul2_rn(make_float2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), sc);
+    const float2 rad0 = __ffma2_rn(x0, x0, one), rad1 = __ffma2_rn(x1, x1, one);
+    const float2 rs0 = make_float2(rsqrt_approx(rad0.x), rsqrt_approx(rad0.y));
+    const float2 rs1 = make_float2(rsqrt_approx(rad1.x), rsqrt_approx(rad1.y));
+    // T = |x| + sqrt(1 + x^2); an infinite score has rad * rsqrt(rad) = inf * 0: take |x| there
+    float2 T0 = __ffma2_rn(rad0, rs0, make_float2(fabsf(x0.x), fabsf(x0.y)));
+    float2 T1 = __ffma2_rn(rad1, rs1, make_float2(fabsf(x1.x), fabsf(x1.y)));
+    T0.x = (rad0.x < 3.0e38f) ? T0.x : fabsf(x0.x); T0.y = (rad0.y < 3.0e38f) ? T0.y : fabsf(x0.y);
+    T1.x = (rad1.x < 3.0e38f) ? T1.x : fabsf(x1.x); T1.y = (rad1.y < 3.0e38f) ? T1.y : fabsf(x1.y);
+    float2 t0 = make_float2(x0.x >= 0.f ? T0.x : __fdividef(1.0f, T0.x), x0.y >= 0.f ? T0.y : __fdividef(1.0f, T0.y));
+    float2 t1 = make_float2(x1.x >= 0.f ? T1.x : __fdividef(1.0f, T1.x), x1.y >= 0.f ? T1.y : __fdividef(1.0f, T1.y));
+    t0 = __fmul2_rn(t0, sg); t1 = __fmul2_rn(t1, sg);
+#pragma unroll
+    for (int k = 0; k < LOG2N; ++k) { t0 = __fmul2_rn(t0, t0); t1 = __fmul2_rn(t1, t1); }
+    if (DIAG) {
+      t0.x = (col0 + i <= r) ? t0.x : 0.f;     t0.y = (col0 + i + 1 <= r) ? t0.y : 0.f;
+      t1.x = (col0 + i + 2 <= r) ? t1.x : 0.f; t1.y = (col0 + i + 3 <= r) ? t1.y : 0.f;
+    }
+    la = __fadd2_rn(la, t0);
+    lb = __fadd2_rn(lb, t1);
+    packed[i >> 1] = pack_bf16(t0.x, t0.y);
+    packed[(i >> 1) + 1] = pack_bf16(t1.x, t1.y);
+  }
+}
+
+// Second pass: the tile's shifted weights, written back as in weigh_tile.
+template <int LOG2N, bool DIAG>
+__device__ __forceinline__ void weigh_tile_shifted(uint32_t s_taddr, int r, float scale, float sigma, float2& la, float2& lb,
+                                                   uint64_t* p_half, uint64_t* p_full) {
+  uint32_t a[32], b[32], packed[16];
+  tmem_ld_32x32(s_taddr, a);
+  tmem_ld_wait_for(a);
+  tmem_ld_32x32(s_taddr + 32, b);
+  weigh_shifted<LOG2N, DIAG>(a, scale, sigma, 0, r, la, lb, packed);
+  tmem_st_32x16(s_taddr + p_col_of(0), packed);
+  tmem_ld_wait_for(b);
+  tmem_ld_32x32(s_taddr + 64, a);
+  weigh_shifted<LOG2N, DIAG>(b, scale, sigma, 32, r, la, lb, packed);
+  tmem_st_32x16(s_taddr + p_col_of(32), packed);
+  signal_weights(p_half);
+  tmem_ld_wait_for(a);
+  tmem_ld_32x32(s_taddr + 96, b);
+  weigh_shifted<LOG2N, DIAG>(a, scale, sigma, 64, r, la, lb, packed);
+  tmem_st_32x16(s_taddr + p_col_of(64), packed);
+  tmem_ld_wait_for(b);
+  weigh_shifted<LOG2N, DIAG>(b, scale, sigma, 96, r, la, lb, packed);
+  tmem_st_32x16(s_taddr + p_col_of(96), packed);
+  signal_weights(p_full);
 }
 
 // Position in the K/V ring: slot and the parity of how often the ring has wrapped.
@@ -321,7 +417,7 @@ struct ScaleSplit {
 #define ALG_T(acc, expr) (expr)
 #endif
 
-template <int D, int LOG2N, int SPLIT>
+template <int D, int LOG2N, int SPLIT, bool SHIFT>
 __global__ void __launch_bounds__(nthreads<SPLIT>(), 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p, const ScaleSplit sc,
@@ -337,7 +433,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (lane == 0) ctl->shift_mode = sh ? 1 : 0;
   }
   __syncthreads();
-  if (ctl->shift_mode != 0) return;               // the guard failed: the stable kernel does this launch's work
+  // each form runs only when it is the one called for: under a guard the unshifted kernel leaves when the
+  // guard failed and the shifted kernel leaves when it held
+  if ((ctl->shift_mode != 0) != SHIFT) return;
 
   if (threadIdx.x == 0) {
     for (int w = 0; w < 2; ++w) { mbar_init(&ctl->q_full[w], 1); mbar_init(&ctl->q_ready[w], 1); mbar_init(&ctl->q_free[w], 1); }
@@ -354,7 +452,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     ctl->abort_flag = 0;
    
     fence_barrier_init();
-    if (blockIdx.x == 0 && p.stat_kind != nullptr) *p.stat_kind = ALG_VARIANT_NOSHIFT;
+    if (blockIdx.x == 0 && p.stat_kind != nullptr) *p.stat_kind = SHIFT ? ALG_VARIANT_SHIFT : ALG_VARIANT_NOSHIFT;
   }
   if (warp == 1) {
     tmem_alloc(&ctl->tmem_base, TMEM_COLS);
@@ -570,7 +668,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     for (int k = 0; ok && item_at(p, lists, k, it); ++k) {
       const int nk = (w == 0) ? it.n0 : it.n1;
       float l = 0.f;                                // the sink's weight, fetched while the first scores are computed
-      if (p.sink != nullptr) l = pow2n<LOG2N>(rho_stable(p.sink[it.h] * p.inv_c)) * sc.inv_mn;
+      float m_run = -1.0e30f;                       // shifted form: running row maximum (kernel units) ...
+      if (p.sink != nullptr) {
+        if (SHIFT) { m_run = p.sink[it.h] * p.inv_c; l = 1.0f; }   // ... which starts at the sink, whose weight under its own shift is 1
+        else l = pow2n<LOG2N>(rho_stable(p.sink[it.h] * p.inv_c)) * sc.inv_mn;
+      }
       float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
       for (int j = 0; j < nk && ok; ++j) {
         if (!ALG_T(tm0, bw.wait(&ctl->s_full[w], (tiles_before + j) & 1u))) { ok = false; break; }
@@ -585,7 +687,37 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #ifdef ALG_ATTN_TIMING
         const long long tc0 = clock64();
 #endif
-        if (SPLIT == 2) {
+        if (SHIFT) {
+          // pass 1: the tile's row maximum; then the rescale factor of what has been accumulated so far
+          const float tmax = (j == nk - 1) ? tile_row_max<true>(s_taddr, r, p.scale) : tile_row_max<false>(s_taddr, r, p.scale);
+          const float m_new = fmaxf(m_run, tmax);
+          if (j == 0 && p.sink == nullptr) m_run = m_new;          // without a sink the first tile sets the maximum
+          const float sigma = rho_stable(-m_new);
+          const float alpha = pow2n<LOG2N>(rho_stable(m_run) * sigma);
+          // O_w of the earlier tiles is at rest (S_w(j) complete means P_w(j-1).V complete): rescale it in
+          // tensor memory where some row's maximum moved; an unchanged row multiplies by exactly 1
+          const bool moved = j > 0 && alpha != 1.0f;
+          if (__any_sync(0xffffffffu, moved)) {
+            const float a_row = (j > 0) ? alpha : 1.0f;
+#pragma unroll 1
+            for (int chunk = 0; chunk < D / 32; ++chunk) {
+              uint32_t o[32];
+              const uint32_t o_taddr = tmem_base + lane_sel + C::O_COL + w * D + chunk * 32;
+              tmem_ld_32x32(o_taddr, o);
+              tmem_ld_wait_for(o);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * a_row);
+              tmem_st_32x32(o_taddr, o);
+            }
+            tmem_st_wait();
+          }
+          l *= alpha;                                      // sink and earlier tiles, now relative to the new maximum
+          m_run = m_new;
+          if (j == nk - 1) weigh_tile_shifted<LOG2N, true>(s_taddr, r, p.scale, sigma, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
+          else weigh_tile_shifted<LOG2N, false>(s_taddr, r, p.scale, sigma, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
+          l += (la.x + la.y) + (lb.x + lb.y);              // this tile's weights
+          la = make_float2(0.f, 0.f); lb = make_float2(0.f, 0.f);
+        } else if (SPLIT == 2) {
           if (j == nk - 1) weigh_half_tile<LOG2N, true>(s_taddr, half, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);   // diagonal tile: masked
           else weigh_half_tile<LOG2N, false>(s_taddr, half, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
         } else {
@@ -617,7 +749,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       tc_fence_after();
       item_at(p, lists, k, it);                            // recomputed: nothing of it stays live over the tile loop
-      l += part;
+      l += part;                                    // shifted form: the last tile's sums (already at the final maximum)
       const float inv = 1.0f / l;
       const int row = it.row0 + w * BQ + r;
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + it.b * p.os.b + it.h * p.os.h + int64_t(row) * p.os.t;
@@ -642,8 +774,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
 #ifndef ALG_ATTN_TIMING
-      // 1 / l of the reference = 1 / (l' m^n)
-      if (p.stat != nullptr && half == 0) p.stat[(int64_t(it.b) * p.H + it.h) * p.Tq + row] = inv * sc.inv_mn;
+      // unshifted: 1 / l of the reference = 1 / (l' m^n); shifted: rho(-m) l^(-1/n)  (flash.py:271-284)
+      if (p.stat != nullptr && half == 0)
+        p.stat[(int64_t(it.b) * p.H + it.h) * p.Tq + row] = SHIFT ? rho_stable(-m_run) * inv_root_rt(l, LOG2N) : inv * sc.inv_mn;
 #endif
     }
 #ifdef ALG_ATTN_TIMING
@@ -702,7 +835,7 @@ int make_qkv_map(CUtensorMap* tm, const void* base, const Strides3& s, int B, in
   return make_tmap_bf16(tm, base, 4, dims, strides, box, true);
 }
 
-template <int D, int LOG2N, int SPLIT>
+template <int D, int LOG2N, int SPLIT, bool SHIFT>
 int launch_dns(const AttnParams& p, cudaStream_t stream) {
   CUtensorMap tq, tk, tv;
   if (int rc = make_qkv_map(&tq, p.q, p.qs, p.B, p.H, p.Tq, D)) return rc;
@@ -717,8 +850,9 @@ int launch_dns(const AttnParams& p, cudaStream_t stream) {
     sc.pow2 = float(ldexp(1.0, ex - 1));
     sc.kappa = float(1.0 / (m * m));
     sc.inv_mn = float(pow(m, -double(1 << LOG2N)));
+    if (SHIFT) { sc.pow2 = 1.0f; sc.kappa = 1.0f; sc.inv_mn = 1.0f; }   // the shifted form scales its scores itself
   }
-  auto kern = attn_tc_kernel<D, LOG2N, SPLIT>;
+  auto kern = attn_tc_kernel<D, LOG2N, SPLIT, SHIFT>;
   static PerDeviceOnce configured;
   int sms = 0;
   if (int rc = configured.run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes<D>())); }, &sms)) return rc;
@@ -745,8 +879,9 @@ int launch_dns(const AttnParams& p, cudaStream_t stream) {
 template <int D, int LOG2N>
 int launch_dn(const AttnParams& p, cudaStream_t stream) {
   static const int forced = [] { const char* e = getenv("ALG_ATTN_SPLIT"); return e != nullptr ? atoi(e) : 0; }();
+  if (p.tc_shift) return launch_dns<D, LOG2N, 1, true>(p, stream);     // one thread sees its whole row of a tile
   const int split = forced == 1 || forced == 2 ? forced : (D == 64 ? 2 : 1);
-  return split == 1 ? launch_dns<D, LOG2N, 1>(p, stream) : launch_dns<D, LOG2N, 2>(p, stream);
+  return split == 1 ? launch_dns<D, LOG2N, 1, false>(p, stream) : launch_dns<D, LOG2N, 2, false>(p, stream);
 }
 
 template <int D>
@@ -766,7 +901,7 @@ bool attn_tcgen05_supports(const AttnParams& p, int dtype) {
   const bool strides_fit = p.qs.t > 0 && p.ks.t > 0 && p.vs.t > 0 && p.qs.h >= 0 && p.qs.b >= 0 &&
                            p.ks.h >= 0 && p.ks.b >= 0 && p.vs.h >= 0 && p.vs.b >= 0;
   return dtype == ALG_BF16 && p.causal && p.Tq == p.Tk && p.Tq % (2 * BQ) == 0 && (p.D == 64 || p.D == 128) &&
-         p.log2n >= 3 && p.log2n <= 5 && p.variant != ALG_VARIANT_SHIFT && strides_fit &&
+         p.log2n >= 3 && p.log2n <= 5 && strides_fit &&
          (p.B == 1 || p.qs.b > 0) && (p.H == 1 || p.qs.h > 0);
 }
 

@@ -230,8 +230,9 @@ int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
     p.guard_slots = attn_tcgen05_grid(p);
     if (size_t(p.guard_slots) * sizeof(GuardWords) > kGuardBytes) { set_error("attention: more CTAs than guard records"); return ALG_ERR_UNSUPPORTED; }
     if (int rc = launch_attn_tcgen05(ps, stream)) return rc;
-    p.run_if = 2;                                       // the stable path runs only if the guard failed
-    return launch_attn_mma(p, a->dtype, stream);
+    p.run_if = 2;                                       // the max-shifted form runs only if the guard failed
+    p.tc_shift = 1;
+    return launch_attn_tcgen05(p, stream);
   }
   if (guarded && !guard_given) ALG_CUDA_TRY(cudaMemsetAsync(guard, 0, sizeof(GuardWords), stream));
   if (prologue || (guarded && !guard_given)) {
@@ -270,17 +271,21 @@ int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
     }
   }
 
-  const bool fast_ok = a->variant != ALG_VARIANT_SHIFT && !(a->score_clamp > 0.0f) && attn_tcgen05_supports(p, a->dtype);
+  // the tcgen05 kernel has the unshifted form without a score clamp and the max-shifted form
+  const bool shape_ok = attn_tcgen05_supports(p, a->dtype);
+  const bool fast_ok = shape_ok && (a->variant == ALG_VARIANT_SHIFT || !(a->score_clamp > 0.0f));
   if (a->impl == ALG_IMPL_TCGEN05 && !fast_ok) {
-    set_error("attention: the tcgen05 kernel covers bf16, causal Tq == Tk multiple of 128, unshifted or guarded");
+    set_error("attention: the tcgen05 kernel covers bf16, causal Tq == Tk multiple of 256, head_dim 64 or 128, no score clamp");
     return ALG_ERR_UNSUPPORTED;
   }
   if (fast_ok && a->impl != ALG_IMPL_MMA) {
+    if (a->variant == ALG_VARIANT_SHIFT) { p.tc_shift = 1; return launch_attn_tcgen05(p, stream); }
     p.run_if = guarded ? 1 : 0;
     if (int rc = launch_attn_tcgen05(p, stream)) return rc;
     if (!guarded) return ALG_OK;
-    p.run_if = 2;                                       // the stable path runs only if the guard failed
-    return launch_attn_mma(p, a->dtype, stream);
+    p.run_if = 2;                                       // the max-shifted form runs only if the guard failed
+    p.tc_shift = 1;
+    return launch_attn_tcgen05(p, stream);
   }
   p.run_if = 0;
   return launch_attn_mma(p, a->dtype, stream);
@@ -316,6 +321,11 @@ int alg_qkv_proj_fwd(const alg_qkv_proj_args* a, void* stream_) {
   }
   p.guard = static_cast<GuardWords*>(a->guard);
   p.status = a->status;
+  if (a->row_ss != nullptr && (a->ss_slots < 1 || !(a->row_eps > 0.0f) || !aligned16(a->row_ss))) {
+    set_error("qkv_proj: row_ss needs ss_slots >= 1, a positive row_eps and 16-byte alignment");
+    return ALG_ERR_INVALID;
+  }
+  p.row_ss = a->row_ss; p.ss_slots = a->ss_slots; p.row_eps = a->row_eps;
   if (a->M == 0) return ALG_OK;
   if (p.guard != nullptr) ALG_CUDA_TRY(cudaMemsetAsync(p.guard, 0, sizeof(GuardWords), stream));
   return launch_proj(p, a->x, a->w, 0, stream);
@@ -335,7 +345,54 @@ int alg_glu_proj_fwd(const alg_glu_proj_args* a, void* stream_) {
   p.out = static_cast<__nv_bfloat16*>(a->out); p.ld_out = a->ld_out;
   p.f = a->f; p.beta = a->beta; p.D = 64;
   p.status = a->status;
+  if (a->row_ss != nullptr && (a->ss_slots < 1 || !(a->row_eps > 0.0f) || !aligned16(a->row_ss))) {
+    set_error("glu_proj: row_ss needs ss_slots >= 1, a positive row_eps and 16-byte alignment");
+    return ALG_ERR_INVALID;
+  }
+  p.row_ss = a->row_ss; p.ss_slots = a->ss_slots; p.row_eps = a->row_eps;
   return launch_proj(p, a->x, a->w, 1, stream);
+}
+
+int alg_resid_proj_ss_slots(int M, int N) {
+  if (M < 1 || N < 1) return 0;
+  const int bn = proj_resid_tile_width(M, N);
+  return 2 * ((N + bn - 1) / bn);
+}
+
+int alg_resid_proj_fwd(const alg_resid_proj_args* a, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a == nullptr || a->x == nullptr || a->w == nullptr || a->resid == nullptr || a->out == nullptr) {
+    set_error("resid_proj: null argument");
+    return ALG_ERR_INVALID;
+  }
+  if (a->M < 0 || a->K < 64 || a->K % 64 != 0 || a->N < 64 || a->N % 64 != 0 || a->ld_x < a->K || a->ld_x % 8 != 0 ||
+      a->ld_resid < a->N || a->ld_resid % 8 != 0 || a->ld_out < a->N || a->ld_out % 8 != 0) {
+    set_error("resid_proj: K and N multiples of 64, row strides multiples of 8 and wide enough");
+    return ALG_ERR_INVALID;
+  }
+  if (!aligned16(a->x) || !aligned16(a->w) || !aligned16(a->resid) || !aligned16(a->out) ||
+      (a->ss_out != nullptr && !aligned16(a->ss_out))) {
+    set_error("resid_proj: 16-byte alignment required");
+    return ALG_ERR_INVALID;
+  }
+  if (a->M == 0) return ALG_OK;
+  ProjParams p{};
+  p.M = a->M; p.K = a->K; p.N = a->N; p.ld_x = a->ld_x;
+  p.out = static_cast<__nv_bfloat16*>(a->out); p.ld_out = a->ld_out;
+  p.resid = static_cast<const __nv_bfloat16*>(a->resid); p.ld_resid = a->ld_resid;
+  p.ss_out = a->ss_out;
+  p.D = 64;
+  p.status = a->status;
+  return launch_proj(p, a->x, a->w, 3, stream);
+}
+
+int alg_row_sumsq(const void* x, int64_t rows, int d, int64_t ld_x, float* ss_out, void* stream) {
+  if (rows < 0 || d < 8 || d % 8 != 0 || ld_x < d || ld_x % 8 != 0 || (rows > 0 && (x == nullptr || ss_out == nullptr)) ||
+      !aligned16(x)) {
+    set_error("row_sumsq: d a multiple of 8, row stride a multiple of 8 and >= d, 16-byte aligned rows");
+    return ALG_ERR_INVALID;
+  }
+  return launch_row_sumsq(x, rows, d, ld_x, ss_out, static_cast<cudaStream_t>(stream));
 }
 
 size_t alg_attn_bwd_workspace_bytes(const alg_attn_bwd_args* a) {

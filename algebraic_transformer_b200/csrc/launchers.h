@@ -71,6 +71,7 @@ struct AttnParams {
   int run_if;              // 0 always, 1 only when the guard holds, 2 only when it fails
   int* status;
   GuardWords* guard_out;   // tcgen05 kernel only: CTA i writes the maxima of the rows it looked at to guard_out[i]
+  int tc_shift;            // tcgen05 kernel only: launch the max-shifted form (it runs when the shift is called for)
 };
 int launch_attn_mma(const AttnParams& p, int dtype, cudaStream_t stream);
 bool attn_tcgen05_supports(const AttnParams& p, int dtype);
@@ -162,8 +163,19 @@ struct ProjParams {
   float inv_c, clamp, n_over_c, gscale;   // 1/c, logit clamp, n/c, upstream gradient / M
   int head_kind;                          // ALG_HEAD_ALG_CE, or ALG_HEAD_CE: `l` holds the rows' logsumexp
   int* status;
+  // row scale of the QKV / GLU epilogues: tau = rsqrt(sum over slots of row_ss[slot][row] / K + row_eps)
+  const float* row_ss;     // (ss_slots, M) partial sums of squares of the input rows, or nullptr (tau = 1)
+  int ss_slots;
+  float row_eps;
+  // residual epilogue
+  const __nv_bfloat16* resid;   // (M, N) added to the product
+  int64_t ld_resid;
+  float* ss_out;           // (2 * ceil(N / tile width), M) partial sums of squares of the rows written, or nullptr
 };
-int launch_proj(const ProjParams& p, const void* x, const void* w, int epi, cudaStream_t stream);   // epi 0 QKV, 1 GLU, 2 head dz
+int launch_proj(const ProjParams& p, const void* x, const void* w, int epi, cudaStream_t stream);   // epi 0 QKV, 1 GLU, 2 head dz, 3 residual
+int proj_resid_tile_width(int M, int N);
+// prefill_ops.cu
+int launch_row_sumsq(const void* x, int64_t rows, int d, int64_t ld, float* ss_out, cudaStream_t stream);
 
 // ---- decode -------------------------------------------------------------------------
 struct DecodeParams {

@@ -157,6 +157,36 @@ int launch_alu_glu(const void* gate, const void* up, void* out, int64_t rows, in
   return ALG_OK;
 }
 
+// Sum of squares of every row: one warp per row, 16-byte loads.
+__global__ void __launch_bounds__(256) row_sumsq_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int d, int64_t ld,
+                                                        float* __restrict__ ss_out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_global = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t warps_total = (int64_t(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t row = warp_global; row < rows; row += warps_total) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + row * ld);
+    float ss = 0.f;
+    for (int vi = lane; vi < d / 8; vi += 32) {
+      float v[8];
+      unpack8(src[vi], v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) ss_out[row] = ss;
+  }
+}
+
+int launch_row_sumsq(const void* x, int64_t rows, int d, int64_t ld, float* ss_out, cudaStream_t stream) {
+  if (rows == 0) return ALG_OK;
+  int64_t blocks = (rows + 7) / 8;
+  if (blocks > int64_t(sm_count()) * 8) blocks = int64_t(sm_count()) * 8;
+  row_sumsq_kernel<<<unsigned(blocks), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows, d, ld, ss_out);
+  ALG_CUDA_TRY(cudaGetLastError());
+  count_launch();
+  return ALG_OK;
+}
+
 }  // namespace alg
 
 using namespace alg;

@@ -10,6 +10,13 @@
 //   DZ   z = h . E^T once more, then the Alg-CE head's logit gradient dz from the saved row
 //        statistic (src/algebraic/kernels/fused_head.py:120-156), written as bf16 for the two
 //        library GEMMs dh = dz . E and dE = dz^T . h that follow, as the reference does.
+//   RESID out = resid + x . W^T (the block's out- and down-projection with its residual add,
+//        src/algebraic/model.py:183, 193: the product rounded to bf16, then a bf16 add), and per
+//        row the sum of squares of what was written, as one partial per 128 or 64 output columns:
+//        the RMS normalisation that follows in the reference (model.py:141-143) is then carried
+//        by the NEXT projection, which multiplies its accumulator rows by tau = rsqrt(mean + eps)
+//        (`row_ss`) and has the norm's gain folded into its weight columns.  The normalised
+//        activations never exist in memory and the norm is no launch of its own.
 //   GLU  [gate | up] = x . W_gu^T, then out = gate * ALU(up) — src/algebraic/model.py:184-193
 //        with algebraic.py's alu.  The weight rows are interleaved in blocks of 128 (gate
 //        block j, up block j, ...) so that one 256-wide accumulator tile holds both operands of
@@ -35,11 +42,12 @@ namespace {
 
 using namespace sm100;
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int BM = 128, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int BN_MAX = 256;                      // accumulator tile width: 256, or 128 for the residual GEMM on few rows
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + BN_MAX * BK * 2;   // ring slots are sized for the wide tile
 constexpr int NTHREADS = 320, EPI_THREADS = 256;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t IDESC = make_idesc_bf16(BM, BN, 0, 0);
 
 struct __align__(16) Control {
   uint64_t full[STAGES], empty[STAGES], tfull[2], tempty[2];
@@ -53,7 +61,7 @@ constexpr size_t SMEM_BYTES = STAGE_OFF + 8 * WARP_STAGE_BYTES + 1024;
 static_assert(sizeof(Control) <= 256, "control block outgrew its slot");
 static_assert(SMEM_BYTES + 1024 <= 232448, "shared memory budget (dynamic + the static gain table)");
 
-enum { EPI_QKV = 0, EPI_GLU = 1, EPI_DZ = 2 };
+enum { EPI_QKV = 0, EPI_GLU = 1, EPI_DZ = 2, EPI_RESID = 3 };
 
 __device__ __forceinline__ __nv_bfloat162 as_bf162(uint32_t u) { return *reinterpret_cast<__nv_bfloat162*>(&u); }
 __device__ __forceinline__ uint32_t as_u32(__nv_bfloat162 h) { return *reinterpret_cast<uint32_t*>(&h); }
@@ -91,6 +99,64 @@ __device__ __forceinline__ void store_rows64(const WarpOut& w, int lane, const u
     if (r < w.rows && ch * 8 < cols) *reinterpret_cast<uint4*>(w.base + int64_t(r) * w.ld + col + ch * 8) = val;
   }
   __syncwarp();
+}
+
+// The reverse: 64 consecutive elements of this thread's row of a row-major bf16 matrix (`base` = the
+// warp's first row, column 0) -> 32 packed pairs in registers, read as whole lines through the
+// same staging buffer.  Rows beyond `rows` read as zero.
+__device__ __forceinline__ void load_rows64(unsigned char* stage, const __nv_bfloat16* base, int64_t ld, int rows, int lane,
+                                            uint32_t* v, int col) {
+  const int sub = lane >> 3, ch = lane & 7;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int r = 4 * k + sub;
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    if (r < rows) val = *reinterpret_cast<const uint4*>(base + int64_t(r) * ld + col + ch * 8);
+    *reinterpret_cast<uint4*>(stage + r * 128 + ((ch ^ (r & 7)) << 4)) = val;
+  }
+  __syncwarp();
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const uint4 val = *reinterpret_cast<const uint4*>(stage + lane * 128 + ((c ^ (lane & 7)) << 4));
+    v[4 * c] = val.x; v[4 * c + 1] = val.y; v[4 * c + 2] = val.z; v[4 * c + 3] = val.w;
+  }
+  __syncwarp();
+}
+
+// ---- residual epilogue: 64 output columns of one row -------------------------------------------
+// out = resid + round_bf16(acc), a bf16 add (src/algebraic/model.py:183, 193: `x + a @ w`, both bf16);
+// returns the sum of squares of the 64 values written.
+__device__ __forceinline__ float resid_cols(const ProjParams& p, uint32_t taddr, const WarpOut& wo, const __nv_bfloat16* rbase,
+                                            int lane, int col) {
+  uint32_t res[32], out[32];
+  load_rows64(wo.stage, rbase, p.ld_resid, wo.rows, lane, res, col);
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32(taddr + c * 32, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t prod = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+      const uint32_t y = as_u32(__hadd2(as_bf162(res[c * 16 + i]), as_bf162(prod)));
+      out[c * 16 + i] = y;
+      ss = fmaf(pair_lo(y), pair_lo(y), ss);
+      ss = fmaf(pair_hi(y), pair_hi(y), ss);
+    }
+  }
+  store_rows64(wo, lane, out, col);
+  return ss;
+}
+
+// tau of this row for a projection whose input is the un-normalised residual stream: the partial sums
+// of squares the producing kernel left, added in slot order.
+__device__ __forceinline__ float row_tau(const ProjParams& p, int row, bool live) {
+  if (p.row_ss == nullptr) return 1.0f;
+  float ss = 0.f;
+  if (live)
+    for (int s = 0; s < p.ss_slots; ++s) ss += p.row_ss[int64_t(s) * p.M + row];
+  return rsqrtf(ss * (1.0f / float(p.K)) + p.row_eps);
 }
 
 // ---- head-backward epilogue: dz for 128 vocabulary columns of one row ------------------------
@@ -165,7 +231,7 @@ __device__ __forceinline__ void dz_cols(const ProjParams& p, uint32_t taddr, con
 template <int D>
 __device__ __forceinline__ void qkv_head(const ProjParams& p, const float* s_gain, uint32_t taddr, int kind,
                                          const uint32_t* tc, const uint32_t* ts, const WarpOut& wo, int lane, int col,
-                                         bool live, float& best_q, float& best_k, float& best_v) {
+                                         bool live, float tau_row, float& best_q, float& best_k, float& best_v) {
   constexpr int NP = D / 2, QP = D / 4;                // packed pairs per head / per half
   uint32_t pk[NP];                                     // the projection rounded to bf16 (the GEMM's output dtype)
   float ss = 0.f;
@@ -183,7 +249,7 @@ __device__ __forceinline__ void qkv_head(const ProjParams& p, const float* s_gai
       if (DOUBLE && c + 1 < D / 32) tmem_ld_32x32(taddr + (c + 1) * 32, nxt);
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const uint32_t w = pack_bf16(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1]));
+        const uint32_t w = pack_bf16(__uint_as_float(cur[2 * i]) * tau_row, __uint_as_float(cur[2 * i + 1]) * tau_row);
         pk[c * 16 + i] = w;
         if (kind == 2) {
           vmax2 = __hmax2(vmax2, __habs2(as_bf162(w)));
@@ -247,11 +313,11 @@ __device__ __forceinline__ void qkv_head(const ProjParams& p, const float* s_gai
 
 // ---- GLU epilogue ---------------------------------------------------------------------------
 // gu[0..15] = 16 gate accumulators, gu[16..31] = the matching up accumulators -> 8 packed outputs
-__device__ __forceinline__ void glu16(const uint32_t* gu, float beta, uint32_t* out) {
+__device__ __forceinline__ void glu16(const uint32_t* gu, float beta, float tau_row, uint32_t* out) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const uint32_t gp = pack_bf16(__uint_as_float(gu[2 * i]), __uint_as_float(gu[2 * i + 1]));
-    const uint32_t up = pack_bf16(__uint_as_float(gu[16 + 2 * i]), __uint_as_float(gu[16 + 2 * i + 1]));
+    const uint32_t gp = pack_bf16(__uint_as_float(gu[2 * i]) * tau_row, __uint_as_float(gu[2 * i + 1]) * tau_row);
+    const uint32_t up = pack_bf16(__uint_as_float(gu[16 + 2 * i]) * tau_row, __uint_as_float(gu[16 + 2 * i + 1]) * tau_row);
     // both values of the pair through the packed fp32 instructions
     const float2 uv = make_float2(pair_lo(up), pair_hi(up));
     const float2 one = make_float2(1.f, 1.f);
@@ -272,7 +338,7 @@ __device__ __forceinline__ void glu16(const uint32_t* gu, float beta, uint32_t* 
 
 // 64 output features of one row: gate columns from t_gate, up columns from t_up
 __device__ __forceinline__ void glu_cols(const ProjParams& p, uint32_t t_gate, uint32_t t_up, const WarpOut& wo, int lane,
-                                         int col) {
+                                         int col, float tau_row) {
   uint32_t a[32], b[32], o[32];
   tmem_ld_32x16(t_gate, a);
   tmem_ld_32x16(t_up, a + 16);
@@ -285,18 +351,19 @@ __device__ __forceinline__ void glu_cols(const ProjParams& p, uint32_t t_gate, u
       tmem_ld_32x16(t_gate + (c + 1) * 16, nxt);
       tmem_ld_32x16(t_up + (c + 1) * 16, nxt + 16);
     }
-    glu16(cur, p.beta, o + 8 * c);
+    glu16(cur, p.beta, tau_row, o + 8 * c);
   }
   store_rows64(wo, lane, o, col);
 }
 
-template <int EPI, int D>
+template <int EPI, int D, int BN>
 __global__ void __launch_bounds__(NTHREADS, 1)
 proj_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const ProjParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Control* ctl = reinterpret_cast<Control*>(smem + size_t(STAGES) * STAGE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t IDESC = make_idesc_bf16(BM, BN, 0, 0);
   __shared__ __align__(16) float s_gain[2 * 128];      // QKV epilogue: q gains [0,128), k gains [128,256)
   if (EPI == EPI_QKV && threadIdx.x < 2 * D) {
     const float* g = (threadIdx.x < D) ? p.q_gain : p.k_gain;
@@ -333,7 +400,7 @@ proj_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!bw.wait(&ctl->empty[stage], phase ^ 1u)) { ok = false; break; }
           unsigned char* dst = smem + size_t(stage) * STAGE_BYTES;
-          mbar_arrive_expect_tx(&ctl->full[stage], STAGE_BYTES);
+          mbar_arrive_expect_tx(&ctl->full[stage], A_BYTES + BN * BK * 2);
           tma_load_2d(dst, &tm_x, &ctl->full[stage], kb * BK, m * BM);
           tma_load_2d(dst + A_BYTES, &tm_w, &ctl->full[stage], kb * BK, n * BN);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -341,27 +408,31 @@ proj_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      uint32_t stage = 0, phase = 0, tile_count = 0;
-      const uint32_t a_lo0 = sw128_desc_lo(smem_u32(smem), 16), b_lo0 = sw128_desc_lo(smem_u32(smem) + A_BYTES, 16);
-      bool ok = true;
-      for (int u = blockIdx.x; u < tiles && ok; u += gridDim.x, ++tile_count) {
-        const uint32_t buf = tile_count & 1u, tphase = (tile_count >> 1) & 1u;
-        if (!bw.wait(&ctl->tempty[buf], tphase ^ 1u)) { ok = false; break; }
+    // The whole warp runs the loop and one elected lane issues: an issue then costs the thread about
+    // 32 cycles instead of 48, which matters for the 128-wide tile, whose MMAs take only 64.
+    uint32_t stage = 0, phase = 0, tile_count = 0;
+    const uint32_t a_lo0 = sw128_desc_lo(smem_u32(smem), 16), b_lo0 = sw128_desc_lo(smem_u32(smem) + A_BYTES, 16);
+    auto wait_all = [&](uint64_t* bar, uint32_t parity) { return __all_sync(0xffffffffu, bw.wait(bar, parity)) != 0; };
+    bool ok = true;
+    for (int u = blockIdx.x; u < tiles && ok; u += gridDim.x, ++tile_count) {
+      const uint32_t buf = tile_count & 1u, tphase = (tile_count >> 1) & 1u;
+      if (!wait_all(&ctl->tempty[buf], tphase ^ 1u)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * BN;
+      for (int kb = 0; kb < kblocks; ++kb) {
+        if (!wait_all(&ctl->full[stage], phase)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < kblocks; ++kb) {
-          if (!bw.wait(&ctl->full[stage], phase)) { ok = false; break; }
-          tc_fence_after();
+        if (elect_one()) {
           const uint32_t a_lo = a_lo0 + stage * (STAGE_BYTES >> 4), b_lo = b_lo0 + stage * (STAGE_BYTES >> 4);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
             umma_f16_ss_parts(d_tmem, a_lo + k * (UMMA_K * 2 >> 4), SW128_DESC_HI, b_lo + k * (UMMA_K * 2 >> 4),
                               SW128_DESC_HI, IDESC, (kb | k) != 0 ? 1u : 0u);
           umma_commit(&ctl->empty[stage]);             // smem stage is free once these MMAs retire
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (kb == kblocks - 1) umma_commit(&ctl->tfull[buf]);   // accumulator tile complete
         }
-        if (ok) umma_commit(&ctl->tfull[buf]);          // accumulator tile complete
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
     }
   } else {
@@ -394,6 +465,7 @@ proj_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
           ts[4 * i] = sv.x; ts[4 * i + 1] = sv.y; ts[4 * i + 2] = sv.z; ts[4 * i + 3] = sv.w;
         }
       }
+      const float tau_row = (EPI == EPI_QKV || EPI == EPI_GLU) ? row_tau(p, row, live) : 1.0f;   // before the wait, like the table rows
       if (!bw.wait(&ctl->tfull[buf], tphase)) { ok = false; break; }
       tc_fence_after();
       const uint32_t tbuf = tmem_base + lane_sel + buf * BN;
@@ -405,7 +477,7 @@ proj_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
           const int lcol = half * 128 + hh * D;          // column inside the tile
           const int gcol = n * BN + lcol;                // output feature
           if (gcol >= p.N) break;
-          qkv_head<D>(p, s_gain, tbuf + lcol, gcol / hd, tc, ts, wo, lane, gcol, live, best_q, best_k, best_v);
+          qkv_head<D>(p, s_gain, tbuf + lcol, gcol / hd, tc, ts, wo, lane, gcol, live, tau_row, best_q, best_k, best_v);
         }
       } else if (EPI == EPI_DZ) {
         // per-row constants of the head's backward: 1 / l_i and the common factor g / N
@@ -417,10 +489,20 @@ proj_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
           tgt = p.targets[row] - p.vocab_offset;
         }
         dz_cols(p, tbuf + half * 128, wo, lane, n * BN + half * 128, a_i, inv_l, tgt);
+      } else if (EPI == EPI_RESID) {
+        // this thread's BN / 2 columns of its row, 64 at a time; one partial sum of squares per thread
+        const __nv_bfloat16* rbase = p.resid + int64_t(wrow) * p.ld_resid;
+        float ss = 0.f;
+#pragma unroll 1
+        for (int u64 = 0; u64 < BN / 128; ++u64) {
+          const int lcol = half * (BN / 2) + u64 * 64;
+          if (n * BN + lcol < p.N) ss += resid_cols(p, tbuf + lcol, wo, rbase, lane, n * BN + lcol);
+        }
+        if (p.ss_out != nullptr && live) p.ss_out[int64_t(n * 2 + half) * p.M + row] = ss;
       } else {
         const int fcol = n * 128 + half * 64;            // output feature of this thread's first column
         if (fcol < p.f)
-          glu_cols(p, tbuf + half * 64, tbuf + 128 + half * 64, wo, lane, fcol);
+          glu_cols(p, tbuf + half * 64, tbuf + 128 + half * 64, wo, lane, fcol, tau_row);
       }
       tc_fence_before();
       mbar_arrive(&ctl->tempty[buf]);                    // this thread is done reading the buffer
@@ -453,9 +535,9 @@ proj_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
   }
 }
 
-template <int EPI, int D>
+template <int EPI, int D, int BN = BN_MAX>
 int launch_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const ProjParams& p, int grid, cudaStream_t stream) {
-  auto kern = proj_tc_kernel<EPI, D>;
+  auto kern = proj_tc_kernel<EPI, D, BN>;
   static PerDeviceOnce configured;
   if (int rc = configured.run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES)); })) return rc;
   kern<<<grid, NTHREADS, SMEM_BYTES, stream>>>(tm_x, tm_w, p);
@@ -466,6 +548,16 @@ int launch_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const ProjP
 
 }  // namespace
 
+// The residual GEMM's tile is 128 x 256 unless 128 x 128 tiles spread better over the SMs (few rows: a
+// rank's share of a batch split over many GPUs).  Cost model: rounds of tiles per CTA times the time of
+// one tile, a narrow tile taking a little more than half of a wide one.
+int proj_resid_tile_width(int M, int N) {
+  const int sms = sm_count(), mt = (M + BM - 1) / BM;
+  const int wide = mt * ((N + 255) / 256), narrow = mt * ((N + 127) / 128);
+  const double cost_wide = double((wide + sms - 1) / sms), cost_narrow = 0.55 * double((narrow + sms - 1) / sms);
+  return cost_narrow < cost_wide ? 128 : 256;
+}
+
 int launch_proj(const ProjParams& p, const void* x, const void* w, int epi, cudaStream_t stream) {
   if (p.M == 0) return ALG_OK;
   CUtensorMap tm_x, tm_w;
@@ -475,15 +567,18 @@ int launch_proj(const ProjParams& p, const void* x, const void* w, int epi, cuda
     const uint32_t box[2] = {BK, BM};
     if (int rc = make_tmap_bf16(&tm_x, x, 2, dims, strides, box, true)) return rc;
   }
+  const int bn = epi == 3 ? proj_resid_tile_width(p.M, p.N) : BN_MAX;
   {
     const uint64_t dims[2] = {uint64_t(p.K), uint64_t(p.N)};
     const uint64_t strides[1] = {uint64_t(p.K)};
-    const uint32_t box[2] = {BK, BN};
+    const uint32_t box[2] = {BK, uint32_t(bn)};
     if (int rc = make_tmap_bf16(&tm_w, w, 2, dims, strides, box, true)) return rc;
   }
   const int sms = sm_count();
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + bn - 1) / bn);
   const int grid = tiles < sms ? tiles : sms;
+  if (epi == 3) return bn == 128 ? launch_variant<EPI_RESID, 64, 128>(tm_x, tm_w, p, grid, stream)
+                                 : launch_variant<EPI_RESID, 64, 256>(tm_x, tm_w, p, grid, stream);
   if (epi == 1) return launch_variant<EPI_GLU, 64>(tm_x, tm_w, p, grid, stream);
   if (epi == 2) return launch_variant<EPI_DZ, 64>(tm_x, tm_w, p, grid, stream);
   return p.D == 64 ? launch_variant<EPI_QKV, 64>(tm_x, tm_w, p, grid, stream)

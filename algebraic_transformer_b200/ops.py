@@ -228,15 +228,18 @@ def alu_glu(gate: torch.Tensor, up: torch.Tensor, beta: float = 0.5, out=None) -
 def qkv_projection(x: torch.Tensor, w: torch.Tensor, n_heads: int, seq_len: int, cos: torch.Tensor,
                    sin: torch.Tensor, q_gain: Optional[torch.Tensor] = None, k_gain: Optional[torch.Tensor] = None,
                    eps: float = 1e-5, attn_c: float = 8.0, guard_words: Optional[torch.Tensor] = None,
-                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   out: Optional[torch.Tensor] = None, row_ss: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The q, k, v projections of a block with the QK-norm, the Cayley rotation and the range
     guard's maxima fused into the GEMM (src/algebraic/model.py:165-174).
 
     x: (M, d) bf16 rows in (batch, position) order, position = row % seq_len.  w: (3*H*D, d) bf16,
     one row per output feature (q heads, k heads, v heads).  cos, sin: (>= seq_len, D/2) bf16.
     Returns (M, 3*H*D) bf16: q and k normalised and rotated, v as projected.  `guard_words`
-    (4 int32, device) receives the maxima for `flash_attention(..., guard_words=...)`."""
-    _require_cuda(x, w, cos, sin, q_gain, k_gain, guard_words)
+    (4 int32, device) receives the maxima for `flash_attention(..., guard_words=...)`.
+    `row_ss` (slots, M) float32: x is the un-normalised residual stream and the block's RMS norm is
+    applied here as a row scale (the norm's gain folded into `w` by the caller); see `resid_projection`."""
+    _require_cuda(x, w, cos, sin, q_gain, k_gain, guard_words, row_ss)
+    _check_row_ss(row_ss, x.shape[0])
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.ndim != 2 or w.ndim != 2 or x.stride(1) != 1:
         raise ValueError("qkv_projection needs bf16 (M, d) activations and (3*H*D, d) weights")
     M, d = x.shape
@@ -256,7 +259,8 @@ def qkv_projection(x: torch.Tensor, w: torch.Tensor, n_heads: int, seq_len: int,
         raise ValueError("out must be contiguous (M, 3*H*D)")
     a = L.QkvProjArgs(x=x.data_ptr(), w=w.data_ptr(), qkv=y.data_ptr(), q_gain=_ptr(q_gain), k_gain=_ptr(k_gain),
                       cos=cos.data_ptr(), sin=sin.data_ptr(), eps=float(eps), M=M, d=d, H=n_heads, D=D, T=int(seq_len),
-                      ld_x=x.stride(0), attn_c=float(attn_c), guard=_ptr(guard_words), status=None)
+                      ld_x=x.stride(0), attn_c=float(attn_c), guard=_ptr(guard_words), status=None,
+                      row_ss=_ptr(row_ss), ss_slots=0 if row_ss is None else row_ss.shape[0], row_eps=float(eps))
     L.check(L.load().alg_qkv_proj_fwd(a, _stream()))
     return y
 
@@ -271,10 +275,13 @@ def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor
 
 
 @_on_tensor_device
-def glu_projection(x: torch.Tensor, w: torch.Tensor, beta: float = 0.5, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def glu_projection(x: torch.Tensor, w: torch.Tensor, beta: float = 0.5, out: Optional[torch.Tensor] = None,
+                   row_ss: Optional[torch.Tensor] = None, eps: float = 1e-5) -> torch.Tensor:
     """gate * alu(up, beta) with gate = x @ w_g and up = x @ w_u computed by the same kernel
-    (src/algebraic/model.py:184-193); `w` comes from `interleave_gate_up`.  x: (M, d) bf16."""
-    _require_cuda(x, w)
+    (src/algebraic/model.py:184-193); `w` comes from `interleave_gate_up`.  x: (M, d) bf16.
+    `row_ss`, `eps`: as in `qkv_projection` (the norm in front of gate and up applied as a row scale)."""
+    _require_cuda(x, w, row_ss)
+    _check_row_ss(row_ss, x.shape[0])
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.ndim != 2 or w.ndim != 2 or x.stride(1) != 1:
         raise ValueError("glu_projection needs bf16 (M, d) activations and (2f, d) weights")
     M, d = x.shape
@@ -283,9 +290,57 @@ def glu_projection(x: torch.Tensor, w: torch.Tensor, beta: float = 0.5, out: Opt
     f = w.shape[0] // 2
     y = torch.empty((M, f), dtype=torch.bfloat16, device=x.device) if out is None else out
     a = L.GluProjArgs(x=x.data_ptr(), w=w.data_ptr(), out=y.data_ptr(), M=M, d=d, f=f, ld_x=x.stride(0),
-                      ld_out=y.stride(0), beta=float(beta), status=None)
+                      ld_out=y.stride(0), beta=float(beta), status=None, row_ss=_ptr(row_ss),
+                      ss_slots=0 if row_ss is None else row_ss.shape[0], row_eps=float(eps))
     L.check(L.load().alg_glu_proj_fwd(a, _stream()))
     return y
+
+
+def _check_row_ss(row_ss, M):
+    if row_ss is not None and (row_ss.dtype != torch.float32 or row_ss.ndim != 2 or row_ss.shape[1] != M
+                               or not row_ss.is_contiguous()):
+        raise ValueError("row_ss must be contiguous float32 (slots, M)")
+
+
+@_on_tensor_device
+def resid_projection(x: torch.Tensor, w: torch.Tensor, resid: torch.Tensor, out: Optional[torch.Tensor] = None,
+                     want_row_ss: bool = True):
+    """`resid + x @ w.T` as one GEMM with the add in its epilogue (the block's `x + a @ w_o` and
+    `x + (gate * act) @ w_d`, src/algebraic/model.py:183, 193), plus — `want_row_ss` — the per-row
+    partial sums of squares of the result, (slots, M) float32, which let the NEXT projection apply the
+    RMS norm that follows as a row scale (`qkv_projection(row_ss=...)`, `glu_projection(row_ss=...)`).
+    x: (M, K) bf16; w: (N, K) bf16, one row per output feature; resid: (M, N) bf16; `out` may be `resid`.
+    Returns `(out, row_ss or None)`."""
+    _require_cuda(x, w, resid, out)
+    if any(t.dtype != torch.bfloat16 or t.ndim != 2 or t.stride(1) != 1 for t in (x, w, resid)):
+        raise ValueError("resid_projection needs bf16 matrices with contiguous rows")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or not w.is_contiguous() or resid.shape != (M, N) or K % 64 or N % 64:
+        raise ValueError("shapes: x (M, K), w (N, K) contiguous, resid (M, N); K and N multiples of 64")
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device) if out is None else out
+    if y.shape != (M, N) or y.dtype != torch.bfloat16 or y.stride(1) != 1:
+        raise ValueError("out must be bf16 (M, N) with contiguous rows")
+    lib = L.load()
+    ss = None
+    if want_row_ss and M > 0:
+        ss = torch.empty((lib.alg_resid_proj_ss_slots(M, N), M), dtype=torch.float32, device=x.device)
+    a = L.ResidProjArgs(x=x.data_ptr(), w=w.data_ptr(), resid=resid.data_ptr(), out=y.data_ptr(), ss_out=_ptr(ss),
+                        M=M, K=K, N=N, ld_x=x.stride(0), ld_resid=resid.stride(0), ld_out=y.stride(0), status=None)
+    L.check(lib.alg_resid_proj_fwd(a, _stream()))
+    return y, ss
+
+
+@_on_tensor_device
+def row_sumsq(x: torch.Tensor) -> torch.Tensor:
+    """(1, M) float32 sums of squares of the rows of a bf16 (M, d) matrix: the `row_ss` of a projection
+    whose input did not come out of `resid_projection` (the first block of a model)."""
+    _require_cuda(x)
+    if x.dtype != torch.bfloat16 or x.ndim != 2 or x.stride(1) != 1:
+        raise ValueError("row_sumsq needs a bf16 matrix with contiguous rows")
+    ss = torch.empty((1, x.shape[0]), dtype=torch.float32, device=x.device)
+    L.check(L.load().alg_row_sumsq(x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), ss.data_ptr(), _stream()))
+    return ss
 
 
 # ------------------------------------------------------------------------ attention

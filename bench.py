@@ -42,8 +42,10 @@ ATTN = dict(B=1, H=16, T=8192, D=128, n=16, c=8.0)
 HEAD = dict(N=8192, d=768, V=50304, n=8, c=2.0, target_hi=50257)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel at the headline
-# shape, from the ncu capture summarised in profiles/attn_tc_kernel_config5_seq8192.md.
-ATTN_DRAM_TRAFFIC_BYTES = 159.0e6
+# shape, from the ncu capture summarised in profiles/attn_tc_kernel_config5_seq8192.md (the guarded
+# call's launch: 165.1 MB read, of which the in-kernel guard statistics add what L2 does not hold,
+# 14.7 MB written).
+ATTN_DRAM_TRAFFIC_BYTES = 179.9e6
 REPS = 5                      # repetitions of the timed region; the median is reported
 
 

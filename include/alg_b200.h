@@ -387,6 +387,13 @@ typedef struct {
   float attn_c;            /* q is scaled by 1 / (sqrt(D) attn_c) for the guard's statistic */
   void* guard;
   int* status;             /* device int, may be NULL */
+  /* Optional: x is the UN-normalised residual stream and the block's RMS norm (model.py:141-143, 164) is
+   * carried by this call: every accumulator row is multiplied by tau = rsqrt(sum_s row_ss[s][row] / d +
+   * row_eps) before anything else happens to it, and the caller has multiplied the norm's gain into the
+   * columns of w.  row_ss: (ss_slots, M) fp32 as alg_resid_proj_fwd or alg_row_sumsq left them; NULL = off. */
+  const float* row_ss;
+  int ss_slots;
+  float row_eps;
 } alg_qkv_proj_args;
 ALG_API int alg_qkv_proj_fwd(const alg_qkv_proj_args* args, void* stream);
 
@@ -398,8 +405,37 @@ typedef struct {
   int64_t ld_x, ld_out;
   float beta;
   int* status;             /* device int, may be NULL */
+  const float* row_ss;     /* as in alg_qkv_proj_args (model.py:184: the norm in front of gate and up) */
+  int ss_slots;
+  float row_eps;
 } alg_glu_proj_args;
 ALG_API int alg_glu_proj_fwd(const alg_glu_proj_args* args, void* stream);
+
+/* The block's out-projection and down-projection with their residual add:
+ *   out = resid + x . w^T        Replaces: `x + a @ w_o`, `x + (gate * act) @ w_d`   src/algebraic/model.py:183, 193
+ * (the product rounded to bf16, then a bf16 add, as the reference's bf16 expression does), and, when
+ * ss_out is given, per row the sum of squares of what was written, as alg_resid_proj_ss_slots(M, N)
+ * partials of M floats each — what the NEXT projection needs to apply the RMS norm that follows in
+ * the reference (model.py:141-143) without a pass of its own (`row_ss` of alg_qkv_proj_fwd /
+ * alg_glu_proj_fwd).  x: (M, K) bf16, row stride ld_x; w: (N, K) bf16 contiguous (one row per output
+ * feature); resid, out: (M, N) bf16 with row strides ld_resid, ld_out (out may alias resid).
+ * K a multiple of 64, N a multiple of 64, strides multiples of 8, pointers 16-byte aligned. */
+typedef struct {
+  const void* x;
+  const void* w;
+  const void* resid;
+  void* out;
+  float* ss_out;           /* (alg_resid_proj_ss_slots(M, N), M) fp32, or NULL */
+  int M, K, N;
+  int64_t ld_x, ld_resid, ld_out;
+  int* status;             /* device int, may be NULL */
+} alg_resid_proj_args;
+ALG_API int alg_resid_proj_ss_slots(int M, int N);
+ALG_API int alg_resid_proj_fwd(const alg_resid_proj_args* args, void* stream);
+
+/* Sum of squares of every row of a (rows, d) bf16 matrix: ss_out[row], one slot, for the first
+ * projection of a model (its input comes from the embedding's norm, not from a residual GEMM). */
+ALG_API int alg_row_sumsq(const void* x, int64_t rows, int d, int64_t ld_x, float* ss_out, void* stream);
 
 /* Backward of the Alg-CE head, first half: the logit gradient.  Replaces fused_head._bwd_kernel
  * (src/algebraic/kernels/fused_head.py:120-156), which also writes dz in bf16 and leaves

@@ -314,6 +314,42 @@ def test_config5_long_context_sampled(impl):
         assert rel_l2(got[:, h:h + 1], want) < 1e-2
 
 
+@pytest.mark.parametrize("D,T", [(64, 512), (128, 1024), (128, 2304)])
+@pytest.mark.parametrize("n,c", [(16, 8.0), (8, 1.0), (32, 8.0)])
+@pytest.mark.parametrize("case", ["normal", "sink", "big", "all_negative", "late_maximum"])
+def test_shifted_form_on_tcgen05(D, T, n, c, case):
+    """The max-shifted accumulation (flash.py:235-259) on the tcgen05 kernel, forced with shift=True and
+    impl="tcgen05": ordinary scores with and without a sink, scores of the order of 1e3 (far outside the
+    guard), rows whose scores are all far below zero (no sink: the first tile sets the maximum), and rows
+    whose maximum arrives in a late key tile, so that the output accumulated in tensor memory has to be
+    rescaled.  Output and the saved statistic rho(-m) l^(-1/n) against the oracle."""
+    B, H = 1, 2
+    q, k, v = (randn((B, H, T, D), 950 + i, torch.bfloat16) for i in range(3))
+    sink = None
+    if case == "sink":
+        sink = randn((H,), 955, scale=0.5)
+    elif case == "big":
+        q = (q.float() * 30).bfloat16()
+        k = (k.float() * 30).bfloat16()
+    elif case == "all_negative":
+        q = (1 + 0.05 * q.float()).bfloat16() * 6
+        k = ((-1 + 0.05 * k.float()) * 6).bfloat16()
+    elif case == "late_maximum":
+        k[:, :, T - 200] = (q[:, :, T - 100].float() * 4).bfloat16()     # one key that most late rows score highest on
+        k[:, :, 700 % T] = (q[:, :, T - 50].float() * 2).bfloat16()
+    want = R.asinh_attention(q, k, v, n=n, c=c, sink_logit=sink)
+    qd, kd, vd, sd = dev(q, k, v, sink)
+    got, stat, kind = A.flash_attention(qd, kd, vd, sd, kind="asinh", n=n, c=c, block=256, shift=True, impl="tcgen05",
+                                        return_stat=True)
+    assert int(kind) == 2
+    assert torch.isfinite(got).all() and torch.isfinite(stat).all()
+    assert rel_l2(got, want) < 1e-2
+    want_stat = R.attention_row_stat(q, k, n=n, c=c, sink_logit=sink, shifted=True)
+    assert rel_l2(stat, want_stat) < 5e-3
+    again = A.flash_attention(qd, kd, vd, sd, kind="asinh", n=n, c=c, block=256, shift=True, impl="tcgen05")
+    assert torch.equal(got, again)
+
+
 @pytest.mark.parametrize("T", [16384, 32768])
 def test_config5_longer_sequences_sampled(T):
     """benchmark configuration 5 at T = 16384 and 32768: (1,16,T,128) bf16 through the guarded public

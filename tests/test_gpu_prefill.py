@@ -104,19 +104,66 @@ def test_glu_projection_fused_epilogue(M, d, f):
     assert rel_l2(got, want) < 6e-3
 
 
-@pytest.mark.parametrize("fused", [True, False])
+@pytest.mark.parametrize("M,K,N", [(300, 256, 768), (4096, 2048, 768), (1000, 2688, 1024), (130, 64, 64)])
+def test_residual_projection_and_row_statistic(M, K, N):
+    """`resid + x @ w.T` with the reference's rounding (product to bf16, then a bf16 add; model.py:183,
+    193) on both tile widths, in place, and the row sums of squares it leaves for the next norm."""
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn((M, K), generator=g).bfloat16()
+    w = (torch.randn((N, K), generator=g) * 0.05).bfloat16()
+    resid = torch.randn((M, N), generator=g).bfloat16()
+    prod = (x.float() @ w.float().t()).bfloat16()
+    want = (resid.float() + prod.float()).bfloat16()
+    rd = resid.to(DEV)
+    got, ss = A.resid_projection(x.to(DEV), w.to(DEV), rd, out=rd)           # in place
+    assert got.data_ptr() == rd.data_ptr() and ss.shape[1] == M
+    assert rel_l2(got, want) < 4e-3                                              # fp32 summation order only
+    want_ss = got.float().pow(2).sum(-1).cpu()
+    np.testing.assert_allclose(ss.sum(0).cpu(), want_ss, rtol=1e-5)
+    np.testing.assert_allclose(A.row_sumsq(got)[0].cpu(), want_ss, rtol=1e-5)
+
+
+def test_projections_apply_the_block_norm_as_a_row_scale():
+    """qkv_projection / glu_projection fed the un-normalised stream plus its row statistic, with the
+    norm's gain folded into the weights, against normalising first (model.py:164-169, 184-187)."""
+    M, d, H, D, T, f = 512, 256, 2, 64, 256, 512
+    g = torch.Generator().manual_seed(77)
+    x = (torch.randn((M, d), generator=g) * 3).bfloat16()
+    gain = 0.5 + torch.rand(d, generator=g)
+    wq = torch.randn((3 * H * D, d), generator=g) * 0.05
+    wg, wu = torch.randn((f, d), generator=g) * 0.05, torch.randn((f, d), generator=g) * 0.2
+    cos, sin = A.cayley_table_geometric(D, T, device=DEV)
+    cos, sin = cos.bfloat16().contiguous(), sin.bfloat16().contiguous()
+    ones = torch.ones(D, device=DEV)
+    h = A.ops.rms_norm(x.to(DEV), gain.to(DEV), 1e-5)
+    ss = A.row_sumsq(x.to(DEV))
+    want = A.qkv_projection(h, wq.bfloat16().to(DEV), H, T, cos, sin, ones, ones, 1e-5, 8.0)
+    got = A.qkv_projection(x.to(DEV), (wq * gain).bfloat16().to(DEV), H, T, cos, sin, ones, ones, 1e-5, 8.0, row_ss=ss)
+    assert rel_l2(got, want) < 8e-3                                              # rounding points differ, nothing else
+    w_plain = A.interleave_gate_up(wg.bfloat16(), wu.bfloat16()).to(DEV)
+    w_fold = A.interleave_gate_up((wg * gain).bfloat16(), (wu * gain).bfloat16()).to(DEV)
+    want = A.glu_projection(h, w_plain, 0.5)
+    got = A.glu_projection(x.to(DEV), w_fold, 0.5, row_ss=ss, eps=1e-5)
+    assert rel_l2(got, want) < 1.5e-2
+
+
+@pytest.mark.parametrize("fused", [True, "auto", "proj_only", False])
 @pytest.mark.parametrize("head_dim,T", [(64, 256), (128, 512)])
 def test_tiny_prefill_matches_reference_model(head_dim, T, fused):
     cfg = P.PrefillConfig(vocab_size=1000, d_model=2 * head_dim, n_layers=2, n_heads=2, d_ff=256)
     params = P.init_params(cfg, seed=0)
     g = torch.Generator().manual_seed(1)
-    for k in ("q_gain", "k_gain"):                       # exercise non-trivial gains and sinks
+    for k in ("q_gain", "k_gain", "ln1", "ln2"):         # exercise non-trivial gains and sinks
         params[k] = 0.75 + 0.5 * torch.rand(params[k].shape, generator=g)
     params["sink"] = torch.randn(params["sink"].shape, generator=g) * 0.3
     tokens = torch.randint(0, cfg.vocab_size, (2, T), generator=g)
     want_h = M.forward_hidden(params, tokens, cfg)
     obj_w, pt_w = M.head_loss(params, want_h, tokens, cfg)
-    model = P.Prefill(cfg, params, DEV, seq_len=T, fused_proj=fused)
+    # True: norms and residual adds inside the GEMMs; "auto": chosen per call (these sizes take the fused path);
+    # "proj_only": stand-alone norms and library residual GEMMs around the fused projections; False: nothing fused
+    fused_norm = {True: True, "auto": None, "proj_only": False, False: False}[fused]
+    model = P.Prefill(cfg, params, DEV, seq_len=T, fused_proj=bool(fused), fused_norm=fused_norm)
+    assert model.fused_norm is fused_norm
     got_h = model.hidden(tokens.to(DEV))
     assert rel_l2(got_h, want_h) < 2e-2                  # two layers of bf16 activations
     obj, pt, nll = model.loss(tokens.to(DEV), tokens.to(DEV), want_nll=True)
