@@ -68,7 +68,7 @@ class QkvProjArgs(C.Structure):
                 ("k_gain", C.c_void_p), ("cos", C.c_void_p), ("sin", C.c_void_p), ("eps", C.c_float),
                 ("M", C.c_int), ("d", C.c_int), ("H", C.c_int), ("D", C.c_int), ("T", C.c_int),
                 ("ld_x", C.c_int64), ("attn_c", C.c_float), ("guard", C.c_void_p), ("status", C.c_void_p),
-                ("row_ss", C.c_void_p), ("ss_slots", C.c_int), ("row_eps", C.c_float)]
+                ("row_ss", C.c_void_p), ("ss_slots", C.c_int), ("row_eps", C.c_float), ("guard_is_zero", C.c_int)]
 
 
 class GluProjArgs(C.Structure):

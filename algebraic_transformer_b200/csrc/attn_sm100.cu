@@ -332,73 +332,78 @@ __device__ __forceinline__ bool item_at(const AttnParams& p, const ItemLists& li
   return true;
 }
 
-// The range guard's three maxima (src/algebraic/kernels/flash.py:834-849) taken by one otherwise idle
-// warp while the CTA does its attention work: the largest squared row norm of q in score units, the
-// largest squared row norm of k, the largest |v|, each over the rows this CTA looks at (the reader
-// takes the largest over the CTAs' records).  A lane owns a row (all of its 16-byte loads in
-// flight at once, no shuffles); the rows of the whole problem are dealt over all CTAs.  The
-// reference takes the norm of q after re-rounding q / (sqrt(D) c) to the input dtype; here the
+// The range guard's three maxima (src/algebraic/kernels/flash.py:834-849) - the largest squared row norm
+// of q in score units, the largest squared row norm of k, the largest |v| - are taken inside the
+// attention kernel, each CTA over a share of the rows, and written as one record per CTA (plain
+// stores: nothing to zero beforehand, nothing to contend for; the reader takes the largest over the
+// records).  The arithmetic costs issue slots that the weight warps also want, so it is spread over
+// three of the four sub-partitions of the SM instead of loading one:
+//   q  the Q scaler (warp 2) sums the squares of the Q tiles it passes over in shared memory anyway;
+//   k  warp 3, a lane per row, 16-byte loads of the whole row in flight at once, rows of the whole
+//      problem dealt over all CTAs;
+//   v  the 31 lanes of the producer warp that do not issue TMA copies, the same way.
+// The reference takes the norm of q after re-rounding q / (sqrt(D) c) to the input dtype; here the
 // unrounded norm is multiplied by (1 + 2^-8), an upper bound on what that rounding can add, so the
 // guard can only err towards the shifted (always valid) form.  NaN anywhere fails the guard.
+__device__ __forceinline__ float nan_to_inf(float x) { return (x == x) ? x : __int_as_float(0x7f800000); }   // +inf orders above everything as an unsigned word
+
 template <int D>
-__device__ __forceinline__ void guard_statistics(const AttnParams& p, GuardWords* out, int lane) {
+__device__ __forceinline__ const uint4* guard_row(const void* base, const Strides3& st, int H, int T, int64_t r) {
+  const int t = int(r % T);
+  const int64_t bh = r / T;
+  return reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(base) + (bh / H) * st.b + (bh % H) * st.h + int64_t(t) * st.t);
+}
+
+// Largest squared row norm of k over rows first, first + step, ... (this thread's share); NaN sticks.
+template <int D>
+__device__ __forceinline__ float guard_k_rows(const AttnParams& p, int64_t first, int64_t step) {
   constexpr int NV = D / 8;                       // 16-byte vectors per row
-  const int64_t step = int64_t(gridDim.x) * 32;
-  float best[2] = {0.f, 0.f};
-  for (int which = 0; which < 2; ++which) {
-    const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(which == 0 ? p.q : p.k);
-    const Strides3& st = which == 0 ? p.qs : p.ks;
-    const int T = which == 0 ? p.Tq : p.Tk;
-    const int64_t rows = int64_t(p.B) * p.H * T;
-    float m = 0.f;
-    for (int64_t r = int64_t(blockIdx.x) * 32 + lane; r < rows; r += step) {
-      const int t = int(r % T);
-      const int64_t bh = r / T;
-      const uint4* src = reinterpret_cast<const uint4*>(base + (bh / p.H) * st.b + (bh % p.H) * st.h + int64_t(t) * st.t);
-      uint4 raw[NV];
+  const int64_t rows = int64_t(p.B) * p.H * p.Tk;
+  float m = 0.f;
+  for (int64_t r = first; r < rows; r += step) {
+    const uint4* src = guard_row<D>(p.k, p.ks, p.H, p.Tk, r);
+    uint4 raw[NV];
 #pragma unroll
-      for (int i = 0; i < NV; ++i) raw[i] = __ldg(src + i);
-      float2 acc = make_float2(0.f, 0.f);
+    for (int i = 0; i < NV; ++i) raw[i] = __ldg(src + i);
+    float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
+    for (int i = 0; i < NV; ++i) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); acc = __ffma2_rn(f, f, acc); }
-      }
-      const float ss = acc.x + acc.y;
-      m = (ss > m || ss != ss) ? ss : m;          // a NaN sticks
+      for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); acc = __ffma2_rn(f, f, acc); }
     }
-    best[which] = m;
+    const float ss = acc.x + acc.y;
+    m = (ss > m || ss != ss) ? ss : m;
   }
+  return m;
+}
+
+// Largest |v| over this thread's share of the rows; NaN sticks.
+template <int D>
+__device__ __forceinline__ float guard_v_rows(const AttnParams& p, int64_t first, int64_t step) {
+  constexpr int NV = D / 8;
+  const int64_t rows = int64_t(p.B) * p.H * p.Tk;
   __nv_bfloat162 vm2 = __float2bfloat162_rn(0.f);
-  {
-    const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(p.v);
-    const int64_t rows = int64_t(p.B) * p.H * p.Tk;
-    for (int64_t r = int64_t(blockIdx.x) * 32 + lane; r < rows; r += step) {
-      const int t = int(r % p.Tk);
-      const int64_t bh = r / p.Tk;
-      const uint4* src = reinterpret_cast<const uint4*>(base + (bh / p.H) * p.vs.b + (bh % p.H) * p.vs.h + int64_t(t) * p.vs.t);
-      uint4 raw[NV];
+  for (int64_t r = first; r < rows; r += step) {
+    const uint4* src = guard_row<D>(p.v, p.vs, p.H, p.Tk, r);
+    uint4 raw[NV];
 #pragma unroll
-      for (int i = 0; i < NV; ++i) raw[i] = __ldg(src + i);
+    for (int i = 0; i < NV; ++i) raw[i] = __ldg(src + i);
 #pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
+    for (int i = 0; i < NV; ++i) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) vm2 = __hmax2_nan(vm2, __habs2(h[e]));
-      }
+      for (int e = 0; e < 4; ++e) vm2 = __hmax2_nan(vm2, __habs2(h[e]));
     }
   }
   const float2 vm = __bfloat1622float2(vm2);
-  float stat[3] = {best[0] * (p.scale * p.scale * 1.00390625f), best[1], (vm.x > vm.y || vm.x != vm.x) ? vm.x : vm.y};
-#pragma unroll
-  for (int i = 0; i < 3; ++i) {
-    float x = stat[i];
-    if (!(x == x)) x = __int_as_float(0x7f800000);  // NaN -> +inf, which orders above everything as an unsigned word
-    stat[i] = warp_max(x);
-  }
-  // one record per CTA, plain stores: nothing to zero beforehand, nothing to contend for
-  if (lane == 0) *reinterpret_cast<uint4*>(out + blockIdx.x) = make_uint4(__float_as_uint(stat[0]), __float_as_uint(stat[1]), __float_as_uint(stat[2]), 0u);
+  return (vm.x > vm.y || vm.x != vm.x) ? vm.x : vm.y;
+}
+
+// One word of this CTA's record: the warp's largest value (all 32 lanes call).
+__device__ __forceinline__ void guard_store(unsigned* word, float mine, int lane) {
+  const float m = warp_max(nan_to_inf(mine));
+  if (lane == 0) *word = __float_as_uint(m);
 }
 
 template <int D> constexpr size_t smem_bytes() { return size_t(Cfg<D>::CTL_OFF) + sizeof(Control) + 1024; }
@@ -429,16 +434,23 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (warp == 0) {
+    griddep_wait();                               // launched as a programmatic dependent: q, k, v and (for a stand-by launch)
+                                                  // the guard records come from kernels ahead in the stream
     const bool sh = attn_use_shift(p, lane);
     if (lane == 0) ctl->shift_mode = sh ? 1 : 0;
   }
   __syncthreads();
+  // a stand-by launch behind this one may take its place on every SM this kernel's CTAs leave
+  if (threadIdx.x == 0) griddep_launch_dependents();
   // each form runs only when it is the one called for: under a guard the unshifted kernel leaves when the
   // guard failed and the shifted kernel leaves when it held
   if ((ctl->shift_mode != 0) != SHIFT) return;
 
   if (threadIdx.x == 0) {
-    for (int w = 0; w < 2; ++w) { mbar_init(&ctl->q_full[w], 1); mbar_init(&ctl->q_ready[w], 1); mbar_init(&ctl->q_free[w], 1); }
+    for (int w = 0; w < 2; ++w) {
+      mbar_init(&ctl->q_full[w], 1); mbar_init(&ctl->q_ready[w], 1);
+      mbar_init(&ctl->q_free[w], p.guard_out != nullptr ? 2 : 1);   // the releasing thread, and the Q scaler when it also reads the tile for the guard
+    }
     for (int i = 0; i < C::NKV; ++i) { mbar_init(&ctl->kv_full[i], 1); mbar_init(&ctl->kv_empty[i], 1); }
     for (int w = 0; w < 2; ++w) {
       mbar_init(&ctl->s_full[w], 1);
@@ -500,6 +512,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         else ok = load_kv(0) && load_q(0) && load_kv(1) && load_q(1);
         for (int idx = 2; idx < 2 * it.n1 && ok; ++idx) ok = load_kv(idx);
       }
+    }
+    if (p.guard_out != nullptr) {
+      // the warp's other 31 lanes take the guard's largest |v| meanwhile (the two paths of the warp run
+      // interleaved; they meet again here)
+      float vmax = 0.f;
+      if (lane != 0) vmax = guard_v_rows<D>(p, int64_t(blockIdx.x) * 31 + (lane - 1), int64_t(gridDim.x) * 31);
+      __syncwarp();
+      guard_store(&p.guard_out[blockIdx.x].vmax, vmax, lane);
     }
   } else if (warp == 1) {
     // The MMA warp.  Its own instruction time is the scarce resource: an issue costs the issuing
@@ -618,6 +638,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // the swizzled layout does not matter), make the result visible to the tensor core's reads
     // and release the tile to the MMA warp.
     const __nv_bfloat162 f2 = __float2bfloat162_rn(sc.pow2);
+    const bool stats = p.guard_out != nullptr;      // also takes the guard's largest squared row norm of q
+    float qbest = 0.f;
     bool ok = true;
     for (int k = 0; ok && item_at(p, lists, k, it); ++k) {
       for (int w = 0; w < 2 && ok; ++w) {
@@ -636,12 +658,44 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         __syncwarp();
         if (lane == 0) mbar_arrive(&ctl->q_ready[w]);
       }
+      if (!stats || !ok) continue;
+      // Both tiles are with the MMA warp now.  A second, read-only pass over them (nobody waits for it)
+      // sums the squares of every row; the tile is not overwritten before this warp has said it is done
+      // with it too.  A warp instruction covers four 128-byte rows of a 64-column panel: lane / 8 is the
+      // row, lane % 8 the 16-byte piece (which piece of the row it is does not matter to a sum).
+      for (int w = 0; w < 2; ++w) {
+        const uint4* tile = reinterpret_cast<const uint4*>(smem + C::Q_OFF + w * C::TILE_BYTES);
+#pragma unroll 2
+        for (int i = lane; i < PANEL_BYTES / 16; i += 32) {
+          float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int pn = 0; pn < C::PANELS; ++pn) {
+            const uint4 v = tile[pn * (PANEL_BYTES / 16) + i];
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); acc = __ffma2_rn(f, f, acc); }
+          }
+          float ss = acc.x + acc.y;
+          ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+          ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+          ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+          qbest = (ss > qbest || ss != ss) ? ss : qbest;        // a NaN sticks
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->q_free[w]);
+      }
+    }
+    // the rows were read after the multiplication by 2^e: what is left of the score scale is (scale / 2^e)^2
+    if (stats) {
+      const float rest = p.scale / sc.pow2;
+      guard_store(&p.guard_out[blockIdx.x].q2, qbest * (rest * rest * 1.00390625f), lane);
     }
   } else if (warp == 3) {
 #ifdef ALG_ATTN_TIMING
     const long long tg0 = clock64();
 #endif
-    if (p.guard_out != nullptr) guard_statistics<D>(p, p.guard_out, lane);
+    if (p.guard_out != nullptr)
+      guard_store(&p.guard_out[blockIdx.x].k2, guard_k_rows<D>(p, int64_t(blockIdx.x) * 32 + lane, int64_t(gridDim.x) * 32), lane);
 #ifdef ALG_ATTN_TIMING
     if (lane == 0 && p.stat != nullptr) p.stat[40 + 2 * blockIdx.x] = float(clock64() - tg0);
 #endif
@@ -866,8 +920,7 @@ int launch_dns(const AttnParams& p, cudaStream_t stream) {
     deal_items(&dealt.lists, units, nblk, grid);
     dealt.units = units; dealt.nblk = nblk; dealt.grid = grid;
   }
-  kern<<<grid, nthreads<SPLIT>(), smem_bytes<D>(), stream>>>(tq, tk, tv, p, sc, dealt.lists);
-  ALG_CUDA_TRY(cudaGetLastError());
+  ALG_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(nthreads<SPLIT>()), smem_bytes<D>(), stream, tq, tk, tv, p, sc, dealt.lists));
   count_launch();
   return ALG_OK;
 }

@@ -230,8 +230,8 @@ int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
     p.guard_slots = attn_tcgen05_grid(p);
     if (size_t(p.guard_slots) * sizeof(GuardWords) > kGuardBytes) { set_error("attention: more CTAs than guard records"); return ALG_ERR_UNSUPPORTED; }
     if (int rc = launch_attn_tcgen05(ps, stream)) return rc;
-    p.run_if = 2;                                       // the max-shifted form runs only if the guard failed
-    p.tc_shift = 1;
+    p.run_if = 2;                                       // the max-shifted form runs only if the guard failed; its CTAs
+    p.tc_shift = 1;                                     // move in as the first kernel's leave and wait there for its records
     return launch_attn_tcgen05(p, stream);
   }
   if (guarded && !guard_given) ALG_CUDA_TRY(cudaMemsetAsync(guard, 0, sizeof(GuardWords), stream));
@@ -327,7 +327,7 @@ int alg_qkv_proj_fwd(const alg_qkv_proj_args* a, void* stream_) {
   }
   p.row_ss = a->row_ss; p.ss_slots = a->ss_slots; p.row_eps = a->row_eps;
   if (a->M == 0) return ALG_OK;
-  if (p.guard != nullptr) ALG_CUDA_TRY(cudaMemsetAsync(p.guard, 0, sizeof(GuardWords), stream));
+  if (p.guard != nullptr && !a->guard_is_zero) ALG_CUDA_TRY(cudaMemsetAsync(p.guard, 0, sizeof(GuardWords), stream));
   return launch_proj(p, a->x, a->w, 0, stream);
 }
 

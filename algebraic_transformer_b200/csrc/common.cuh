@@ -5,6 +5,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <cstdlib>
 #include <stdint.h>
 
 #include <atomic>
@@ -145,6 +146,34 @@ struct GuardWords {
 __device__ __forceinline__ bool guard_in_range(const GuardWords* g, float bound_sq, float vmax_limit) {
   float q2 = __uint_as_float(g->q2), k2 = __uint_as_float(g->k2), vm = __uint_as_float(g->vmax);
   return (q2 * k2 <= bound_sq) && (vm <= vmax_limit);
+}
+
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute may
+// start while the kernel before it in the stream still runs; griddep_wait() in it returns once
+// that kernel has finished and its writes are visible (a no-op in a kernel launched the plain way).
+// griddep_launch_dependents() in the earlier kernel says this CTA does not mind: the next kernel's CTAs
+// are placed as soon as every CTA here has said so or left, wherever there is room.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() {
+#ifndef ALG_PDL_NO_TRIGGER
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+
+// Launch `kern` so that it may start before the kernel ahead of it in `stream` has finished
+// (programmatic dependent launch); the kernel itself calls griddep_wait() before it touches
+// anything the earlier kernel writes.
+template <typename... Formal, typename... Actual>
+inline cudaError_t launch_dependent(void (*kern)(Formal...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Actual&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  static const bool plain = getenv("ALG_NO_PDL") != nullptr;      // measurement aid: ordinary stream order
+  cfg.attrs = attr; cfg.numAttrs = plain ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<Formal>(args)...);
 }
 
 }  // namespace alg

@@ -10,7 +10,8 @@
 // accumulates w * V for the 8 columns it holds.  No step of the key loop involves the whole
 // CTA, so nothing but the ring's barriers paces it; the eight warp states are merged once at
 // the end with the same exact rescale, and the (acc, m, l) states of the splits are merged,
-// with the sink, by decode_combine_kernel.  All mbarrier waits are bounded.
+// with the sink, by decode_combine_kernel (a programmatic dependent launch: its CTAs are resident
+// and waiting when the last split finishes).  All mbarrier waits are bounded.
 #include "common.cuh"
 #include "launchers.h"
 #include "sm100_ptx.cuh"
@@ -65,6 +66,7 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     fence_barrier_init();
   }
   __syncthreads();
+  if (threadIdx.x == 0) griddep_launch_dependents();   // the combine kernel's CTAs may take their places and wait
   const BoundedWait bw{&ctl->abort_flag, 1000000000ull};
 
   if (warp == CONSUMERS / 32) {                 // producer warp
@@ -208,6 +210,7 @@ __global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeParams p)
   const float* part = p.part + int64_t(bh) * p.splits * (D + 2);
   const bool has_sink = p.sink != nullptr;
   const float bs = has_sink ? p.sink[h] * p.inv_c : -1e30f;
+  griddep_wait();                                // launched while the split kernel still runs: its states are complete from here on
   float mm = bs;                                 // all loads below are independent of one another
   for (int s = threadIdx.x; s < p.splits; s += D) {
     const float ms = part[s * (D + 2) + D];
@@ -254,8 +257,7 @@ int launch_d(const DecodeParams& p, cudaStream_t stream) {
   if (int rc = configured.run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(decode_smem<D>())); })) return rc;
   kern<<<dim3(p.splits, p.H, p.B), NTHREADS, decode_smem<D>(), stream>>>(tk, tv, p);
   ALG_CUDA_TRY(cudaGetLastError());
-  decode_combine_kernel<D><<<p.B * p.H, D, 0, stream>>>(p);
-  ALG_CUDA_TRY(cudaGetLastError());
+  ALG_CUDA_TRY(launch_dependent(decode_combine_kernel<D>, dim3(p.B * p.H), dim3(D), 0, stream, p));
   count_launch(2);
   return ALG_OK;
 }

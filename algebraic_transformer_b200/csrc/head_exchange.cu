@@ -40,6 +40,8 @@ __global__ void __launch_bounds__(XT) head_exchange_kernel(const ExchangeParams 
   __shared__ float s_red[XT / 32];
   __shared__ bool s_last;
   const int nb = gridDim.x;
+  griddep_wait();                 // launched as a programmatic dependent of the head kernel ahead in the stream
+  griddep_launch_dependents();
   // call number: read by every block at its start; advanced by the last block to finish
   if (threadIdx.x == 0) s_call = *reinterpret_cast<volatile unsigned*>(p.call_counter) + 1u;
   __syncthreads();
@@ -125,8 +127,7 @@ int head_exchange_blocks(int N) {
 }
 
 int launch_head_exchange(const ExchangeParams& p, cudaStream_t stream) {
-  head_exchange_kernel<<<head_exchange_blocks(p.N), XT, 0, stream>>>(p);
-  ALG_CUDA_TRY(cudaGetLastError());
+  ALG_CUDA_TRY(launch_dependent(head_exchange_kernel, dim3(head_exchange_blocks(p.N)), dim3(XT), 0, stream, p));
   count_launch();
   return ALG_OK;
 }

@@ -166,6 +166,8 @@ __global__ void __launch_bounds__(NTHREADS) head_mma_kernel(const HeadParams p) 
 __global__ void head_reduce_kernel(const float* __restrict__ l_part, const float* __restrict__ zt_part,
                                    const float* __restrict__ m_part, int N, int splits, float* __restrict__ l_out,
                                    float* __restrict__ zt_out) {
+  griddep_wait();                 // launched as a programmatic dependent of the kernel ahead in the stream
+  griddep_launch_dependents();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= N) return;
   float l = 0.f, z = 0.f;
@@ -196,6 +198,8 @@ __global__ void __launch_bounds__(FIN_THREADS) head_finalize_kernel(
     const float* __restrict__ l, const float* __restrict__ zt, int N, int log2n, float inv_c, float clamp,
     float* __restrict__ pt_out, float* __restrict__ nll_out, float* __restrict__ obj_out,
     float* __restrict__ block_sums, unsigned* __restrict__ ticket) {
+  griddep_wait();                 // launched as a programmatic dependent of the kernel ahead in the stream
+  griddep_launch_dependents();
   __shared__ float red[FIN_THREADS / 32];
   __shared__ bool last;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -265,9 +269,8 @@ int launch_head_mma(const HeadParams& p, cudaStream_t stream) {
 }
 
 int launch_head_reduce(const HeadParams& p, cudaStream_t stream) {
-  head_reduce_kernel<<<(p.N + 255) / 256, 256, 0, stream>>>(p.l_part, p.zt_part, p.kind == ALG_HEAD_CE ? p.m_part : nullptr,
-                                                            p.N, p.splits, p.l_out, p.zt_out);
-  ALG_CUDA_TRY(cudaGetLastError());
+  ALG_CUDA_TRY(launch_dependent(head_reduce_kernel, dim3((p.N + 255) / 256), dim3(256), 0, stream, p.l_part, p.zt_part,
+                                p.kind == ALG_HEAD_CE ? p.m_part : nullptr, p.N, p.splits, p.l_out, p.zt_out));
   count_launch();
   return ALG_OK;
 }
@@ -277,9 +280,8 @@ int head_finalize_blocks(int N) { return (N + FIN_THREADS - 1) / FIN_THREADS; }
 int launch_head_finalize(const float* l, const float* zt, int N, int log2n, float inv_c, float clamp,
                          float* pt, float* nll, float* obj, float* block_sums, unsigned* ticket,
                          cudaStream_t stream) {
-  head_finalize_kernel<<<head_finalize_blocks(N), FIN_THREADS, 0, stream>>>(
-      l, zt, N, log2n, inv_c, clamp, pt, nll, obj, block_sums, ticket);
-  ALG_CUDA_TRY(cudaGetLastError());
+  ALG_CUDA_TRY(launch_dependent(head_finalize_kernel, dim3(head_finalize_blocks(N)), dim3(FIN_THREADS), 0, stream, l, zt, N, log2n, inv_c,
+                                clamp, pt, nll, obj, block_sums, ticket));
   count_launch();
   return ALG_OK;
 }

@@ -81,6 +81,10 @@ head_tc_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // Launched as a programmatic dependent: everything above overlapped the tail of the kernel ahead in the
+  // stream; from here on its results are complete.  The kernel behind may move in the same way.
+  griddep_wait();
+  if (threadIdx.x == 0) griddep_launch_dependents();
   const uint32_t tmem_base = ctl->tmem_base;
   const BoundedWait bw{&ctl->abort_flag, 1000000000ull};
   const int ntiles = (p.V_local + BN - 1) / BN;
@@ -248,8 +252,7 @@ int launch_log2n(const CUtensorMap& tm_h, const CUtensorMap& tm_e, const HeadPar
   auto kern = head_tc_kernel<LOG2N>;
   static PerDeviceOnce configured;
   if (int rc = configured.run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES)); })) return rc;
-  kern<<<grid, NTHREADS, SMEM_BYTES, stream>>>(tm_h, tm_e, p, pl.S, pl.tps, pl.units, pl.row_blocks);
-  ALG_CUDA_TRY(cudaGetLastError());
+  ALG_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(NTHREADS), SMEM_BYTES, stream, tm_h, tm_e, p, pl.S, pl.tps, pl.units, pl.row_blocks));
   count_launch();
   return ALG_OK;
 }

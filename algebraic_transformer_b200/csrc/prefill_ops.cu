@@ -32,6 +32,8 @@ __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(_
 template <int VPL, int RPW>
 __global__ void __launch_bounds__(256) rms_rows_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gain,
                                                        __nv_bfloat16* __restrict__ y, int64_t rows, int d, float eps) {
+  griddep_wait();                 // launched as a programmatic dependent of the kernel ahead in the stream
+  griddep_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int64_t warp_global = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t warps_total = (int64_t(gridDim.x) * blockDim.x) >> 5;
@@ -90,6 +92,8 @@ __global__ void __launch_bounds__(256) rms_rows_kernel(const __nv_bfloat16* __re
 __global__ void __launch_bounds__(256) alu_glu_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
                                                       __nv_bfloat16* __restrict__ out, int64_t rows, int f, int64_t ld_in,
                                                       int64_t ld_out, float beta) {
+  griddep_wait();                 // launched as a programmatic dependent of the kernel ahead in the stream
+  griddep_launch_dependents();
   const size_t stride = size_t(gridDim.x) * blockDim.x;
   const int vpr = f / 8;
   const size_t nvec = size_t(rows) * vpr;
@@ -127,18 +131,19 @@ int launch_rms_rows(const void* x, const float* gain, void* y, int64_t rows, int
     set_error("rms_norm: gain must be 16-byte aligned");
     return ALG_ERR_INVALID;
   }
+  cudaError_t err = cudaSuccess;
   switch (vpl) {
-    case 1: rms_rows_kernel<1, RPW><<<unsigned(blocks), 256, 0, stream>>>(xp, gain, yp, rows, d, eps); break;
-    case 2: rms_rows_kernel<2, RPW><<<unsigned(blocks), 256, 0, stream>>>(xp, gain, yp, rows, d, eps); break;
-    case 3: rms_rows_kernel<3, RPW><<<unsigned(blocks), 256, 0, stream>>>(xp, gain, yp, rows, d, eps); break;
-    case 4: rms_rows_kernel<4, RPW><<<unsigned(blocks), 256, 0, stream>>>(xp, gain, yp, rows, d, eps); break;
-    case 5: case 6: rms_rows_kernel<6, 2><<<unsigned(blocks), 256, 0, stream>>>(xp, gain, yp, rows, d, eps); break;
-    case 7: case 8: rms_rows_kernel<8, 2><<<unsigned(blocks), 256, 0, stream>>>(xp, gain, yp, rows, d, eps); break;
+    case 1: err = launch_dependent(rms_rows_kernel<1, RPW>, dim3(unsigned(blocks)), dim3(256), 0, stream, xp, gain, yp, rows, d, eps); break;
+    case 2: err = launch_dependent(rms_rows_kernel<2, RPW>, dim3(unsigned(blocks)), dim3(256), 0, stream, xp, gain, yp, rows, d, eps); break;
+    case 3: err = launch_dependent(rms_rows_kernel<3, RPW>, dim3(unsigned(blocks)), dim3(256), 0, stream, xp, gain, yp, rows, d, eps); break;
+    case 4: err = launch_dependent(rms_rows_kernel<4, RPW>, dim3(unsigned(blocks)), dim3(256), 0, stream, xp, gain, yp, rows, d, eps); break;
+    case 5: case 6: err = launch_dependent(rms_rows_kernel<6, 2>, dim3(unsigned(blocks)), dim3(256), 0, stream, xp, gain, yp, rows, d, eps); break;
+    case 7: case 8: err = launch_dependent(rms_rows_kernel<8, 2>, dim3(unsigned(blocks)), dim3(256), 0, stream, xp, gain, yp, rows, d, eps); break;
     default:
       set_error("rms_norm: row width %d is above the supported 2048", d);
       return ALG_ERR_UNSUPPORTED;
   }
-  ALG_CUDA_TRY(cudaGetLastError());
+  ALG_CUDA_TRY(err);
   count_launch();
   return ALG_OK;
 }
@@ -149,10 +154,8 @@ int launch_alu_glu(const void* gate, const void* up, void* out, int64_t rows, in
   const size_t nvec = size_t(rows) * (f / 8);
   size_t blocks = (nvec + 255) / 256;
   if (blocks > size_t(sm_count()) * 16) blocks = size_t(sm_count()) * 16;
-  alu_glu_kernel<<<unsigned(blocks), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate),
-                                                       static_cast<const __nv_bfloat16*>(up),
-                                                       static_cast<__nv_bfloat16*>(out), rows, f, ld_in, ld_out, beta);
-  ALG_CUDA_TRY(cudaGetLastError());
+  ALG_CUDA_TRY(launch_dependent(alu_glu_kernel, dim3(unsigned(blocks)), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(gate),
+                                static_cast<const __nv_bfloat16*>(up), static_cast<__nv_bfloat16*>(out), rows, f, ld_in, ld_out, beta));
   count_launch();
   return ALG_OK;
 }
@@ -160,6 +163,8 @@ int launch_alu_glu(const void* gate, const void* up, void* out, int64_t rows, in
 // Sum of squares of every row: one warp per row, 16-byte loads.
 __global__ void __launch_bounds__(256) row_sumsq_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int d, int64_t ld,
                                                         float* __restrict__ ss_out) {
+  griddep_wait();                 // launched as a programmatic dependent of the kernel ahead in the stream
+  griddep_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int64_t warp_global = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t warps_total = (int64_t(gridDim.x) * blockDim.x) >> 5;
@@ -181,8 +186,7 @@ int launch_row_sumsq(const void* x, int64_t rows, int d, int64_t ld, float* ss_o
   if (rows == 0) return ALG_OK;
   int64_t blocks = (rows + 7) / 8;
   if (blocks > int64_t(sm_count()) * 8) blocks = int64_t(sm_count()) * 8;
-  row_sumsq_kernel<<<unsigned(blocks), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), rows, d, ld, ss_out);
-  ALG_CUDA_TRY(cudaGetLastError());
+  ALG_CUDA_TRY(launch_dependent(row_sumsq_kernel, dim3(unsigned(blocks)), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), rows, d, ld, ss_out));
   count_launch();
   return ALG_OK;
 }

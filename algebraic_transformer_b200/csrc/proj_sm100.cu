@@ -383,6 +383,10 @@ proj_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // Launched as a programmatic dependent: everything above overlapped the tail of the kernel ahead in the
+  // stream; from here on its results are complete.  The kernel behind may move in the same way.
+  griddep_wait();
+  if (threadIdx.x == 0) griddep_launch_dependents();
   const uint32_t tmem_base = ctl->tmem_base;
   const BoundedWait bw{&ctl->abort_flag, 1000000000ull};
   const int tiles_n = (p.N + BN - 1) / BN;
@@ -540,8 +544,7 @@ int launch_variant(const CUtensorMap& tm_x, const CUtensorMap& tm_w, const ProjP
   auto kern = proj_tc_kernel<EPI, D, BN>;
   static PerDeviceOnce configured;
   if (int rc = configured.run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES)); })) return rc;
-  kern<<<grid, NTHREADS, SMEM_BYTES, stream>>>(tm_x, tm_w, p);
-  ALG_CUDA_TRY(cudaGetLastError());
+  ALG_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(NTHREADS), SMEM_BYTES, stream, tm_x, tm_w, p));
   count_launch();
   return ALG_OK;
 }

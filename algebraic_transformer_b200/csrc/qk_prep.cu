@@ -295,8 +295,10 @@ __global__ void __launch_bounds__(256, 3) qk_rms_bwd_kernel(const RmsBwdParams p
     g[i] = (p.gain != nullptr) ? p.gain[lir * VEC + i] : 1.0f;
     dg[i] = 0.f;
   }
+  griddep_launch_dependents();     // the partial-row sum behind this kernel may take its place and wait
   // four row groups per step, all eight 16-byte loads issued before any is used (memory-level parallelism)
   constexpr int U = 4;
+  const bool narrow = rows < (int64_t(1) << 31);
   for (int64_t base = warp_global * RPW; base < rows; base += warps_total * RPW * U) {
     typename V::Raw rx[U], rd[U];
     int64_t off_dx[U];
@@ -306,10 +308,19 @@ __global__ void __launch_bounds__(256, 3) qk_rms_bwd_kernel(const RmsBwdParams p
       const int64_t row = base + int64_t(u) * warps_total * RPW + sub;
       alive[u] = row < rows;
       const int64_t rr = alive[u] ? row : rows - 1;
-      const int t = int(rr % p.T);
-      const int64_t bh = rr / p.T;
-      const int h = int(bh % p.H);
-      const int64_t b = bh / p.H;
+      int t, h;
+      int64_t b;
+      if (narrow) {                  // 32-bit division: the 64-bit one costs more instructions than the row's arithmetic
+        const uint32_t r32 = uint32_t(rr), bh = r32 / uint32_t(p.T);
+        t = int(r32 - bh * uint32_t(p.T));
+        b = bh / uint32_t(p.H);
+        h = int(bh - uint32_t(b) * uint32_t(p.H));
+      } else {
+        t = int(rr % p.T);
+        const int64_t bh = rr / p.T;
+        h = int(bh % p.H);
+        b = bh / p.H;
+      }
       rx[u] = V::load(reinterpret_cast<const T*>(p.x) + b * p.xs.b + h * p.xs.h + int64_t(t) * p.xs.t + lir * VEC);
       rd[u] = V::load(reinterpret_cast<const T*>(p.dy) + b * p.gs.b + h * p.gs.h + int64_t(t) * p.gs.t + lir * VEC);
       off_dx[u] = b * p.ds.b + h * p.ds.h + int64_t(t) * p.ds.t + lir * VEC;
@@ -360,12 +371,35 @@ __global__ void __launch_bounds__(256, 3) qk_rms_bwd_kernel(const RmsBwdParams p
   }
 }
 
-__global__ void qk_rms_dgain_kernel(const float* __restrict__ partials, int blocks, int D, float* __restrict__ dgain) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= D) return;
-  float s = 0.f;
-  for (int b = 0; b < blocks; ++b) s += partials[int64_t(b) * D + j];
-  dgain[j] = s;
+// Adds the CTAs' partial rows in a fixed order.  One CTA; column j is summed by DGAIN_GROUPS threads,
+// each over every DGAIN_GROUPS-th row with eight independent loads in flight (a single thread per
+// column walking all rows one memory latency at a time took as long as the main kernel), then the
+// groups' sums are added in group order.
+constexpr int DGAIN_GROUPS = 8;
+template <int D>
+__global__ void __launch_bounds__(D * DGAIN_GROUPS) qk_rms_dgain_kernel(const float* __restrict__ partials, int blocks,
+                                                                       float* __restrict__ dgain) {
+  __shared__ float s_sum[DGAIN_GROUPS][D];
+  griddep_wait();                 // a programmatic dependent of the kernel that writes the partial rows
+  const int j = threadIdx.x % D, grp = threadIdx.x / D;
+  float acc[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) acc[u] = 0.f;
+  for (int b0 = grp; b0 < blocks; b0 += 8 * DGAIN_GROUPS) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int b = b0 + u * DGAIN_GROUPS;
+      if (b < blocks) acc[u] += partials[int64_t(b) * D + j];
+    }
+  }
+  s_sum[grp][j] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
+  __syncthreads();
+  if (grp == 0) {
+    float s = 0.f;
+#pragma unroll
+    for (int g2 = 0; g2 < DGAIN_GROUPS; ++g2) s += s_sum[g2][j];
+    dgain[j] = s;
+  }
 }
 
 template <typename T, int D>
@@ -384,8 +418,7 @@ static int launch_rms_bwd_t(const RmsBwdParams& p, cudaStream_t stream) {
   ALG_CUDA_TRY(cudaGetLastError());
   count_launch();
   if (p.dgain != nullptr) {
-    qk_rms_dgain_kernel<<<1, 128, 0, stream>>>(p.partials, int(blocks), D, p.dgain);
-    ALG_CUDA_TRY(cudaGetLastError());
+    ALG_CUDA_TRY(launch_dependent(qk_rms_dgain_kernel<D>, dim3(1), dim3(D * DGAIN_GROUPS), 0, stream, p.partials, int(blocks), p.dgain));
     count_launch();
   }
   return ALG_OK;

@@ -228,14 +228,16 @@ def alu_glu(gate: torch.Tensor, up: torch.Tensor, beta: float = 0.5, out=None) -
 def qkv_projection(x: torch.Tensor, w: torch.Tensor, n_heads: int, seq_len: int, cos: torch.Tensor,
                    sin: torch.Tensor, q_gain: Optional[torch.Tensor] = None, k_gain: Optional[torch.Tensor] = None,
                    eps: float = 1e-5, attn_c: float = 8.0, guard_words: Optional[torch.Tensor] = None,
-                   out: Optional[torch.Tensor] = None, row_ss: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   out: Optional[torch.Tensor] = None, row_ss: Optional[torch.Tensor] = None,
+                   guard_is_zero: bool = False) -> torch.Tensor:
     """The q, k, v projections of a block with the QK-norm, the Cayley rotation and the range
     guard's maxima fused into the GEMM (src/algebraic/model.py:165-174).
 
     x: (M, d) bf16 rows in (batch, position) order, position = row % seq_len.  w: (3*H*D, d) bf16,
     one row per output feature (q heads, k heads, v heads).  cos, sin: (>= seq_len, D/2) bf16.
     Returns (M, 3*H*D) bf16: q and k normalised and rotated, v as projected.  `guard_words`
-    (4 int32, device) receives the maxima for `flash_attention(..., guard_words=...)`.
+    (4 int32, device) receives the maxima for `flash_attention(..., guard_words=...)`; it is zeroed
+    here first unless `guard_is_zero` says the caller has done that on this stream already.
     `row_ss` (slots, M) float32: x is the un-normalised residual stream and the block's RMS norm is
     applied here as a row scale (the norm's gain folded into `w` by the caller); see `resid_projection`."""
     _require_cuda(x, w, cos, sin, q_gain, k_gain, guard_words, row_ss)
@@ -260,7 +262,8 @@ def qkv_projection(x: torch.Tensor, w: torch.Tensor, n_heads: int, seq_len: int,
     a = L.QkvProjArgs(x=x.data_ptr(), w=w.data_ptr(), qkv=y.data_ptr(), q_gain=_ptr(q_gain), k_gain=_ptr(k_gain),
                       cos=cos.data_ptr(), sin=sin.data_ptr(), eps=float(eps), M=M, d=d, H=n_heads, D=D, T=int(seq_len),
                       ld_x=x.stride(0), attn_c=float(attn_c), guard=_ptr(guard_words), status=None,
-                      row_ss=_ptr(row_ss), ss_slots=0 if row_ss is None else row_ss.shape[0], row_eps=float(eps))
+                      row_ss=_ptr(row_ss), ss_slots=0 if row_ss is None else row_ss.shape[0], row_eps=float(eps),
+                      guard_is_zero=int(bool(guard_is_zero)))
     L.check(L.load().alg_qkv_proj_fwd(a, _stream()))
     return y
 

@@ -145,7 +145,9 @@ class Prefill:
         self.p = cast_params(params, self.device, self.fused_proj, self.norm_in_weights)
         self.cos, self.sin = ops.cayley_table_geometric(cfg.head_dim, seq_len, cfg.rope_base, device=self.device)
         self.cos_lp, self.sin_lp = self.cos.bfloat16().contiguous(), self.sin.bfloat16().contiguous()
-        self.guard_words = torch.zeros(4, dtype=torch.int32, device=self.device)
+        # one record of the range guard's maxima per layer: all zeroed by one fill at the start of a step,
+        # so that no memset sits between two kernels of the step
+        self.guard_words = torch.zeros((cfg.n_layers, 4), dtype=torch.int32, device=self.device)
 
     def hidden(self, tokens: torch.Tensor) -> torch.Tensor:
         """Final normalised hidden states (B, T, d) in bf16 (model.forward_hidden, model.py:196-208)."""
@@ -155,16 +157,18 @@ class Prefill:
         x = ops.rms_norm(p["embed"][tokens].contiguous(), p["embed_gain"], cfg.eps).view(B * T, d)
         attn_out = torch.empty((B, T, H, D), dtype=torch.bfloat16, device=self.device)
         use_fused_norm = (B * T <= 4096) if self.fused_norm is None else self.fused_norm
+        if self.fused_proj:
+            self.guard_words.zero_()
         if use_fused_norm:
             # x stays the un-normalised residual stream; `ss` carries the row statistic of the next norm
             ss = ops.row_sumsq(x)
             for layer in range(cfg.n_layers):
                 qkv = ops.qkv_projection(x, p["w_qkv_t"][layer], H, T, self.cos_lp, self.sin_lp, p["q_gain"][layer],
-                                         p["k_gain"][layer], cfg.eps, cfg.attn_c, self.guard_words,
-                                         row_ss=ss).view(B, T, 3, H, D)
+                                         p["k_gain"][layer], cfg.eps, cfg.attn_c, self.guard_words[layer],
+                                         row_ss=ss, guard_is_zero=True).view(B, T, 3, H, D)
                 q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))      # (B,H,T,D) views
                 ops.flash_attention(q, k, v, p["sink"][layer], kind="asinh", n=cfg.attn_n, c=cfg.attn_c, block=T,
-                                    range_guard=True, impl=self.impl, guard_words=self.guard_words,
+                                    range_guard=True, impl=self.impl, guard_words=self.guard_words[layer],
                                     out=attn_out.transpose(1, 2))
                 x, ss = ops.resid_projection(attn_out.view(B * T, d), p["w_o_t"][layer], x, out=x)
                 ff = ops.glu_projection(x, p["w_gu_t"][layer], cfg.alu_beta, row_ss=ss, eps=cfg.eps)
@@ -179,10 +183,11 @@ class Prefill:
             h = ops.rms_norm(x, ln1(layer), cfg.eps)
             if self.fused_proj:
                 qkv = ops.qkv_projection(h, p["w_qkv_t"][layer], H, T, self.cos_lp, self.sin_lp, p["q_gain"][layer],
-                                         p["k_gain"][layer], cfg.eps, cfg.attn_c, self.guard_words).view(B, T, 3, H, D)
+                                         p["k_gain"][layer], cfg.eps, cfg.attn_c, self.guard_words[layer],
+                                         guard_is_zero=True).view(B, T, 3, H, D)
                 q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))      # (B,H,T,D) views
                 ops.flash_attention(q, k, v, p["sink"][layer], kind="asinh", n=cfg.attn_n, c=cfg.attn_c, block=T,
-                                    range_guard=True, impl=self.impl, guard_words=self.guard_words,
+                                    range_guard=True, impl=self.impl, guard_words=self.guard_words[layer],
                                     out=attn_out.transpose(1, 2))
                 x = torch.addmm(x, attn_out.view(B * T, d), w_o(layer))
                 h2 = ops.rms_norm(x, ln2(layer), cfg.eps)

@@ -568,6 +568,22 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
         extra[f"attn_seq{T}"] = {"kernel_ms": ms_k, "kernel_frac_of_bf16_peak": fl / (ms_k * 1e-3) / 1e12 / peak_tf,
                                  "guarded_call_ms": ms_g, "guarded_call_frac_of_bf16_peak": fl / (ms_g * 1e-3) / 1e12 / peak_tf}
         del q, k, v, o
+    # the max-shifted form on the same kernel (what a failed guard costs): explicit shift=True at 8192
+    q, k, v = (x.to(dev) for x in make_attn_inputs(12, (1, ATTN["H"], ATTN["T"], ATTN["D"])))
+    sk = torch.zeros(ATTN["H"], device=dev)
+    o = torch.empty_like(q)
+    f_s = lambda i: A.flash_attention(q, k, v, sk, kind="asinh", n=ATTN["n"], c=ATTN["c"], shift=True, impl=args.kernel, out=o)  # noqa: E731
+    f_u = lambda i: A.ops._attention_unshifted_unclamped(q, k, v, sk, n=ATTN["n"], c=ATTN["c"], impl=args.kernel, out=o)  # noqa: E731
+    for i in range(3):
+        f_s(i)
+    ms_s = cuda_time(f_s, iters, sync)
+    for i in range(3):
+        f_u(i)
+    ms_u = cuda_time(f_u, iters, sync)
+    fl = attn_flops(1, ATTN["H"], ATTN["T"], ATTN["D"])
+    extra["attn_shifted_seq8192"] = {"ms": ms_s, "frac_of_bf16_peak": fl / (ms_s * 1e-3) / 1e12 / peak_tf,
+                                     "unshifted_ms_same_inputs": ms_u, "ratio": ms_s / ms_u}
+    del q, k, v, o
     # the attention shapes inside the prefill models (head_dim 64)
     for name, shape in (("attn_125m_layer", (16, 12, 1024, 64)), ("attn_350m_layer", (8, 16, 2048, 64))):
         q, k, v = (x.to(dev) for x in make_attn_inputs(13, shape))
@@ -593,9 +609,11 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
         for i in range(3):
             fn(i)
         ms_r = cuda_time(fn, iters, sync)
-        nbytes = 2.0 * x.numel() * 2
+        # rows in and out; the rotated form also reads each position's fp32 cos/sin table rows once
+        nbytes = 2.0 * x.numel() * 2 + ((cos.numel() + sin.numel()) * 4 if rot else 0)
         extra["qk_rms_rot" if rot else "qk_rms"] = {
-            "workload": f"(1,16,{T},{D}) bf16, 134 MB in + out", "ms": ms_r,
+            "workload": f"(1,16,{T},{D}) bf16, 134 MB in + out" + (", 17 MB of fp32 rotation tables in" if rot else ""),
+            "ms": ms_r,
             "gbs": nbytes / (ms_r * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms_r * 1e-3) / 1e9 / peak_bw}
     # backward of the same normalisation: reads x and dy, writes dx (+ the gain gradient)
     fnb = lambda i: A.ops.qk_rms_norm_backward(x, gain, y, 1e-5)  # noqa: E731

@@ -394,6 +394,9 @@ typedef struct {
   const float* row_ss;
   int ss_slots;
   float row_eps;
+  int guard_is_zero;       /* nonzero: the caller has zeroed `guard` in this stream since it was last maximised, so
+                              this call enqueues no memset (a caller with one record per layer zeroes them all at
+                              the start of its step, and no memset then sits between two kernels of the step) */
 } alg_qkv_proj_args;
 ALG_API int alg_qkv_proj_fwd(const alg_qkv_proj_args* args, void* stream);
 
