@@ -78,6 +78,7 @@ template <int D> struct Cfg {
   static constexpr uint32_t O_COL = 256;                    // O_w at O_COL + D w
   static constexpr uint32_t IDESC_S = make_idesc_bf16(BQ, BKEY, 0, 0);
   static constexpr uint32_t IDESC_PV = make_idesc_bf16(BQ, D, 0, 1);   // V is [key][d]: MN-major B
+  static constexpr uint32_t IDESC_PV64 = make_idesc_bf16(BQ, 64, 0, 1); // fp32 rows: 64 output columns from a hi|lo tile
 };
 
 struct __align__(16) Control {
@@ -95,12 +96,14 @@ __device__ __forceinline__ constexpr uint32_t p_col_of(uint32_t scol) { return 3
 
 // W (16 or 32) scores y -> W weights (y + sqrt(kappa + y^2))^n, two at a time on the packed fp32
 // pipe (fma.f32x2 / mul.f32x2); row-sum partials in `la`, `lb`; bf16 pairs in `packed`.
-template <int LOG2N, bool DIAG, int W>
+// With HILO, packed[W/2 ..] additionally receives the bf16 pairs of what the first rounding left
+// over (w - bf16(w)), so that hi + lo carries 16 bits of each weight into the P.V products.
+template <int LOG2N, bool DIAG, int W, bool HILO = false>
 __device__ __forceinline__ void weigh(const uint32_t* s, float kappa, int col0, int r, float2& la, float2& lb,
                                       uint32_t* packed) {
   if (DIAG && col0 > (r | 31)) {                    // warp-uniform: the block lies above the diagonal for all 32 rows
 #pragma unroll
-    for (int i = 0; i < W / 2; ++i) packed[i] = 0u;
+    for (int i = 0; i < (HILO ? W : W / 2); ++i) packed[i] = 0u;
     return;
   }
   const float2 kp = make_float2(kappa, kappa);
@@ -120,8 +123,13 @@ __device__ __forceinline__ void weigh(const uint32_t* s, float kappa, int col0, 
     }
     la = __fadd2_rn(la, t0);
     lb = __fadd2_rn(lb, t1);
-    packed[i >> 1] = pack_bf16(t0.x, t0.y);
-    packed[(i >> 1) + 1] = pack_bf16(t1.x, t1.y);
+    const uint32_t h0 = pack_bf16(t0.x, t0.y), h1 = pack_bf16(t1.x, t1.y);
+    packed[i >> 1] = h0;
+    packed[(i >> 1) + 1] = h1;
+    if (HILO) {
+      packed[W / 2 + (i >> 1)] = pack_bf16(t0.x - __uint_as_float(h0 << 16), t0.y - __uint_as_float(h0 & 0xffff0000u));
+      packed[W / 2 + (i >> 1) + 1] = pack_bf16(t1.x - __uint_as_float(h1 << 16), t1.y - __uint_as_float(h1 & 0xffff0000u));
+    }
   }
 }
 
@@ -156,6 +164,32 @@ __device__ __forceinline__ void weigh_tile(uint32_t s_taddr, int r, float kappa,
   tmem_ld_wait_for(b);
   weigh<LOG2N, DIAG, 32>(b, kappa, 96, r, la, lb, packed);
   tmem_st_32x16(s_taddr + p_col_of(96), packed);
+  signal_weights(p_full);
+}
+
+// fp32 rows: the weights go back as two bf16 halves, hi in the first 16 columns of each 32-column
+// block of scores and lo in the other 16 (the whole block is overwritten, still after it was read).
+template <int LOG2N, bool DIAG>
+__device__ __forceinline__ void weigh_tile_hilo(uint32_t s_taddr, int r, float kappa, float2& la, float2& lb,
+                                                uint64_t* p_half, uint64_t* p_full) {
+  uint32_t a[32], b[32], packed[32];
+  tmem_ld_32x32(s_taddr, a);
+  tmem_ld_wait_for(a);
+  tmem_ld_32x32(s_taddr + 32, b);
+  weigh<LOG2N, DIAG, 32, true>(a, kappa, 0, r, la, lb, packed);
+  tmem_st_32x32(s_taddr, packed);
+  tmem_ld_wait_for(b);
+  tmem_ld_32x32(s_taddr + 64, a);
+  weigh<LOG2N, DIAG, 32, true>(b, kappa, 32, r, la, lb, packed);
+  tmem_st_32x32(s_taddr + 32, packed);
+  signal_weights(p_half);
+  tmem_ld_wait_for(a);
+  tmem_ld_32x32(s_taddr + 96, b);
+  weigh<LOG2N, DIAG, 32, true>(a, kappa, 64, r, la, lb, packed);
+  tmem_st_32x32(s_taddr + 64, packed);
+  tmem_ld_wait_for(b);
+  weigh<LOG2N, DIAG, 32, true>(b, kappa, 96, r, la, lb, packed);
+  tmem_st_32x32(s_taddr + 96, packed);
   signal_weights(p_full);
 }
 
@@ -332,78 +366,73 @@ __device__ __forceinline__ bool item_at(const AttnParams& p, const ItemLists& li
   return true;
 }
 
-// The range guard's three maxima (src/algebraic/kernels/flash.py:834-849) - the largest squared row norm
-// of q in score units, the largest squared row norm of k, the largest |v| - are taken inside the
-// attention kernel, each CTA over a share of the rows, and written as one record per CTA (plain
-// stores: nothing to zero beforehand, nothing to contend for; the reader takes the largest over the
-// records).  The arithmetic costs issue slots that the weight warps also want, so it is spread over
-// three of the four sub-partitions of the SM instead of loading one:
-//   q  the Q scaler (warp 2) sums the squares of the Q tiles it passes over in shared memory anyway;
-//   k  warp 3, a lane per row, 16-byte loads of the whole row in flight at once, rows of the whole
-//      problem dealt over all CTAs;
-//   v  the 31 lanes of the producer warp that do not issue TMA copies, the same way.
-// The reference takes the norm of q after re-rounding q / (sqrt(D) c) to the input dtype; here the
+// The range guard's three maxima (src/algebraic/kernels/flash.py:834-849) taken by one otherwise idle
+// warp while the CTA does its attention work: the largest squared row norm of q in score units, the
+// largest squared row norm of k, the largest |v|, each over the rows this CTA looks at (the reader
+// takes the largest over the CTAs' records).  A lane owns a row (all of its 16-byte loads in
+// flight at once, no shuffles); the rows of the whole problem are dealt over all CTAs.  The
+// reference takes the norm of q after re-rounding q / (sqrt(D) c) to the input dtype; here the
 // unrounded norm is multiplied by (1 + 2^-8), an upper bound on what that rounding can add, so the
 // guard can only err towards the shifted (always valid) form.  NaN anywhere fails the guard.
-__device__ __forceinline__ float nan_to_inf(float x) { return (x == x) ? x : __int_as_float(0x7f800000); }   // +inf orders above everything as an unsigned word
-
 template <int D>
-__device__ __forceinline__ const uint4* guard_row(const void* base, const Strides3& st, int H, int T, int64_t r) {
-  const int t = int(r % T);
-  const int64_t bh = r / T;
-  return reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(base) + (bh / H) * st.b + (bh % H) * st.h + int64_t(t) * st.t);
-}
-
-// Largest squared row norm of k over rows first, first + step, ... (this thread's share); NaN sticks.
-template <int D>
-__device__ __forceinline__ float guard_k_rows(const AttnParams& p, int64_t first, int64_t step) {
+__device__ __forceinline__ void guard_statistics(const AttnParams& p, GuardWords* out, int lane) {
   constexpr int NV = D / 8;                       // 16-byte vectors per row
-  const int64_t rows = int64_t(p.B) * p.H * p.Tk;
-  float m = 0.f;
-  for (int64_t r = first; r < rows; r += step) {
-    const uint4* src = guard_row<D>(p.k, p.ks, p.H, p.Tk, r);
-    uint4 raw[NV];
+  const int64_t step = int64_t(gridDim.x) * 32;
+  float best[2] = {0.f, 0.f};
+  for (int which = 0; which < 2; ++which) {
+    const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(which == 0 ? p.q : p.k);
+    const Strides3& st = which == 0 ? p.qs : p.ks;
+    const int T = which == 0 ? p.Tq : p.Tk;
+    const int64_t rows = int64_t(p.B) * p.H * T;
+    float m = 0.f;
+    for (int64_t r = int64_t(blockIdx.x) * 32 + lane; r < rows; r += step) {
+      const int t = int(r % T);
+      const int64_t bh = r / T;
+      const uint4* src = reinterpret_cast<const uint4*>(base + (bh / p.H) * st.b + (bh % p.H) * st.h + int64_t(t) * st.t);
+      uint4 raw[NV];
 #pragma unroll
-    for (int i = 0; i < NV; ++i) raw[i] = __ldg(src + i);
-    float2 acc = make_float2(0.f, 0.f);
+      for (int i = 0; i < NV; ++i) raw[i] = __ldg(src + i);
+      float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
+      for (int i = 0; i < NV; ++i) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); acc = __ffma2_rn(f, f, acc); }
+        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); acc = __ffma2_rn(f, f, acc); }
+      }
+      const float ss = acc.x + acc.y;
+      m = (ss > m || ss != ss) ? ss : m;          // a NaN sticks
     }
-    const float ss = acc.x + acc.y;
-    m = (ss > m || ss != ss) ? ss : m;
+    best[which] = m;
   }
-  return m;
-}
-
-// Largest |v| over this thread's share of the rows; NaN sticks.
-template <int D>
-__device__ __forceinline__ float guard_v_rows(const AttnParams& p, int64_t first, int64_t step) {
-  constexpr int NV = D / 8;
-  const int64_t rows = int64_t(p.B) * p.H * p.Tk;
   __nv_bfloat162 vm2 = __float2bfloat162_rn(0.f);
-  for (int64_t r = first; r < rows; r += step) {
-    const uint4* src = guard_row<D>(p.v, p.vs, p.H, p.Tk, r);
-    uint4 raw[NV];
+  {
+    const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(p.v);
+    const int64_t rows = int64_t(p.B) * p.H * p.Tk;
+    for (int64_t r = int64_t(blockIdx.x) * 32 + lane; r < rows; r += step) {
+      const int t = int(r % p.Tk);
+      const int64_t bh = r / p.Tk;
+      const uint4* src = reinterpret_cast<const uint4*>(base + (bh / p.H) * p.vs.b + (bh % p.H) * p.vs.h + int64_t(t) * p.vs.t);
+      uint4 raw[NV];
 #pragma unroll
-    for (int i = 0; i < NV; ++i) raw[i] = __ldg(src + i);
+      for (int i = 0; i < NV; ++i) raw[i] = __ldg(src + i);
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
+      for (int i = 0; i < NV; ++i) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) vm2 = __hmax2_nan(vm2, __habs2(h[e]));
+        for (int e = 0; e < 4; ++e) vm2 = __hmax2_nan(vm2, __habs2(h[e]));
+      }
     }
   }
   const float2 vm = __bfloat1622float2(vm2);
-  return (vm.x > vm.y || vm.x != vm.x) ? vm.x : vm.y;
-}
-
-// One word of this CTA's record: the warp's largest value (all 32 lanes call).
-__device__ __forceinline__ void guard_store(unsigned* word, float mine, int lane) {
-  const float m = warp_max(nan_to_inf(mine));
-  if (lane == 0) *word = __float_as_uint(m);
+  float stat[3] = {best[0] * (p.scale * p.scale * 1.00390625f), best[1], (vm.x > vm.y || vm.x != vm.x) ? vm.x : vm.y};
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    float x = stat[i];
+    if (!(x == x)) x = __int_as_float(0x7f800000);  // NaN -> +inf, which orders above everything as an unsigned word
+    stat[i] = warp_max(x);
+  }
+  // one record per CTA, plain stores: nothing to zero beforehand, nothing to contend for
+  if (lane == 0) *reinterpret_cast<uint4*>(out + blockIdx.x) = make_uint4(__float_as_uint(stat[0]), __float_as_uint(stat[1]), __float_as_uint(stat[2]), 0u);
 }
 
 template <int D> constexpr size_t smem_bytes() { return size_t(Cfg<D>::CTL_OFF) + sizeof(Control) + 1024; }
@@ -422,12 +451,18 @@ struct ScaleSplit {
 #define ALG_T(acc, expr) (expr)
 #endif
 
-template <int D, int LOG2N, int SPLIT, bool SHIFT>
+// F32 (with D = 128, SPLIT = 1, unshifted): head_dim-64 fp32 rows.  q, k, v arrive as bf16 tiles of
+// 128 columns, the first 64 the bf16 rounding of the fp32 values (hi) and the other 64 what it left
+// over (lo); every product is issued as hi.hi + hi.lo + lo.hi into the same accumulator, for the
+// scores and - with the weights split the same way - for the output, which is written as fp32.
+template <int D, int LOG2N, int SPLIT, bool SHIFT, bool F32 = false>
 __global__ void __launch_bounds__(nthreads<SPLIT>(), 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p, const ScaleSplit sc,
                const __grid_constant__ ItemLists lists) {
   using C = Cfg<D>;
+  static_assert(!F32 || (D == 128 && SPLIT == 1 && !SHIFT), "the fp32 mode: hi|lo tiles of head_dim 64, unshifted form");
+  constexpr int DV = F32 ? 64 : D;                  // output columns
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Control* ctl = reinterpret_cast<Control*>(smem + C::CTL_OFF);
@@ -440,17 +475,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     if (lane == 0) ctl->shift_mode = sh ? 1 : 0;
   }
   __syncthreads();
-  // a stand-by launch behind this one may take its place on every SM this kernel's CTAs leave
-  if (threadIdx.x == 0) griddep_launch_dependents();
   // each form runs only when it is the one called for: under a guard the unshifted kernel leaves when the
   // guard failed and the shifted kernel leaves when it held
   if ((ctl->shift_mode != 0) != SHIFT) return;
 
   if (threadIdx.x == 0) {
-    for (int w = 0; w < 2; ++w) {
-      mbar_init(&ctl->q_full[w], 1); mbar_init(&ctl->q_ready[w], 1);
-      mbar_init(&ctl->q_free[w], p.guard_out != nullptr ? 2 : 1);   // the releasing thread, and the Q scaler when it also reads the tile for the guard
-    }
+    for (int w = 0; w < 2; ++w) { mbar_init(&ctl->q_full[w], 1); mbar_init(&ctl->q_ready[w], 1); mbar_init(&ctl->q_free[w], 1); }
     for (int i = 0; i < C::NKV; ++i) { mbar_init(&ctl->kv_full[i], 1); mbar_init(&ctl->kv_empty[i], 1); }
     for (int w = 0; w < 2; ++w) {
       mbar_init(&ctl->s_full[w], 1);
@@ -513,14 +543,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int idx = 2; idx < 2 * it.n1 && ok; ++idx) ok = load_kv(idx);
       }
     }
-    if (p.guard_out != nullptr) {
-      // the warp's other 31 lanes take the guard's largest |v| meanwhile (the two paths of the warp run
-      // interleaved; they meet again here)
-      float vmax = 0.f;
-      if (lane != 0) vmax = guard_v_rows<D>(p, int64_t(blockIdx.x) * 31 + (lane - 1), int64_t(gridDim.x) * 31);
-      __syncwarp();
-      guard_store(&p.guard_out[blockIdx.x].vmax, vmax, lane);
-    }
   } else if (warp == 1) {
     // The MMA warp.  Its own instruction time is the scarce resource: an issue costs the issuing
     // thread 30 to 50 cycles (the lower figure when the whole warp runs the loop and one elected
@@ -552,10 +574,22 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       ALG_TI0
       const uint32_t qa = q_lo0 + w * (C::TILE_BYTES >> 4), ka = k_lo0 + slot * (C::TILE_BYTES >> 4);
       const uint32_t d_tmem = tmem_base + C::S_COL + w * 128;
+      if constexpr (F32) {                         // q_hi.k_hi + q_hi.k_lo + q_lo.k_hi: panel 0 holds hi, panel 1 lo
+        constexpr uint32_t LO = PANEL_BYTES >> 4;
 #pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks) {
-        const uint32_t off = ((ks >> 2) * PANEL_BYTES + (ks & 3) * 32) >> 4;
-        umma_f16_ss_parts(d_tmem, qa + off, SW128_DESC_HI, ka + off, SW128_DESC_HI, C::IDESC_S, ks != 0 ? 1u : 0u);
+        for (int g = 0; g < 3; ++g) {
+          const uint32_t qo = (g == 2) ? LO : 0u, ko = (g == 1) ? LO : 0u;
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_f16_ss_parts(d_tmem, qa + qo + ((ks * 32) >> 4), SW128_DESC_HI, ka + ko + ((ks * 32) >> 4), SW128_DESC_HI, C::IDESC_S,
+                              (g != 0 || ks != 0) ? 1u : 0u);
+        }
+      } else {
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = ((ks >> 2) * PANEL_BYTES + (ks & 3) * 32) >> 4;
+          umma_f16_ss_parts(d_tmem, qa + off, SW128_DESC_HI, ka + off, SW128_DESC_HI, C::IDESC_S, ks != 0 ? 1u : 0u);
+        }
       }
       ALG_TI1
     };
@@ -564,11 +598,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       ALG_TI0
       const uint32_t va = v_lo0 + slot * (C::TILE_BYTES >> 4);
       const uint32_t d_tmem = tmem_base + C::O_COL + w * D, p_tmem = tmem_base + C::S_COL + w * 128;
+      if constexpr (F32) {                         // p_hi.v_hi + p_lo.v_hi + p_hi.v_lo; p_lo sits 16 columns behind p_hi
+        constexpr uint32_t LO = PANEL_BYTES >> 4;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {                 // 16 keys = 8 packed-bf16 columns of P per step
-        const int ks = 4 * h64 + i;
-        umma_f16_ts_parts(d_tmem, p_tmem + p_col_of(16 * ks), va + ks * (2048 >> 4), SW128_DESC_HI, C::IDESC_PV,
-                          (first && ks == 0) ? 0u : 1u);
+        for (int g = 0; g < 3; ++g) {
+          const uint32_t po = (g == 1) ? 16u : 0u, vo = (g == 2) ? LO : 0u;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int ks = 4 * h64 + i;
+            umma_f16_ts_parts(d_tmem, p_tmem + p_col_of(16 * ks) + po, va + vo + ks * (2048 >> 4), SW128_DESC_HI, C::IDESC_PV64,
+                              (first && ks == 0 && g == 0) ? 0u : 1u);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {               // 16 keys = 8 packed-bf16 columns of P per step
+          const int ks = 4 * h64 + i;
+          umma_f16_ts_parts(d_tmem, p_tmem + p_col_of(16 * ks), va + ks * (2048 >> 4), SW128_DESC_HI, C::IDESC_PV,
+                            (first && ks == 0) ? 0u : 1u);
+        }
       }
       ALG_TI1
     };
@@ -638,8 +686,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // the swizzled layout does not matter), make the result visible to the tensor core's reads
     // and release the tile to the MMA warp.
     const __nv_bfloat162 f2 = __float2bfloat162_rn(sc.pow2);
-    const bool stats = p.guard_out != nullptr;      // also takes the guard's largest squared row norm of q
-    float qbest = 0.f;
     bool ok = true;
     for (int k = 0; ok && item_at(p, lists, k, it); ++k) {
       for (int w = 0; w < 2 && ok; ++w) {
@@ -658,44 +704,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         __syncwarp();
         if (lane == 0) mbar_arrive(&ctl->q_ready[w]);
       }
-      if (!stats || !ok) continue;
-      // Both tiles are with the MMA warp now.  A second, read-only pass over them (nobody waits for it)
-      // sums the squares of every row; the tile is not overwritten before this warp has said it is done
-      // with it too.  A warp instruction covers four 128-byte rows of a 64-column panel: lane / 8 is the
-      // row, lane % 8 the 16-byte piece (which piece of the row it is does not matter to a sum).
-      for (int w = 0; w < 2; ++w) {
-        const uint4* tile = reinterpret_cast<const uint4*>(smem + C::Q_OFF + w * C::TILE_BYTES);
-#pragma unroll 2
-        for (int i = lane; i < PANEL_BYTES / 16; i += 32) {
-          float2 acc = make_float2(0.f, 0.f);
-#pragma unroll
-          for (int pn = 0; pn < C::PANELS; ++pn) {
-            const uint4 v = tile[pn * (PANEL_BYTES / 16) + i];
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); acc = __ffma2_rn(f, f, acc); }
-          }
-          float ss = acc.x + acc.y;
-          ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-          ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-          ss += __shfl_xor_sync(0xffffffffu, ss, 4);
-          qbest = (ss > qbest || ss != ss) ? ss : qbest;        // a NaN sticks
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&ctl->q_free[w]);
-      }
-    }
-    // the rows were read after the multiplication by 2^e: what is left of the score scale is (scale / 2^e)^2
-    if (stats) {
-      const float rest = p.scale / sc.pow2;
-      guard_store(&p.guard_out[blockIdx.x].q2, qbest * (rest * rest * 1.00390625f), lane);
     }
   } else if (warp == 3) {
 #ifdef ALG_ATTN_TIMING
     const long long tg0 = clock64();
 #endif
-    if (p.guard_out != nullptr)
-      guard_store(&p.guard_out[blockIdx.x].k2, guard_k_rows<D>(p, int64_t(blockIdx.x) * 32 + lane, int64_t(gridDim.x) * 32), lane);
+    if (p.guard_out != nullptr) guard_statistics<D>(p, p.guard_out, lane);
 #ifdef ALG_ATTN_TIMING
     if (lane == 0 && p.stat != nullptr) p.stat[40 + 2 * blockIdx.x] = float(clock64() - tg0);
 #endif
@@ -774,6 +788,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         } else if (SPLIT == 2) {
           if (j == nk - 1) weigh_half_tile<LOG2N, true>(s_taddr, half, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);   // diagonal tile: masked
           else weigh_half_tile<LOG2N, false>(s_taddr, half, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
+        } else if (F32) {
+          if (j == nk - 1) weigh_tile_hilo<LOG2N, true>(s_taddr, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
+          else weigh_tile_hilo<LOG2N, false>(s_taddr, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
         } else {
           if (j == nk - 1) weigh_tile<LOG2N, true>(s_taddr, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
           else weigh_tile<LOG2N, false>(s_taddr, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
@@ -806,8 +823,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       l += part;                                    // shifted form: the last tile's sums (already at the final maximum)
       const float inv = 1.0f / l;
       const int row = it.row0 + w * BQ + r;
-      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + it.b * p.os.b + it.h * p.os.h + int64_t(row) * p.os.t;
-      constexpr int CHUNKS = D / 32 / SPLIT;         // a split group divides the output columns as well
+      const int64_t o_off = it.b * p.os.b + it.h * p.os.h + int64_t(row) * p.os.t;
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + o_off;
+      constexpr int CHUNKS = DV / 32 / SPLIT;        // a split group divides the output columns as well
 #pragma unroll 1
       for (int chunk = half * CHUNKS; chunk < (half + 1) * CHUNKS; ++chunk) {
         uint32_t o[32];
@@ -816,6 +834,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (chunk == (half + 1) * CHUNKS - 1) {     // O_w is in registers: the next item may overwrite it
           tc_fence_before();
           mbar_arrive(&ctl->o_free[w]);
+        }
+        if constexpr (F32) {
+          float* frow = reinterpret_cast<float*>(p.o) + o_off + chunk * 32;
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<float4*>(frow + 4 * c) = make_float4(__uint_as_float(o[4 * c]) * inv, __uint_as_float(o[4 * c + 1]) * inv,
+                                                                   __uint_as_float(o[4 * c + 2]) * inv, __uint_as_float(o[4 * c + 3]) * inv);
+          continue;
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -889,7 +915,7 @@ int make_qkv_map(CUtensorMap* tm, const void* base, const Strides3& s, int B, in
   return make_tmap_bf16(tm, base, 4, dims, strides, box, true);
 }
 
-template <int D, int LOG2N, int SPLIT, bool SHIFT>
+template <int D, int LOG2N, int SPLIT, bool SHIFT, bool F32 = false>
 int launch_dns(const AttnParams& p, cudaStream_t stream) {
   CUtensorMap tq, tk, tv;
   if (int rc = make_qkv_map(&tq, p.q, p.qs, p.B, p.H, p.Tq, D)) return rc;
@@ -906,7 +932,7 @@ int launch_dns(const AttnParams& p, cudaStream_t stream) {
     sc.inv_mn = float(pow(m, -double(1 << LOG2N)));
     if (SHIFT) { sc.pow2 = 1.0f; sc.kappa = 1.0f; sc.inv_mn = 1.0f; }   // the shifted form scales its scores itself
   }
-  auto kern = attn_tc_kernel<D, LOG2N, SPLIT, SHIFT>;
+  auto kern = attn_tc_kernel<D, LOG2N, SPLIT, SHIFT, F32>;
   static PerDeviceOnce configured;
   int sms = 0;
   if (int rc = configured.run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes<D>())); }, &sms)) return rc;
@@ -948,7 +974,70 @@ int launch_d(const AttnParams& p, cudaStream_t stream) {
   return ALG_ERR_UNSUPPORTED;
 }
 
+// ---- fp32 rows (head_dim 64): split into bf16 hi | lo tiles of 128 columns ---------------------
+// x (B, H, T, 64) fp32 with strides -> y (B, H, T, 128) bf16 dense: y[.., j] = bf16(x[.., j]) and
+// y[.., 64 + j] = bf16(x[.., j] - y[.., j]).  hi + lo carries 16 bits of the mantissa, and the three
+// products hi.hi + hi.lo + lo.hi reproduce an fp32 product to about 2^-16 (src/algebraic/kernels/
+// flash.py computes its fp32 path in fp32; the parity bar for fp32 I/O is rel-L2 1e-3).
+struct SplitJob { const float* x; __nv_bfloat16* y; Strides3 xs; int T; };
+struct SplitBatch { SplitJob t[3]; int B, H; };
+
+__global__ void __launch_bounds__(256) split_f32_kernel(const SplitBatch batch) {
+  griddep_wait();
+  const SplitJob& job = batch.t[blockIdx.y];
+  const int64_t vecs = int64_t(batch.B) * batch.H * job.T * 16;       // float4 pieces: 16 per row
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < vecs; i += int64_t(gridDim.x) * blockDim.x) {
+    const int piece = int(i & 15);
+    const int64_t row = i >> 4;
+    const int t = int(row % job.T);
+    const int64_t bh = row / job.T;
+    const float4 v = *reinterpret_cast<const float4*>(job.x + (bh / batch.H) * job.xs.b + (bh % batch.H) * job.xs.h + int64_t(t) * job.xs.t + piece * 4);
+    const uint32_t h0 = pack_bf16(v.x, v.y), h1 = pack_bf16(v.z, v.w);
+    const uint32_t l0 = pack_bf16(v.x - __uint_as_float(h0 << 16), v.y - __uint_as_float(h0 & 0xffff0000u));
+    const uint32_t l1 = pack_bf16(v.z - __uint_as_float(h1 << 16), v.w - __uint_as_float(h1 & 0xffff0000u));
+    __nv_bfloat16* out = job.y + row * 128 + piece * 4;
+    *reinterpret_cast<uint2*>(out) = make_uint2(h0, h1);
+    *reinterpret_cast<uint2*>(out + 64) = make_uint2(l0, l1);
+  }
+}
+
 }  // namespace
+
+size_t attn_tcgen05_f32_split_bytes(int B, int H, int T) { return size_t(B) * H * T * 128 * sizeof(__nv_bfloat16); }
+
+bool attn_tcgen05_f32_supports(const AttnParams& p, int dtype) {
+  return dtype == ALG_F32 && p.causal && p.Tq == p.Tk && p.Tq % (2 * BQ) == 0 && p.D == 64 && p.log2n >= 3 && p.log2n <= 5;
+}
+
+// p describes the fp32 problem (q, k, v, o fp32 with their strides); `split` holds three buffers of
+// attn_tcgen05_f32_split_bytes each.  Unshifted form only (under a guard the kernel leaves when the
+// guard calls for the shift, like the bf16 one).
+int launch_attn_tcgen05_f32(const AttnParams& p, void* split, cudaStream_t stream) {
+  const size_t each = attn_tcgen05_f32_split_bytes(p.B, p.H, p.Tq);
+  unsigned char* base = static_cast<unsigned char*>(split);
+  SplitBatch batch{};
+  batch.B = p.B; batch.H = p.H;
+  batch.t[0] = {static_cast<const float*>(p.q), reinterpret_cast<__nv_bfloat16*>(base), p.qs, p.Tq};
+  batch.t[1] = {static_cast<const float*>(p.k), reinterpret_cast<__nv_bfloat16*>(base + each), p.ks, p.Tk};
+  batch.t[2] = {static_cast<const float*>(p.v), reinterpret_cast<__nv_bfloat16*>(base + 2 * each), p.vs, p.Tk};
+  const int64_t vecs = int64_t(p.B) * p.H * p.Tq * 16;
+  int64_t blocks = (vecs + 255) / 256;
+  if (blocks > int64_t(sm_count()) * 8) blocks = int64_t(sm_count()) * 8;
+  ALG_CUDA_TRY(launch_dependent(split_f32_kernel, dim3(unsigned(blocks), 3), dim3(256), 0, stream, batch));
+  count_launch();
+  AttnParams ps = p;
+  ps.q = batch.t[0].y; ps.k = batch.t[1].y; ps.v = batch.t[2].y;
+  const Strides3 dense = {int64_t(p.H) * p.Tq * 128, int64_t(p.Tq) * 128, 128};
+  ps.qs = dense; ps.ks = dense; ps.vs = dense;
+  ps.guard_out = nullptr;
+  switch (p.log2n) {
+    case 3: return launch_dns<128, 3, 1, false, true>(ps, stream);
+    case 4: return launch_dns<128, 4, 1, false, true>(ps, stream);
+    case 5: return launch_dns<128, 5, 1, false, true>(ps, stream);
+  }
+  set_error("attention (tcgen05): n must be 8, 16 or 32");
+  return ALG_ERR_UNSUPPORTED;
+}
 
 bool attn_tcgen05_supports(const AttnParams& p, int dtype) {
   const bool strides_fit = p.qs.t > 0 && p.ks.t > 0 && p.vs.t > 0 && p.qs.h >= 0 && p.qs.b >= 0 &&

@@ -154,6 +154,22 @@ size_t alg_attn_workspace_bytes(const alg_attn_args* a) {
     bytes += align256(size_t(a->B) * a->H * a->Tq * a->D * es);
     bytes += align256(size_t(a->B) * a->H * a->Tk * a->D * es);
   }
+  // fp32 rows the tcgen05 kernel can take (head_dim 64, causal self-attention over a multiple of 256): room for
+  // the bf16 hi | lo copies of q, k, v.  A call that brings less than this runs on the mma.sync kernel.
+  if (a->dtype == ALG_F32 && a->D == 64 && a->causal && a->Tq == a->Tk && a->Tq > 0 && a->Tq % 256 == 0)
+    bytes = align256(bytes) + 3 * align256(attn_tcgen05_f32_split_bytes(a->B, a->H, a->Tq));
+  return bytes;
+}
+
+// The part of the attention workspace every call may need (guard records, prologue outputs): a call
+// without the fp32 split buffers is still valid with this much.
+static size_t attn_workspace_bytes_without_split(const alg_attn_args* a) {
+  size_t bytes = kGuardBytes;
+  if (attn_has_prologue(a)) {
+    const size_t es = elem_size(a->dtype);
+    bytes += align256(size_t(a->B) * a->H * a->Tq * a->D * es);
+    bytes += align256(size_t(a->B) * a->H * a->Tk * a->D * es);
+  }
   return bytes;
 }
 
@@ -174,7 +190,7 @@ int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
   const bool guard_given = a->guard_words != nullptr && a->variant == ALG_VARIANT_GUARD;
   if (guard_given && prologue) { set_error("attention: guard_words describe ready-made q, k, v; not with the fused prologue"); return ALG_ERR_INVALID; }
   if (guard_given && !aligned16(a->guard_words)) { set_error("attention: guard_words must be 16-byte aligned"); return ALG_ERR_INVALID; }
-  const size_t need = alg_attn_workspace_bytes(a);
+  const size_t need = attn_workspace_bytes_without_split(a);
   const bool need_ws = prologue || (a->variant == ALG_VARIANT_GUARD && !guard_given);
   if (need_ws && (a->workspace == nullptr || a->workspace_bytes < need || !aligned16(a->workspace))) {
     set_error("attention: workspace of %zu bytes (16-byte aligned) required, got %zu", need, a->workspace_bytes);
@@ -271,11 +287,24 @@ int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
     }
   }
 
+  // fp32 rows of head_dim 64: the same tcgen05 kernel on bf16 hi | lo copies, when the caller's workspace has
+  // room for them; the max-shifted form (explicit, or a failed guard) stays on the mma.sync kernel
+  const size_t split_off = align256(need), split_each = align256(attn_tcgen05_f32_split_bytes(a->B, a->H, a->Tq));
+  const bool f32_tc = attn_tcgen05_f32_supports(p, a->dtype) && a->variant != ALG_VARIANT_SHIFT && !(a->score_clamp > 0.0f) &&
+                      a->impl != ALG_IMPL_MMA && ws != nullptr && aligned16(ws) && a->workspace_bytes >= split_off + 3 * split_each;
+  if (f32_tc) {
+    p.run_if = guarded ? 1 : 0;
+    if (int rc = launch_attn_tcgen05_f32(p, ws + split_off, stream)) return rc;
+    if (!guarded) return ALG_OK;
+    p.run_if = 2;                                       // the max-shifted form runs only if the guard failed
+    return launch_attn_mma(p, a->dtype, stream);
+  }
   // the tcgen05 kernel has the unshifted form without a score clamp and the max-shifted form
   const bool shape_ok = attn_tcgen05_supports(p, a->dtype);
   const bool fast_ok = shape_ok && (a->variant == ALG_VARIANT_SHIFT || !(a->score_clamp > 0.0f));
   if (a->impl == ALG_IMPL_TCGEN05 && !fast_ok) {
-    set_error("attention: the tcgen05 kernel covers bf16, causal Tq == Tk multiple of 256, head_dim 64 or 128, no score clamp");
+    set_error("attention: the tcgen05 kernel covers causal Tq == Tk multiple of 256 without a score clamp: bf16 with head_dim 64 or 128, fp32 "
+              "with head_dim 64 in the unshifted form given the workspace alg_attn_workspace_bytes asks for");
     return ALG_ERR_UNSUPPORTED;
   }
   if (fast_ok && a->impl != ALG_IMPL_MMA) {

@@ -148,17 +148,15 @@ __device__ __forceinline__ bool guard_in_range(const GuardWords* g, float bound_
   return (q2 * k2 <= bound_sq) && (vm <= vmax_limit);
 }
 
-// Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute may
-// start while the kernel before it in the stream still runs; griddep_wait() in it returns once
-// that kernel has finished and its writes are visible (a no-op in a kernel launched the plain way).
-// griddep_launch_dependents() in the earlier kernel says this CTA does not mind: the next kernel's CTAs
-// are placed as soon as every CTA here has said so or left, wherever there is room.
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute is
+// placed on an SM as soon as the CTAs of the kernel before it in the stream have left it, instead of
+// after that whole kernel has drained; griddep_wait() in it returns once that kernel has finished
+// and its writes are visible (a no-op in a kernel launched the plain way).  So a kernel's set-up
+// (barriers, tensor memory, descriptor prefetch) and its launch latency overlap the tail of the one
+// before.  The earlier kernels do not announce themselves early (griddepcontrol.launch_dependents):
+// measured on the prefill step, CTAs that sit waiting beside a running kernel cost a long step 1-2 %,
+// while leaving it to each CTA's exit keeps the whole gain of the short steps (3 % at 2048 tokens).
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void griddep_launch_dependents() {
-#ifndef ALG_PDL_NO_TRIGGER
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-#endif
-}
 
 // Launch `kern` so that it may start before the kernel ahead of it in `stream` has finished
 // (programmatic dependent launch); the kernel itself calls griddep_wait() before it touches

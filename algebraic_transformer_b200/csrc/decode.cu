@@ -10,8 +10,8 @@
 // accumulates w * V for the 8 columns it holds.  No step of the key loop involves the whole
 // CTA, so nothing but the ring's barriers paces it; the eight warp states are merged once at
 // the end with the same exact rescale, and the (acc, m, l) states of the splits are merged,
-// with the sink, by decode_combine_kernel (a programmatic dependent launch: its CTAs are resident
-// and waiting when the last split finishes).  All mbarrier waits are bounded.
+// with the sink, by decode_combine_kernel (a programmatic dependent launch: its CTAs move in as
+// the split kernel's leave).  All mbarrier waits are bounded.
 #include "common.cuh"
 #include "launchers.h"
 #include "sm100_ptx.cuh"
@@ -66,7 +66,6 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     fence_barrier_init();
   }
   __syncthreads();
-  if (threadIdx.x == 0) griddep_launch_dependents();   // the combine kernel's CTAs may take their places and wait
   const BoundedWait bw{&ctl->abort_flag, 1000000000ull};
 
   if (warp == CONSUMERS / 32) {                 // producer warp

@@ -41,7 +41,6 @@ __global__ void __launch_bounds__(XT) head_exchange_kernel(const ExchangeParams 
   __shared__ bool s_last;
   const int nb = gridDim.x;
   griddep_wait();                 // launched as a programmatic dependent of the head kernel ahead in the stream
-  griddep_launch_dependents();
   // call number: read by every block at its start; advanced by the last block to finish
   if (threadIdx.x == 0) s_call = *reinterpret_cast<volatile unsigned*>(p.call_counter) + 1u;
   __syncthreads();

@@ -167,7 +167,6 @@ __global__ void head_reduce_kernel(const float* __restrict__ l_part, const float
                                    const float* __restrict__ m_part, int N, int splits, float* __restrict__ l_out,
                                    float* __restrict__ zt_out) {
   griddep_wait();                 // launched as a programmatic dependent of the kernel ahead in the stream
-  griddep_launch_dependents();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= N) return;
   float l = 0.f, z = 0.f;
@@ -199,7 +198,6 @@ __global__ void __launch_bounds__(FIN_THREADS) head_finalize_kernel(
     float* __restrict__ pt_out, float* __restrict__ nll_out, float* __restrict__ obj_out,
     float* __restrict__ block_sums, unsigned* __restrict__ ticket) {
   griddep_wait();                 // launched as a programmatic dependent of the kernel ahead in the stream
-  griddep_launch_dependents();
   __shared__ float red[FIN_THREADS / 32];
   __shared__ bool last;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;

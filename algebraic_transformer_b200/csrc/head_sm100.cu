@@ -82,9 +82,8 @@ head_tc_kernel(const __grid_constant__ CUtensorMap tm_h, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   // Launched as a programmatic dependent: everything above overlapped the tail of the kernel ahead in the
-  // stream; from here on its results are complete.  The kernel behind may move in the same way.
+  // stream; from here on its results are complete.
   griddep_wait();
-  if (threadIdx.x == 0) griddep_launch_dependents();
   const uint32_t tmem_base = ctl->tmem_base;
   const BoundedWait bw{&ctl->abort_flag, 1000000000ull};
   const int ntiles = (p.V_local + BN - 1) / BN;

@@ -79,6 +79,11 @@ bool attn_tcgen05_supports(const AttnParams& p, int dtype);
 bool attn_tcgen05_takes_guard_statistics(const AttnParams& p);
 int attn_tcgen05_grid(const AttnParams& p);          // CTAs of that kernel = records it writes to guard_out
 int launch_attn_tcgen05(const AttnParams& p, cudaStream_t stream);
+// fp32 rows of head_dim 64 on the same kernel: q, k, v are first split into bf16 hi | lo tiles (three
+// buffers of attn_tcgen05_f32_split_bytes each, at `split`); unshifted form, fp32 output
+bool attn_tcgen05_f32_supports(const AttnParams& p, int dtype);
+size_t attn_tcgen05_f32_split_bytes(int B, int H, int T);
+int launch_attn_tcgen05_f32(const AttnParams& p, void* split, cudaStream_t stream);
 
 // Shared by both attention kernels: does this launch use the max-shifted form?  Called by all 32
 // lanes of one warp; every lane gets the answer.

@@ -33,7 +33,6 @@ template <int VPL, int RPW>
 __global__ void __launch_bounds__(256) rms_rows_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gain,
                                                        __nv_bfloat16* __restrict__ y, int64_t rows, int d, float eps) {
   griddep_wait();                 // launched as a programmatic dependent of the kernel ahead in the stream
-  griddep_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int64_t warp_global = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t warps_total = (int64_t(gridDim.x) * blockDim.x) >> 5;
@@ -93,7 +92,6 @@ __global__ void __launch_bounds__(256) alu_glu_kernel(const __nv_bfloat16* __res
                                                       __nv_bfloat16* __restrict__ out, int64_t rows, int f, int64_t ld_in,
                                                       int64_t ld_out, float beta) {
   griddep_wait();                 // launched as a programmatic dependent of the kernel ahead in the stream
-  griddep_launch_dependents();
   const size_t stride = size_t(gridDim.x) * blockDim.x;
   const int vpr = f / 8;
   const size_t nvec = size_t(rows) * vpr;
@@ -164,7 +162,6 @@ int launch_alu_glu(const void* gate, const void* up, void* out, int64_t rows, in
 __global__ void __launch_bounds__(256) row_sumsq_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows, int d, int64_t ld,
                                                         float* __restrict__ ss_out) {
   griddep_wait();                 // launched as a programmatic dependent of the kernel ahead in the stream
-  griddep_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int64_t warp_global = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t warps_total = (int64_t(gridDim.x) * blockDim.x) >> 5;

@@ -295,7 +295,6 @@ __global__ void __launch_bounds__(256, 3) qk_rms_bwd_kernel(const RmsBwdParams p
     g[i] = (p.gain != nullptr) ? p.gain[lir * VEC + i] : 1.0f;
     dg[i] = 0.f;
   }
-  griddep_launch_dependents();     // the partial-row sum behind this kernel may take its place and wait
   // four row groups per step, all eight 16-byte loads issued before any is used (memory-level parallelism)
   constexpr int U = 4;
   const bool narrow = rows < (int64_t(1) << 31);

@@ -350,6 +350,46 @@ def test_shifted_form_on_tcgen05(D, T, n, c, case):
     assert torch.equal(got, again)
 
 
+@pytest.mark.parametrize("T", [256, 1024, 1280])
+@pytest.mark.parametrize("n,c", [(16, 8.0), (8, 1.0), (32, 8.0)])
+@pytest.mark.parametrize("case", ["plain", "sink", "guard_holds", "guard_fails", "strided"])
+def test_fp32_rows_on_tcgen05(T, n, c, case):
+    """fp32 q, k, v of head_dim 64 on the tcgen05 kernel (impl="tcgen05" is an error where that kernel does
+    not apply): rows split into bf16 hi | lo halves, every product as hi.hi + hi.lo + lo.hi.  The fp32 bar of
+    1e-3 (plain bf16 operands miss it) against the oracle, for the unshifted form with and without a sink,
+    under the guard when it holds (unshifted statistic) and when it fails (the max-shifted mma.sync kernel
+    takes over: statistic of the shifted kind), and on strided (B, T, H, D) views."""
+    B, H, D = 2, 3, 64
+    q, k, v = (randn((B, H, T, D), 970 + i) for i in range(3))
+    sink = randn((H,), 975, scale=0.5) if case in ("sink", "guard_holds") else None
+    # bounded_scores is the reference's internal flag of the guard's in-range branch: the unshifted
+    # kernel without a guard pass and without the score clamp of the public unguarded link
+    kw = dict(shift=False, bounded_scores=True)
+    if case in ("guard_holds", "guard_fails"):
+        kw = dict(range_guard=True)
+    if case == "guard_fails":
+        q = q * 40
+        k = k * 40
+    want = R.asinh_attention(q, k, v, n=n, c=c, sink_logit=sink)
+    if case == "strided":
+        qd, kd, vd = (t.transpose(1, 2).contiguous().to(DEV).transpose(1, 2) for t in (q, k, v))
+        sd = None
+    else:
+        qd, kd, vd, sd = dev(q, k, v, sink)
+    got, stat, kind = A.flash_attention(qd, kd, vd, sd, kind="asinh", n=n, c=c, block=256, impl="tcgen05", return_stat=True, **kw)
+    assert got.dtype == torch.float32 and torch.isfinite(got).all()
+    assert rel_l2(got, want) < 1e-3
+    shifted = case == "guard_fails"
+    assert int(kind) == (2 if shifted else 1)
+    want_stat = R.attention_row_stat(q, k, n=n, c=c, sink_logit=sink, shifted=shifted)
+    assert rel_l2(stat, want_stat) < 1e-3
+    # the mma.sync kernel on the same inputs: two independent paths to the same fp32 result
+    other = A.flash_attention(qd, kd, vd, sd, kind="asinh", n=n, c=c, block=256, impl="mma", **kw)
+    assert rel_l2(got, other) < 1e-3
+    again = A.flash_attention(qd, kd, vd, sd, kind="asinh", n=n, c=c, block=256, impl="tcgen05", **kw)
+    assert torch.equal(got, again)
+
+
 @pytest.mark.parametrize("T", [16384, 32768])
 def test_config5_longer_sequences_sampled(T):
     """benchmark configuration 5 at T = 16384 and 32768: (1,16,T,128) bf16 through the guarded public
