@@ -584,6 +584,26 @@ def run_extra(A, dist, vocab_shard, dev, rank, world, sync, max_over_ranks, pk, 
     extra["attn_shifted_seq8192"] = {"ms": ms_s, "frac_of_bf16_peak": fl / (ms_s * 1e-3) / 1e12 / peak_tf,
                                      "unshifted_ms_same_inputs": ms_u, "ratio": ms_s / ms_u}
     del q, k, v, o
+    # configuration 1 on the GPU: (4,12,1024,64) fp32, QK-norm + rotation prologue, guarded call; the tcgen05
+    # kernel on bf16 hi | lo halves against the mma.sync kernel on the same inputs
+    shape1 = (4, 12, 1024, 64)
+    g1 = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(shape1, generator=g1).to(dev) for _ in range(3))
+    sk = (torch.randn(shape1[1], generator=g1) * 0.02).to(dev)
+    gain1 = torch.ones(shape1[3], device=dev)
+    cos1, sin1 = A.cayley_table_geometric(shape1[3], shape1[2], device=dev)
+    o = torch.empty_like(q)
+    line = {"shape": list(shape1), "dtype": "f32", "flop_convention": "bf16-equivalent 4 B H T^2 D / 2 (each product is issued three times)"}
+    for which in ("auto", "mma"):
+        f_1 = lambda i: A.flash_attention(q, k, v, sk, kind="asinh", n=16, c=8.0, range_guard=True, q_gain=gain1, k_gain=gain1,  # noqa: E731
+                                          cos=cos1, sin=sin1, impl=which, out=o)
+        for i in range(3):
+            f_1(i)
+        ms_1 = cuda_time(f_1, iters, sync)
+        line["ms" if which == "auto" else "ms_mma_sync"] = ms_1
+        line["tflops" if which == "auto" else "tflops_mma_sync"] = attn_flops(*shape1) / (ms_1 * 1e-3) / 1e12
+    extra["attn_config1_fp32"] = line
+    del q, k, v, o
     # the attention shapes inside the prefill models (head_dim 64)
     for name, shape in (("attn_125m_layer", (16, 12, 1024, 64)), ("attn_350m_layer", (8, 16, 2048, 64))):
         q, k, v = (x.to(dev) for x in make_attn_inputs(13, shape))
