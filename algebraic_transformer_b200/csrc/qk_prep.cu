@@ -330,12 +330,18 @@ __global__ void __launch_bounds__(256, 3) qk_rms_bwd_kernel(const RmsBwdParams p
     float x[VEC], d[VEC];
     V::unpack(rx[u], x);
     V::unpack(rd[u], d);
-    float ss = 0.f, su = 0.f;
+    // two elements per instruction on the packed fp32 pipe: this kernel is bound by its instruction count
+    // as much as by HBM (one thread per 16 bytes of each stream)
+    float2 gd[VEC / 2];
+    float2 ss2 = make_float2(0.f, 0.f), su2 = make_float2(0.f, 0.f);
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-      ss = fmaf(x[i], x[i], ss);
-      su = fmaf(g[i] * d[i], x[i], su);
+    for (int i = 0; i < VEC / 2; ++i) {
+      const float2 xi = make_float2(x[2 * i], x[2 * i + 1]);
+      gd[i] = __fmul2_rn(make_float2(g[2 * i], g[2 * i + 1]), make_float2(d[2 * i], d[2 * i + 1]));
+      ss2 = __ffma2_rn(xi, xi, ss2);
+      su2 = __ffma2_rn(gd[i], xi, su2);
     }
+    float ss = ss2.x + ss2.y, su = su2.x + su2.y;
 #pragma unroll
     for (int o = LPR / 2; o > 0; o >>= 1) {
       ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -343,11 +349,16 @@ __global__ void __launch_bounds__(256, 3) qk_rms_bwd_kernel(const RmsBwdParams p
     }
     const float tau = rsqrtf(ss * (1.0f / D) + p.eps);
     const float coef = tau * tau * su * (1.0f / D);
+    const float2 ncoef2 = make_float2(-coef, -coef), tau2 = make_float2(live ? tau : 0.f, live ? tau : 0.f);
     float out[VEC];
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-      out[i] = tau * (g[i] * d[i] - x[i] * coef);
-      if (live) dg[i] = fmaf(d[i] * x[i], tau, dg[i]);
+    for (int i = 0; i < VEC / 2; ++i) {
+      const float2 xi = make_float2(x[2 * i], x[2 * i + 1]);
+      const float2 o2 = __fmul2_rn(__ffma2_rn(xi, ncoef2, gd[i]), make_float2(tau, tau));     // tau (g dy - x coef)
+      out[2 * i] = o2.x; out[2 * i + 1] = o2.y;
+      float2 dg2 = make_float2(dg[2 * i], dg[2 * i + 1]);
+      dg2 = __ffma2_rn(__fmul2_rn(make_float2(d[2 * i], d[2 * i + 1]), xi), tau2, dg2);       // a dead row adds d x 0
+      dg[2 * i] = dg2.x; dg[2 * i + 1] = dg2.y;
     }
     if (live) V::store(reinterpret_cast<T*>(p.dx) + off_dx[u], out);
     }

@@ -135,7 +135,8 @@ class Prefill:
         # per step up to 4096 tokens per call (a rank's share of a batch split over several GPUs), 2-5 %
         # slower at 16384, where the library's two-CTA 256 x 256 tiles win.  None = choose per call by the
         # token count; the weights are laid out once for both (norm gains folded into the q|k|v and
-        # gate|up weights either way, so the stand-alone norm of the other path runs without a gain).
+        # gate|up weights either way: above 4096 tokens the library takes the residual GEMMs, a pass that
+        # only reads x leaves the row statistic, and the norms still ride in the two wide projections).
         if fused_norm and not self.fused_proj:
             raise ValueError("fused_norm needs the fused projections")
         self.fused_norm = fused_norm if (fused_norm is None or not self.fused_proj) else bool(fused_norm)
@@ -180,6 +181,20 @@ class Prefill:
         w_o = (lambda l: p["w_o_t"][l].t()) if self.norm_in_weights else (lambda l: p["w_o"][l])
         w_d = (lambda l: p["w_d_t"][l].t()) if self.norm_in_weights else (lambda l: p["w_d"][l])
         for layer in range(cfg.n_layers):
+            if self.norm_in_weights:
+                # library residual GEMMs, but the block norms still ride in the two wide projections: a pass
+                # that only reads x for its row statistic replaces one that reads x and writes norm(x)
+                qkv = ops.qkv_projection(x, p["w_qkv_t"][layer], H, T, self.cos_lp, self.sin_lp, p["q_gain"][layer],
+                                         p["k_gain"][layer], cfg.eps, cfg.attn_c, self.guard_words[layer],
+                                         row_ss=ops.row_sumsq(x), guard_is_zero=True).view(B, T, 3, H, D)
+                q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))      # (B,H,T,D) views
+                ops.flash_attention(q, k, v, p["sink"][layer], kind="asinh", n=cfg.attn_n, c=cfg.attn_c, block=T,
+                                    range_guard=True, impl=self.impl, guard_words=self.guard_words[layer],
+                                    out=attn_out.transpose(1, 2))
+                x = torch.addmm(x, attn_out.view(B * T, d), w_o(layer))
+                ff = ops.glu_projection(x, p["w_gu_t"][layer], cfg.alu_beta, row_ss=ops.row_sumsq(x), eps=cfg.eps)
+                x = torch.addmm(x, ff, w_d(layer))
+                continue
             h = ops.rms_norm(x, ln1(layer), cfg.eps)
             if self.fused_proj:
                 qkv = ops.qkv_projection(h, p["w_qkv_t"][layer], H, T, self.cos_lp, self.sin_lp, p["q_gain"][layer],

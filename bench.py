@@ -293,7 +293,7 @@ def main():
         torch.cuda.current_stream().wait_stream(s_down)    # the last result is on the host
 
     e2e_loop(3)
-    e2e_steps = max(3, min(args.steps, 10))
+    e2e_steps = max(3, min(args.steps, 40))              # fill and drain of the three-stream pipeline are inside the region
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync()
     ev0.record()
