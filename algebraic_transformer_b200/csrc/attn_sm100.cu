@@ -841,16 +841,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           for (int c = 0; c < 8; ++c)
             *reinterpret_cast<float4*>(frow + 4 * c) = make_float4(__uint_as_float(o[4 * c]) * inv, __uint_as_float(o[4 * c + 1]) * inv,
                                                                    __uint_as_float(o[4 * c + 2]) * inv, __uint_as_float(o[4 * c + 3]) * inv);
-          continue;
-        }
+        } else {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint4 val;
-          val.x = pack_bf16(__uint_as_float(o[8 * c + 0]) * inv, __uint_as_float(o[8 * c + 1]) * inv);
-          val.y = pack_bf16(__uint_as_float(o[8 * c + 2]) * inv, __uint_as_float(o[8 * c + 3]) * inv);
-          val.z = pack_bf16(__uint_as_float(o[8 * c + 4]) * inv, __uint_as_float(o[8 * c + 5]) * inv);
-          val.w = pack_bf16(__uint_as_float(o[8 * c + 6]) * inv, __uint_as_float(o[8 * c + 7]) * inv);
-          *reinterpret_cast<uint4*>(orow + chunk * 32 + c * 8) = val;
+          for (int c = 0; c < 4; ++c) {
+            uint4 val;
+            val.x = pack_bf16(__uint_as_float(o[8 * c + 0]) * inv, __uint_as_float(o[8 * c + 1]) * inv);
+            val.y = pack_bf16(__uint_as_float(o[8 * c + 2]) * inv, __uint_as_float(o[8 * c + 3]) * inv);
+            val.z = pack_bf16(__uint_as_float(o[8 * c + 4]) * inv, __uint_as_float(o[8 * c + 5]) * inv);
+            val.w = pack_bf16(__uint_as_float(o[8 * c + 6]) * inv, __uint_as_float(o[8 * c + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + chunk * 32 + c * 8) = val;
+          }
         }
       }
 #ifndef ALG_ATTN_TIMING
