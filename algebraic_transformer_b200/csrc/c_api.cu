@@ -512,7 +512,8 @@ int alg_head_bwd_dz(const alg_head_bwd_args* a, void* stream_) {
 
 size_t alg_decode_workspace_bytes(const alg_decode_args* a) {
   if (a == nullptr) return 0;
-  return size_t(a->B) * a->H * decode_splits(a->B, a->H, a->Tk) * (a->D + 2) * sizeof(float);
+  // the splits' partial states, then one arrival word per (batch, head)
+  return align256(size_t(a->B) * a->H * decode_splits(a->B, a->H, a->Tk) * (a->D + 2) * sizeof(float)) + size_t(a->B) * a->H * 8;
 }
 
 int alg_attn_decode(const alg_decode_args* a, void* stream) {
@@ -543,6 +544,11 @@ int alg_attn_decode(const alg_decode_args* a, void* stream) {
   p.keys_per_split = decode_keys_per_split(a->B, a->H, a->Tk);
   p.status = nullptr;
   p.part = static_cast<float*>(a->workspace);
+  if (!aligned16(a->workspace)) { set_error("decode: workspace must be 16-byte aligned"); return ALG_ERR_INVALID; }
+  p.arrivals = reinterpret_cast<unsigned long long*>(static_cast<unsigned char*>(a->workspace) +
+                                                     align256(size_t(a->B) * a->H * p.splits * (a->D + 2) * sizeof(float)));
+  static std::atomic<unsigned long long> calls{0};
+  p.call = (calls.fetch_add(1) + 1) & ((1ull << 47) - 1);
   return launch_decode(p, static_cast<cudaStream_t>(stream));
 }
 

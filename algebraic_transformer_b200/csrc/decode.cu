@@ -9,9 +9,11 @@
 // (rho(m_old) rho(-m_new))^n applied to the warp's accumulators when m moves), and every lane
 // accumulates w * V for the 8 columns it holds.  No step of the key loop involves the whole
 // CTA, so nothing but the ring's barriers paces it; the eight warp states are merged once at
-// the end with the same exact rescale, and the (acc, m, l) states of the splits are merged,
-// with the sink, by decode_combine_kernel (a programmatic dependent launch: its CTAs move in as
-// the split kernel's leave).  All mbarrier waits are bounded.
+// the end with the same exact rescale and written out as the split's (acc, m, l) state.  The split
+// that finishes last for its (batch, head) merges the states, with the sink, and writes the output
+// row: one launch.  "Last" is decided by an arrival word per (batch, head) that carries the call's
+// number, so that nothing has to be zeroed between calls (a word left by another call counts as
+// zero arrivals).  All mbarrier waits are bounded.
 #include "common.cuh"
 #include "launchers.h"
 #include "sm100_ptx.cuh"
@@ -27,6 +29,7 @@ struct __align__(16) DecodeCtl {
   uint64_t full[STAGES], empty[STAGES];
   int abort_flag;
   int tile_ok;
+  int last_split;
   float x[2][TILE], w[2][TILE];
   float red[8];
 };
@@ -42,6 +45,54 @@ __device__ __forceinline__ void unpack8(const uint4& r, float* v) {
     float2 f = __bfloat1622float2(h[i]);
     v[2 * i] = f.x; v[2 * i + 1] = f.y;
   }
+}
+
+constexpr int MAX_SPLITS = 1024;
+
+// Merge the splits (and the sink) of one (batch, head); called by every thread of the CTA that
+// arrived last, thread d < D owns output column d.  `scratch`: 2 * MAX_SPLITS floats of shared memory.
+template <int D>
+__device__ __forceinline__ void decode_combine(const DecodeParams& p, int b, int h, float* scratch) {
+  float* s_f = scratch;                          // rescale factor per split
+  float* s_l = scratch + MAX_SPLITS;
+  float* s_red = scratch + 2 * MAX_SPLITS;       // D / 32 partial maxima
+  const int bh = b * p.H + h;
+  const float* part = p.part + int64_t(bh) * p.splits * (D + 2);
+  const bool has_sink = p.sink != nullptr;
+  const float bs = has_sink ? p.sink[h] * p.inv_c : -1e30f;
+  const bool mine = threadIdx.x < D;
+  float mm = bs;                                 // all loads below are independent of one another
+  if (mine) {
+    for (int s = threadIdx.x; s < p.splits; s += D) {
+      const float ms = __ldcg(part + s * (D + 2) + D);      // written by other CTAs: read past L1
+      s_f[s] = ms;
+      s_l[s] = __ldcg(part + s * (D + 2) + D + 1);
+      mm = fmaxf(mm, ms);
+    }
+    mm = warp_max(mm);
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = mm;
+  }
+  __syncthreads();
+  mm = s_red[0];
+#pragma unroll
+  for (int i = 1; i < D / 32; ++i) mm = fmaxf(mm, s_red[i]);
+  const float ns = rho_stable(-mm);
+  if (mine) {
+    for (int s = threadIdx.x; s < p.splits; s += D) {
+      const float ms = s_f[s];
+      s_f[s] = (ms > -1e29f) ? pow2n_rt(rho_stable(ms) * ns, p.log2n) : 0.f;
+    }
+  }
+  __syncthreads();
+  if (!mine) return;
+  float lt = has_sink ? pow2n_rt(rho_stable(bs) * ns, p.log2n) : 0.f;
+  float at = 0.f;
+#pragma unroll 8
+  for (int s = 0; s < p.splits; ++s) {
+    lt = fmaf(s_f[s], s_l[s], lt);
+    at = fmaf(s_f[s], __ldcg(part + s * (D + 2) + threadIdx.x), at);
+  }
+  reinterpret_cast<__nv_bfloat16*>(p.o)[int64_t(bh) * D + threadIdx.x] = __float2bfloat16_rn(at / lt);
 }
 
 template <int D>
@@ -66,6 +117,7 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     fence_barrier_init();
   }
   __syncthreads();
+  griddep_wait();                               // launched as a programmatic dependent of the kernel ahead in the stream
   const BoundedWait bw{&ctl->abort_flag, 1000000000ull};
 
   if (warp == CONSUMERS / 32) {                 // producer warp
@@ -187,56 +239,34 @@ decode_partial_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         out[D] = fine ? mm : -1e30f;
         out[D + 1] = fine ? l : 0.f;
       }
+      __threadfence();                                     // the state is visible before this split counts as arrived
     }
   }
+  __syncthreads();
+  // ---- arrival: the split that completes the count merges all states of its (batch, head)
+  if (threadIdx.x == 0) {
+    unsigned long long* word = p.arrivals + (int64_t(b) * p.H + h);
+    unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(word), next;
+    for (;;) {                                             // at most `splits` contenders, each retries a few times
+      next = ((seen >> 16) == p.call) ? seen + 1 : ((p.call << 16) | 1ull);
+      const unsigned long long prev = atomicCAS(word, seen, next);
+      if (prev == seen) break;
+      seen = prev;
+    }
+    ctl->last_split = int(next & 0xffffull) == p.splits ? 1 : 0;
+    // the last one leaves the word at zero: a replay of this very launch (a captured graph carries the
+    // same call number) starts counting afresh
+    if (ctl->last_split) *reinterpret_cast<volatile unsigned long long*>(word) = 0ull;
+    __threadfence();
+  }
+  __syncthreads();
+  if (ctl->last_split) decode_combine<D>(p, b, h, reinterpret_cast<float*>(smem));
   __syncthreads();
   if (ctl->abort_flag != 0 && threadIdx.x == 0) {
     if (p.status != nullptr) atomicExch(p.status, ALG_DEV_TIMEOUT);
     const uint64_t t0 = global_timer_ns();                 // let issued loads land before the CTA retires
     while (global_timer_ns() - t0 < 200000ull) { }
   }
-}
-
-constexpr int MAX_SPLITS = 1024;
-
-// Merge the splits (and the sink) of one (batch, head): thread d owns output column d.
-template <int D>
-__global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeParams p) {
-  __shared__ float s_f[MAX_SPLITS];             // rescale factor per split
-  __shared__ float s_l[MAX_SPLITS];
-  __shared__ float s_red[D / 32];
-  const int bh = blockIdx.x, h = bh % p.H;
-  const float* part = p.part + int64_t(bh) * p.splits * (D + 2);
-  const bool has_sink = p.sink != nullptr;
-  const float bs = has_sink ? p.sink[h] * p.inv_c : -1e30f;
-  griddep_wait();                                // launched while the split kernel still runs: its states are complete from here on
-  float mm = bs;                                 // all loads below are independent of one another
-  for (int s = threadIdx.x; s < p.splits; s += D) {
-    const float ms = part[s * (D + 2) + D];
-    s_f[s] = ms;
-    s_l[s] = part[s * (D + 2) + D + 1];
-    mm = fmaxf(mm, ms);
-  }
-  mm = warp_max(mm);
-  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = mm;
-  __syncthreads();
-  mm = s_red[0];
-#pragma unroll
-  for (int i = 1; i < D / 32; ++i) mm = fmaxf(mm, s_red[i]);
-  const float ns = rho_stable(-mm);
-  for (int s = threadIdx.x; s < p.splits; s += D) {
-    const float ms = s_f[s];
-    s_f[s] = (ms > -1e29f) ? pow2n_rt(rho_stable(ms) * ns, p.log2n) : 0.f;
-  }
-  __syncthreads();
-  float lt = has_sink ? pow2n_rt(rho_stable(bs) * ns, p.log2n) : 0.f;
-  float at = 0.f;
-#pragma unroll 4
-  for (int s = 0; s < p.splits; ++s) {
-    lt = fmaf(s_f[s], s_l[s], lt);
-    at = fmaf(s_f[s], part[s * (D + 2) + threadIdx.x], at);
-  }
-  reinterpret_cast<__nv_bfloat16*>(p.o)[int64_t(bh) * D + threadIdx.x] = __float2bfloat16_rn(at / lt);
 }
 
 int make_kv_map(CUtensorMap* tm, const void* base, const Strides3& s, int B, int H, int T, int D) {
@@ -254,10 +284,8 @@ int launch_d(const DecodeParams& p, cudaStream_t stream) {
   auto kern = decode_partial_kernel<D>;
   static PerDeviceOnce configured;
   if (int rc = configured.run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(decode_smem<D>())); })) return rc;
-  kern<<<dim3(p.splits, p.H, p.B), NTHREADS, decode_smem<D>(), stream>>>(tk, tv, p);
-  ALG_CUDA_TRY(cudaGetLastError());
-  ALG_CUDA_TRY(launch_dependent(decode_combine_kernel<D>, dim3(p.B * p.H), dim3(D), 0, stream, p));
-  count_launch(2);
+  ALG_CUDA_TRY(launch_dependent(kern, dim3(p.splits, p.H, p.B), dim3(NTHREADS), decode_smem<D>(), stream, tk, tv, p));
+  count_launch();
   return ALG_OK;
 }
 
@@ -265,7 +293,7 @@ int launch_d(const DecodeParams& p, cudaStream_t stream) {
 
 // Splits are whole 64-key tiles.  The grid is ONE wave: at most two CTAs per SM (a
 // second wave would pay the ring's start-up latency again: 62 -> 56 us on a 32768-key cache),
-// never more splits than the combine kernel's table.
+// never more splits than the merging CTA's table.
 int decode_splits(int B, int H, int Tk) {
   const int bh = B * H > 0 ? B * H : 1;
   const int tiles = (Tk + TILE - 1) / TILE;

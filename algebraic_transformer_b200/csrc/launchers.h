@@ -196,6 +196,8 @@ struct DecodeParams {
   int splits;
   int keys_per_split;      // multiple of the 64-key tile
   float* part;             // (B*H, splits, D + 2) fp32 partials: acc[D], m, l
+  unsigned long long* arrivals;   // (B*H) words: call number << 16 | splits of that call that have written their partial
+  unsigned long long call;        // this call's number (unique per process): stale words of other calls read as zero arrivals
   int* status;
 };
 int decode_splits(int B, int H, int Tk);

@@ -222,6 +222,9 @@ ALG_API int alg_attn_bwd(const alg_attn_bwd_args* args, void* stream);
  * src/algebraic/benchmarking.py:250-263); semantics are asinh_power_weights with an
  * all-true mask, src/algebraic/algebraic.py:186-204.  Uses the max-shifted form.
  * q: (B,H,1,D), k,v: (B,H,Tk,D) bf16, o: (B,H,1,D) bf16.
+ * One launch: the CTA that finishes last for a (batch, head) merges the splits' states.  The workspace
+ * (16-byte aligned) holds those states and one arrival word per (batch, head); it needs no
+ * initialisation, but two calls in flight at the same time must not share one.
  * ---------------------------------------------------------------------------------- */
 typedef struct {
   const void* q;

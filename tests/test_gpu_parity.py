@@ -11,6 +11,7 @@ import pytest
 import torch
 
 import algebraic_transformer_b200 as A
+from algebraic_transformer_b200 import _lib as L
 from oracle import algebraic_ref as R
 
 pytestmark = pytest.mark.gpu
@@ -517,6 +518,36 @@ def test_decode_single_query(D, Tk):
     got2 = A.decode_attention(*dev(q, k, v), None, n=16, c=8.0).cpu()
     want2 = R.asinh_attention(q, k, v, n=16, c=8.0, causal=False)
     assert rel_l2(got2, want2) < 1e-2
+
+
+@pytest.mark.parametrize("B,H,D,Tk", [(2, 4, 128, 4096), (1, 3, 64, 700), (3, 16, 64, 64)])
+def test_decode_is_one_launch_and_repeats(B, H, D, Tk):
+    """The split that arrives last merges its (batch, head): the arrival words live in the workspace, are never
+    zeroed by the host, and must come out right on the first call (whatever the workspace held), on repeated
+    calls, and when one captured launch is replayed (same call number every time)."""
+    q, k, v = randn((B, H, 1, D), 11, torch.bfloat16), randn((B, H, Tk, D), 12, torch.bfloat16), \
+        randn((B, H, Tk, D), 13, torch.bfloat16)
+    sink = randn((H,), 14, scale=0.5)
+    want = R.asinh_attention(q, k, v, n=16, c=8.0, sink_logit=sink, causal=False)
+    qd, kd, vd, sd = dev(q, k, v, sink)
+    lib = L.load()
+    before = lib.alg_kernel_launches()
+    first = A.decode_attention(qd, kd, vd, sd, n=16, c=8.0)
+    assert lib.alg_kernel_launches() - before == 1
+    assert rel_l2(first, want) < 1e-2
+    for _ in range(3):
+        assert torch.equal(A.decode_attention(qd, kd, vd, sd, n=16, c=8.0), first)
+    out = torch.empty_like(first)
+    A.decode_attention(qd, kd, vd, sd, n=16, c=8.0, out=out)          # warm: workspace exists before capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        A.decode_attention(qd, kd, vd, sd, n=16, c=8.0, out=out)
+    for _ in range(3):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, first)
 
 
 # -------------------------------------------------------------------------------- head
