@@ -2,9 +2,13 @@
 //
 // Covers the unshifted accumulation of the reference (src/algebraic/kernels/flash.py:
 // 227-234): p = rho_fast(x)^n, l = rho(b')^n + sum p, o = (sum p v) / l, stat = 1/l — the
-// branch the range guard selects for QK-normalised inputs.  bf16 I/O, causal, Tq == Tk a
-// multiple of 256, head_dim 64 or 128.  Because nothing is rescaled in this form, the
-// output accumulator simply stays in tensor memory from the first key tile to the last.
+// branch the range guard selects for QK-normalised inputs - and its max-shifted form.  bf16 I/O
+// (fp32 at head_dim 64, see the F32 mode), causal, Tq == Tk of any length, head_dim 64 or 128.
+// Because nothing is rescaled in the unshifted form, the output accumulator simply stays in
+// tensor memory from the first key tile to the last.  A sequence that does not fill its last
+// 256-row block needs no special case beyond masked stores: TMA fills rows past the end with
+// zeros, keys past the end lie above the diagonal of every real row, and rows past the end
+// compute finite values nobody stores.
 //
 // One CTA owns 256 consecutive query rows of one (batch, head): two 128-row tiles.
 //   warp 0 (one lane)  TMA: both Q tiles once, then K_j / V_j tiles through a ring
@@ -348,7 +352,7 @@ struct ItemLists {
 // The k-th work item of this CTA.
 struct Item { int b, h, row0, n0, n1; };
 __device__ __forceinline__ bool item_at(const AttnParams& p, const ItemLists& lists, int k, Item& it) {
-  const int units = p.B * p.H, nblk = p.Tq / (2 * BQ), G = int(gridDim.x);
+  const int units = p.B * p.H, nblk = (p.Tq + 2 * BQ - 1) / (2 * BQ), G = int(gridDim.x);
   int idx;
   if (lists.listed) {
     const int at = int(lists.start[blockIdx.x]) + k;
@@ -835,6 +839,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           tc_fence_before();
           mbar_arrive(&ctl->o_free[w]);
         }
+        if (row >= p.Tq) continue;                   // a row past the end of a sequence that does not fill its last tile
         if constexpr (F32) {
           float* frow = reinterpret_cast<float*>(p.o) + o_off + chunk * 32;
 #pragma unroll
@@ -855,7 +860,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
 #ifndef ALG_ATTN_TIMING
       // unshifted: 1 / l of the reference = 1 / (l' m^n); shifted: rho(-m) l^(-1/n)  (flash.py:271-284)
-      if (p.stat != nullptr && half == 0)
+      if (p.stat != nullptr && half == 0 && row < p.Tq)
         p.stat[(int64_t(it.b) * p.H + it.h) * p.Tq + row] = SHIFT ? rho_stable(-m_run) * inv_root_rt(l, LOG2N) : inv * sc.inv_mn;
 #endif
     }
@@ -941,7 +946,7 @@ int launch_dns(const AttnParams& p, cudaStream_t stream) {
   // the deal depends on three integers only: keep the last one (a launch path must stay cheap)
   struct Dealt { int units, nblk, grid; ItemLists lists; };
   static thread_local Dealt dealt = {-1, -1, -1, {}};
-  const int units = p.B * p.H, nblk = p.Tq / (2 * BQ);
+  const int units = p.B * p.H, nblk = (p.Tq + 2 * BQ - 1) / (2 * BQ);
   if (dealt.units != units || dealt.nblk != nblk || dealt.grid != grid) {
     deal_items(&dealt.lists, units, nblk, grid);
     dealt.units = units; dealt.nblk = nblk; dealt.grid = grid;
@@ -1006,7 +1011,7 @@ __global__ void __launch_bounds__(256) split_f32_kernel(const SplitBatch batch) 
 size_t attn_tcgen05_f32_split_bytes(int B, int H, int T) { return size_t(B) * H * T * 128 * sizeof(__nv_bfloat16); }
 
 bool attn_tcgen05_f32_supports(const AttnParams& p, int dtype) {
-  return dtype == ALG_F32 && p.causal && p.Tq == p.Tk && p.Tq % (2 * BQ) == 0 && p.D == 64 && p.log2n >= 3 && p.log2n <= 5;
+  return dtype == ALG_F32 && p.causal && p.Tq == p.Tk && p.Tq >= 1 && p.D == 64 && p.log2n >= 3 && p.log2n <= 5;
 }
 
 // p describes the fp32 problem (q, k, v, o fp32 with their strides); `split` holds three buffers of
@@ -1042,7 +1047,7 @@ int launch_attn_tcgen05_f32(const AttnParams& p, void* split, cudaStream_t strea
 bool attn_tcgen05_supports(const AttnParams& p, int dtype) {
   const bool strides_fit = p.qs.t > 0 && p.ks.t > 0 && p.vs.t > 0 && p.qs.h >= 0 && p.qs.b >= 0 &&
                            p.ks.h >= 0 && p.ks.b >= 0 && p.vs.h >= 0 && p.vs.b >= 0;
-  return dtype == ALG_BF16 && p.causal && p.Tq == p.Tk && p.Tq % (2 * BQ) == 0 && (p.D == 64 || p.D == 128) &&
+  return dtype == ALG_BF16 && p.causal && p.Tq == p.Tk && p.Tq >= 1 && (p.D == 64 || p.D == 128) &&
          p.log2n >= 3 && p.log2n <= 5 && strides_fit &&
          (p.B == 1 || p.qs.b > 0) && (p.H == 1 || p.qs.h > 0);
 }
@@ -1051,7 +1056,7 @@ bool attn_tcgen05_supports(const AttnParams& p, int dtype) {
 // proportion to B H T^2 D: from T D = 3/4 Mi elements per head on, the statistics are ready well
 // before the attention is (T >= 6144 at head_dim 128).
 int attn_tcgen05_grid(const AttnParams& p) {
-  const int items = p.B * p.H * (p.Tq / (2 * BQ)), sms = sm_count();
+  const int items = p.B * p.H * ((p.Tq + 2 * BQ - 1) / (2 * BQ)), sms = sm_count();
   return items < sms ? items : sms;
 }
 

@@ -154,9 +154,9 @@ size_t alg_attn_workspace_bytes(const alg_attn_args* a) {
     bytes += align256(size_t(a->B) * a->H * a->Tq * a->D * es);
     bytes += align256(size_t(a->B) * a->H * a->Tk * a->D * es);
   }
-  // fp32 rows the tcgen05 kernel can take (head_dim 64, causal self-attention over a multiple of 256): room for
+  // fp32 rows the tcgen05 kernel can take (head_dim 64, causal self-attention): room for
   // the bf16 hi | lo copies of q, k, v.  A call that brings less than this runs on the mma.sync kernel.
-  if (a->dtype == ALG_F32 && a->D == 64 && a->causal && a->Tq == a->Tk && a->Tq > 0 && a->Tq % 256 == 0)
+  if (a->dtype == ALG_F32 && a->D == 64 && a->causal && a->Tq == a->Tk && a->Tq > 0)
     bytes = align256(bytes) + 3 * align256(attn_tcgen05_f32_split_bytes(a->B, a->H, a->Tq));
   return bytes;
 }
@@ -303,7 +303,7 @@ int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
   const bool shape_ok = attn_tcgen05_supports(p, a->dtype);
   const bool fast_ok = shape_ok && (a->variant == ALG_VARIANT_SHIFT || !(a->score_clamp > 0.0f));
   if (a->impl == ALG_IMPL_TCGEN05 && !fast_ok) {
-    set_error("attention: the tcgen05 kernel covers causal Tq == Tk multiple of 256 without a score clamp: bf16 with head_dim 64 or 128, fp32 "
+    set_error("attention: the tcgen05 kernel covers causal Tq == Tk without a score clamp: bf16 with head_dim 64 or 128, fp32 "
               "with head_dim 64 in the unshifted form given the workspace alg_attn_workspace_bytes asks for");
     return ALG_ERR_UNSUPPORTED;
   }

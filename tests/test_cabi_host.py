@@ -110,14 +110,16 @@ def test_workspace_sizes():
     assert lib.alg_attn_workspace_bytes(a) == 8192
     a.cos = 16
     assert lib.alg_attn_workspace_bytes(a) == 8192 + 2 * (2 * 3 * 512 * 64 * 2)
-    # fp32 rows the tcgen05 kernel can take (head_dim 64, causal, Tq == Tk a multiple of 256): room for the
+    # fp32 rows the tcgen05 kernel can take (head_dim 64, causal, Tq == Tk): room for the
     # bf16 hi | lo copies of q, k, v on top; other fp32 shapes ask for no more than bf16 ones
     f = L.AttnArgs(B=2, H=3, Tq=512, Tk=512, D=64, dtype=L.ALG_F32, causal=1)
     assert lib.alg_attn_workspace_bytes(f) == 8192 + 3 * (2 * 3 * 512 * 128 * 2)
     f.causal = 0
     assert lib.alg_attn_workspace_bytes(f) == 8192
-    f.causal, f.Tq, f.Tk = 1, 384, 384
+    f.causal, f.Tq, f.Tk = 1, 384, 512
     assert lib.alg_attn_workspace_bytes(f) == 8192
+    f.Tq, f.Tk = 300, 300                                   # any length: rows, not tiles, are copied
+    assert lib.alg_attn_workspace_bytes(f) == 8192 + 3 * ((2 * 3 * 300 * 128 * 2 + 255) // 256 * 256)
     h = L.HeadArgs(N=8192, d=768, V_local=50304)
     assert lib.alg_head_workspace_bytes(h) >= 2 * 8192 * 4
     assert lib.alg_head_finalize_workspace_bytes(8192) >= 32 * 4 + 16

@@ -391,6 +391,34 @@ def test_fp32_rows_on_tcgen05(T, n, c, case):
     assert torch.equal(got, again)
 
 
+@pytest.mark.parametrize("T", [1, 100, 128, 257, 384, 1000, 1500])
+@pytest.mark.parametrize("D,dtype", [(64, torch.bfloat16), (128, torch.bfloat16), (64, torch.float32)])
+@pytest.mark.parametrize("mode", ["guarded", "shift"])
+def test_any_sequence_length_on_tcgen05(T, D, dtype, mode):
+    """Causal self-attention over lengths that do not fill the last 256-row block (impl="tcgen05" is an error
+    where that kernel does not apply): rows and keys past the end are TMA zero fill, masked by causality and
+    never stored.  Output and statistic against the oracle; the memory just behind the output stays untouched."""
+    if dtype == torch.float32 and mode == "shift":
+        pytest.skip("fp32 rows run the max-shifted form on the mma.sync kernel")
+    B, H = 2, 3
+    q, k, v = (randn((B, H, T, D), 990 + i, dtype) for i in range(3))
+    sink = randn((H,), 995, scale=0.5)
+    want = R.asinh_attention(q, k, v, n=16, c=8.0, sink_logit=sink)
+    qd, kd, vd, sd = dev(q, k, v, sink)
+    # the output is a view into a larger buffer pre-filled with a sentinel: a store past row T would show
+    buf = torch.full((B, H, T + 8, D), 7.0, dtype=dtype, device=DEV)
+    out = buf[:, :, :T]
+    kw = dict(range_guard=True) if mode == "guarded" else dict(shift=True)
+    got, stat, kind = A.flash_attention(qd, kd, vd, sd, kind="asinh", n=16, c=8.0, block=T, impl="tcgen05", return_stat=True,
+                                        out=out, **kw)
+    assert int(kind) == (1 if mode == "guarded" else 2)
+    assert torch.isfinite(got).all() and torch.isfinite(stat).all()
+    assert rel_l2(got, want) < (1e-3 if dtype == torch.float32 else 1e-2)
+    assert bool((buf[:, :, T:] == 7.0).all())
+    want_stat = R.attention_row_stat(q, k, n=16, c=8.0, sink_logit=sink, shifted=mode == "shift")
+    assert rel_l2(stat, want_stat) < 5e-3
+
+
 @pytest.mark.parametrize("T", [16384, 32768])
 def test_config5_longer_sequences_sampled(T):
     """benchmark configuration 5 at T = 16384 and 32768: (1,16,T,128) bf16 through the guarded public
