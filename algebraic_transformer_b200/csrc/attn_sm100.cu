@@ -88,6 +88,7 @@ template <int D> struct Cfg {
 struct __align__(16) Control {
   uint64_t q_full[2], q_ready[2], q_free[2], kv_full[MAX_NKV], kv_empty[MAX_NKV];
   uint64_t s_full[2], p_half[2], p_full[2], o_full[2], o_free[2];
+  uint64_t s_read[2], pv_done[2];   // head_dim 64: scores read (S_w may be overwritten), second P.V product of a tile done
   uint64_t l_part[2], l_total[2];   // split weight groups: hand-over of the row sums between the column halves
   uint32_t tmem_base;
   int abort_flag;
@@ -225,6 +226,47 @@ __device__ __forceinline__ void weigh_half_tile(uint32_t s_taddr, int half, int 
   weigh<LOG2N, DIAG, 16>(b, kappa, c0 + 80, r, la, lb, packed);
   tmem_st_32x8(base + 72, packed);
   signal_weights(p_full);
+}
+
+// Head_dim 64 leaves tensor memory for the weights to have columns of their own (P_w beside S_w instead of
+// inside it).  Then S_w can be overwritten by the next tile's scores as soon as this group has READ the
+// current ones, which it says through `s_read` after its last load - a quarter of the tile's arithmetic
+// before it is done - instead of after the second P.V product has consumed the weights; the wait for the
+// next scores, a quarter of a group's time per tile before, all but disappears.  What still orders P_w:
+// the first half is only rewritten after "scores there" (which the MMA warp commits behind the first P.V
+// product of the previous tile), the second half after `pv_done` of the previous tile.
+template <int LOG2N, bool DIAG>
+__device__ __forceinline__ bool weigh_half_tile_early(uint32_t s_taddr, uint32_t p_taddr, int half, int r, float kappa, float2& la,
+                                                      float2& lb, uint64_t* p_half, uint64_t* p_full, uint64_t* s_read,
+                                                      uint64_t* pv_done, bool wait_pv, uint32_t pv_parity, const BoundedWait& bw,
+                                                      uint64_t* release_v) {
+  uint32_t a[16], b[16], packed[8];
+  const int c0 = 32 * half;
+  const uint32_t base = s_taddr + c0, pbase = p_taddr + 16 * half;     // weights of S column c sit in P column c / 2
+  tmem_ld_32x16(base, a);
+  tmem_ld_wait_for16(a);
+  tmem_ld_32x16(base + 16, b);
+  weigh<LOG2N, DIAG, 16>(a, kappa, c0, r, la, lb, packed);
+  tmem_st_32x8(pbase, packed);
+  tmem_ld_wait_for16(b);
+  tmem_ld_32x16(base + 64, a);
+  weigh<LOG2N, DIAG, 16>(b, kappa, c0 + 16, r, la, lb, packed);
+  tmem_st_32x8(pbase + 8, packed);
+  signal_weights(p_half);
+  tmem_ld_wait_for16(a);
+  tmem_ld_32x16(base + 80, b);
+  weigh<LOG2N, DIAG, 16>(a, kappa, c0 + 64, r, la, lb, packed);
+  tmem_ld_wait_for16(b);
+  tc_fence_before();
+  mbar_arrive(s_read);                              // every score of this tile is in registers
+  if (wait_pv && !bw.wait(pv_done, pv_parity)) return false;
+  tc_fence_after();
+  if (release_v != nullptr) mbar_arrive(release_v); // the previous tile's V is no longer read either
+  tmem_st_32x8(pbase + 32, packed);
+  weigh<LOG2N, DIAG, 16>(b, kappa, c0 + 80, r, la, lb, packed);
+  tmem_st_32x8(pbase + 40, packed);
+  signal_weights(p_full);
+  return true;
 }
 
 // ---- max-shifted form (src/algebraic/kernels/flash.py:235-259): p = (rho(x) rho(-m'))^n with the
@@ -467,6 +509,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   using C = Cfg<D>;
   static_assert(!F32 || (D == 128 && SPLIT == 1 && !SHIFT), "the fp32 mode: hi|lo tiles of head_dim 64, unshifted form");
   constexpr int DV = F32 ? 64 : D;                  // output columns
+  // head_dim 64, unshifted, split weight groups: P_w has tensor-memory columns of its own and S_w is re-issued
+  // early (see weigh_half_tile_early); the layout is then S 0..255, P 256..383, O 384..511
+  constexpr bool EARLY = (D == 64 && SPLIT == 2 && !SHIFT && !F32);
+  constexpr uint32_t O_COL = EARLY ? 384u : C::O_COL;
+  constexpr uint32_t P_COL = 256u;                  // EARLY only: P_w at P_COL + 64 w
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Control* ctl = reinterpret_cast<Control*>(smem + C::CTL_OFF);
@@ -488,6 +535,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     for (int i = 0; i < C::NKV; ++i) { mbar_init(&ctl->kv_full[i], 1); mbar_init(&ctl->kv_empty[i], 1); }
     for (int w = 0; w < 2; ++w) {
       mbar_init(&ctl->s_full[w], 1);
+      mbar_init(&ctl->s_read[w], 128 * SPLIT);
+      mbar_init(&ctl->pv_done[w], 1);
       mbar_init(&ctl->p_half[w], 128 * SPLIT);
       mbar_init(&ctl->p_full[w], 128 * SPLIT);
       mbar_init(&ctl->o_full[w], 1);
@@ -601,7 +650,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     auto issue_pv = [&](int w, int slot, int h64, bool first) {
       ALG_TI0
       const uint32_t va = v_lo0 + slot * (C::TILE_BYTES >> 4);
-      const uint32_t d_tmem = tmem_base + C::O_COL + w * D, p_tmem = tmem_base + C::S_COL + w * 128;
+      const uint32_t d_tmem = tmem_base + O_COL + w * D;
+      const uint32_t p_tmem = EARLY ? tmem_base + P_COL + w * 64 : tmem_base + C::S_COL + w * 128;
       if constexpr (F32) {                         // p_hi.v_hi + p_lo.v_hi + p_hi.v_lo; p_lo sits 16 columns behind p_hi
         constexpr uint32_t LO = PANEL_BYTES >> 4;
 #pragma unroll
@@ -618,8 +668,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
         for (int i = 0; i < 4; ++i) {               // 16 keys = 8 packed-bf16 columns of P per step
           const int ks = 4 * h64 + i;
-          umma_f16_ts_parts(d_tmem, p_tmem + p_col_of(16 * ks), va + ks * (2048 >> 4), SW128_DESC_HI, C::IDESC_PV,
-                            (first && ks == 0) ? 0u : 1u);
+          umma_f16_ts_parts(d_tmem, p_tmem + (EARLY ? uint32_t(8 * ks) : p_col_of(16 * ks)), va + ks * (2048 >> 4), SW128_DESC_HI,
+                            C::IDESC_PV, (first && ks == 0) ? 0u : 1u);
         }
       }
       ALG_TI1
@@ -647,6 +697,37 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         // Both tiles of this step are waited for up front (they are normally long there), so
         // that nothing stands between "weights ready" and the issue of P.V and the next S.
         if (!ALG_T(tm0, kv_wait(vc)) || (j + 1 < n1 && !ALG_T(tm0, kv_wait(kc)))) { ok = false; break; }
+        if constexpr (EARLY) {
+          // per query tile: first P.V half, then the NEXT scores as soon as the current ones have been read,
+          // then the second P.V half (announced by itself: the weight warps order their writes to P_w by it)
+          bool fine = true;
+#pragma unroll
+          for (int w = 0; w < 2 && fine; ++w) {
+            const int nw = w == 0 ? n0 : n1, tw = w == 0 ? t0 : t1;
+            if (j >= nw) continue;
+            if (!ALG_T(tm1, wait_all(&ctl->p_half[w], (tw + j) & 1u))) { fine = false; break; }
+            if (j == 0 && k > 0 && !wait_all(&ctl->o_free[w], (k - 1) & 1u)) { fine = false; break; }
+            tc_fence_after();
+            if (elect_one()) issue_pv(w, vc.slot, 0, j == 0);
+            __syncwarp();
+            if (j + 1 < nw) {
+              if (!ALG_T(tm2, wait_all(&ctl->s_read[w], (tw + j) & 1u))) { fine = false; break; }
+              tc_fence_after();
+              if (elect_one()) { issue_s(w, kc.slot); umma_commit(&ctl->s_full[w]); }
+              __syncwarp();
+            }
+            if (!ALG_T(tm1, wait_all(&ctl->p_full[w], (tw + j) & 1u))) { fine = false; break; }
+            tc_fence_after();
+            if (elect_one()) {
+              issue_pv(w, vc.slot, 1, false);
+              umma_commit(&ctl->pv_done[w]);
+              if (j + 1 == nw) umma_commit(&ctl->o_full[w]);
+            }
+            __syncwarp();
+          }
+          if (!fine) { ok = false; break; }
+          continue;
+        }
         if (j < n0) {
           if (!ALG_T(tm1, wait_all(&ctl->p_half[0], (t0 + j) & 1u))) { ok = false; break; }
           // the first product of an item overwrites O_0: the previous output must have been read
@@ -734,6 +815,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // an item mean its Q tile can be.  The releasing thread walks the K/V ring in load order.
     const bool releaser = (ww % (4 * SPLIT)) == 0 && lane == 0;
     RingCursor<C::NKV> rel;
+    // EARLY: K and V slots are released at different moments, so each has its own position in the ring
+    // (loads go K_0 V_0 K_1 V_1 ...: the K slots are every other one from 0, the V slots from 1)
+    int kslot = 0, vslot = 1 % C::NKV;
+    const uint32_t p_taddr = tmem_base + lane_sel + P_COL + w * 64;
 #ifdef ALG_ATTN_TIMING
     const long long t_begin = clock64();
 #endif
@@ -751,8 +836,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tc_fence_after();
         if (releaser) {
           if (w == 1) {
-            if (j > 0) { mbar_arrive(&ctl->kv_empty[rel.slot]); rel.next(); }    // V_{j-1}
-            mbar_arrive(&ctl->kv_empty[rel.slot]); rel.next();                   // K_j
+            if (EARLY) {                                                         // K_j; V_{j-1} follows at pv_done
+              mbar_arrive(&ctl->kv_empty[kslot]); kslot = (kslot + 2) % C::NKV;
+            } else {
+              if (j > 0) { mbar_arrive(&ctl->kv_empty[rel.slot]); rel.next(); }  // V_{j-1}
+              mbar_arrive(&ctl->kv_empty[rel.slot]); rel.next();                 // K_j
+            }
           }
           if (j == nk - 1) mbar_arrive(&ctl->q_free[w]);
         }
@@ -789,6 +878,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           else weigh_tile_shifted<LOG2N, false>(s_taddr, r, p.scale, sigma, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
           l += (la.x + la.y) + (lb.x + lb.y);              // this tile's weights
           la = make_float2(0.f, 0.f); lb = make_float2(0.f, 0.f);
+        } else if (EARLY) {
+          const int tile = tiles_before + j;               // this group's tiles, counted over all items
+          // V_{j-1} of this item goes back to the ring once its second P.V product is done (the item's last V
+          // tile waits for "output ready" below)
+          uint64_t* release_v = (releaser && w == 1 && j > 0) ? &ctl->kv_empty[vslot] : nullptr;
+          if (release_v != nullptr) vslot = (vslot + 2) % C::NKV;
+          if (j == nk - 1) ok = weigh_half_tile_early<LOG2N, true>(s_taddr, p_taddr, half, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w],
+                                                                   &ctl->s_read[w], &ctl->pv_done[w], tile > 0, uint32_t(tile - 1) & 1u, bw, release_v);
+          else ok = weigh_half_tile_early<LOG2N, false>(s_taddr, p_taddr, half, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w],
+                                                        &ctl->s_read[w], &ctl->pv_done[w], tile > 0, uint32_t(tile - 1) & 1u, bw, release_v);
         } else if (SPLIT == 2) {
           if (j == nk - 1) weigh_half_tile<LOG2N, true>(s_taddr, half, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);   // diagonal tile: masked
           else weigh_half_tile<LOG2N, false>(s_taddr, half, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
@@ -810,7 +909,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         mbar_arrive(&ctl->l_part[w]);
       }
       if (!ok || !bw.wait(&ctl->o_full[w], k & 1u)) { ok = false; break; }
-      if (releaser && w == 1) { mbar_arrive(&ctl->kv_empty[rel.slot]); rel.next(); }   // the item's last V tile
+      if (releaser && w == 1) {                                                        // the item's last V tile
+        if (EARLY) { mbar_arrive(&ctl->kv_empty[vslot]); vslot = (vslot + 2) % C::NKV; }
+        else { mbar_arrive(&ctl->kv_empty[rel.slot]); rel.next(); }
+      }
       if (SPLIT == 2) {
         if (half == 0) {                            // ... which returns the row's total through the same word
           if (!bw.wait(&ctl->l_part[w], k & 1u)) { ok = false; break; }
@@ -833,7 +935,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll 1
       for (int chunk = half * CHUNKS; chunk < (half + 1) * CHUNKS; ++chunk) {
         uint32_t o[32];
-        tmem_ld_32x32(tmem_base + lane_sel + C::O_COL + w * D + chunk * 32, o);
+        tmem_ld_32x32(tmem_base + lane_sel + O_COL + w * D + chunk * 32, o);
         tmem_ld_wait_for(o);
         if (chunk == (half + 1) * CHUNKS - 1) {     // O_w is in registers: the next item may overwrite it
           tc_fence_before();
