@@ -295,34 +295,55 @@ __global__ void __launch_bounds__(256, 3) qk_rms_bwd_kernel(const RmsBwdParams p
     g[i] = (p.gain != nullptr) ? p.gain[lir * VEC + i] : 1.0f;
     dg[i] = 0.f;
   }
-  // four row groups per step, all eight 16-byte loads issued before any is used (memory-level parallelism)
+  // Four row groups per step, all eight 16-byte loads issued before any is used (memory-level parallelism).
+  // A step of a warp covers U * RPW CONSECUTIVE rows: where they all lie in one (batch, head) - the rule - the
+  // row -> (batch, head, position) arithmetic is done once per step for the whole warp and a row's three
+  // offsets are one multiply-add each.  (With one division chain per row group the kernel executed 196
+  // warp instructions per row-group lane, nearly half of them addressing, and ran at 52 % issue
+  // utilisation: instruction-bound as much as HBM-bound.)
   constexpr int U = 4;
+  constexpr int STEP_ROWS = U * RPW;
   const bool narrow = rows < (int64_t(1) << 31);
-  for (int64_t base = warp_global * RPW; base < rows; base += warps_total * RPW * U) {
+  for (int64_t base = warp_global * STEP_ROWS; base < rows; base += warps_total * STEP_ROWS) {
     typename V::Raw rx[U], rd[U];
     int64_t off_dx[U];
     bool alive[U];
+    // position of the step's first row (warp-uniform)
+    int64_t bh0, b0;
+    int t0, h0;
+    if (narrow) {                      // 32-bit division where the row count allows
+      const uint32_t q1 = uint32_t(base) / uint32_t(p.T), q2 = q1 / uint32_t(p.H);
+      bh0 = q1; t0 = int(uint32_t(base) - q1 * uint32_t(p.T)); b0 = q2; h0 = int(q1 - q2 * uint32_t(p.H));
+    } else {
+      bh0 = base / p.T; t0 = int(base - bh0 * p.T); h0 = int(bh0 % p.H); b0 = bh0 / p.H;
+    }
+    const bool one_head = t0 + STEP_ROWS <= p.T;
+    const int64_t x0 = b0 * p.xs.b + h0 * p.xs.h + int64_t(t0) * p.xs.t + lir * VEC;
+    const int64_t g0 = b0 * p.gs.b + h0 * p.gs.h + int64_t(t0) * p.gs.t + lir * VEC;
+    const int64_t d0 = b0 * p.ds.b + h0 * p.ds.h + int64_t(t0) * p.ds.t + lir * VEC;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int64_t row = base + int64_t(u) * warps_total * RPW + sub;
+      const int in_step = u * RPW + sub;
+      const int64_t row = base + in_step;
       alive[u] = row < rows;
-      const int64_t rr = alive[u] ? row : rows - 1;
-      int t, h;
-      int64_t b;
-      if (narrow) {                  // 32-bit division: the 64-bit one costs more instructions than the row's arithmetic
-        const uint32_t r32 = uint32_t(rr), bh = r32 / uint32_t(p.T);
-        t = int(r32 - bh * uint32_t(p.T));
-        b = bh / uint32_t(p.H);
-        h = int(bh - uint32_t(b) * uint32_t(p.H));
-      } else {
-        t = int(rr % p.T);
+      int64_t ox, og, od;
+      if (one_head) {
+        ox = x0 + int64_t(in_step) * p.xs.t;
+        og = g0 + int64_t(in_step) * p.gs.t;
+        od = d0 + int64_t(in_step) * p.ds.t;
+      } else {                         // the step straddles a (batch, head) boundary or the end: per-row arithmetic
+        const int64_t rr = alive[u] ? row : rows - 1;
+        const int t = int(rr % p.T);
         const int64_t bh = rr / p.T;
-        h = int(bh % p.H);
-        b = bh / p.H;
+        const int h = int(bh % p.H);
+        const int64_t b = bh / p.H;
+        ox = b * p.xs.b + h * p.xs.h + int64_t(t) * p.xs.t + lir * VEC;
+        og = b * p.gs.b + h * p.gs.h + int64_t(t) * p.gs.t + lir * VEC;
+        od = b * p.ds.b + h * p.ds.h + int64_t(t) * p.ds.t + lir * VEC;
       }
-      rx[u] = V::load(reinterpret_cast<const T*>(p.x) + b * p.xs.b + h * p.xs.h + int64_t(t) * p.xs.t + lir * VEC);
-      rd[u] = V::load(reinterpret_cast<const T*>(p.dy) + b * p.gs.b + h * p.gs.h + int64_t(t) * p.gs.t + lir * VEC);
-      off_dx[u] = b * p.ds.b + h * p.ds.h + int64_t(t) * p.ds.t + lir * VEC;
+      rx[u] = V::load(reinterpret_cast<const T*>(p.x) + ox);
+      rd[u] = V::load(reinterpret_cast<const T*>(p.dy) + og);
+      off_dx[u] = od;
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
