@@ -420,10 +420,26 @@ __device__ __forceinline__ bool item_at(const AttnParams& p, const ItemLists& li
 // reference takes the norm of q after re-rounding q / (sqrt(D) c) to the input dtype; here the
 // unrounded norm is multiplied by (1 + 2^-8), an upper bound on what that rounding can add, so the
 // guard can only err towards the shifted (always valid) form.  NaN anywhere fails the guard.
+// Row r of a (B, H, T, D) tensor with strides `st`; 32-bit division where the row count allows (the 64-bit
+// one costs more instructions than the row's arithmetic).
+__device__ __forceinline__ const uint4* guard_row(const void* base, const Strides3& st, int H, int T, int64_t r, bool narrow) {
+  int64_t b;
+  int h, t;
+  if (narrow) {
+    const uint32_t bh = uint32_t(r) / uint32_t(T), bb = bh / uint32_t(H);
+    t = int(uint32_t(r) - bh * uint32_t(T)); h = int(bh - bb * uint32_t(H)); b = bb;
+  } else {
+    const int64_t bh = r / T;
+    t = int(r - bh * T); h = int(bh % H); b = bh / H;
+  }
+  return reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(base) + b * st.b + h * st.h + int64_t(t) * st.t);
+}
+
 template <int D>
 __device__ __forceinline__ void guard_statistics(const AttnParams& p, GuardWords* out, int lane) {
   constexpr int NV = D / 8;                       // 16-byte vectors per row
   const int64_t step = int64_t(gridDim.x) * 32;
+  const bool narrow = int64_t(p.B) * p.H * max(p.Tq, p.Tk) < (int64_t(1) << 31);
   float best[2] = {0.f, 0.f};
   for (int which = 0; which < 2; ++which) {
     const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(which == 0 ? p.q : p.k);
@@ -432,9 +448,7 @@ __device__ __forceinline__ void guard_statistics(const AttnParams& p, GuardWords
     const int64_t rows = int64_t(p.B) * p.H * T;
     float m = 0.f;
     for (int64_t r = int64_t(blockIdx.x) * 32 + lane; r < rows; r += step) {
-      const int t = int(r % T);
-      const int64_t bh = r / T;
-      const uint4* src = reinterpret_cast<const uint4*>(base + (bh / p.H) * st.b + (bh % p.H) * st.h + int64_t(t) * st.t);
+      const uint4* src = guard_row(base, st, p.H, T, r, narrow);
       uint4 raw[NV];
 #pragma unroll
       for (int i = 0; i < NV; ++i) raw[i] = __ldg(src + i);
@@ -455,9 +469,7 @@ __device__ __forceinline__ void guard_statistics(const AttnParams& p, GuardWords
     const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(p.v);
     const int64_t rows = int64_t(p.B) * p.H * p.Tk;
     for (int64_t r = int64_t(blockIdx.x) * 32 + lane; r < rows; r += step) {
-      const int t = int(r % p.Tk);
-      const int64_t bh = r / p.Tk;
-      const uint4* src = reinterpret_cast<const uint4*>(base + (bh / p.H) * p.vs.b + (bh % p.H) * p.vs.h + int64_t(t) * p.vs.t);
+      const uint4* src = guard_row(base, p.vs, p.H, p.Tk, r, narrow);
       uint4 raw[NV];
 #pragma unroll
       for (int i = 0; i < NV; ++i) raw[i] = __ldg(src + i);
