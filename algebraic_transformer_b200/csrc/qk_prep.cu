@@ -132,12 +132,14 @@ __global__ void __launch_bounds__(256, MODE == 0 ? 4 : 3) qk_prep_kernel(const P
         float v[VEC];
         V::unpack(raw[u], v);
         if constexpr (MODE >= 1) {
-          float ss = 0.0f;
+          float2 ss2 = make_float2(0.0f, 0.0f);        // two elements per instruction on the packed fp32 pipe
 #pragma unroll
-          for (int i = 0; i < VEC; ++i) ss = fmaf(v[i], v[i], ss);
+          for (int i = 0; i < VEC; i += 2) { const float2 x2 = make_float2(v[i], v[i + 1]); ss2 = __ffma2_rn(x2, x2, ss2); }
+          float ss = ss2.x + ss2.y;
 #pragma unroll
           for (int o = LPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
           const float tau = rsqrtf(ss * (1.0f / D) + p.eps);
+          const float2 tau2 = make_float2(tau, tau);
           if constexpr (MODE == 2 && sizeof(T) == 2) {
             // bf16 rows.  The reference rotates in bf16 arithmetic (each product and the sum rounded
             // to bf16), which is what HMUL2 / HADD2 compute, two elements per instruction; a pair
@@ -145,7 +147,8 @@ __global__ void __launch_bounds__(256, MODE == 0 ? 4 : 3) qk_prep_kernel(const P
             uint32_t yp[VEC / 2];
 #pragma unroll
             for (int i = 0; i < VEC / 2; ++i) {
-              const uint32_t own = pack_bf16((v[2 * i] * tau) * gain[2 * i], (v[2 * i + 1] * tau) * gain[2 * i + 1]);
+              const float2 sc2 = __fmul2_rn(__fmul2_rn(make_float2(v[2 * i], v[2 * i + 1]), tau2), make_float2(gain[2 * i], gain[2 * i + 1]));
+              const uint32_t own = pack_bf16(sc2.x, sc2.y);
               const uint32_t oth = __shfl_xor_sync(0xffffffffu, own, LPR / 2);
               // first half: x1 c - x2 s ; second half: x2 c + x1 s  ==  own * c + other * (-+ s)
               const __nv_bfloat162 y = __hadd2(__hmul2(*reinterpret_cast<const __nv_bfloat162*>(&own), *reinterpret_cast<const __nv_bfloat162*>(&c2[i])),
@@ -163,7 +166,10 @@ __global__ void __launch_bounds__(256, MODE == 0 ? 4 : 3) qk_prep_kernel(const P
             }
           } else {
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) v[i] = V::round((v[i] * tau) * gain[i]);
+            for (int i = 0; i < VEC; i += 2) {
+              const float2 sc2 = __fmul2_rn(__fmul2_rn(make_float2(v[i], v[i + 1]), tau2), make_float2(gain[i], gain[i + 1]));
+              v[i] = V::round(sc2.x); v[i + 1] = V::round(sc2.y);
+            }
           }
         }
         if constexpr (MODE == 2 && sizeof(T) != 2) {
