@@ -234,7 +234,8 @@ __device__ __forceinline__ void qkv_head(const ProjParams& p, const float* s_gai
                                          bool live, float tau_row, float& best_q, float& best_k, float& best_v) {
   constexpr int NP = D / 2, QP = D / 4;                // packed pairs per head / per half
   uint32_t pk[NP];                                     // the projection rounded to bf16 (the GEMM's output dtype)
-  float ss = 0.f;
+  float2 ss2 = make_float2(0.f, 0.f);                  // packed fp32 throughout: the epilogue's instruction count, not the
+  const float2 tau_row2 = make_float2(tau_row, tau_row);   // main loop, bounds this kernel
   __nv_bfloat162 vmax2 = as_bf162(0u);
   {
     // two chunks in flight for D = 64; for D = 128 the table already holds 64 registers, so one
@@ -249,14 +250,14 @@ __device__ __forceinline__ void qkv_head(const ProjParams& p, const float* s_gai
       if (DOUBLE && c + 1 < D / 32) tmem_ld_32x32(taddr + (c + 1) * 32, nxt);
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const uint32_t w = pack_bf16(__uint_as_float(cur[2 * i]) * tau_row, __uint_as_float(cur[2 * i + 1]) * tau_row);
+        const float2 sc = __fmul2_rn(make_float2(__uint_as_float(cur[2 * i]), __uint_as_float(cur[2 * i + 1])), tau_row2);
+        const uint32_t w = pack_bf16(sc.x, sc.y);
         pk[c * 16 + i] = w;
         if (kind == 2) {
           vmax2 = __hmax2(vmax2, __habs2(as_bf162(w)));
         } else {
-          const float lo = pair_lo(w), hi = pair_hi(w);
-          ss = fmaf(lo, lo, ss);
-          ss = fmaf(hi, hi, ss);
+          const float2 r2 = make_float2(pair_lo(w), pair_hi(w));
+          ss2 = __ffma2_rn(r2, r2, ss2);
         }
       }
       if (!DOUBLE && c + 1 < D / 32) tmem_ld_32x32(taddr + (c + 1) * 32, a);
@@ -271,11 +272,13 @@ __device__ __forceinline__ void qkv_head(const ProjParams& p, const float* s_gai
     for (int h64 = 0; h64 < D / 64; ++h64) store_rows64(wo, lane, pk + 32 * h64, col + 64 * h64);
     return;
   }
-  const float tau = rsqrtf(ss * (1.0f / D) + p.eps);
+  const float tau = rsqrtf((ss2.x + ss2.y) * (1.0f / D) + p.eps);
+  const float2 tau2 = make_float2(tau, tau);
   const float* gain = s_gain + kind * 128;             // shared-memory copy: q gains, then k gains
   const bool exact_scale = (kind == 1) || (p.q_scale_pow2 != 0);
   const float stat_scale = (kind == 0) ? p.q_scale : 1.0f;
-  float stat = 0.f;
+  float2 stat2 = make_float2(0.f, 0.f);
+  const float2 stat_scale2 = make_float2(stat_scale, stat_scale);
 #pragma unroll
   for (int g2i = 0; g2i < QP / 2; ++g2i) {             // two pairs = four gains of each half per step
     const float4 ga = *reinterpret_cast<const float4*>(gain + 4 * g2i);
@@ -285,8 +288,9 @@ __device__ __forceinline__ void qkv_head(const ProjParams& p, const float* s_gai
     for (int jj = 0; jj < 2; ++jj) {
       const int j = g2i * 2 + jj;                      // pair j of the first half, partner pair j + QP
       // x <- round((x * tau) * gain)
-      const uint32_t x1 = pack_bf16((pair_lo(pk[j]) * tau) * g1v[2 * jj], (pair_hi(pk[j]) * tau) * g1v[2 * jj + 1]);
-      const uint32_t x2 = pack_bf16((pair_lo(pk[j + QP]) * tau) * g2v[2 * jj], (pair_hi(pk[j + QP]) * tau) * g2v[2 * jj + 1]);
+      const float2 a1 = __fmul2_rn(__fmul2_rn(make_float2(pair_lo(pk[j]), pair_hi(pk[j])), tau2), make_float2(g1v[2 * jj], g1v[2 * jj + 1]));
+      const float2 a2 = __fmul2_rn(__fmul2_rn(make_float2(pair_lo(pk[j + QP]), pair_hi(pk[j + QP])), tau2), make_float2(g2v[2 * jj], g2v[2 * jj + 1]));
+      const uint32_t x1 = pack_bf16(a1.x, a1.y), x2 = pack_bf16(a2.x, a2.y);
       const __nv_bfloat162 X1 = as_bf162(x1), X2 = as_bf162(x2), Cc = as_bf162(tc[j]), Ss = as_bf162(ts[j]);
       // bf16 arithmetic, every product and sum rounded: (x1 c - x2 s, x1 s + x2 c)
       const uint32_t y1 = as_u32(__hsub2(__hmul2(X1, Cc), __hmul2(X2, Ss)));
@@ -295,13 +299,17 @@ __device__ __forceinline__ void qkv_head(const ProjParams& p, const float* s_gai
       pk[j + QP] = y2;
       uint32_t s1 = y1, s2 = y2;
       if (!exact_scale) {                              // the guard looks at the scaled, re-rounded q
-        s1 = pack_bf16(pair_lo(y1) * stat_scale, pair_hi(y1) * stat_scale);
-        s2 = pack_bf16(pair_lo(y2) * stat_scale, pair_hi(y2) * stat_scale);
+        const float2 b1 = __fmul2_rn(make_float2(pair_lo(y1), pair_hi(y1)), stat_scale2);
+        const float2 b2 = __fmul2_rn(make_float2(pair_lo(y2), pair_hi(y2)), stat_scale2);
+        s1 = pack_bf16(b1.x, b1.y);
+        s2 = pack_bf16(b2.x, b2.y);
       }
-      stat = fmaf(pair_lo(s1), pair_lo(s1), stat); stat = fmaf(pair_hi(s1), pair_hi(s1), stat);
-      stat = fmaf(pair_lo(s2), pair_lo(s2), stat); stat = fmaf(pair_hi(s2), pair_hi(s2), stat);
+      const float2 q1 = make_float2(pair_lo(s1), pair_hi(s1)), q2 = make_float2(pair_lo(s2), pair_hi(s2));
+      stat2 = __ffma2_rn(q1, q1, stat2);
+      stat2 = __ffma2_rn(q2, q2, stat2);
     }
   }
+  const float stat = stat2.x + stat2.y;
   if (live) {
     // a power-of-two scale commutes with every rounding above: apply it to the sum
     if (kind == 0) best_q = fmaxf(best_q, exact_scale ? stat * (stat_scale * stat_scale) : stat);
