@@ -59,6 +59,8 @@
 #include <math.h>
 #include <stdlib.h>
 
+#include <algorithm>
+
 namespace alg {
 namespace {
 
@@ -391,15 +393,28 @@ struct ItemLists {
   int listed;                          // 0: row-wise deal
 };
 
-// The k-th work item of this CTA.
-struct Item { int b, h, row0, n0, n1; };
+// The k-th work item of this CTA.  A listed entry is a 16-bit code: item number (10 bits), part (3 bits) and
+// number of parts - 1 (3 bits).  A problem with fewer items than would keep every SM busy has its long items
+// SPLIT ALONG THE KEYS into up to eight parts (unshifted form only: there the parts' accumulators and row sums
+// simply add up); a part covers a contiguous range of key-tile steps for both query tiles, only the last
+// part holds the diagonal tiles (and only it masks), only the first adds the sink, and every part writes
+// its raw accumulator and row sums to its own slot of the workspace for attn_split_combine_kernel.
+struct Item {
+  int b, h, row0, n0, n1;
+  int k0;                         // first key tile of this part
+  int slot;                       // list position: the part's slot in the workspace
+  bool diag, first, partial;
+};
 __device__ __forceinline__ bool item_at(const AttnParams& p, const ItemLists& lists, int k, Item& it) {
   const int units = p.B * p.H, nblk = (p.Tq + 2 * BQ - 1) / (2 * BQ), G = int(gridDim.x);
-  int idx;
+  int idx, part = 0, parts = 1;
+  it.slot = 0;
   if (lists.listed) {
     const int at = int(lists.start[blockIdx.x]) + k;
     if (at >= int(lists.start[blockIdx.x + 1])) return false;
-    idx = lists.item[at];
+    const int code = lists.item[at];
+    idx = code & 1023; part = (code >> 10) & 7; parts = ((code >> 13) & 7) + 1;
+    it.slot = at;
   } else {
     // row k of the deal goes left to right for even k and right to left for odd k
     idx = k * G + ((k & 1) ? G - 1 - int(blockIdx.x) : int(blockIdx.x));
@@ -408,7 +423,13 @@ __device__ __forceinline__ bool item_at(const AttnParams& p, const ItemLists& li
   const int blk = nblk - 1 - idx / units, bh = idx % units;
   it.b = bh / p.H; it.h = bh % p.H;
   it.row0 = blk * 2 * BQ;
-  it.n0 = 2 * blk + 1; it.n1 = 2 * blk + 2;      // key tiles needed by query tile 0 / 1
+  const int steps = 2 * blk + 2;                 // key tiles needed by query tile 1 (tile 0: one fewer)
+  it.k0 = steps * part / parts;
+  it.n1 = steps * (part + 1) / parts - it.k0;
+  it.diag = part == parts - 1;
+  it.n0 = it.diag ? it.n1 - 1 : it.n1;
+  it.first = part == 0;
+  it.partial = parts > 1;
   return true;
 }
 
@@ -588,7 +609,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           const CUtensorMap* tm = (idx & 1) ? &tm_v : &tm_k;
           for (int pn = 0; pn < C::PANELS; ++pn)
             tma_load_4d(smem + C::KV_OFF + buf * C::TILE_BYTES + pn * PANEL_BYTES, tm, &ctl->kv_full[buf], pn * 64,
-                        (idx >> 1) * BKEY, it.h, it.b);
+                        (it.k0 + (idx >> 1)) * BKEY, it.h, it.b);
           cur.next();
           return true;
         };
@@ -836,9 +857,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #endif
     for (int k = 0; ok && item_at(p, lists, k, it); ++k) {
       const int nk = (w == 0) ? it.n0 : it.n1;
+      const int last_masked = it.diag ? nk - 1 : -1; // the tile that holds this query tile's diagonal (last part of an item only)
       float l = 0.f;                                // the sink's weight, fetched while the first scores are computed
       float m_run = -1.0e30f;                       // shifted form: running row maximum (kernel units) ...
-      if (p.sink != nullptr) {
+      if (p.sink != nullptr && it.first) {
         if (SHIFT) { m_run = p.sink[it.h] * p.inv_c; l = 1.0f; }   // ... which starts at the sink, whose weight under its own shift is 1
         else l = pow2n<LOG2N>(rho_stable(p.sink[it.h] * p.inv_c)) * sc.inv_mn;
       }
@@ -862,7 +884,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #endif
         if (SHIFT) {
           // pass 1: the tile's row maximum; then the rescale factor of what has been accumulated so far
-          const float tmax = (j == nk - 1) ? tile_row_max<true>(s_taddr, r, p.scale) : tile_row_max<false>(s_taddr, r, p.scale);
+          const float tmax = (j == last_masked) ? tile_row_max<true>(s_taddr, r, p.scale) : tile_row_max<false>(s_taddr, r, p.scale);
           const float m_new = fmaxf(m_run, tmax);
           if (j == 0 && p.sink == nullptr) m_run = m_new;          // without a sink the first tile sets the maximum
           const float sigma = rho_stable(-m_new);
@@ -886,7 +908,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
           l *= alpha;                                      // sink and earlier tiles, now relative to the new maximum
           m_run = m_new;
-          if (j == nk - 1) weigh_tile_shifted<LOG2N, true>(s_taddr, r, p.scale, sigma, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
+          if (j == last_masked) weigh_tile_shifted<LOG2N, true>(s_taddr, r, p.scale, sigma, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
           else weigh_tile_shifted<LOG2N, false>(s_taddr, r, p.scale, sigma, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
           l += (la.x + la.y) + (lb.x + lb.y);              // this tile's weights
           la = make_float2(0.f, 0.f); lb = make_float2(0.f, 0.f);
@@ -896,18 +918,18 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           // tile waits for "output ready" below)
           uint64_t* release_v = (releaser && w == 1 && j > 0) ? &ctl->kv_empty[vslot] : nullptr;
           if (release_v != nullptr) vslot = (vslot + 2) % C::NKV;
-          if (j == nk - 1) ok = weigh_half_tile_early<LOG2N, true>(s_taddr, p_taddr, half, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w],
+          if (j == last_masked) ok = weigh_half_tile_early<LOG2N, true>(s_taddr, p_taddr, half, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w],
                                                                    &ctl->s_read[w], &ctl->pv_done[w], tile > 0, uint32_t(tile - 1) & 1u, bw, release_v);
           else ok = weigh_half_tile_early<LOG2N, false>(s_taddr, p_taddr, half, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w],
                                                         &ctl->s_read[w], &ctl->pv_done[w], tile > 0, uint32_t(tile - 1) & 1u, bw, release_v);
         } else if (SPLIT == 2) {
-          if (j == nk - 1) weigh_half_tile<LOG2N, true>(s_taddr, half, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);   // diagonal tile: masked
+          if (j == last_masked) weigh_half_tile<LOG2N, true>(s_taddr, half, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);   // diagonal tile: masked
           else weigh_half_tile<LOG2N, false>(s_taddr, half, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
         } else if (F32) {
-          if (j == nk - 1) weigh_tile_hilo<LOG2N, true>(s_taddr, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
+          if (j == last_masked) weigh_tile_hilo<LOG2N, true>(s_taddr, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
           else weigh_tile_hilo<LOG2N, false>(s_taddr, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
         } else {
-          if (j == nk - 1) weigh_tile<LOG2N, true>(s_taddr, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
+          if (j == last_masked) weigh_tile<LOG2N, true>(s_taddr, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
           else weigh_tile<LOG2N, false>(s_taddr, r, sc.kappa, la, lb, &ctl->p_half[w], &ctl->p_full[w]);
         }
 #ifdef ALG_ATTN_TIMING
@@ -953,6 +975,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           tc_fence_before();
           mbar_arrive(&ctl->o_free[w]);
         }
+        if (!SHIFT && !F32 && it.partial) {          // one part of a split item: the raw accumulator, for the combine kernel
+          float* dst = p.split_ws + (int64_t(it.slot) * 2 * BQ + w * BQ + r) * (DV + 4) + chunk * 32;
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<uint4*>(dst + 4 * c) = make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+          continue;
+        }
         if (row >= p.Tq) continue;                   // a row past the end of a sequence that does not fill its last tile
         if constexpr (F32) {
           float* frow = reinterpret_cast<float*>(p.o) + o_off + chunk * 32;
@@ -971,6 +1000,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             *reinterpret_cast<uint4*>(orow + chunk * 32 + c * 8) = val;
           }
         }
+      }
+      if (!SHIFT && !F32 && it.partial) {            // its row sums (the sink's weight included by the first part)
+        if (half == 0) p.split_ws[(int64_t(it.slot) * 2 * BQ + w * BQ + r) * (DV + 4) + DV] = l;
+        continue;
       }
 #ifndef ALG_ATTN_TIMING
       // unshifted: 1 / l of the reference = 1 / (l' m^n); shifted: rho(-m) l^(-1/n)  (flash.py:271-284)
@@ -1004,27 +1037,177 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   }
 }
 
-// Greedy deal of the items (cost of row block blk: its 4 blk + 3 score tiles) over `grid` CTAs.
-void deal_items(ItemLists* out, int units, int nblk, int grid) {
+// Greedy deal (every entry, heaviest first, to the CTA with the least work so far) of the items, or of the
+// parts of items when the problem is short: cost of row block blk = its 4 blk + 3 score tiles.  `split`: a
+// problem whose heaviest item is well above a CTA's fair share of the work may have its long items cut along the
+// keys (item_at says how a part reads its range), at most eight parts per item.  A part writes its fp32
+// accumulator (132 KB at head_dim 128) and the combine kernel reads it back, as much traffic as four key-tile
+// steps load: measured, parts of 4 to 8 steps made every short problem slower ((1,16,2048,128): 36 -> 82 us), so
+// a part is at least MIN_PART_TILES score tiles (16 steps) long and sequences up to 2048 are never split.  The
+// part size is chosen by trying a few and dealing each: the estimate is the heaviest CTA's tiles plus what the
+// parts' traffic and the second kernel cost (in tiles; fitted to (1,2,8192,128): 113 -> 85 us with 160 parts of
+// 32 tiles), and the unsplit deal stays when it is not beaten.  Returns the number of list entries that are parts.
+constexpr int MIN_PART_TILES = 32, MAX_SPLIT_ENTRIES = 512;
+struct DealEntry { int cost; uint16_t code; };
+
+// the entries for parts of about `target` tiles (0: whole items); returns their number, or -1 if they do not fit
+int deal_entries(DealEntry* entry, int units, int nblk, int target, int* parts_total) {
   const int items = units * nblk;
-  out->listed = 0;
-  if (items > MAX_LISTED || grid > MAX_LIST_CTAS) return;
-  int load[MAX_LIST_CTAS] = {0}, count[MAX_LIST_CTAS] = {0};
-  uint16_t owner[MAX_LISTED];
-  for (int i = 0; i < items; ++i) {                      // items are already in order of falling cost
+  int entries = 0;
+  *parts_total = 0;
+  for (int i = 0; i < items; ++i) {
+    const int blk = nblk - 1 - i / units, cost = 4 * blk + 3, steps = 2 * blk + 2;
+    int parts = 1;
+    if (target > 0 && cost > target) {
+      parts = (cost + target - 1) / target;
+      if (parts > 8) parts = 8;
+      if (parts > steps / 2) parts = steps / 2;
+    }
+    if (entries + parts > (target > 0 ? MAX_SPLIT_ENTRIES : MAX_LISTED)) return -1;
+    for (int pt = 0; pt < parts; ++pt) {
+      const int k0 = steps * pt / parts, k1 = steps * (pt + 1) / parts;
+      entry[entries].cost = 2 * (k1 - k0) - (pt == parts - 1 ? 1 : 0);
+      entry[entries].code = uint16_t(i | (pt << 10) | ((parts - 1) << 13));
+      ++entries;
+    }
+    if (parts > 1) *parts_total += parts;
+  }
+  if (*parts_total > 0)                                  // parts are lighter than whole items of the same row block: restore the order
+    std::stable_sort(entry, entry + entries, [](const DealEntry& a, const DealEntry& b) { return a.cost > b.cost; });
+  return entries;
+}
+
+// deal `entries` over `grid` CTAs; returns the heaviest CTA's load
+int deal_greedy(const DealEntry* entry, int entries, int grid, uint16_t* owner, int* count) {
+  int load[MAX_LIST_CTAS] = {0};
+  for (int c = 0; c < grid; ++c) count[c] = 0;
+  int worst = 0;
+  for (int i = 0; i < entries; ++i) {
     int best = 0;
     for (int c = 1; c < grid; ++c)
       if (load[c] < load[best]) best = c;
     owner[i] = uint16_t(best);
-    load[best] += 4 * (nblk - 1 - i / units) + 3;
+    load[best] += entry[i].cost;
     ++count[best];
+    if (load[best] > worst) worst = load[best];
   }
+  return worst;
+}
+
+int deal_items(ItemLists* out, int units, int nblk, int grid, bool split) {
+  const int items = units * nblk;
+  out->listed = 0;
+  if (items > MAX_LISTED || grid > MAX_LIST_CTAS) return 0;
+  static thread_local DealEntry entry[MAX_LISTED];
+  static thread_local uint16_t owner[MAX_LISTED];
+  int count[MAX_LIST_CTAS];
+  long total = 0;
+  for (int i = 0; i < items; ++i) total += 4 * (nblk - 1 - i / units) + 3;
+  const int share = int((total + grid - 1) / grid), heaviest = 4 * (nblk - 1) + 3;
+  int best_target = 0, parts_total = 0;
+  if (split && 2 * heaviest > 3 * share) {
+    int entries = deal_entries(entry, units, nblk, 0, &parts_total);
+    int best_score = deal_greedy(entry, entries, grid, owner, count);
+    for (int target = MIN_PART_TILES; target < heaviest; target += (target < 64 ? 8 : (target < 128 ? 16 : 64))) {
+      entries = deal_entries(entry, units, nblk, target, &parts_total);
+      if (entries < 0 || parts_total == 0) continue;
+      const int score = deal_greedy(entry, entries, grid, owner, count) + parts_total / 10 + 6;
+      if (score < best_score) { best_score = score; best_target = target; }
+    }
+  }
+  const int entries = deal_entries(entry, units, nblk, best_target, &parts_total);
+  deal_greedy(entry, entries, grid, owner, count);
   out->start[0] = 0;
   for (int c = 0; c < grid; ++c) out->start[c + 1] = uint16_t(out->start[c] + count[c]);
   int fill[MAX_LIST_CTAS];
   for (int c = 0; c < grid; ++c) fill[c] = out->start[c];
-  for (int i = 0; i < items; ++i) out->item[fill[owner[i]]++] = uint16_t(i);
+  for (int i = 0; i < entries; ++i) out->item[fill[owner[i]]++] = entry[i].code;
   out->listed = 1;
+  return parts_total;
+}
+
+// The deal depends on four integers only: keep the last few (a launch path must stay cheap, and a call asks
+// twice - once for the workspace size, with splitting, once at the launch, with or without).
+struct Dealt { int units, nblk, grid, split, parts; ItemLists lists; };
+const Dealt& dealt_for(int units, int nblk, int grid, bool split) {
+  constexpr int KEPT = 6;
+  static thread_local Dealt kept[KEPT];
+  static thread_local int used = 0, next = 0;
+  for (int i = 0; i < used; ++i)
+    if (kept[i].units == units && kept[i].nblk == nblk && kept[i].grid == grid && kept[i].split == int(split)) return kept[i];
+  Dealt& d = kept[next];
+  next = (next + 1) % KEPT;
+  if (used < KEPT) ++used;
+  d.units = units; d.nblk = nblk; d.grid = grid; d.split = int(split);
+  d.parts = deal_items(&d.lists, units, nblk, grid, split);
+  return d;
+}
+
+// Adds up the parts of every split item: out = (sum of accumulators) / (sum of row sums), the statistic 1 / l.
+// Grid (list entries, 8): the entry that is part 0 of a split item does the item's work, every other entry
+// leaves at once; a CTA takes 32 of the item's 256 rows, a warp four of them, a lane DV / 32 columns of a row, and
+// all of a warp's loads are issued before any is used (a thread per row walking its parts one load latency at a
+// time made this kernel as long as the attention it finishes).
+template <int DV>
+__global__ void __launch_bounds__(256) attn_split_combine_kernel(const __grid_constant__ ItemLists lists, const AttnParams p, int entries,
+                                                                 float inv_mn) {
+  griddep_wait();                                        // a programmatic dependent of the attention kernel
+  __shared__ int slots[8];
+  const int code = lists.item[blockIdx.x];
+  const int idx = code & 1023, parts = ((code >> 13) & 7) + 1;
+  if (((code >> 10) & 7) != 0 || parts == 1) return;
+  for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+    const int c = lists.item[i];
+    if ((c & 1023) == idx && ((c >> 13) & 7) + 1 == parts) slots[(c >> 10) & 7] = i;
+  }
+  __syncthreads();
+  constexpr int CPL = DV / 32;                           // columns per lane
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int units = p.B * p.H, nblk = (p.Tq + 2 * BQ - 1) / (2 * BQ);
+  const int blk = nblk - 1 - idx / units, bh = idx % units, b = bh / p.H, h = bh % p.H;
+  const int in_item0 = blockIdx.y * 32 + warp * 4;       // this warp's first row inside the item (query tile = row / 128)
+  float acc[4][CPL], l[4];
+#pragma unroll
+  for (int rr = 0; rr < 4; ++rr) {
+    l[rr] = 0.f;
+#pragma unroll
+    for (int c = 0; c < CPL; ++c) acc[rr][c] = 0.f;
+  }
+  for (int pt = 0; pt < parts; ++pt) {
+    const float* base = p.split_ws + (int64_t(slots[pt]) * 2 * BQ + in_item0) * (DV + 4);
+    float v[4][CPL], lv[4];
+#pragma unroll
+    for (int rr = 0; rr < 4; ++rr) {
+      const float* row = base + rr * (DV + 4);
+      if (CPL == 4) {
+        const float4 x = __ldcg(reinterpret_cast<const float4*>(row + lane * 4));
+        v[rr][0] = x.x; v[rr][1] = x.y; v[rr][CPL - 2] = x.z; v[rr][CPL - 1] = x.w;
+      } else {
+        const float2 x = __ldcg(reinterpret_cast<const float2*>(row + lane * 2));
+        v[rr][0] = x.x; v[rr][1] = x.y;
+      }
+      lv[rr] = __ldcg(row + DV);
+    }
+#pragma unroll
+    for (int rr = 0; rr < 4; ++rr) {
+      l[rr] += lv[rr];
+#pragma unroll
+      for (int c = 0; c < CPL; ++c) acc[rr][c] += v[rr][c];
+    }
+  }
+#pragma unroll
+  for (int rr = 0; rr < 4; ++rr) {
+    const int row = blk * 2 * BQ + in_item0 + rr;
+    if (row >= p.Tq) continue;
+    const float inv = 1.0f / l[rr];
+    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.o) + b * p.os.b + h * p.os.h + int64_t(row) * p.os.t;
+    if (CPL == 4)
+      *reinterpret_cast<uint2*>(orow + lane * 4) = make_uint2(pack_bf16(acc[rr][0] * inv, acc[rr][1] * inv),
+                                                              pack_bf16(acc[rr][CPL - 2] * inv, acc[rr][CPL - 1] * inv));
+    else
+      *reinterpret_cast<uint32_t*>(orow + lane * 2) = pack_bf16(acc[rr][0] * inv, acc[rr][1] * inv);
+    if (p.stat != nullptr && lane == 0) p.stat[(int64_t(b) * p.H + h) * p.Tq + row] = inv * inv_mn;
+  }
 }
 
 int make_qkv_map(CUtensorMap* tm, const void* base, const Strides3& s, int B, int H, int T, int D) {
@@ -1057,15 +1240,18 @@ int launch_dns(const AttnParams& p, cudaStream_t stream) {
   if (int rc = configured.run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes<D>())); }, &sms)) return rc;
   const int grid = attn_tcgen05_grid(p);
   (void)sms;
-  // the deal depends on three integers only: keep the last one (a launch path must stay cheap)
-  struct Dealt { int units, nblk, grid; ItemLists lists; };
-  static thread_local Dealt dealt = {-1, -1, -1, {}};
   const int units = p.B * p.H, nblk = (p.Tq + 2 * BQ - 1) / (2 * BQ);
-  if (dealt.units != units || dealt.nblk != nblk || dealt.grid != grid) {
-    deal_items(&dealt.lists, units, nblk, grid);
-    dealt.units = units; dealt.nblk = nblk; dealt.grid = grid;
+  // short problems: long items are cut along the keys when the caller's workspace has room for the parts' slots
+  static const bool never_split = getenv("ALG_ATTN_NO_KEY_SPLIT") != nullptr;      // measurement aid
+  const bool may_split = !SHIFT && !F32 && p.split_ws != nullptr && !never_split;
+  const Dealt* dealt = &dealt_for(units, nblk, grid, may_split);
+  if (dealt->parts > 0 && int(dealt->lists.start[grid]) > p.split_slots) dealt = &dealt_for(units, nblk, grid, false);
+  ALG_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(nthreads<SPLIT>()), smem_bytes<D>(), stream, tq, tk, tv, p, sc, dealt->lists));
+  if (dealt->parts > 0) {
+    const int entries = int(dealt->lists.start[grid]);
+    ALG_CUDA_TRY(launch_dependent(attn_split_combine_kernel<D>, dim3(entries, 8), dim3(256), 0, stream, dealt->lists, p, entries, sc.inv_mn));
+    count_launch();
   }
-  ALG_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(nthreads<SPLIT>()), smem_bytes<D>(), stream, tq, tk, tv, p, sc, dealt.lists));
   count_launch();
   return ALG_OK;
 }
@@ -1169,9 +1355,19 @@ bool attn_tcgen05_supports(const AttnParams& p, int dtype) {
 // One warp per SM streams 6 B H T D bytes at about 5 GB/s per SM while the kernel needs time in
 // proportion to B H T^2 D: from T D = 3/4 Mi elements per head on, the statistics are ready well
 // before the attention is (T >= 6144 at head_dim 128).
+// One CTA per SM; a problem with fewer items than that still gets up to eight CTAs per item, because its long
+// items may be split along the keys (a CTA whose list stays empty leaves at once).
 int attn_tcgen05_grid(const AttnParams& p) {
-  const int items = p.B * p.H * ((p.Tq + 2 * BQ - 1) / (2 * BQ)), sms = sm_count();
-  return items < sms ? items : sms;
+  const int64_t items = int64_t(p.B) * p.H * ((p.Tq + 2 * BQ - 1) / (2 * BQ));
+  const int sms = sm_count();
+  return int(items * 8 < sms ? items * 8 : sms);
+}
+
+size_t attn_tcgen05_split_bytes(const AttnParams& p) {
+  if (p.D != 64 && p.D != 128) return 0;
+  const int units = p.B * p.H, nblk = (p.Tq + 2 * BQ - 1) / (2 * BQ), grid = attn_tcgen05_grid(p);
+  const Dealt& d = dealt_for(units, nblk, grid, true);
+  return d.parts > 0 ? size_t(d.lists.start[grid]) * 2 * BQ * (p.D + 4) * sizeof(float) : 0;
 }
 
 bool attn_tcgen05_takes_guard_statistics(const AttnParams& p) { return int64_t(p.Tq) * p.D >= 786432; }

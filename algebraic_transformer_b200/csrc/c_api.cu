@@ -146,6 +146,8 @@ int alg_qk_rms_bwd(const alg_qk_rms_bwd_args* a, void* stream) {
   return launch_rms_bwd(p, a->dtype, static_cast<cudaStream_t>(stream));
 }
 
+static size_t attn_key_split_bytes(const alg_attn_args* a);
+
 size_t alg_attn_workspace_bytes(const alg_attn_args* a) {
   if (a == nullptr) return 0;
   size_t bytes = kGuardBytes;                           // guard words: one record, or one per CTA of the tcgen05 kernel
@@ -158,7 +160,20 @@ size_t alg_attn_workspace_bytes(const alg_attn_args* a) {
   // the bf16 hi | lo copies of q, k, v.  A call that brings less than this runs on the mma.sync kernel.
   if (a->dtype == ALG_F32 && a->D == 64 && a->causal && a->Tq == a->Tk && a->Tq > 0)
     bytes = align256(bytes) + 3 * align256(attn_tcgen05_f32_split_bytes(a->B, a->H, a->Tq));
+  // bf16 problems too short to keep every SM busy: slots for the parts of items split along the keys.  A call
+  // that brings less than this runs unsplit.
+  bytes = align256(bytes) + attn_key_split_bytes(a);
   return bytes;
+}
+
+// Workspace the tcgen05 kernel's key split would use for this call (0: not that kernel, or nothing to split).
+static size_t attn_key_split_bytes(const alg_attn_args* a) {
+  if (a->dtype != ALG_BF16 || !a->causal || a->Tq != a->Tk || a->Tq < 1 || a->B < 1 || a->H < 1 || (a->D != 64 && a->D != 128) ||
+      a->variant == ALG_VARIANT_SHIFT || a->impl == ALG_IMPL_MMA || a->score_clamp > 0.0f)
+    return 0;
+  AttnParams p{};
+  p.B = a->B; p.H = a->H; p.Tq = a->Tq; p.Tk = a->Tk; p.D = a->D;
+  return attn_tcgen05_split_bytes(p);
 }
 
 // The part of the attention workspace every call may need (guard records, prologue outputs): a call
@@ -219,6 +234,15 @@ int alg_attn_fwd(const alg_attn_args* a, void* stream_) {
   p.score_clamp = a->score_clamp > 0.0f ? a->score_clamp : __int_as_float_host(0x7f800000);
 
   unsigned char* ws = static_cast<unsigned char*>(a->workspace);
+  // short bf16 problems: the slots for a split along the keys sit at the end of the workspace (a call that
+  // brings less runs unsplit)
+  {
+    const size_t split_bytes = attn_key_split_bytes(a), all_bytes = alg_attn_workspace_bytes(a);
+    if (split_bytes > 0 && ws != nullptr && aligned16(ws) && a->workspace_bytes >= all_bytes) {
+      p.split_ws = reinterpret_cast<float*>(ws + all_bytes - split_bytes);
+      p.split_slots = int(split_bytes / (size_t(2) * 128 * (a->D + 4) * sizeof(float)));
+    }
+  }
   GuardWords* guard = guard_given ? static_cast<GuardWords*>(const_cast<void*>(a->guard_words)) : reinterpret_cast<GuardWords*>(ws);
   const bool guarded = a->variant == ALG_VARIANT_GUARD;
   // Speculation: when the guard's maxima still have to be measured and the sequences are long, the

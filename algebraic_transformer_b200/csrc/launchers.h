@@ -72,12 +72,15 @@ struct AttnParams {
   int* status;
   GuardWords* guard_out;   // tcgen05 kernel only: CTA i writes the maxima of the rows it looked at to guard_out[i]
   int tc_shift;            // tcgen05 kernel only: launch the max-shifted form (it runs when the shift is called for)
+  float* split_ws;         // tcgen05 kernel only: slots for the parts of items split along the keys, or NULL (no splitting)
+  int split_slots;         // how many such slots the buffer holds
 };
 int launch_attn_mma(const AttnParams& p, int dtype, cudaStream_t stream);
 bool attn_tcgen05_supports(const AttnParams& p, int dtype);
 // Long enough sequences leave one warp of the tcgen05 kernel time to take the guard's maxima itself.
 bool attn_tcgen05_takes_guard_statistics(const AttnParams& p);
 int attn_tcgen05_grid(const AttnParams& p);          // CTAs of that kernel = records it writes to guard_out
+size_t attn_tcgen05_split_bytes(const AttnParams& p);  // workspace the key-split of a short problem would use (0: it would not split)
 int launch_attn_tcgen05(const AttnParams& p, cudaStream_t stream);
 // fp32 rows of head_dim 64 on the same kernel: q, k, v are first split into bf16 hi | lo tiles (three
 // buffers of attn_tcgen05_f32_split_bytes each, at `split`); unshifted form, fp32 output

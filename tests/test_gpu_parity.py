@@ -419,6 +419,40 @@ def test_any_sequence_length_on_tcgen05(T, D, dtype, mode):
     assert rel_l2(stat, want_stat) < 5e-3
 
 
+@pytest.mark.parametrize("B,H,T,D,splits", [(1, 2, 2048, 128, False), (1, 1, 4096, 64, True), (1, 3, 3900, 128, True),
+                                             (2, 2, 4096, 64, True), (1, 2, 8192, 128, True)])
+@pytest.mark.parametrize("with_sink", [False, True])
+def test_short_problems_split_along_the_keys(B, H, T, D, splits, with_sink):
+    """Few long items for 148 SMs: the long items are cut along the keys into parts of at least 16 key-tile steps whose
+    raw accumulators and row sums a second kernel adds up (the sink's weight counted once); sequences up to 2048 are
+    never split.  Output and statistic against the oracle (sampled rows at 8192), bit-equal repeats, and bit-equal to
+    the guarded call on the same inputs."""
+    q, k, v = (randn((B, H, T, D), 930 + i, torch.bfloat16) for i in range(3))
+    sink = randn((H,), 935, scale=0.5) if with_sink else None
+    qd, kd, vd, sd = dev(q, k, v, sink)
+    lib = L.load()
+    before = lib.alg_kernel_launches()
+    got, stat, kind = A.flash_attention(qd, kd, vd, sd, kind="asinh", n=16, c=8.0, block=T, shift=False, bounded_scores=True,
+                                        impl="tcgen05", return_stat=True)
+    assert lib.alg_kernel_launches() - before == (2 if splits else 1)   # the attention kernel and, if it split, the combine kernel
+    assert int(kind) == 1
+    rows = slice(None) if T <= 4096 else slice(T - 300, T)
+    if T <= 4096:
+        want = R.asinh_attention(q, k, v, n=16, c=8.0, sink_logit=sink)
+        want_stat = R.attention_row_stat(q, k, n=16, c=8.0, sink_logit=sink, shifted=False)
+    else:                                                    # the last 300 rows of the square problem
+        want = R.asinh_attention(q[:, :, T - 300:], k, v, n=16, c=8.0, sink_logit=sink)
+        want_stat = R.attention_row_stat(q[:, :, T - 300:], k, n=16, c=8.0, sink_logit=sink, shifted=False)
+    assert torch.isfinite(got).all() and torch.isfinite(stat).all()
+    assert rel_l2(got[:, :, rows], want) < 1e-2
+    assert rel_l2(stat[:, :, rows], want_stat) < 5e-3
+    again = A.flash_attention(qd, kd, vd, sd, kind="asinh", n=16, c=8.0, block=T, shift=False, bounded_scores=True, impl="tcgen05")
+    assert torch.equal(got, again)
+    # the guarded call on the same inputs (statistics inside the kernel or a pass in front, stand-by launch behind)
+    guarded = A.flash_attention(qd, kd, vd, sd, kind="asinh", n=16, c=8.0, block=T, range_guard=True, impl="tcgen05")
+    assert torch.equal(got, guarded)
+
+
 @pytest.mark.parametrize("T", [16384, 32768])
 def test_config5_longer_sequences_sampled(T):
     """benchmark configuration 5 at T = 16384 and 32768: (1,16,T,128) bf16 through the guarded public
