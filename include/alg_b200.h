@@ -173,6 +173,9 @@ typedef struct {
  * stat_kind may hold the speculative result.  Otherwise a statistics pass runs first.  Either way
  * the call only enqueues kernels (and at most a 16-byte memset) on `stream`: it creates no stream or
  * event of its own and can be captured into a CUDA graph.
+ * bf16 problems with few long items for the GPU's SMs (say two heads of 8192 positions) have those items split
+ * along the keys; the parts' accumulators live in the workspace and a second kernel adds them up.
+ * alg_attn_workspace_bytes includes that room, and a call that brings less runs unsplit.
  * fp32 rows of head_dim 64 (causal, Tq == Tk, unshifted form or guard, no score clamp) run on
  * the tcgen05 kernel too: q, k, v are copied into the workspace as bf16 hi | lo halves and every product is
  * formed as hi.hi + hi.lo + lo.hi; alg_attn_workspace_bytes includes the room for those copies, and a call that
