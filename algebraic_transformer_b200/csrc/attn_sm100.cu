@@ -1130,7 +1130,7 @@ int deal_items(ItemLists* out, int units, int nblk, int grid, bool split) {
 // twice - once for the workspace size, with splitting, once at the launch, with or without).
 struct Dealt { int units, nblk, grid, split, parts; ItemLists lists; };
 const Dealt& dealt_for(int units, int nblk, int grid, bool split) {
-  constexpr int KEPT = 6;
+  constexpr int KEPT = 16;
   static thread_local Dealt kept[KEPT];
   static thread_local int used = 0, next = 0;
   for (int i = 0; i < used; ++i)
