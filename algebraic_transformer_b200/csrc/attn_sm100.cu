@@ -405,6 +405,10 @@ struct Item {
   int slot;                       // list position: the part's slot in the workspace
   bool diag, first, partial;
 };
+// KS = false is the kernel for lists without parts (every problem large enough to fill the GPU): the part
+// arithmetic and the partial epilogue are compiled out, which the head_dim-64 kernel with its 96 registers
+// per thread notices (5 % at the 125M layer shape).
+template <bool KS>
 __device__ __forceinline__ bool item_at(const AttnParams& p, const ItemLists& lists, int k, Item& it) {
   const int units = p.B * p.H, nblk = (p.Tq + 2 * BQ - 1) / (2 * BQ), G = int(gridDim.x);
   int idx, part = 0, parts = 1;
@@ -413,8 +417,8 @@ __device__ __forceinline__ bool item_at(const AttnParams& p, const ItemLists& li
     const int at = int(lists.start[blockIdx.x]) + k;
     if (at >= int(lists.start[blockIdx.x + 1])) return false;
     const int code = lists.item[at];
-    idx = code & 1023; part = (code >> 10) & 7; parts = ((code >> 13) & 7) + 1;
-    it.slot = at;
+    if (KS) { idx = code & 1023; part = (code >> 10) & 7; parts = ((code >> 13) & 7) + 1; it.slot = at; }
+    else idx = code;
   } else {
     // row k of the deal goes left to right for even k and right to left for odd k
     idx = k * G + ((k & 1) ? G - 1 - int(blockIdx.x) : int(blockIdx.x));
@@ -534,13 +538,14 @@ struct ScaleSplit {
 // 128 columns, the first 64 the bf16 rounding of the fp32 values (hi) and the other 64 what it left
 // over (lo); every product is issued as hi.hi + hi.lo + lo.hi into the same accumulator, for the
 // scores and - with the weights split the same way - for the output, which is written as fp32.
-template <int D, int LOG2N, int SPLIT, bool SHIFT, bool F32 = false>
+template <int D, int LOG2N, int SPLIT, bool SHIFT, bool F32 = false, bool KS = false>
 __global__ void __launch_bounds__(nthreads<SPLIT>(), 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p, const ScaleSplit sc,
                const __grid_constant__ ItemLists lists) {
   using C = Cfg<D>;
   static_assert(!F32 || (D == 128 && SPLIT == 1 && !SHIFT), "the fp32 mode: hi|lo tiles of head_dim 64, unshifted form");
+  static_assert(!KS || (!SHIFT && !F32), "items are split along the keys in the unshifted bf16 form only");
   constexpr int DV = F32 ? 64 : D;                  // output columns
   // head_dim 64, unshifted, split weight groups: P_w has tensor-memory columns of its own and S_w is re-issued
   // early (see weigh_half_tile_early); the layout is then S 0..255, P 256..383, O 384..511
@@ -601,7 +606,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
       bool ok = true;
       RingCursor<C::NKV> cur;                       // runs on over all items
-      for (int k = 0; ok && item_at(p, lists, k, it); ++k) {
+      for (int k = 0; ok && item_at<KS>(p, lists, k, it); ++k) {
         auto load_kv = [&](int idx) {               // K_0, V_0, K_1, V_1, ... of this item
           const int buf = cur.slot;
           if (!bw.wait(&ctl->kv_empty[buf], cur.phase ^ 1u)) return false;
@@ -711,7 +716,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const long long t_begin = clock64();
 #endif
     bool ok = true;
-    for (int k = 0; ok && item_at(p, lists, k, it); ++k) {
+    for (int k = 0; ok && item_at<KS>(p, lists, k, it); ++k) {
       const int n0 = it.n0, n1 = it.n1;
       if (!wait_all(&ctl->q_ready[0], k & 1u) || !kv_wait(cur)) { ok = false; break; }
       tc_fence_after();
@@ -805,7 +810,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // and release the tile to the MMA warp.
     const __nv_bfloat162 f2 = __float2bfloat162_rn(sc.pow2);
     bool ok = true;
-    for (int k = 0; ok && item_at(p, lists, k, it); ++k) {
+    for (int k = 0; ok && item_at<KS>(p, lists, k, it); ++k) {
       for (int w = 0; w < 2 && ok; ++w) {
         if (!bw.wait(&ctl->q_full[w], k & 1u)) { ok = false; break; }
         if (sc.pow2 != 1.0f) {
@@ -855,12 +860,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #ifdef ALG_ATTN_TIMING
     const long long t_begin = clock64();
 #endif
-    for (int k = 0; ok && item_at(p, lists, k, it); ++k) {
+    for (int k = 0; ok && item_at<KS>(p, lists, k, it); ++k) {
       const int nk = (w == 0) ? it.n0 : it.n1;
-      const int last_masked = it.diag ? nk - 1 : -1; // the tile that holds this query tile's diagonal (last part of an item only)
+      const int last_masked = (!KS || it.diag) ? nk - 1 : -1; // the tile that holds this query tile's diagonal (last part of an item only)
       float l = 0.f;                                // the sink's weight, fetched while the first scores are computed
       float m_run = -1.0e30f;                       // shifted form: running row maximum (kernel units) ...
-      if (p.sink != nullptr && it.first) {
+      if (p.sink != nullptr && (!KS || it.first)) {
         if (SHIFT) { m_run = p.sink[it.h] * p.inv_c; l = 1.0f; }   // ... which starts at the sink, whose weight under its own shift is 1
         else l = pow2n<LOG2N>(rho_stable(p.sink[it.h] * p.inv_c)) * sc.inv_mn;
       }
@@ -959,7 +964,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
       tc_fence_after();
-      item_at(p, lists, k, it);                            // recomputed: nothing of it stays live over the tile loop
+      item_at<KS>(p, lists, k, it);                            // recomputed: nothing of it stays live over the tile loop
       l += part;                                    // shifted form: the last tile's sums (already at the final maximum)
       const float inv = 1.0f / l;
       const int row = it.row0 + w * BQ + r;
@@ -975,7 +980,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           tc_fence_before();
           mbar_arrive(&ctl->o_free[w]);
         }
-        if (!SHIFT && !F32 && it.partial) {          // one part of a split item: the raw accumulator, for the combine kernel
+        if (KS && it.partial) {                      // one part of a split item: the raw accumulator, for the combine kernel
           float* dst = p.split_ws + (int64_t(it.slot) * 2 * BQ + w * BQ + r) * (DV + 4) + chunk * 32;
 #pragma unroll
           for (int c = 0; c < 8; ++c)
@@ -1001,7 +1006,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
         }
       }
-      if (!SHIFT && !F32 && it.partial) {            // its row sums (the sink's weight included by the first part)
+      if (KS && it.partial) {                        // its row sums (the sink's weight included by the first part)
         if (half == 0) p.split_ws[(int64_t(it.slot) * 2 * BQ + w * BQ + r) * (DV + 4) + DV] = l;
         continue;
       }
@@ -1217,6 +1222,16 @@ int make_qkv_map(CUtensorMap* tm, const void* base, const Strides3& s, int B, in
   return make_tmap_bf16(tm, base, 4, dims, strides, box, true);
 }
 
+template <int D, int LOG2N, int SPLIT, bool SHIFT, bool F32, bool KS>
+int launch_kernel(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, const ScaleSplit& sc,
+                  const ItemLists& lists, int grid, cudaStream_t stream) {
+  auto kern = attn_tc_kernel<D, LOG2N, SPLIT, SHIFT, F32, KS>;
+  static PerDeviceOnce configured;
+  if (int rc = configured.run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes<D>())); })) return rc;
+  ALG_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(nthreads<SPLIT>()), smem_bytes<D>(), stream, tq, tk, tv, p, sc, lists));
+  return ALG_OK;
+}
+
 template <int D, int LOG2N, int SPLIT, bool SHIFT, bool F32 = false>
 int launch_dns(const AttnParams& p, cudaStream_t stream) {
   CUtensorMap tq, tk, tv;
@@ -1234,19 +1249,18 @@ int launch_dns(const AttnParams& p, cudaStream_t stream) {
     sc.inv_mn = float(pow(m, -double(1 << LOG2N)));
     if (SHIFT) { sc.pow2 = 1.0f; sc.kappa = 1.0f; sc.inv_mn = 1.0f; }   // the shifted form scales its scores itself
   }
-  auto kern = attn_tc_kernel<D, LOG2N, SPLIT, SHIFT, F32>;
-  static PerDeviceOnce configured;
-  int sms = 0;
-  if (int rc = configured.run([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_bytes<D>())); }, &sms)) return rc;
   const int grid = attn_tcgen05_grid(p);
-  (void)sms;
   const int units = p.B * p.H, nblk = (p.Tq + 2 * BQ - 1) / (2 * BQ);
   // short problems: long items are cut along the keys when the caller's workspace has room for the parts' slots
   static const bool never_split = getenv("ALG_ATTN_NO_KEY_SPLIT") != nullptr;      // measurement aid
   const bool may_split = !SHIFT && !F32 && p.split_ws != nullptr && !never_split;
   const Dealt* dealt = &dealt_for(units, nblk, grid, may_split);
   if (dealt->parts > 0 && int(dealt->lists.start[grid]) > p.split_slots) dealt = &dealt_for(units, nblk, grid, false);
-  ALG_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(nthreads<SPLIT>()), smem_bytes<D>(), stream, tq, tk, tv, p, sc, dealt->lists));
+  if constexpr (!SHIFT && !F32) {
+    if (dealt->parts > 0) {
+      if (int rc = launch_kernel<D, LOG2N, SPLIT, SHIFT, F32, true>(tq, tk, tv, p, sc, dealt->lists, grid, stream)) return rc;
+    } else if (int rc = launch_kernel<D, LOG2N, SPLIT, SHIFT, F32, false>(tq, tk, tv, p, sc, dealt->lists, grid, stream)) return rc;
+  } else if (int rc = launch_kernel<D, LOG2N, SPLIT, SHIFT, F32, false>(tq, tk, tv, p, sc, dealt->lists, grid, stream)) return rc;
   if (dealt->parts > 0) {
     const int entries = int(dealt->lists.start[grid]);
     ALG_CUDA_TRY(launch_dependent(attn_split_combine_kernel<D>, dim3(entries, 8), dim3(256), 0, stream, dealt->lists, p, entries, sc.inv_mn));
